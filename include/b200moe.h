@@ -1,0 +1,82 @@
+/* b200moe: C ABI of the B200-native (sm_100a) NVFP4 fused-MoE library.
+ *
+ * Plain pointers and sizes only: no torch types, no exceptions, no device allocation inside any call. Every device
+ * buffer belongs to the caller; `stream` is a cudaStream_t passed as void*. All functions return 0 on success or a
+ * negative B200MOE_ERR_* code; kernels are enqueued on `stream` and nothing synchronises unless stated.
+ *
+ * Each entry point names the interface of the reference project (sm120fp4) that it replaces, by file:line.
+ */
+#ifndef B200MOE_H
+#define B200MOE_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_OK 0
+#define B200MOE_ERR_ARG (-1)       /* null pointer, negative size, misaligned buffer, expert id out of range */
+#define B200MOE_ERR_SHAPE (-2)     /* a dimension the kernels do not take */
+#define B200MOE_ERR_CUDA (-3)      /* a CUDA call failed: b200moe_last_cuda_error() */
+#define B200MOE_ERR_DEVICE (-4)    /* not an sm_100 device / tensor-map driver entry point missing */
+#define B200MOE_ERR_TIMEOUT (-5)   /* a bounded device-side wait ran out */
+#define B200MOE_ERR_WORKSPACE (-6) /* workspace too small */
+#define B200MOE_ERR_LIMIT (-7)     /* size beyond a stated maximum */
+
+typedef struct b200moe_layer b200moe_layer; /* opaque decode-layer handle (host memory) */
+
+int b200moe_version(void);
+const char* b200moe_error_string(int code);
+const char* b200moe_last_cuda_error(void);
+
+/* ---- block-scale layout: sm120fp4/layouts.py:56-68 (to_128x4) and :71-78 (from_128x4), batched over `batch`
+ * matrices. sf_linear u8 [batch, rows, cols]; sf_swizzled u8 [batch, pad128(rows) * pad4(cols)], padding written 0. */
+int b200moe_to_128x4(const void* sf_linear, void* sf_swizzled, int batch, int rows, int cols, void* stream);
+int b200moe_from_128x4(const void* sf_swizzled, void* sf_linear, int batch, int rows, int cols, void* stream);
+
+/* ---- quantizer: sm120fp4/reference.py:68-71 (global_scale_for) and :74-90 (quantize_nvfp4). dtype 0 = bf16, 1 = f32.
+ * b200moe_global_scale: gs_out[0] = 2688 / max(amax|x|, 1e-12) with the reference's rounding; amax_scratch_u32 is 4
+ * bytes of device scratch. b200moe_quantize_nvfp4: destination row r quantises source row src_row[r] (null: r; negative:
+ * zero codes and scales); packed u8 [rows, K/2]; sf u8 row-major [rows, K/16] (sf_layout 0) or 128x4-swizzled over
+ * [rows, K/16] (sf_layout 1; the caller sizes the buffer for the padded extent). Bit-exact with the reference. */
+int b200moe_global_scale(const void* x, int dtype, long long n, void* amax_scratch_u32, float* gs_out, void* stream);
+int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_row, int rows, int K, const float* global_scale,
+                           void* packed, void* sf, int sf_layout, void* stream);
+
+/* ---- router: sm120fp4/kernels/moe_w4a16.py:85-91 (route; padded form of k_route :48-83) and the torch router of
+ * sm120fp4/kernels/fc1_w4a16.py:272-279. ids i32 [P] -> experts i32 [Umax] (ascending, -1 padding), offsets i32
+ * [Umax+1] (exclusive scan, P padding), pairs i32 [P] (pair indices grouped by expert, ascending within). */
+long long b200moe_route_workspace_bytes(int P, int E);
+int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* workspace,
+                  long long workspace_bytes, void* stream);
+
+/* ---- decode layer (M <= 16 tokens, W4A16): sm120fp4/vllm_backend.py:95-121 (Weights) and :147-190 (forward/_slice).
+ * q1 u8 [E, 2I, H/2] rows [up ; gate]; s1 u8 [E, pad128(2I) * pad4(H/16)] 128x4-swizzled per expert; q2 u8 [E, H, I/2];
+ * s2 u8 [E, pad128(H) * pad4(I/16)] 128x4-swizzled per expert; alpha f32 [E] (weight_scale_2). H % 128 == 0,
+ * I % 64 == 0, E <= 256, top_k <= 16. The handle keeps the pointers; the buffers must outlive it. */
+int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, int top_k, const void* q1, const void* s1_128x4,
+                         const float* alpha1, const void* q2, const void* s2_128x4, const float* alpha2);
+void b200moe_layer_destroy(b200moe_layer* layer);
+long long b200moe_layer_workspace_bytes(const b200moe_layer* layer);
+int b200moe_layer_workspace_init(const b200moe_layer* layer, void* workspace, long long workspace_bytes, void* stream);
+int b200moe_layer_sm_count(const b200moe_layer* layer);
+
+/* forward: x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]; one launch
+ * (routing + FC1 + SiLU*mul + FC2 + weighted combine). Replaces Weights._slice, sm120fp4/vllm_backend.py:174-190. */
+int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,
+                           int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream);
+/* FC1 alone -> act bf16 [M*top_k, I], row = pair index: sm120fp4/kernels/fc1_w4a16.py:251-262, fc1_mma.py:266-282. */
+int b200moe_decode_fc1(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                       void* act_bf16, void* workspace, long long workspace_bytes, void* stream);
+/* FC2 alone from act bf16 [M*top_k, I]: sm120fp4/kernels/fc2_w4a16.py:276-279, fc2_mma_pf.py:403-421. */
+int b200moe_decode_fc2(const b200moe_layer* layer, const void* act_bf16, const int* topk_ids, const float* topk_weights, int M,
+                       void* out_bf16, void* workspace, long long workspace_bytes, void* stream);
+/* routing tables written by the last decode call, in the router's padded form (device-to-device copies on stream) */
+int b200moe_layer_route_tables(const b200moe_layer* layer, const void* workspace, int M, int* experts, int* offsets,
+                               int* pairs, void* stream);
+/* status word of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT or B200MOE_ERR_ARG (bad expert id) */
+int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H */

@@ -1,0 +1,233 @@
+// C ABI of the library: layer handle (tensor maps + geometry), workspace layout, decode entry points.
+// No torch types, no exceptions, no device allocation: every device buffer is the caller's.
+#include "common.cuh"
+#include "decode_params.h"
+#include <cudaTypedefs.h>
+#include <stdlib.h>
+#include <string.h>
+#include <new>
+
+namespace b200 {
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  }
+  return fn;
+}
+
+// u8 matrix [rows, row_bytes] -> tensor map with a 128-byte x box_rows box, 128B shared-memory swizzle, zero OOB fill.
+static int make_codes_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return B200MOE_ERR_DEVICE;
+  if (((uintptr_t)base & 15) || (row_bytes & 15)) return B200MOE_ERR_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+}  // namespace b200
+
+using namespace b200;
+
+struct b200moe_layer {
+  int E, H, I, top_k;
+  int sms;
+  const void *q1, *s1, *q2, *s2;
+  const float *alpha1, *alpha2;
+  CUtensorMap tm1, tm2;
+  int KB1, KB2, CB1, NB2, KT1, KT2;
+  long long s1_stride, s2_stride;
+  // workspace layout (byte offsets)
+  long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, ws_bytes;
+  int umax_cap;
+};
+
+static inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
+
+extern "C" int b200moe_version(void) { return 100; }
+
+extern "C" const char* b200moe_error_string(int code) {
+  switch (code) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_ERR_ARG: return "bad argument (null pointer, negative size or misaligned buffer)";
+    case B200MOE_ERR_SHAPE: return "shape not taken by the kernels";
+    case B200MOE_ERR_CUDA: return "CUDA call failed";
+    case B200MOE_ERR_DEVICE: return "no sm_100 device or tensor-map driver entry point missing";
+    case B200MOE_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case B200MOE_ERR_WORKSPACE: return "workspace too small";
+    case B200MOE_ERR_LIMIT: return "size beyond the stated maximum";
+    default: return "unknown error";
+  }
+}
+
+extern "C" const char* b200moe_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda_error); }
+
+// Decode-layer handle. q1 u8 [E, 2I, H/2] rows [up ; gate]; s1 u8 [E, pad128(2I), pad4(H/16)] in the 128x4 swizzle;
+// q2 u8 [E, H, I/2]; s2 u8 [E, pad128(H), pad4(I/16)] in the 128x4 swizzle; alpha f32 [E] (= 1 / global scale).
+extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, int top_k, const void* q1, const void* s1_128x4,
+                                    const float* alpha1, const void* q2, const void* s2_128x4, const float* alpha2) {
+  if (!out || !q1 || !s1_128x4 || !alpha1 || !q2 || !s2_128x4 || !alpha2) return B200MOE_ERR_ARG;
+  if (E <= 0 || E > 256 || top_k <= 0 || top_k > 16 || H <= 0 || I <= 0) return B200MOE_ERR_SHAPE;
+  if (H % 128 || I % 64) return B200MOE_ERR_SHAPE;   // FC2 output blocks of 128 rows, FC1 column blocks of 64
+  if (((uintptr_t)s1_128x4 & 15) || ((uintptr_t)s2_128x4 & 15)) return B200MOE_ERR_ARG;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  cudaDeviceProp prop;
+  B200_CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) return B200MOE_ERR_DEVICE;
+  b200moe_layer* L = new (std::nothrow) b200moe_layer;
+  if (!L) return B200MOE_ERR_ARG;
+  memset(L, 0, sizeof(*L));
+  L->E = E, L->H = H, L->I = I, L->top_k = top_k, L->sms = prop.multiProcessorCount;
+  L->q1 = q1, L->s1 = s1_128x4, L->q2 = q2, L->s2 = s2_128x4, L->alpha1 = alpha1, L->alpha2 = alpha2;
+  L->KB1 = (H + 255) / 256, L->KB2 = (I + 255) / 256;
+  L->CB1 = I / 64, L->NB2 = H / 128;
+  L->KT1 = (H / 16 + 3) / 4, L->KT2 = (I / 16 + 3) / 4;
+  L->s1_stride = align_up(2LL * I, 128) * L->KT1 * 4;
+  L->s2_stride = align_up((long long)H, 128) * L->KT2 * 4;
+  int rc = make_codes_map(&L->tm1, q1, (long long)E * 2 * I, H / 2, 64);
+  if (rc == B200MOE_OK) rc = make_codes_map(&L->tm2, q2, (long long)E * H, I / 2, 128);
+  if (rc != B200MOE_OK) { delete L; return rc; }
+  // workspace
+  const int V = 2 * L->sms;
+  L->umax_cap = E < 16 * top_k ? E : 16 * top_k;
+  long long o = 0;
+  L->off_status = o, o += 256;                                               // status + grid barrier words
+  L->off_cnt1 = o, o = align_up(o + (long long)L->umax_cap * L->CB1 * 4, 256);
+  L->off_cnt2 = o, o = align_up(o + (long long)L->NB2 * 4, 256);
+  L->off_scratch = o, o = align_up(o + (long long)V * 2 * 128 * 16 * 4, 256);
+  L->off_actfrag = o, o = align_up(o + (long long)L->umax_cap * L->KB2 * 8192, 256);
+  L->off_tables = o, o = align_up(o + (long long)(2 * L->umax_cap + 1 + 16 * top_k) * 4, 256);
+  L->off_actbf16 = o, o = align_up(o + (long long)16 * top_k * I * 2, 256);
+  L->ws_bytes = o;
+  *out = L;
+  return B200MOE_OK;
+}
+
+extern "C" void b200moe_layer_destroy(b200moe_layer* L) { delete L; }
+
+extern "C" long long b200moe_layer_workspace_bytes(const b200moe_layer* L) { return L ? L->ws_bytes : B200MOE_ERR_ARG; }
+
+// Zero the workspace (counters, barrier words, status, activation padding). Once after allocation, and again after a
+// call that returned a timeout status.
+extern "C" int b200moe_layer_workspace_init(const b200moe_layer* L, void* ws, long long ws_bytes, void* stream) {
+  if (!L || !ws) return B200MOE_ERR_ARG;
+  if (ws_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
+  B200_CUDA_TRY(cudaMemsetAsync(ws, 0, (size_t)L->ws_bytes, (cudaStream_t)stream));
+  return B200MOE_OK;
+}
+
+static int decode_common(const b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* act_bf16,
+                         int phases, int write_tables, void* ws, long long ws_bytes, void* stream) {
+  if (!L || !ids || !wts || !ws) return B200MOE_ERR_ARG;
+  if ((phases & 1) && !x) return B200MOE_ERR_ARG;
+  if ((phases & 2) && !out) return B200MOE_ERR_ARG;
+  if (M < 0) return B200MOE_ERR_ARG;
+  if (M > 16) return B200MOE_ERR_LIMIT;
+  if (ws_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
+  if (((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return B200MOE_ERR_ARG;
+  if (M == 0) return B200MOE_OK;
+  uint8_t* w = (uint8_t*)ws;
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.tm1 = L->tm1, p.tm2 = L->tm2;
+  p.s1 = (const uint8_t*)L->s1, p.s2 = (const uint8_t*)L->s2;
+  p.alpha1 = L->alpha1, p.alpha2 = L->alpha2;
+  p.x = (const __nv_bfloat16*)x, p.ids = ids, p.wts = wts, p.out = (__nv_bfloat16*)out;
+  p.act_bf16 = (__nv_bfloat16*)act_bf16;
+  p.actfrag = (__half*)(w + L->off_actfrag);
+  p.scratch = (float*)(w + L->off_scratch);
+  p.cnt1 = (unsigned*)(w + L->off_cnt1), p.cnt2 = (unsigned*)(w + L->off_cnt2);
+  p.status = (int*)(w + L->off_status);
+  p.gridbar = (unsigned*)(w + L->off_status + 64);
+  p.Umax = L->E < M * L->top_k ? L->E : M * L->top_k;
+  if (write_tables) {
+    p.experts_out = (int*)(w + L->off_tables);
+    p.offsets_out = p.experts_out + L->umax_cap;
+    p.pairs_out = p.offsets_out + L->umax_cap + 1;
+  }
+  p.s1_expert_stride = L->s1_stride, p.s2_expert_stride = L->s2_stride;
+  p.M = M, p.E = L->E, p.H = L->H, p.I = L->I, p.top_k = L->top_k, p.phases = phases;
+  p.KB1 = L->KB1, p.KB2 = L->KB2, p.CB1 = L->CB1, p.NB2 = L->NB2, p.KT1 = L->KT1, p.KT2 = L->KT2;
+  const int nb8 = M <= 8 ? 1 : 2;
+  const int slab = nb8 * 4096;
+  const int limit = 227 * 1024;
+  int NS = 8;
+  for (; NS >= 2; NS -= 2) {
+    const int region = (L->KB1 * slab > NS * slab) ? L->KB1 * slab : NS * slab;
+    if (b200_decode_smem_bytes(NS, region) <= limit) { p.region_bytes = region; break; }
+  }
+  if (NS < 2) return B200MOE_ERR_SHAPE;
+  p.NS = NS;
+  return b200_decode_launch(p, L->sms, b200_decode_smem_bytes(NS, p.region_bytes), (cudaStream_t)stream);
+}
+
+// The whole decode layer: out[M, H] (bf16) = sum_j w[t,j] * FC2_e(silu(gate) * up), e = ids[t,j]. M <= 16.
+// Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
+extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
+                                      int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
+  return decode_common(L, x_bf16, topk_ids, topk_weights, M, out_bf16, nullptr, 3, 1, workspace, workspace_bytes, stream);
+}
+
+// FC1 alone (sm120fp4/kernels/fc1_w4a16.py:251-262, fc1_mma.py:266-282): act[M*top_k, I] bf16, row = pair index.
+extern "C" int b200moe_decode_fc1(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                                  void* act_bf16, void* workspace, long long workspace_bytes, void* stream) {
+  if (!act_bf16) return B200MOE_ERR_ARG;
+  return decode_common(L, x_bf16, topk_ids, topk_weights, M, nullptr, act_bf16, 1, 1, workspace, workspace_bytes, stream);
+}
+
+// FC2 alone (sm120fp4/kernels/fc2_w4a16.py:276-279, fc2_mma_pf.py:403-421): consumes act[M*top_k, I] bf16.
+extern "C" int b200moe_decode_fc2(const b200moe_layer* L, const void* act_bf16, const int* topk_ids, const float* topk_weights, int M,
+                                  void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
+  if (!L || !act_bf16 || !topk_ids || !workspace) return B200MOE_ERR_ARG;
+  if (M < 0) return B200MOE_ERR_ARG;
+  if (M > 16) return B200MOE_ERR_LIMIT;
+  if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
+  if (M == 0) return B200MOE_OK;
+  // routing tables first (phase mask 0 runs only the prologue), then the fragment-ordered copy of the activations
+  int rc = decode_common(L, nullptr, topk_ids, topk_weights, M, nullptr, nullptr, 0, 1, workspace, workspace_bytes, stream);
+  if (rc != B200MOE_OK) return rc;
+  uint8_t* w = (uint8_t*)workspace;
+  const int umax = L->E < M * L->top_k ? L->E : M * L->top_k;
+  rc = b200_act_to_frag_launch(act_bf16, topk_ids, (const int*)(w + L->off_tables), umax, M, L->top_k, L->I, L->KB2,
+                               w + L->off_actfrag, (cudaStream_t)stream);
+  if (rc != B200MOE_OK) return rc;
+  return decode_common(L, nullptr, topk_ids, topk_weights, M, out_bf16, nullptr, 2, 0, workspace, workspace_bytes, stream);
+}
+
+// Copy out the routing tables the last decode call wrote: experts [Umax], offsets [Umax+1], pairs [M*top_k] (device to
+// device, on the stream), in the padded form of the reference's GPU router.
+extern "C" int b200moe_layer_route_tables(const b200moe_layer* L, const void* workspace, int M, int* experts, int* offsets, int* pairs,
+                                          void* stream) {
+  if (!L || !workspace || !experts || !offsets || !pairs || M < 0 || M > 16) return B200MOE_ERR_ARG;
+  const uint8_t* w = (const uint8_t*)workspace;
+  const int umax = L->E < M * L->top_k ? L->E : M * L->top_k;
+  const int* t = (const int*)(w + L->off_tables);
+  cudaStream_t st = (cudaStream_t)stream;
+  B200_CUDA_TRY(cudaMemcpyAsync(experts, t, umax * sizeof(int), cudaMemcpyDeviceToDevice, st));
+  B200_CUDA_TRY(cudaMemcpyAsync(offsets, t + L->umax_cap, (umax + 1) * sizeof(int), cudaMemcpyDeviceToDevice, st));
+  B200_CUDA_TRY(cudaMemcpyAsync(pairs, t + 2 * L->umax_cap + 1, M * L->top_k * sizeof(int), cudaMemcpyDeviceToDevice, st));
+  return B200MOE_OK;
+}
+
+// Read the status word (synchronises the stream): 0, or B200MOE_ERR_TIMEOUT / B200MOE_ERR_ARG (expert id out of range).
+extern "C" int b200moe_layer_status(const b200moe_layer* L, const void* workspace, void* stream) {
+  if (!L || !workspace) return B200MOE_ERR_ARG;
+  int st = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&st, (const uint8_t*)workspace + L->off_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  if (st == 0) return B200MOE_OK;
+  return st == 4 ? B200MOE_ERR_ARG : B200MOE_ERR_TIMEOUT;
+}
+
+extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }

@@ -1,0 +1,601 @@
+// The decode-regime (M <= 16 tokens) W4A16 MoE layer as ONE persistent kernel: routing, FC1 (+SiLU*mul) and FC2
+// (+ top-k weighted combine). It replaces the reference's three launches k_route / k_fc1* / k_fc2* of
+// sm120fp4/kernels/{moe_w4a16,fc1_w4a16,fc1_mma,fc2_w4a16,fc2_mma_pf}.py; the arithmetic contract is theirs
+// (FP4 code x E4M3 block scale, fp32 accumulation, alpha applied in fp32, __expf SiLU, one rounding of the output).
+//
+// Structure (B200-first, memory-bound):
+//  * one CTA per SM; warp 8 is the TMA producer, warps 0-3 and 4-7 are two consumer groups ("workers").
+//  * the work is a flat list of weight tiles: FC1 tile = 64 up rows + 64 gate rows x 256 K-codes (two 8 KB TMA boxes,
+//    128B swizzle) + their 128x4 scale runs; FC2 tile = 128 output rows x 256 K-codes + scale run + the activation slab
+//    of that expert / K-box. Every worker owns a contiguous, equal share of the flat list (stream-K), so any number of
+//    touched experts balances over the 2 x #SM workers.
+//  * tiles land in a ring of shared-memory stages guarded by full/empty mbarriers; the producer runs ahead of the math by
+//    the ring depth and, across the FC1->FC2 dependency, prefetches FC2 weight tiles before the grid-wide barrier opens.
+//  * math: codes -> f16 with cvt.rn.f16x2.e2m1x2, times the E4M3 scale (exact in f16), mma.sync m16n8k16 f16 with fp32
+//    accumulators, tokens as the N dimension ("global token columns": column j is token j for every expert, so partial
+//    sums of different experts add in registers and the routing weight is applied per expert in fp32).
+//  * a tile range that cuts a unit writes its partial sums to an L2-resident scratch; the last arriver (atomic counter)
+//    adds the pieces in worker order, so the result is bit-identical from call to call.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "decode_params.h"
+
+namespace b200 {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kGroupThreads = 128;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kSlotBytes = 20480;      // 16 KB codes + 4 KB scales
+constexpr int kCodesBytes = 16384;
+constexpr int kMaxE = 256, kMaxP = 256;
+
+enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_GRID = 3, ST_BAD_ID = 4 };
+
+struct Tables {
+  int ids[kMaxP];
+  float wts[kMaxP];
+  int cnt[kMaxE];      // pairs per expert
+  int base[kMaxE];     // inclusive scan of cnt
+  int uidx[kMaxE];     // inclusive scan of touched flags
+  int experts[kMaxE];  // touched experts ascending
+  int U;
+  volatile int abort_flag;
+  int last_flag[2];
+  uint64_t full[8];
+  uint64_t empty[8];
+};
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
+// Worker v's share [s, e) of T tiles over V workers; worker_of(f) inverts it.
+__device__ __forceinline__ int share_begin(int v, int T, int V) { return (int)(((long long)v * T) / V); }
+__device__ __forceinline__ int worker_of(int f, int T, int V) { return (int)((((long long)f + 1) * V - 1) / T); }
+// Workers in [vlo, vhi] that own at least one tile (with fewer tiles than workers some shares are empty).
+__device__ __forceinline__ int live_workers(int vlo, int vhi, int T, int V) {
+  int n = 0;
+  for (int pv = vlo; pv <= vhi; ++pv) n += share_begin(pv + 1, T, V) > share_begin(pv, T, V);
+  return n;
+}
+
+// One weight tile through the tensor cores for one warp: two 16-row blocks (rb) x 256 K-codes, NB8 token octets.
+template <int NB8>
+__device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uint32_t sc0, int rt0, uint32_t sc1, int rt1,
+                                         bool kt_valid, uint32_t bfrag, int lane, float (&acc)[2][NB8][4]) {
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t sfw[2][2];
+  {
+    const int r00 = rt0 + g, r01 = rt0 + g + 8, r10 = rt1 + g, r11 = rt1 + g + 8;
+    sfw[0][0] = kt_valid ? lds32(sc0 + t * 512 + (r00 & 31) * 16 + (r00 >> 5) * 4) : 0u;
+    sfw[0][1] = kt_valid ? lds32(sc0 + t * 512 + (r01 & 31) * 16 + (r01 >> 5) * 4) : 0u;
+    sfw[1][0] = kt_valid ? lds32(sc1 + t * 512 + (r10 & 31) * 16 + (r10 >> 5) * 4) : 0u;
+    sfw[1][1] = kt_valid ? lds32(sc1 + t * 512 + (r11 & 31) * 16 + (r11 >> 5) * 4) : 0u;
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint4 bq[4][NB8];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+      for (int n = 0; n < NB8; ++n) bq[jj][n] = lds128(bfrag + ((((h * 4 + jj) * NB8 + n) * 32 + lane) << 4));
+#pragma unroll
+    for (int rb = 0; rb < 2; ++rb) {
+      const int ra = (rb == 0 ? row0 : row1) + g;   // stage row of fragment row g; fragment row g+8 is ra+8
+      const uint32_t chunk = (uint32_t)(((2 * t + h) ^ (ra & 7)) << 4);
+      const uint4 qa = lds128(codes + ra * 128 + chunk);
+      const uint4 qb = lds128(codes + (ra + 8) * 128 + chunk);
+      const uint32_t sa = cvt_e4m3x2_f16x2(sfw[rb][0] >> (16 * h));
+      const uint32_t sb = cvt_e4m3x2_f16x2(sfw[rb][1] >> (16 * h));
+      const uint32_t sa_lo = prmt(sa, sa, 0x1010), sa_hi = prmt(sa, sa, 0x3232);
+      const uint32_t sb_lo = prmt(sb, sb, 0x1010), sb_hi = prmt(sb, sb, 0x3232);
+      const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+      for (int wd = 0; wd < 4; ++wd) {
+        uint32_t da[4], db[4];
+        cvt_e2m1x8_f16x2(wa[wd], da);
+        cvt_e2m1x8_f16x2(wb[wd], db);
+        const uint32_t s_a = wd < 2 ? sa_lo : sa_hi, s_b = wd < 2 ? sb_lo : sb_hi;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          da[i] = hmul2_u32(da[i], s_a);
+          db[i] = hmul2_u32(db[i], s_b);
+        }
+#pragma unroll
+        for (int n = 0; n < NB8; ++n) {
+          mma_f16_16816(acc[rb][n], da[0], db[0], da[1], db[1], bq[wd][n].x, bq[wd][n].y);
+          mma_f16_16816(acc[rb][n], da[2], db[2], da[3], db[3], bq[wd][n].z, bq[wd][n].w);
+        }
+      }
+    }
+  }
+}
+
+// half index inside the fragment-ordered activation buffer of one expert slot, for K index k and token tok
+template <int NB8>
+__device__ __forceinline__ int frag_index(int k, int tok) {
+  const int kb = k >> 8, tq = (k & 255) >> 6, h = (k & 63) >> 5, jj = (k & 31) >> 3;
+  const int lane = ((tok & 7) << 2) | tq;
+  return kb * (NB8 * 2048) + ((((h * 4 + jj) * NB8 + (tok >> 3)) * 32 + lane) << 3) + (k & 7);
+}
+
+template <int NB8>
+__global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constant__ DecodeParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int NS = P.NS;                          // ring stages (even); worker g uses slots 2*i+g
+  uint8_t* ring = smem;
+  uint8_t* region = smem + NS * kSlotBytes;     // FC1: x in fragment order (f16); FC2: activation slabs per ring slot
+  Tables& T = *reinterpret_cast<Tables*>(region + P.region_bytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int npairs = P.M * P.top_k;
+  const int V = 2 * gridDim.x;
+
+  // ---------------------------------------------------------------- prologue: barriers + routing tables (every CTA)
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&T.full[s], 1);
+      mbar_init(&T.empty[s], 4);
+    }
+    T.abort_flag = 0;
+    T.last_flag[0] = T.last_flag[1] = 0;
+    fence_mbar_init();
+  }
+  if (tid < kMaxE) T.cnt[tid] = 0;
+  __syncthreads();
+  for (int p = tid; p < npairs; p += kThreads) {
+    int e = P.ids[p];
+    if (e < 0 || e >= P.E) { *P.status = ST_BAD_ID; e = 0; }
+    T.ids[p] = e;
+    T.wts[p] = P.wts[p];
+    atomicAdd(&T.cnt[e], 1);
+  }
+  __syncthreads();
+  if (warp == 0) {   // inclusive scans over kMaxE entries, 8 per lane
+    int c[8], f[8], sc = 0, sf = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      c[i] = T.cnt[lane * 8 + i];
+      f[i] = c[i] > 0;
+      sc += c[i];
+      sf += f[i];
+    }
+    int ic = sc, iff = sf;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, iff, o);
+      if (lane >= o) { ic += a; iff += b; }
+    }
+    int rc = ic - sc, rf = iff - sf;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      rc += c[i];
+      rf += f[i];
+      T.base[lane * 8 + i] = rc;
+      T.uidx[lane * 8 + i] = rf;
+    }
+    if (lane == 31) T.U = iff;
+  }
+  __syncthreads();
+  if (tid < kMaxE && T.cnt[tid] > 0) T.experts[T.uidx[tid] - 1] = tid;
+  __syncthreads();
+  const int U = T.U;
+
+  if (blockIdx.x == 0 && P.experts_out) {   // the routing tables in the reference's padded form
+    const int Umax = P.Umax;
+    for (int e = tid; e < P.E; e += kThreads)
+      if (T.cnt[e] > 0) {
+        P.experts_out[T.uidx[e] - 1] = e;
+        P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e];
+      }
+    for (int u = U + tid; u < Umax; u += kThreads) {
+      P.experts_out[u] = -1;
+      P.offsets_out[u + 1] = npairs;
+    }
+    if (tid == 0) P.offsets_out[U] = npairs;
+    for (int p = tid; p < npairs; p += kThreads) {
+      const int e = T.ids[p];
+      int r = 0;
+      for (int q = 0; q < p; ++q) r += T.ids[q] == e;
+      P.pairs_out[T.base[e] - T.cnt[e] + r] = p;
+    }
+  }
+
+  const bool do1 = (P.phases & 1) != 0, do2 = (P.phases & 2) != 0;
+  const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
+  const int T1 = do1 ? U * CB1 * KB1 : 0;
+  const int T2 = do2 ? NB2 * U * KB2 : 0;
+  const int slab_bytes = NB8 * 4096;
+
+  if (warp == kConsumerWarps) {
+    // ============================================================== producer (one thread)
+    if (lane == 0) {
+      prefetch_tensormap(&P.tm1);
+      prefetch_tensormap(&P.tm2);
+      const uint64_t pol = policy_evict_first();
+      const unsigned gen0 = P.gridbar ? ld_acquire_gpu(P.gridbar + 1) : 0u;
+      bool passed = !do1;            // without an FC1 phase the activations are already in place
+      int s1[2], n1[2], s2[2], n2[2];
+      for (int g = 0; g < 2; ++g) {
+        const int v = 2 * blockIdx.x + g;
+        s1[g] = share_begin(v, T1, V);
+        n1[g] = share_begin(v + 1, T1, V) - s1[g];
+        s2[g] = share_begin(v, T2, V);
+        n2[g] = share_begin(v + 1, T2, V) - s2[g];
+      }
+      const int per = NS / 2;
+      int pend_slot[8];
+      const uint8_t* pend_src[8];
+      int npend = 0;
+      auto wait_grid = [&]() {
+        if (passed) return;
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 24); ++it) {
+          if (ld_acquire_gpu(P.gridbar + 1) != gen0) { ok = true; break; }
+          if (T.abort_flag) break;
+          __nanosleep(128);
+        }
+        if (!ok) { T.abort_flag = 1; *P.status = ST_TIMEOUT_GRID; }
+        fence_proxy_async();
+        for (int i = 0; i < npend; ++i)
+          bulk_load(region + pend_slot[i] * slab_bytes, pend_src[i], slab_bytes, &T.full[pend_slot[i]]);
+        npend = 0;
+        passed = true;
+      };
+      const int nmax = max(n1[0] + n2[0], n1[1] + n2[1]);
+      for (int j = 0; j < nmax; ++j) {
+        for (int g = 0; g < 2; ++g) {
+          if (j >= n1[g] + n2[g]) continue;
+          const int slot = 2 * (j % per) + g, use = j / per;
+          const bool is2 = j >= n1[g];
+          if (use >= 1) {
+            // the previous occupant of this slot was an FC2 tile still waiting for its activations: open the gate first
+            if (!passed && (j - per) >= n1[g]) wait_grid();
+            if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_EMPTY;
+          }
+          uint8_t* st = ring + slot * kSlotBytes;
+          if (!is2) {
+            const int f = s1[g] + j;
+            const int kb = f % KB1, q = f / KB1, cb = q % CB1, u = q / CB1;
+            const int e = T.experts[u];
+            const int nkt = min(4, P.KT1 - 4 * kb);
+            const int up_row = 64 * cb, gate_row = P.I + 64 * cb;
+            mbar_expect_tx(&T.full[slot], kCodesBytes + 2 * nkt * 512);
+            tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + up_row, &T.full[slot], pol);
+            tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + gate_row, &T.full[slot], pol);
+            const uint8_t* sbase = P.s1 + (long long)e * P.s1_expert_stride;
+            bulk_load_hint(st + kCodesBytes, sbase + ((long long)(up_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+            bulk_load_hint(st + kCodesBytes + 2048, sbase + ((long long)(gate_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+          } else {
+            const int f = s2[g] + (j - n1[g]);
+            const int kb = f % KB2, q = f / KB2, u = q % U, nb = q / U;
+            const int e = T.experts[u];
+            const int nkt = min(4, P.KT2 - 4 * kb);
+            mbar_expect_tx(&T.full[slot], kCodesBytes + nkt * 512 + slab_bytes);
+            tma_load_2d_hint(st, &P.tm2, 128 * kb, e * P.H + 128 * nb, &T.full[slot], pol);
+            bulk_load_hint(st + kCodesBytes, P.s2 + (long long)e * P.s2_expert_stride + ((long long)nb * P.KT2 + 4 * kb) * 512,
+                           nkt * 512, &T.full[slot], pol);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(P.actfrag) + ((long long)u * KB2 + kb) * slab_bytes;
+            if (passed) bulk_load(region + slot * slab_bytes, src, slab_bytes, &T.full[slot]);
+            else { pend_slot[npend] = slot; pend_src[npend] = src; ++npend; }
+          }
+        }
+      }
+      if (npend > 0) wait_grid();
+    }
+    __syncwarp();
+  } else {
+    // ============================================================== consumers: two groups of four warps
+    const int grp = warp >> 2, w = warp & 3;
+    const int v = 2 * blockIdx.x + grp;
+    const int gtid = tid & (kGroupThreads - 1);
+    const int g = lane >> 2, t = lane & 3;
+    const int per = NS / 2;
+    const uint32_t ring_a = smem_u32(ring), region_a = smem_u32(region);
+    int j = 0;   // this group's tile sequence number (ring position)
+
+    if (do1) {
+      // ---- stage x as f16 in fragment order (all 256 consumer threads), zero beyond M tokens / H columns
+      const int chunks_per_tok = KB1 * 32;   // 16-byte chunks (8 values) per token over the padded K
+      for (int i = tid; i < 8 * NB8 * chunks_per_tok; i += kConsumerWarps * 32) {
+        const int tok = i / chunks_per_tok, c8 = i % chunks_per_tok, k = c8 * 8;
+        uint4 outv = make_uint4(0u, 0u, 0u, 0u);
+        if (tok < P.M && k < P.H) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(P.x + (long long)tok * P.H + k);
+          const uint32_t wsrc[4] = {raw.x, raw.y, raw.z, raw.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float lo = __uint_as_float(wsrc[q] << 16), hi = __uint_as_float(wsrc[q] & 0xffff0000u);
+            const __half2 hv = __floats2half2_rn(fminf(fmaxf(lo, -65504.f), 65504.f), fminf(fmaxf(hi, -65504.f), 65504.f));
+            o[q] = *reinterpret_cast<const uint32_t*>(&hv);
+          }
+          outv = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        *reinterpret_cast<uint4*>(region + frag_index<NB8>(k, tok) * 2) = outv;
+      }
+      named_bar_sync(3, kConsumerWarps * 32);
+
+      // ---- FC1 pieces of this worker
+      const int fs = share_begin(v, T1, V), fe = share_begin(v + 1, T1, V);
+      int f = fs;
+      while (f < fe) {
+        const int q = f / KB1, cb = q % CB1, u = q / CB1;
+        const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
+        const int e = T.experts[u];
+        float acc[2][NB8][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int n = 0; n < NB8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+        const int rt_up = ((64 * cb) & 127) + 16 * w, rt_gate = ((P.I + 64 * cb) & 127) + 16 * w;
+        for (int kb = k0; kb < k1; ++kb, ++j) {
+          const int slot = 2 * (j % per) + grp, use = j / per;
+          if (!mbar_wait(&T.full[slot], use & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+          const uint32_t st = ring_a + slot * kSlotBytes;
+          mma_tile<NB8>(st, 16 * w, 64 + 16 * w, st + kCodesBytes, rt_up, st + kCodesBytes + 2048, rt_gate,
+                        4 * kb + t < P.KT1, region_a + kb * (NB8 * 4096), lane, acc);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&T.empty[slot]);
+        }
+        f += k1 - k0;
+        // ---- finish the unit: directly when this piece covers all of K, else through the scratch and a last arriver
+        bool finalize = true;
+        if (!(k0 == 0 && k1 == KB1)) {
+          const int slot_id = (f - (k1 - k0)) == fs ? 0 : 1;
+          float* mine = P.scratch + ((long long)(v * 2 + slot_id) * kGroupThreads + gtid) * 16;
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int n = 0; n < NB8; ++n)
+              *reinterpret_cast<float4*>(mine + (a * NB8 + n) * 4) = make_float4(acc[a][n][0], acc[a][n][1], acc[a][n][2], acc[a][n][3]);
+          __threadfence();
+          named_bar_sync(1 + grp, kGroupThreads);
+          const int vlo = worker_of(q * KB1, T1, V), vhi = worker_of(q * KB1 + KB1 - 1, T1, V);
+          if (gtid == 0) {
+            const unsigned old = atomicAdd(P.cnt1 + q, 1u);
+            const int last = old + 1u == (unsigned)live_workers(vlo, vhi, T1, V);
+            if (last) P.cnt1[q] = 0;
+            T.last_flag[grp] = last;
+          }
+          named_bar_sync(1 + grp, kGroupThreads);
+          finalize = T.last_flag[grp] != 0;
+          if (finalize) {
+            __threadfence();
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+              for (int n = 0; n < NB8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+            for (int pv = vlo; pv <= vhi; ++pv) {   // pieces in worker order: a fixed summation order
+              if (share_begin(pv + 1, T1, V) == share_begin(pv, T1, V)) continue;
+              const int pslot = share_begin(pv, T1, V) < q * KB1 ? 1 : 0;   // a piece that starts the worker's share is slot 0
+              const float* src = P.scratch + ((long long)(pv * 2 + pslot) * kGroupThreads + gtid) * 16;
+#pragma unroll
+              for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int n = 0; n < NB8; ++n) {
+                  const float4 pf = __ldcg(reinterpret_cast<const float4*>(src + (a * NB8 + n) * 4));
+                  acc[a][n][0] += pf.x, acc[a][n][1] += pf.y, acc[a][n][2] += pf.z, acc[a][n][3] += pf.w;
+                }
+            }
+          }
+          named_bar_sync(1 + grp, kGroupThreads);   // last_flag may be rewritten by the next unit only after all read it
+        }
+        if (finalize) {
+          const float alpha = P.alpha1[e];
+          __half* af = P.actfrag + (long long)u * KB2 * (NB8 * 2048);
+#pragma unroll
+          for (int n = 0; n < NB8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int tok = 8 * n + 2 * t + (i & 1);
+              const int c = 64 * cb + 16 * w + g + ((i >> 1) << 3);   // intermediate column (K index of FC2)
+              // is token tok routed to expert e, and through which pair?
+              int pair = -1;
+              if (tok < P.M)
+                for (int s = 0; s < P.top_k; ++s)
+                  if (T.ids[tok * P.top_k + s] == e) pair = tok * P.top_k + s;
+              float a = 0.f;
+              if (pair >= 0) {
+                a = silu_mul(alpha * acc[1][n][i], alpha * acc[0][n][i]);
+                a = fminf(fmaxf(a, -65504.f), 65504.f);
+              }
+              af[frag_index<NB8>(c, tok)] = __float2half_rn(a);
+              if (P.act_bf16 && pair >= 0)
+                for (int s = 0; s < P.top_k; ++s)
+                  if (T.ids[tok * P.top_k + s] == e) P.act_bf16[(long long)(tok * P.top_k + s) * P.I + c] = __float2bfloat16_rn(a);
+            }
+          if (cb == CB1 - 1 && (P.I & 255)) {   // zero the K padding of this expert's activation slabs
+            for (int i = gtid; i < (KB2 * 256 - P.I) * 8 * NB8; i += kGroupThreads)
+              af[frag_index<NB8>(P.I + i / (8 * NB8), i % (8 * NB8))] = __float2half_rn(0.f);
+          }
+        }
+      }
+      if (do2) {
+        // ---- publish FC1's results and arrive at the grid-wide barrier (the producer is the only waiter)
+        __threadfence();
+        fence_proxy_async();
+        named_bar_sync(1 + grp, kGroupThreads);
+        if (gtid == 0) {
+          const unsigned old = atomicAdd(P.gridbar, 1u);
+          if (old == (unsigned)(V - 1)) {
+            P.gridbar[0] = 0;
+            __threadfence();
+            atomicAdd(P.gridbar + 1, 1u);
+          }
+        }
+      }
+    }
+
+    if (do2) {
+      // ---- FC2 pieces of this worker: tiles ordered (output block nb, expert u, K box kb)
+      const int fs = share_begin(v, T2, V), fe = share_begin(v + 1, T2, V);
+      const int per_nb = U * KB2;
+      int f = fs;
+      while (f < fe) {
+        const int nb = f / per_nb;
+        const int pe = min(fe, (nb + 1) * per_nb);   // end of this piece
+        float oacc[2][NB8][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int n = 0; n < NB8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) oacc[a][n][i] = 0.f;
+        const int piece_start = f;
+        while (f < pe) {
+          const int q = f / KB2, u = q % U;
+          const int k0 = f % KB2, k1 = min(KB2, k0 + (pe - f));
+          const int e = T.experts[u];
+          float acc[2][NB8][4];
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int n = 0; n < NB8; ++n)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+          for (int kb = k0; kb < k1; ++kb, ++j) {
+            const int slot = 2 * (j % per) + grp, use = j / per;
+            if (!mbar_wait(&T.full[slot], use & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+            const uint32_t st = ring_a + slot * kSlotBytes;
+            mma_tile<NB8>(st, 32 * w, 32 * w + 16, st + kCodesBytes, 32 * w, st + kCodesBytes, 32 * w + 16,
+                          4 * kb + t < P.KT2, region_a + slot * slab_bytes, lane, acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&T.empty[slot]);
+          }
+          f += k1 - k0;
+          // routing weight x alpha2 for this lane's token columns, applied in fp32
+          const float alpha = P.alpha2[e];
+#pragma unroll
+          for (int n = 0; n < NB8; ++n)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int tok = 8 * n + 2 * t + c;
+              float sc = 0.f;
+              if (tok < P.M)
+                for (int s = 0; s < P.top_k; ++s)
+                  if (T.ids[tok * P.top_k + s] == e) sc += T.wts[tok * P.top_k + s];
+              sc *= alpha;
+#pragma unroll
+              for (int a = 0; a < 2; ++a) {
+                oacc[a][n][c] += sc * acc[a][n][c];
+                oacc[a][n][2 + c] += sc * acc[a][n][2 + c];
+              }
+            }
+        }
+        // ---- every output block is shared by several workers: partial sums to the scratch, last arriver reduces
+        {
+          const int slot_id = piece_start == fs ? 0 : 1;
+          float* mine = P.scratch + ((long long)(v * 2 + slot_id) * kGroupThreads + gtid) * 16;
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int n = 0; n < NB8; ++n)
+              *reinterpret_cast<float4*>(mine + (a * NB8 + n) * 4) = make_float4(oacc[a][n][0], oacc[a][n][1], oacc[a][n][2], oacc[a][n][3]);
+          __threadfence();
+          named_bar_sync(1 + grp, kGroupThreads);
+          const int vlo = worker_of(nb * per_nb, T2, V), vhi = worker_of((nb + 1) * per_nb - 1, T2, V);
+          if (gtid == 0) {
+            const unsigned old = atomicAdd(P.cnt2 + nb, 1u);
+            const int last = old + 1u == (unsigned)live_workers(vlo, vhi, T2, V);
+            if (last) P.cnt2[nb] = 0;
+            T.last_flag[grp] = last;
+          }
+          named_bar_sync(1 + grp, kGroupThreads);
+          const bool last = T.last_flag[grp] != 0;
+          if (last) {
+            __threadfence();
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+              for (int n = 0; n < NB8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) oacc[a][n][i] = 0.f;
+            for (int pv = vlo; pv <= vhi; ++pv) {
+              if (share_begin(pv + 1, T2, V) == share_begin(pv, T2, V)) continue;
+              const int pslot = share_begin(pv, T2, V) < nb * per_nb ? 1 : 0;
+              const float* src = P.scratch + ((long long)(pv * 2 + pslot) * kGroupThreads + gtid) * 16;
+#pragma unroll
+              for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int n = 0; n < NB8; ++n) {
+                  const float4 pf = __ldcg(reinterpret_cast<const float4*>(src + (a * NB8 + n) * 4));
+                  oacc[a][n][0] += pf.x, oacc[a][n][1] += pf.y, oacc[a][n][2] += pf.z, oacc[a][n][3] += pf.w;
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+              for (int n = 0; n < NB8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int tok = 8 * n + 2 * t + (i & 1);
+                  const int row = 128 * nb + 32 * w + 16 * a + g + ((i >> 1) << 3);
+                  if (tok < P.M) P.out[(long long)tok * P.H + row] = __float2bfloat16_rn(oacc[a][n][i]);
+                }
+          }
+          named_bar_sync(1 + grp, kGroupThreads);
+        }
+      }
+    }
+  }
+  // Every TMA copy this CTA issued has been consumed by a full-barrier wait above. If a bounded wait ran out (abort flag
+  // set, status word written), give copies still in flight time to land before the CTA retires.
+  __syncthreads();
+  if (T.abort_flag)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+}
+
+// bf16 activations [P, I] (row = pair index) -> the fragment-ordered f16 buffer the FC2 phase streams. Used only by the
+// stand-alone FC2 entry point; the fused layer writes that buffer from FC1's epilogue.
+template <int NB8>
+__global__ void __launch_bounds__(256) k_act_to_frag(const __nv_bfloat16* __restrict__ act, const int* __restrict__ ids,
+                                                     const int* __restrict__ experts, int Umax, int M, int top_k, int I, int KB2,
+                                                     __half* __restrict__ actfrag) {
+  const int u = blockIdx.x;
+  if (u >= Umax) return;
+  const int e = experts[u];
+  if (e < 0) return;
+  const int kpad = KB2 * 256;
+  for (int i = threadIdx.x; i < kpad * 8 * NB8; i += blockDim.x) {
+    const int tok = i / kpad, k = i % kpad;
+    float a = 0.f;
+    if (tok < M && k < I)
+      for (int s = 0; s < top_k; ++s)
+        if (ids[tok * top_k + s] == e) a = __bfloat162float(act[(long long)(tok * top_k + s) * I + k]);
+    a = fminf(fmaxf(a, -65504.f), 65504.f);
+    actfrag[(long long)u * KB2 * (NB8 * 2048) + frag_index<NB8>(k, tok)] = __float2half_rn(a);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+int b200_decode_smem_bytes(int NS, int region_bytes) { return 1024 + NS * kSlotBytes + region_bytes + (int)sizeof(Tables); }
+
+int b200_decode_launch(const DecodeParams& p, int grid, int smem_bytes, cudaStream_t st) {
+  void* args[] = {(void*)&p};
+  const void* fn = p.M <= 8 ? (const void*)k_moe_decode<1> : (const void*)k_moe_decode<2>;
+  static thread_local int configured[2] = {0, 0};
+  const int which = p.M <= 8 ? 0 : 1;
+  if (configured[which] < smem_bytes) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    configured[which] = smem_bytes;
+  }
+  B200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, (size_t)smem_bytes, st));
+  return B200MOE_OK;
+}
+
+int b200_act_to_frag_launch(const void* act, const int* ids, const int* experts, int Umax, int M, int top_k, int I, int KB2,
+                            void* actfrag, cudaStream_t st) {
+  if (M <= 8)
+    k_act_to_frag<1><<<Umax, 256, 0, st>>>((const __nv_bfloat16*)act, ids, experts, Umax, M, top_k, I, KB2, (__half*)actfrag);
+  else
+    k_act_to_frag<2><<<Umax, 256, 0, st>>>((const __nv_bfloat16*)act, ids, experts, Umax, M, top_k, I, KB2, (__half*)actfrag);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}

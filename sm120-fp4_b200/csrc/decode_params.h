@@ -1,0 +1,46 @@
+// Kernel parameter block of the fused decode layer (passed by value as a __grid_constant__).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace b200 {
+
+struct DecodeParams {
+  CUtensorMap tm1;   // FC1 codes viewed u8 [E*2I rows, H/2 bytes], box 128 B x 64 rows, 128B swizzle
+  CUtensorMap tm2;   // FC2 codes viewed u8 [E*H rows, I/2 bytes], box 128 B x 128 rows, 128B swizzle
+  const uint8_t* s1;  // FC1 block scales, 128x4 swizzle per expert
+  const uint8_t* s2;  // FC2 block scales, 128x4 swizzle per expert
+  const float* alpha1;
+  const float* alpha2;
+  const __nv_bfloat16* x;   // [M, H]
+  const int* ids;           // [M, top_k]
+  const float* wts;         // [M, top_k]
+  __nv_bfloat16* out;       // [M, H]
+  __nv_bfloat16* act_bf16;  // optional [M*top_k, I], row = pair index
+  __half* actfrag;          // workspace: FC1 output in the fragment order FC2 streams
+  float* scratch;           // workspace: split-unit partial sums, 2 slots x 128 threads x 16 floats per worker
+  unsigned* cnt1;           // workspace: arrival counters per FC1 unit (self-resetting)
+  unsigned* cnt2;           // workspace: arrival counters per FC2 output block (self-resetting)
+  unsigned* gridbar;        // workspace: [0] arrivals, [1] generation
+  int* status;              // workspace: 0, or the code of the first bounded wait that ran out
+  int* experts_out;         // optional routing tables in the reference's padded form
+  int* offsets_out;
+  int* pairs_out;
+  long long s1_expert_stride, s2_expert_stride;
+  int M, E, H, I, top_k, Umax;
+  int phases;               // bit 0: FC1, bit 1: FC2
+  int NS;                   // ring stages (even)
+  int region_bytes;         // shared-memory region for x fragments / activation slabs
+  int KB1, KB2;             // 256-code K boxes of FC1 (over H) and FC2 (over I)
+  int CB1, NB2;             // 64-column blocks of FC1, 128-row blocks of FC2
+  int KT1, KT2;             // 4-column scale tiles along K
+};
+
+}  // namespace b200
+
+int b200_decode_smem_bytes(int NS, int region_bytes);
+int b200_decode_launch(const b200::DecodeParams& p, int grid, int smem_bytes, cudaStream_t st);
+int b200_act_to_frag_launch(const void* act, const int* ids, const int* experts, int Umax, int M, int top_k, int I, int KB2,
+                            void* actfrag, cudaStream_t st);

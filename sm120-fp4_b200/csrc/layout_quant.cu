@@ -1,0 +1,204 @@
+// 128x4 block-scale swizzle and the bf16/fp32 -> NVFP4 quantizer, bit-exact restatements on the GPU of
+// sm120fp4/layouts.py:39-78 and sm120fp4/reference.py:28-90. Both are byte-moving, HBM-bound kernels.
+#include "common.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------------------------ 128x4 layout
+// offset(r, c) = ((r/128) * nkt + c/4) * 512 + (r%32)*16 + ((r%128)/32)*4 + c%4, nkt = ceil(cols/4)
+__device__ __forceinline__ long long sf_offset_128x4(int r, int c, int nkt) {
+  return ((long long)(r >> 7) * nkt + (c >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (c & 3);
+}
+
+// One thread per 4-byte group of the swizzled buffer (one row, four scale columns). Padding groups are written as zero.
+__global__ void __launch_bounds__(256) k_to_128x4(const uint8_t* __restrict__ lin, uint8_t* __restrict__ swz, int batch,
+                                                  int rows, int cols, int prow, int nkt) {
+  const long long per = (long long)prow * nkt;
+  const long long total = per * batch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / per);
+    const long long j = i % per;
+    const int kt = (int)(j % nkt);
+    const int r = (int)(j / nkt);
+    uint32_t v = 0;
+    if (r < rows) {
+      const uint8_t* src = lin + ((long long)b * rows + r) * cols + kt * 4;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (kt * 4 + c < cols) v |= (uint32_t)src[c] << (8 * c);
+    }
+    *reinterpret_cast<uint32_t*>(swz + (long long)b * prow * nkt * 4 + sf_offset_128x4(r, kt * 4, nkt)) = v;
+  }
+}
+
+__global__ void __launch_bounds__(256) k_from_128x4(const uint8_t* __restrict__ swz, uint8_t* __restrict__ lin, int batch,
+                                                    int rows, int cols, int prow, int nkt) {
+  const long long per = (long long)rows * cols;
+  const long long total = per * batch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / per);
+    const long long j = i % per;
+    const int c = (int)(j % cols);
+    const int r = (int)(j / cols);
+    lin[i] = swz[(long long)b * prow * nkt * 4 + sf_offset_128x4(r, c, nkt)];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ quantizer
+// amax over a flat array; non-negative floats order like their bit patterns, so one atomicMax per block suffices.
+template <typename T>
+__global__ void __launch_bounds__(256) k_amax(const T* __restrict__ x, long long n, unsigned* __restrict__ amax_bits) {
+  float m = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf((float)x[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, wm[w]);
+    atomicMax(amax_bits, __float_as_uint(m));
+  }
+}
+
+// global_scale = reciprocal(max(amax, 1e-12)) * 2688: PyTorch evaluates the reference's `2688.0 / amax` with a Python
+// scalar numerator as reciprocal-then-multiply (two roundings), and the golden vectors pin that.
+__global__ void k_global_scale(const unsigned* __restrict__ amax_bits, float* __restrict__ gs) {
+  const float amax = fmaxf(__uint_as_float(*amax_bits), 1e-12f);
+  *gs = __fmul_rn(__frcp_rn(amax), 2688.0f);
+}
+
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  // round to nearest, ties to the even code, saturate at 6, sign bit kept on zero (sm120fp4/reference.py:28-44)
+  const float m = fabsf(v);
+  uint32_t c = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
+  return c | ((__float_as_uint(v) >> 31) << 3);
+}
+
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&v)[16]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 f = reinterpret_cast<const float4*>(p)[i];
+    v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+  }
+}
+
+// Quantize one 16-element block: returns the E4M3 scale byte, writes 8 packed bytes.
+__device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], float gs, uint2& packed) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float sf_f = fminf(__fmul_rn(__fdiv_rn(amax, 6.0f), gs), 448.0f);
+  const __nv_fp8_storage_t sfb = __nv_cvt_float_to_fp8(sf_f, __NV_SATFINITE, __NV_E4M3);  // RNE, subnormals kept
+  const float sf_val = __half2float(__half(__nv_cvt_fp8_to_halfraw(sfb, __NV_E4M3)));
+  const float scale = sf_val > 0.f ? __fdiv_rn(gs, sf_val) : 0.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) lo |= e2m1_code(__fmul_rn(v[i], scale)) << (4 * i);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) hi |= e2m1_code(__fmul_rn(v[8 + i], scale)) << (4 * i);
+  packed = make_uint2(lo, hi);
+  return (uint8_t)sfb;
+}
+
+// One thread per 16-element block. Destination row r reads source row src_row[r] (or r when src_row is null); a
+// negative source row writes zero codes and zero scales (padding rows of a per-expert segment).
+// sf_layout 0: row-major [rows, K/16]; 1: 128x4 swizzle over [rows, K/16] (rows padded by the caller's buffer).
+template <typename T>
+__global__ void __launch_bounds__(256) k_quantize_nvfp4(const T* __restrict__ x, const int* __restrict__ src_row, int rows,
+                                                        int K, const float* __restrict__ gs_ptr, uint8_t* __restrict__ packed,
+                                                        uint8_t* __restrict__ sf, int sf_layout) {
+  const int bpr = K >> 4;
+  const int nkt = (bpr + 3) >> 2;
+  const float gs = *gs_ptr;
+  const long long total = (long long)rows * bpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / bpr), b = (int)(i % bpr);
+    const int s = src_row ? src_row[r] : r;
+    uint2 pk = make_uint2(0u, 0u);
+    uint8_t sb = 0;
+    if (s >= 0) {
+      float v[16];
+      load16(x + (long long)s * K + b * 16, v);
+      sb = quantize_block16(v, gs, pk);
+    }
+    *reinterpret_cast<uint2*>(packed + (long long)r * (K >> 1) + b * 8) = pk;
+    if (sf_layout == 0) sf[(long long)r * bpr + b] = sb;
+    else sf[sf_offset_128x4(r, b, nkt)] = sb;
+  }
+}
+
+static inline int grid_for(long long work, int block, int cap = 148 * 16) {
+  long long g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  return (int)(g > cap ? cap : g);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200moe_to_128x4(const void* sf_linear, void* sf_swizzled, int batch, int rows, int cols, void* stream) {
+  if (!sf_linear || !sf_swizzled || batch < 0 || rows < 0 || cols < 0) return B200MOE_ERR_ARG;
+  if (batch == 0 || rows == 0 || cols == 0) return B200MOE_OK;
+  const int prow = (rows + 127) / 128 * 128, nkt = (cols + 3) / 4;
+  k_to_128x4<<<grid_for((long long)batch * prow * nkt, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)sf_linear, (uint8_t*)sf_swizzled, batch, rows, cols, prow, nkt);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_from_128x4(const void* sf_swizzled, void* sf_linear, int batch, int rows, int cols, void* stream) {
+  if (!sf_linear || !sf_swizzled || batch < 0 || rows < 0 || cols < 0) return B200MOE_ERR_ARG;
+  if (batch == 0 || rows == 0 || cols == 0) return B200MOE_OK;
+  const int prow = (rows + 127) / 128 * 128, nkt = (cols + 3) / 4;
+  k_from_128x4<<<grid_for((long long)batch * rows * cols, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)sf_swizzled, (uint8_t*)sf_linear, batch, rows, cols, prow, nkt);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_global_scale(const void* x, int dtype, long long n, void* amax_scratch_u32, float* gs_out, void* stream) {
+  if (!x || !amax_scratch_u32 || !gs_out || n < 0) return B200MOE_ERR_ARG;
+  if (dtype != 0 && dtype != 1) return B200MOE_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200_CUDA_TRY(cudaMemsetAsync(amax_scratch_u32, 0, sizeof(unsigned), st));
+  if (n > 0) {
+    if (dtype == 0) k_amax<<<grid_for(n, 256 * 8), 256, 0, st>>>((const __nv_bfloat16*)x, n, (unsigned*)amax_scratch_u32);
+    else k_amax<<<grid_for(n, 256 * 8), 256, 0, st>>>((const float*)x, n, (unsigned*)amax_scratch_u32);
+    B200_LAUNCH_CHECK();
+  }
+  k_global_scale<<<1, 1, 0, st>>>((const unsigned*)amax_scratch_u32, gs_out);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_row, int rows, int K, const float* global_scale,
+                                      void* packed, void* sf, int sf_layout, void* stream) {
+  if (!x || !global_scale || !packed || !sf || rows < 0) return B200MOE_ERR_ARG;
+  if (K <= 0 || K % 16) return B200MOE_ERR_SHAPE;
+  if ((dtype != 0 && dtype != 1) || (sf_layout != 0 && sf_layout != 1)) return B200MOE_ERR_ARG;
+  if (((uintptr_t)x & 15) || ((uintptr_t)packed & 7)) return B200MOE_ERR_ARG;
+  if (rows == 0) return B200MOE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int g = grid_for((long long)rows * (K / 16), 256);
+  if (dtype == 0)
+    k_quantize_nvfp4<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, src_row, rows, K, global_scale, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
+  else
+    k_quantize_nvfp4<<<g, 256, 0, st>>>((const float*)x, src_row, rows, K, global_scale, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}

@@ -1,0 +1,137 @@
+// Token-to-expert routing: counts, exclusive scan, stable permutation. Bit-exact with the torch router of
+// sm120fp4/kernels/fc1_w4a16.py:272-279 (stable argsort of the flattened ids) and with the fixed-size padded form the
+// reference's GPU router writes (sm120fp4/kernels/moe_w4a16.py:48-83: unused expert slots -1, unused offsets P).
+// The reference ranks each pair with an O(P^2) loop in one block; here a stable counting sort over chunks of pairs
+// scales to prefill sizes (P = 65,536 and beyond): no atomic decides any position.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int ROUTE_MAXE = 1024;   // experts per layer the router takes
+constexpr int ROUTE_CHUNK = 512;   // pairs per chunk (one warp walks a chunk in order)
+
+// Pass 1: per-chunk histogram. One block of 128 threads per chunk; counts are order-independent.
+__global__ void __launch_bounds__(128) k_route_hist(const int* __restrict__ ids, int P, int E, int* __restrict__ hist,
+                                                    int* __restrict__ bad) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  const int p0 = blockIdx.x * ROUTE_CHUNK, p1 = min(P, p0 + ROUTE_CHUNK);
+  for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) {
+    const int e = ids[p];
+    if (e < 0 || e >= E) { *bad = 1; continue; }
+    atomicAdd(&sh[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[(long long)blockIdx.x * E + e] = sh[e];
+}
+
+// Pass 2 (one block of 1024 threads): per expert, exclusive scan of the chunk counts in place (chunk-local base of
+// that expert); then scan over experts for the expert bases and the touched-expert index; write the tables.
+__global__ void __launch_bounds__(1024) k_route_scan(int* __restrict__ hist, int nchunks, int P, int E, int Umax,
+                                                     int* __restrict__ experts, int* __restrict__ offsets,
+                                                     int* __restrict__ expert_base /* [E], start of expert e in pairs */,
+                                                     int* __restrict__ num_touched) {
+  __shared__ int cnt[ROUTE_MAXE], base[ROUTE_MAXE], uidx[ROUTE_MAXE];
+  const int t = threadIdx.x;
+  int c = 0;
+  if (t < E) {
+    for (int b = 0; b < nchunks; ++b) {
+      const int v = hist[(long long)b * E + t];
+      hist[(long long)b * E + t] = c;
+      c += v;
+    }
+  }
+  cnt[t] = c;
+  base[t] = c;
+  uidx[t] = c > 0 ? 1 : 0;
+  __syncthreads();
+  for (int o = 1; o < ROUTE_MAXE; o <<= 1) {   // inclusive Hillis-Steele scans of counts and touched flags
+    const int b = t >= o ? base[t - o] : 0, u = t >= o ? uidx[t - o] : 0;
+    __syncthreads();
+    base[t] += b;
+    uidx[t] += u;
+    __syncthreads();
+  }
+  const int U = uidx[ROUTE_MAXE - 1];
+  if (t < E) {
+    expert_base[t] = base[t] - c;
+    if (c > 0 && uidx[t] - 1 < Umax) {
+      experts[uidx[t] - 1] = t;
+      offsets[uidx[t] - 1] = base[t] - c;
+    }
+  }
+  for (int u = U + t; u < Umax; u += blockDim.x) {
+    experts[u] = -1;
+    offsets[u + 1] = P;
+  }
+  if (t == 0) {
+    if (U <= Umax) offsets[U] = P;
+    if (num_touched) *num_touched = U;
+  }
+}
+
+// Pass 3: one warp per chunk walks its pairs in index order, 32 at a time. Within a step, pairs of the same expert are
+// ranked by lane; across steps a per-expert running count in shared memory carries the order. Position of pair p =
+// expert_base[e] + (pairs of e in earlier chunks) + (pairs of e earlier in this chunk).
+__global__ void __launch_bounds__(32) k_route_place(const int* __restrict__ ids, int P, int E, const int* __restrict__ hist,
+                                                    const int* __restrict__ expert_base, int* __restrict__ pairs) {
+  extern __shared__ int run[];
+  const int lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) run[e] = expert_base[e] + hist[(long long)blockIdx.x * E + e];
+  __syncwarp();
+  const int p0 = blockIdx.x * ROUTE_CHUNK, p1 = min(P, p0 + ROUTE_CHUNK);
+  for (int s = p0; s < p1; s += 32) {
+    const int p = s + lane;
+    const bool live = p < p1;
+    int e = live ? ids[p] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned active = __ballot_sync(0xffffffffu, e >= 0);
+    if (e >= 0) {
+      const unsigned peers = __match_any_sync(active, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int pos = run[e] + rank;
+      pairs[pos] = p;
+      __syncwarp(active);
+      if (rank == __popc(peers) - 1) run[e] += __popc(peers);   // the last peer advances the running count
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" long long b200moe_route_workspace_bytes(int P, int E) {
+  if (P < 0 || E <= 0) return B200MOE_ERR_ARG;
+  const long long nchunks = (P + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  return (nchunks * E + E + 2) * (long long)sizeof(int);
+}
+
+// ids int32 [P] -> experts int32 [Umax], offsets int32 [Umax+1], pairs int32 [P]; Umax slots as the caller sized them
+// (the reference uses min(E, P)). workspace: b200moe_route_workspace_bytes(P, E) bytes of device memory.
+extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* workspace,
+                             long long workspace_bytes, void* stream) {
+  if (!ids || !experts || !offsets || !pairs || !workspace || P < 0 || Umax < 0) return B200MOE_ERR_ARG;
+  if (E <= 0 || E > ROUTE_MAXE) return B200MOE_ERR_SHAPE;
+  if (workspace_bytes < b200moe_route_workspace_bytes(P, E)) return B200MOE_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nchunks = (P + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  int* hist = (int*)workspace;
+  int* expert_base = hist + (long long)nchunks * E;
+  int* bad = expert_base + E;
+  int* num_touched = bad + 1;
+  B200_CUDA_TRY(cudaMemsetAsync(bad, 0, 2 * sizeof(int), st));
+  if (nchunks > 0) {
+    k_route_hist<<<nchunks, 128, E * sizeof(int), st>>>(ids, P, E, hist, bad);
+    B200_LAUNCH_CHECK();
+  }
+  k_route_scan<<<1, 1024, 0, st>>>(hist, nchunks, P, E, Umax, experts, offsets, expert_base, num_touched);
+  B200_LAUNCH_CHECK();
+  if (nchunks > 0) {
+    k_route_place<<<nchunks, 32, E * sizeof(int), st>>>(ids, P, E, hist, expert_base, pairs);
+    B200_LAUNCH_CHECK();
+  }
+  return B200MOE_OK;
+}

@@ -1,0 +1,205 @@
+"""The engine-free operator: `Weights` and `Weights.forward`, with the constructor and call signature of
+sm120fp4/vllm_backend.py:95-172, on the B200 kernels of this package.
+
+Differences from the reference, all widening: any hidden size that is a multiple of 128 and intermediate size that is a
+multiple of 64 (the reference takes 2048 x {768, 1024} only, vllm_backend.py:44-45,102-103); block scales may be handed
+over already in the 128x4 swizzle (`scale_layout="128x4"`) or row-major as the checkpoint stores them (converted once on
+the device); a decode batch (up to 16 tokens) is ONE kernel launch instead of router + FC1 + FC2.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import sys
+from types import SimpleNamespace
+
+import torch
+
+from . import _lib
+from .layouts import padded_sf_shape, to_128x4
+
+ENV = "SM120FP4_MOE"
+PREFILL_ENV = "SM120FP4_PREFILL"
+METHOD_NAME = "modelopt_fp4"
+MAXM = 16  # tokens per decode launch
+
+
+def enabled() -> bool:
+    return os.environ.get(ENV, "") == "1"
+
+
+def prefill_mode() -> str:
+    """"w4a4" (default: batches above MAXM tokens run the W4A4 tensor-core path when activation scales were given) or
+    "slices" (SM120FP4_PREFILL=slices: slices of MAXM tokens through the decode kernel). The reference's value "cutlass"
+    (sm120fp4/vllm_backend.py:55-61) is accepted as a synonym of the default."""
+    return "slices" if os.environ.get(PREFILL_ENV, "") == "slices" else "w4a4"
+
+
+def prefill_explicit() -> bool:
+    return os.environ.get(PREFILL_ENV, "") in ("cutlass", "w4a4")
+
+
+def rotate_halves(t: torch.Tensor, inter: int) -> torch.Tensor:
+    """[gate; up] -> [up; gate] along dim 1 (sm120fp4/vllm_backend.py:90-92)."""
+    return torch.cat([t[:, inter:], t[:, :inter]], dim=1).contiguous()
+
+
+class Weights:
+    """The layer's weights and work buffers as the kernels read them (sm120fp4/vllm_backend.py:95-121)."""
+
+    def __init__(self, q1: torch.Tensor, s1: torch.Tensor, alpha1: torch.Tensor, q2: torch.Tensor, s2: torch.Tensor,
+                 alpha2: torch.Tensor, top_k: int, scale_layout: str = "linear"):
+        if q1.dim() != 3:
+            raise ValueError("checkpoint layout expected: q1 [E,2I,H/2] s1 [E,2I,H/16] q2 [E,H,I/2] s2 [E,H,I/16]")
+        e_n, two_i, h2 = q1.shape
+        self.E, self.I, self.H, self.k = e_n, two_i // 2, h2 * 2, top_k
+        if self.H % 128 or self.I % 64 or two_i % 2:
+            raise ValueError(f"the kernels take a hidden size that is a multiple of 128 and an intermediate size that is a multiple of 64, not {self.H}/{self.I}")
+        if e_n > 256 or not 1 <= top_k <= 16:
+            raise ValueError(f"the kernels take at most 256 experts and top_k in 1..16, not {e_n}/{top_k}")
+        if q1.dtype != torch.uint8 or q2.dtype != torch.uint8 or s1.dtype != torch.uint8 or s2.dtype != torch.uint8:
+            raise TypeError("codes and block scales must be uint8 views")
+        if scale_layout not in ("linear", "128x4"):
+            raise ValueError("scale_layout is 'linear' (checkpoint order) or '128x4' (swizzled per expert)")
+        p1, p2 = padded_sf_shape(two_i, self.H // 16), padded_sf_shape(self.H, self.I // 16)
+        want1 = (e_n, two_i, self.H // 16) if scale_layout == "linear" else (e_n, *p1)
+        want2 = (e_n, self.H, self.I // 16) if scale_layout == "linear" else (e_n, *p2)
+        if tuple(q2.shape) != (e_n, self.H, self.I // 2) or s1.numel() != want1[0] * want1[1] * want1[2] \
+                or s2.numel() != want2[0] * want2[1] * want2[2]:
+            raise ValueError("checkpoint layout expected: q1 [E,2I,H/2] s1 [E,2I,H/16] q2 [E,H,I/2] s2 [E,H,I/16]")
+        if alpha1.dtype != torch.float32 or alpha2.dtype != torch.float32 or alpha1.numel() != e_n or alpha2.numel() != e_n:
+            raise TypeError("one float32 global scale per expert and projection")
+        if not q1.is_cuda:
+            raise RuntimeError("Weights lives on a CUDA device; there is no CPU path in this package")
+        self.q1, self.alpha1 = q1.contiguous(), alpha1.contiguous()
+        self.q2, self.alpha2 = q2.contiguous(), alpha2.contiguous()
+        if scale_layout == "linear":
+            self.s1_linear, self.s2_linear = s1.contiguous().view(want1), s2.contiguous().view(want2)
+            self.s1 = to_128x4(self.s1_linear)          # [E, pad128(2I), pad4(H/16)]
+            self.s2 = to_128x4(self.s2_linear)
+        else:
+            self.s1_linear = self.s2_linear = None
+            self.s1, self.s2 = s1.contiguous().view(want1), s2.contiguous().view(want2)
+        h = _lib.lib()
+        handle = C.c_void_p()
+        _lib.check(h.b200moe_layer_create(C.byref(handle), self.E, self.H, self.I, self.k, _lib.ptr(self.q1), _lib.ptr(self.s1),
+                                          _lib.ptr(self.alpha1), _lib.ptr(self.q2), _lib.ptr(self.s2), _lib.ptr(self.alpha2)),
+                   "Weights")
+        self._h = handle
+        dev = q1.device
+        self.ws_bytes = int(h.b200moe_layer_workspace_bytes(self._h))
+        self.workspace = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=dev)
+        umax, pmax = min(e_n, MAXM * top_k), MAXM * top_k
+        self.experts = torch.empty(umax, dtype=torch.int32, device=dev)
+        self.offsets = torch.empty(umax + 1, dtype=torch.int32, device=dev)
+        self.pairs = torch.empty(pmax, dtype=torch.int32, device=dev)
+        self.act = torch.empty(pmax, self.I, dtype=torch.bfloat16, device=dev)
+        self.prefill = None   # set by enable_prefill: the W4A4 path above MAXM tokens
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                _lib.lib().b200moe_layer_destroy(self._h)
+                self._h = None
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+    # ------------------------------------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
+                pdl: bool | None = None) -> torch.Tensor:
+        """The MoE forward for a batch of any size (sm120fp4/vllm_backend.py:147-172). `pdl` is accepted for signature
+        compatibility; the decode layer is a single launch, so there is no dependent launch to toggle."""
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.H:
+            raise TypeError(f"x must be bf16 [tokens, {self.H}]")
+        m = x.shape[0]
+        if tuple(topk_ids.shape) != (m, self.k) or tuple(topk_weights.shape) != (m, self.k):
+            raise ValueError("topk_ids and topk_weights must be [tokens, top_k]")
+        x = x.contiguous()
+        ids = topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights.to(torch.float32).contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        if m > MAXM and self.prefill is not None and prefill_mode() != "slices":
+            return self.prefill.forward(x, ids, wts, out)
+        for s in range(0, m, MAXM):
+            e = min(m, s + MAXM)
+            self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e])
+        return out
+
+    def _slice(self, x, ids, wts, out) -> None:
+        _lib.check(_lib.lib().b200moe_decode_forward(self._h, _lib.ptr(x), _lib.ptr(ids), _lib.ptr(wts), x.shape[0], _lib.ptr(out),
+                                                     _lib.ptr(self.workspace), self.ws_bytes, _lib.stream_ptr()), "forward")
+
+    def fc1(self, x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, act: torch.Tensor) -> None:
+        """FC1 + SiLU*mul alone: act bf16 [tokens*top_k, I], row = pair index."""
+        _lib.check(_lib.lib().b200moe_decode_fc1(self._h, _lib.ptr(x), _lib.ptr(ids), _lib.ptr(wts), x.shape[0], _lib.ptr(act),
+                                                 _lib.ptr(self.workspace), self.ws_bytes, _lib.stream_ptr()), "fc1")
+
+    def fc2(self, act: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor) -> None:
+        """FC2 + weighted combine alone, from act bf16 [tokens*top_k, I]."""
+        _lib.check(_lib.lib().b200moe_decode_fc2(self._h, _lib.ptr(act), _lib.ptr(ids), _lib.ptr(wts), ids.shape[0], _lib.ptr(out),
+                                                 _lib.ptr(self.workspace), self.ws_bytes, _lib.stream_ptr()), "fc2")
+
+    def route_tables(self, m: int):
+        """The routing tables the last decode launch of `m` tokens wrote, in the router's padded form."""
+        umax, p = min(self.E, m * self.k), m * self.k
+        ex, off, pairs = self.experts[:umax], self.offsets[:umax + 1], self.pairs[:p]
+        _lib.check(_lib.lib().b200moe_layer_route_tables(self._h, _lib.ptr(self.workspace), m, _lib.ptr(ex), _lib.ptr(off), _lib.ptr(pairs),
+                                                         _lib.stream_ptr()), "route_tables")
+        return ex, off, pairs
+
+    def status(self) -> None:
+        """Synchronise and raise if a bounded device-side wait ran out or an expert id was out of range."""
+        _lib.check(_lib.lib().b200moe_layer_status(self._h, _lib.ptr(self.workspace), _lib.stream_ptr()), "status")
+
+    def reset_workspace(self) -> None:
+        _lib.check(_lib.lib().b200moe_layer_workspace_init(self._h, _lib.ptr(self.workspace), self.ws_bytes, _lib.stream_ptr()), "reset")
+
+    def expert_bytes(self) -> int:
+        """Packed FP4 + scale bytes of one expert (sm120fp4/kernels/bench_moe_baseline.py:190-191)."""
+        return 3 * self.I * self.H // 2 + 3 * self.I * self.H // 16
+
+
+def weights_from_vllm_layout(w13: torch.Tensor, w13_scale: torch.Tensor, w13_scale_2: torch.Tensor, w2: torch.Tensor,
+                             w2_scale: torch.Tensor, w2_scale_2: torch.Tensor, top_k: int) -> Weights:
+    """Build Weights from the tensors vLLM's loader fills: w13 [E, 2I, H/2] as [gate; up], e4m3 block scales [E, 2I, H/16],
+    w13_scale_2 [E, 2] (gate, up), w2 [E, H, I/2], w2 scales [E, H, I/16], w2_scale_2 [E] (sm120fp4/vllm_backend.py:193-206)."""
+    e_n, two_i = w13.shape[0], w13.shape[1]
+    inter = two_i // 2
+    g = w13_scale_2.reshape(e_n, -1).to(torch.float32)
+    if g.shape[1] == 2 and not torch.equal(g[:, 0], g[:, 1]):
+        n = int((g[:, 0] != g[:, 1]).sum())
+        raise ValueError(f"gate and up global scales differ on {n} of {e_n} experts; FC1 applies one alpha per expert")
+    alpha1 = g[:, 0].contiguous()
+    return Weights(rotate_halves(w13, inter).view(torch.uint8), rotate_halves(w13_scale, inter).view(torch.uint8), alpha1,
+                   w2.view(torch.uint8), w2_scale.view(torch.uint8), w2_scale_2.to(torch.float32).reshape(-1), top_k)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+def _vllm():
+    from vllm.model_executor.layers.quantization import register_quantization_config
+    return SimpleNamespace(register=register_quantization_config)
+
+
+def classes() -> SimpleNamespace:
+    from . import vllm_classes as vc
+    return SimpleNamespace(Config=vc.SM120Fp4Config, Method=vc.SM120Fp4MoEMethod)
+
+
+def _log(msg: str) -> None:
+    try:
+        from vllm.logger import init_logger
+        init_logger("vllm.sm120fp4").info("sm120fp4_b200: %s", msg)
+    except Exception:  # noqa: BLE001 - logging must never fail the engine
+        print("sm120fp4_b200:", msg, file=sys.stderr)
+
+
+def register() -> bool:
+    """The `vllm.general_plugins` entry point (sm120fp4/vllm_backend.py:232-245): re-registers `modelopt_fp4` with
+    SM120Fp4Config when SM120FP4_MOE=1; a no-op otherwise."""
+    if not enabled():
+        return False
+    v = _vllm()
+    v.register(METHOD_NAME)(classes().Config)
+    _log(f"{METHOD_NAME} now resolves to SM120Fp4Config ({ENV}=1); routed-experts layers the kernels fit run on them")
+    return True

@@ -1,0 +1,43 @@
+"""Test helpers: build one synthetic layer both as the GPU operator and as the CPU oracle's weights."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import nvfp4_oracle as O
+
+
+def make_layer(experts, hidden, inter, top_k, seed=0, std=0.02, device="cuda", scale_layout="linear"):
+    """(Weights on the GPU, ExpertWeights for the oracle). Weights are drawn on the CPU (seeded), quantised on the GPU by
+    the library's quantizer (bit-exact with the reference, tested separately) and copied back for the oracle."""
+    import sm120fp4_b200 as pkg
+    from sm120fp4_b200 import synth
+    from sm120fp4_b200.vllm_backend import Weights
+
+    w13, w2 = synth.layer_weights_bf16(experts, hidden, inter, seed=seed, std=std)
+    q1, s1, a1, q2, s2, a2 = [], [], [], [], [], []
+    for e in range(experts):
+        q, s, gs = pkg.quantize_nvfp4(w13[e].to(device))
+        q1.append(q), s1.append(s), a1.append(1.0 / gs)
+        q, s, gs = pkg.quantize_nvfp4(w2[e].to(device))
+        q2.append(q), s2.append(s), a2.append(1.0 / gs)
+    q1, s1, a1 = torch.stack(q1), torch.stack(s1), torch.cat(a1)
+    q2, s2, a2 = torch.stack(q2), torch.stack(s2), torch.cat(a2)
+    if scale_layout == "128x4":
+        w = Weights(q1, pkg.to_128x4(s1), a1, q2, pkg.to_128x4(s2), a2, top_k, scale_layout="128x4")
+    else:
+        w = Weights(q1, s1, a1, q2, s2, a2, top_k)
+    ow = O.ExpertWeights(q1.cpu().numpy(), s1.cpu().numpy(), a1.cpu().numpy(), q2.cpu().numpy(), s2.cpu().numpy(), a2.cpu().numpy())
+    return w, ow
+
+
+def check_layer_output(got: torch.Tensor, want: np.ndarray, what=""):
+    """The parity bar of the layer: bf16 max-abs error <= 2e-2 x output RMS; also reports the normwise error."""
+    g = got.float().cpu().numpy()
+    assert np.isfinite(g).all(), f"{what}: non-finite output"
+    rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
+    err = float(np.abs(g - want).max())
+    rel = float(np.linalg.norm(g - want) / max(np.linalg.norm(want), 1e-30))
+    assert err <= 2e-2 * rms, f"{what}: max-abs error {err:.3e} > 2e-2 * rms ({rms:.3e}); normwise {rel:.3e}"
+    assert rel < 1e-2, f"{what}: normwise error {rel:.3e}"
+    return err / rms, rel

@@ -1,0 +1,54 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/b200moe.h declares (no compute calls here)."""
+import re
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "b200moe.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    import sm120fp4_b200._lib as L
+    h = L.lib()
+    names = declared_symbols()
+    assert len(names) >= 19
+    for n in names:
+        assert hasattr(h, n), f"{n} declared in include/b200moe.h but not exported"
+        assert n in L.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(L.SIGNATURES) == names
+    assert h.b200moe_version() >= 100
+    assert b"workspace" in h.b200moe_error_string(L.ERR_WORKSPACE)
+
+
+def test_argument_errors_need_no_gpu():
+    import sm120fp4_b200._lib as L
+    h = L.lib()
+    assert h.b200moe_to_128x4(None, None, 1, 1, 1, None) == L.ERR_ARG
+    assert h.b200moe_quantize_nvfp4(None, 0, None, 1, 16, None, None, None, 0, None) == L.ERR_ARG
+    assert h.b200moe_route(None, 0, 8, 0, None, None, None, None, 0, None) == L.ERR_ARG
+    assert h.b200moe_route_workspace_bytes(100, 8) > 0
+    assert h.b200moe_layer_workspace_bytes(None) == L.ERR_ARG
+
+
+def test_host_side_mirrors():
+    import pytest
+    import torch
+    from sm120fp4_b200 import moe_layer, padded_sf_shape, vllm_backend as vb
+    assert padded_sf_shape(100, 5) == (128, 8) and padded_sf_shape(1536, 128) == (1536, 128)
+    assert moe_layer.choice(1) == moe_layer.choice(16) and moe_layer.use_pdl(1) is False
+    assert moe_layer.regime(16) == "decode_w4a16" and moe_layer.regime(17) == "prefill_w4a4"
+    with pytest.raises(ValueError):
+        moe_layer.choice(17)
+    t = torch.arange(24).reshape(2, 4, 3)
+    assert torch.equal(vb.rotate_halves(vb.rotate_halves(t, 2), 2), t)
+    assert torch.equal(vb.rotate_halves(t, 2)[:, :2], t[:, 2:])
+    with pytest.raises(ValueError):   # unequal gate/up global scales (sm120fp4/vllm_backend.py:199-202)
+        vb.weights_from_vllm_layout(torch.zeros(2, 128, 64, dtype=torch.uint8), torch.zeros(2, 128, 8, dtype=torch.uint8),
+                                    torch.tensor([[1.0, 2.0], [1.0, 1.0]]), torch.zeros(2, 128, 32, dtype=torch.uint8),
+                                    torch.zeros(2, 128, 4, dtype=torch.uint8), torch.ones(2), 2)
+    with pytest.raises(TypeError):    # codes must be uint8 views
+        vb.Weights(torch.zeros(2, 128, 64), torch.zeros(2, 128, 8, dtype=torch.uint8), torch.ones(2),
+                   torch.zeros(2, 128, 32, dtype=torch.uint8), torch.zeros(2, 128, 4, dtype=torch.uint8), torch.ones(2), 2)
