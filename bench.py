@@ -36,11 +36,13 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def cases(cfg):
+def cases(cfg, only=None):
     from sm120fp4_b200 import synth
     out = []
     for routing in ROUTINGS:
         for m in MS:
+            if only and f"{m}:{routing}" not in only:
+                continue
             x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 1000 + m if routing == "random" else 7, routing)
             out.append(dict(m=m, routing=routing, x=x, ids=ids, wts=wts, touched=int(torch.unique(ids).numel())))
     return out
@@ -126,7 +128,7 @@ def run_ours(a):
     from sm120fp4_b200 import synth
     cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
     layers = build_layers(cfg, a.layers, dev)
-    cs = cases(cfg)
+    cs = cases(cfg, set(a.cases.split(",")) if a.cases else None)
     for c in cs:
         c["xd"], c["idd"], c["wd"] = c["x"].to(dev), c["ids"].to(dev), c["wts"].to(dev)
         c["out"] = torch.empty_like(c["xd"])
@@ -344,6 +346,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16, help="distinct weight sets in the chain (16 x 340 MB = 5.4 GB)")
     ap.add_argument("--shape", default="qwen", choices=("qwen", "gemma"))
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--cases", default="", help="subset of the sweep for profiling, e.g. 16:random,1:fixed8 (default: all ten)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     a = ap.parse_args()
     if a.impl == "reference":

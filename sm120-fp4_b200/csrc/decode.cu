@@ -39,6 +39,7 @@ struct Tables {
   int uidx[kMaxE];     // inclusive scan of touched flags
   int experts[kMaxE];  // touched experts ascending
   int U;
+  unsigned gen0;     // grid-barrier generation at kernel start
   volatile int abort_flag;
   int last_flag[2];
   uint64_t full[8];
@@ -138,6 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
     }
     T.abort_flag = 0;
     T.last_flag[0] = T.last_flag[1] = 0;
+    // read before any group of this CTA can arrive, so the generation cannot have advanced yet
+    T.gen0 = ld_acquire_gpu(P.gridbar + 1);
     fence_mbar_init();
   }
   if (tid < kMaxE) T.cnt[tid] = 0;
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
       prefetch_tensormap(&P.tm1);
       prefetch_tensormap(&P.tm2);
       const uint64_t pol = policy_evict_first();
-      const unsigned gen0 = P.gridbar ? ld_acquire_gpu(P.gridbar + 1) : 0u;
+      const unsigned gen0 = T.gen0;
       bool passed = !do1;            // without an FC1 phase the activations are already in place
       int s1[2], n1[2], s2[2], n2[2];
       for (int g = 0; g < 2; ++g) {

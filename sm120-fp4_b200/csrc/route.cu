@@ -113,7 +113,8 @@ extern "C" long long b200moe_route_workspace_bytes(int P, int E) {
 // (the reference uses min(E, P)). workspace: b200moe_route_workspace_bytes(P, E) bytes of device memory.
 extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* workspace,
                              long long workspace_bytes, void* stream) {
-  if (!ids || !experts || !offsets || !pairs || !workspace || P < 0 || Umax < 0) return B200MOE_ERR_ARG;
+  if (!offsets || !workspace || P < 0 || Umax < 0) return B200MOE_ERR_ARG;
+  if ((P > 0 && (!ids || !pairs)) || (Umax > 0 && !experts)) return B200MOE_ERR_ARG;
   if (E <= 0 || E > ROUTE_MAXE) return B200MOE_ERR_SHAPE;
   if (workspace_bytes < b200moe_route_workspace_bytes(P, E)) return B200MOE_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;

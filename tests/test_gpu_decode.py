@@ -100,7 +100,8 @@ def test_fc1_and_fc2_entry_points():
             want[t * cfg["top_k"] + j] = O.silu(hmid[cfg["inter"]:]) * hmid[:cfg["inter"]]
     got = act.float().cpu().numpy()
     assert np.isfinite(got).all()
-    assert np.abs(got - want).max() <= 2e-2 * np.sqrt((want ** 2).mean()) + 1e-6
+    # act is stored in bf16: allow its rounding (2^-8 relative) on top of the layer's bar
+    assert (np.abs(got - want) <= 2e-2 * np.sqrt((want ** 2).mean()) * 0.25 + np.abs(want) * 2.0 ** -8 + 1e-6).all()
     out2 = torch.empty(m, cfg["hidden"], dtype=torch.bfloat16, device="cuda")
     w.fc2(act, idd, wd, out2)
     w.status()
