@@ -76,6 +76,11 @@ int b200moe_layer_route_tables(const b200moe_layer* layer, const void* workspace
 /* status word of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT or B200MOE_ERR_ARG (bad expert id) */
 int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void* stream);
 
+/* per-worker cycle counters of the last decode launch (8 int64 per worker: consumer wait, math, fix-up, phase-1 end,
+ * producer wait, producer grid wait, producer end, consumer end). Filled only by a library built with -DB200_TIMERS (a
+ * diagnostic build; the reference has no counterpart); returns the number of workers copied. Synchronises the stream. */
+int b200moe_layer_debug_counters(const b200moe_layer* layer, const void* workspace, long long* out, int max_workers, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

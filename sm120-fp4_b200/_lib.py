@@ -32,6 +32,7 @@ SIGNATURES = {
     "b200moe_decode_fc2": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_layer_route_tables": (_I, [_P, _P, _I, _P, _P, _P, _P]),
     "b200moe_layer_status": (_I, [_P, _P, _P]),
+    "b200moe_layer_debug_counters": (_I, [_P, _P, _P, _I, _P]),
 }
 
 

@@ -20,6 +20,10 @@ FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-li
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 
+if os.environ.get("B200MOE_TIMERS") == "1":   # diagnostic build: per-worker cycle counters in the decode kernel
+    FLAGS.append("-DB200_TIMERS")
+
+
 def nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():

@@ -48,7 +48,7 @@ struct b200moe_layer {
   int KB1, KB2, CB1, NB2, KT1, KT2;
   long long s1_stride, s2_stride;
   // workspace layout (byte offsets)
-  long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, ws_bytes;
+  long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, off_debug, ws_bytes;
   int umax_cap;
 };
 
@@ -109,6 +109,7 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   L->off_actfrag = o, o = align_up(o + (long long)L->umax_cap * L->KB2 * 8192, 256);
   L->off_tables = o, o = align_up(o + (long long)(2 * L->umax_cap + 1 + 16 * top_k) * 4, 256);
   L->off_actbf16 = o, o = align_up(o + (long long)16 * top_k * I * 2, 256);
+  L->off_debug = o, o = align_up(o + (long long)V * 8 * 8, 256);
   L->ws_bytes = o;
   *out = L;
   return B200MOE_OK;
@@ -137,6 +138,7 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
   if (ws_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
   if (((uintptr_t)ws & 255) || ((uintptr_t)x & 15)) return B200MOE_ERR_ARG;
   if (M == 0) return B200MOE_OK;
+  if (2 * L->sms > 512) return B200MOE_ERR_DEVICE;   // share tables of the kernel hold 512 workers
   uint8_t* w = (uint8_t*)ws;
   DecodeParams p;
   memset(&p, 0, sizeof(p));
@@ -150,6 +152,7 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
   p.cnt1 = (unsigned*)(w + L->off_cnt1), p.cnt2 = (unsigned*)(w + L->off_cnt2);
   p.status = (int*)(w + L->off_status);
   p.gridbar = (unsigned*)(w + L->off_status + 64);
+  p.debug = (long long*)(w + L->off_debug);
   p.Umax = L->E < M * L->top_k ? L->E : M * L->top_k;
   if (write_tables) {
     p.experts_out = (int*)(w + L->off_tables);
@@ -228,6 +231,16 @@ extern "C" int b200moe_layer_status(const b200moe_layer* L, const void* workspac
   B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
   if (st == 0) return B200MOE_OK;
   return st == 4 ? B200MOE_ERR_ARG : B200MOE_ERR_TIMEOUT;
+}
+
+// Copy the per-worker cycle counters of the last launch to the host (8 int64 per worker, 2 x SM-count workers). Only a
+// library built with -DB200_TIMERS fills them; otherwise they read zero. Synchronises the stream.
+extern "C" int b200moe_layer_debug_counters(const b200moe_layer* L, const void* workspace, long long* out, int max_workers, void* stream) {
+  if (!L || !workspace || !out) return B200MOE_ERR_ARG;
+  const int n = 2 * L->sms < max_workers ? 2 * L->sms : max_workers;
+  B200_CUDA_TRY(cudaMemcpyAsync(out, (const uint8_t*)workspace + L->off_debug, (size_t)n * 64, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  return n;
 }
 
 extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }

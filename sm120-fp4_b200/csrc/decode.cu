@@ -4,7 +4,7 @@
 // (FP4 code x E4M3 block scale, fp32 accumulation, alpha applied in fp32, __expf SiLU, one rounding of the output).
 //
 // Structure (B200-first, memory-bound):
-//  * one CTA per SM; warp 8 is the TMA producer, warps 0-3 and 4-7 are two consumer groups ("workers").
+//  * one CTA per SM; warps 0-3 and 4-7 are two consumer groups ("workers"), warps 8 and 9 their TMA producers.
 //  * the work is a flat list of weight tiles: FC1 tile = 64 up rows + 64 gate rows x 256 K-codes (two 8 KB TMA boxes,
 //    128B swizzle) + their 128x4 scale runs; FC2 tile = 128 output rows x 256 K-codes + scale run + the activation slab
 //    of that expert / K-box. Every worker owns a contiguous, equal share of the flat list (stream-K), so any number of
@@ -24,10 +24,11 @@ namespace b200 {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kGroupThreads = 128;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;   // + one TMA producer warp per consumer group
 constexpr int kSlotBytes = 20480;      // 16 KB codes + 4 KB scales
 constexpr int kCodesBytes = 16384;
 constexpr int kMaxE = 256, kMaxP = 256;
+constexpr int kMaxWorkers = 512;       // 2 x SM count
 
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_GRID = 3, ST_BAD_ID = 4 };
 
@@ -38,8 +39,10 @@ struct Tables {
   int base[kMaxE];     // inclusive scan of cnt
   int uidx[kMaxE];     // inclusive scan of touched flags
   int experts[kMaxE];  // touched experts ascending
+  int sb1[kMaxWorkers + 1];   // first FC1 tile of every worker (stream-K shares); sb1[V] = T1
+  int sb2[kMaxWorkers + 1];   // same for FC2
   int U;
-  unsigned gen0;     // grid-barrier generation at kernel start
+  unsigned gen0;       // grid-barrier generation at kernel start
   volatile int abort_flag;
   int last_flag[2];
   uint64_t full[8];
@@ -48,20 +51,22 @@ struct Tables {
 
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
-// Worker v's share [s, e) of T tiles over V workers; worker_of(f) inverts it.
-__device__ __forceinline__ int share_begin(int v, int T, int V) { return (int)(((long long)v * T) / V); }
-__device__ __forceinline__ int worker_of(int f, int T, int V) { return (int)((((long long)f + 1) * V - 1) / T); }
-// Workers in [vlo, vhi] that own at least one tile (with fewer tiles than workers some shares are empty).
-__device__ __forceinline__ int live_workers(int vlo, int vhi, int T, int V) {
-  int n = 0;
-  for (int pv = vlo; pv <= vhi; ++pv) n += share_begin(pv + 1, T, V) > share_begin(pv, T, V);
-  return n;
-}
+// Owner of flat tile f when worker v owns [v*T/V, (v+1)*T/V): ceil((f+1)*V/T) - 1. Products stay below 2^31 (host check).
+__device__ __forceinline__ int worker_of(int f, int T, int V) { return (int)(((unsigned)(f + 1) * (unsigned)V - 1u) / (unsigned)T); }
+
+#ifdef B200_TIMERS
+#define TIMER_START(var) long long var = clock64()
+#define TIMER_ADD(acc, var) acc += clock64() - var
+#else
+#define TIMER_START(var)
+#define TIMER_ADD(acc, var)
+#endif
 
 // One weight tile through the tensor cores for one warp: two 16-row blocks (rb) x 256 K-codes, NB8 token octets.
+// acc[parity][rb][n][4]: even and odd MMAs of a K run use separate accumulators to halve the dependent chain.
 template <int NB8>
 __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uint32_t sc0, int rt0, uint32_t sc1, int rt1,
-                                         bool kt_valid, uint32_t bfrag, int lane, float (&acc)[2][NB8][4]) {
+                                         bool kt_valid, uint32_t bfrag, int lane, float (&acc)[2][2][NB8][4]) {
   const int g = lane >> 2, t = lane & 3;
   uint32_t sfw[2][2];
   {
@@ -71,7 +76,7 @@ __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uin
     sfw[1][0] = kt_valid ? lds32(sc1 + t * 512 + (r10 & 31) * 16 + (r10 >> 5) * 4) : 0u;
     sfw[1][1] = kt_valid ? lds32(sc1 + t * 512 + (r11 & 31) * 16 + (r11 >> 5) * 4) : 0u;
   }
-#pragma unroll
+#pragma unroll 1
   for (int h = 0; h < 2; ++h) {
     uint4 bq[4][NB8];
 #pragma unroll
@@ -102,8 +107,8 @@ __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uin
         }
 #pragma unroll
         for (int n = 0; n < NB8; ++n) {
-          mma_f16_16816(acc[rb][n], da[0], db[0], da[1], db[1], bq[wd][n].x, bq[wd][n].y);
-          mma_f16_16816(acc[rb][n], da[2], db[2], da[3], db[3], bq[wd][n].z, bq[wd][n].w);
+          mma_f16_16816(acc[0][rb][n], da[0], db[0], da[1], db[1], bq[wd][n].x, bq[wd][n].y);
+          mma_f16_16816(acc[1][rb][n], da[2], db[2], da[3], db[3], bq[wd][n].z, bq[wd][n].w);
         }
       }
     }
@@ -116,6 +121,37 @@ __device__ __forceinline__ int frag_index(int k, int tok) {
   const int kb = k >> 8, tq = (k & 255) >> 6, h = (k & 63) >> 5, jj = (k & 31) >> 3;
   const int lane = ((tok & 7) << 2) | tq;
   return kb * (NB8 * 2048) + ((((h * 4 + jj) * NB8 + (tok >> 3)) * 32 + lane) << 3) + (k & 7);
+}
+
+// Sum the partial results of the workers [vlo, vhi] that own a piece of the unit starting at flat tile `first`, in worker
+// order (fixed summation order), four pieces' loads in flight at a time. v[] has 8*NB8 floats per thread.
+template <int NB8>
+__device__ __forceinline__ void reduce_pieces(const float* __restrict__ scratch, const int* sb, int first, int vlo, int vhi,
+                                              int gtid, float (&v)[8 * NB8]) {
+#pragma unroll
+  for (int i = 0; i < 8 * NB8; ++i) v[i] = 0.f;
+  for (int p0 = vlo; p0 <= vhi; p0 += 4) {
+    float4 tmp[4][2 * NB8];
+    bool live[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int pv = p0 + b;
+      live[b] = pv <= vhi && sb[pv + 1] > sb[pv];
+      const int pslot = (live[b] && sb[pv] < first) ? 1 : 0;   // a piece that starts its worker's share sits in slot 0
+      const float* src = scratch + ((long long)((live[b] ? pv : vlo) * 2 + pslot) * kGroupThreads + gtid) * 16;
+#pragma unroll
+      for (int i = 0; i < 2 * NB8; ++i)
+        tmp[b][i] = live[b] ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (live[b]) {
+#pragma unroll
+        for (int i = 0; i < 2 * NB8; ++i) {
+          v[4 * i] += tmp[b][i].x, v[4 * i + 1] += tmp[b][i].y, v[4 * i + 2] += tmp[b][i].z, v[4 * i + 3] += tmp[b][i].w;
+        }
+      }
+  }
 }
 
 template <int NB8>
@@ -179,9 +215,17 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
     if (lane == 31) T.U = iff;
   }
   __syncthreads();
-  if (tid < kMaxE && T.cnt[tid] > 0) T.experts[T.uidx[tid] - 1] = tid;
-  __syncthreads();
   const int U = T.U;
+  const bool do1 = (P.phases & 1) != 0, do2 = (P.phases & 2) != 0;
+  const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
+  const int T1 = do1 ? U * CB1 * KB1 : 0;
+  const int T2 = do2 ? NB2 * U * KB2 : 0;
+  if (tid < kMaxE && T.cnt[tid] > 0) T.experts[T.uidx[tid] - 1] = tid;
+  for (int v = tid; v <= V; v += kThreads) {   // stream-K shares: worker v owns tiles [sb[v], sb[v+1])
+    T.sb1[v] = (int)(((unsigned)v * (unsigned)T1) / (unsigned)V);
+    T.sb2[v] = (int)(((unsigned)v * (unsigned)T2) / (unsigned)V);
+  }
+  __syncthreads();
 
   if (blockIdx.x == 0 && P.experts_out) {   // the routing tables in the reference's padded form
     const int Umax = P.Umax;
@@ -203,39 +247,35 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
     }
   }
 
-  const bool do1 = (P.phases & 1) != 0, do2 = (P.phases & 2) != 0;
-  const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
-  const int T1 = do1 ? U * CB1 * KB1 : 0;
-  const int T2 = do2 ? NB2 * U * KB2 : 0;
   const int slab_bytes = NB8 * 4096;
+  const int per = NS / 2;
+#ifdef B200_TIMERS
+  long long tm_wait = 0, tm_mma = 0, tm_fix = 0, tm_pwait = 0, tm_pgrid = 0;
+  const long long tm_begin = clock64();
+#endif
 
-  if (warp == kConsumerWarps) {
-    // ============================================================== producer (one thread)
+  if (warp >= kConsumerWarps) {
+    // ============================================================== producers: warp 8 feeds group 0, warp 9 group 1
     if (lane == 0) {
+      const int grp = warp - kConsumerWarps;
+      const int v = 2 * blockIdx.x + grp;
       prefetch_tensormap(&P.tm1);
       prefetch_tensormap(&P.tm2);
       const uint64_t pol = policy_evict_first();
       const unsigned gen0 = T.gen0;
       bool passed = !do1;            // without an FC1 phase the activations are already in place
-      int s1[2], n1[2], s2[2], n2[2];
-      for (int g = 0; g < 2; ++g) {
-        const int v = 2 * blockIdx.x + g;
-        s1[g] = share_begin(v, T1, V);
-        n1[g] = share_begin(v + 1, T1, V) - s1[g];
-        s2[g] = share_begin(v, T2, V);
-        n2[g] = share_begin(v + 1, T2, V) - s2[g];
-      }
-      const int per = NS / 2;
-      int pend_slot[8];
-      const uint8_t* pend_src[8];
+      const int n1 = T.sb1[v + 1] - T.sb1[v], n2 = T.sb2[v + 1] - T.sb2[v];
+      int pend_slot[4];
+      const uint8_t* pend_src[4];
       int npend = 0;
       auto wait_grid = [&]() {
         if (passed) return;
+        TIMER_START(t0);
         bool ok = false;
         for (uint32_t it = 0; it < (1u << 24); ++it) {
           if (ld_acquire_gpu(P.gridbar + 1) != gen0) { ok = true; break; }
           if (T.abort_flag) break;
-          __nanosleep(128);
+          __nanosleep(64);
         }
         if (!ok) { T.abort_flag = 1; *P.status = ST_TIMEOUT_GRID; }
         fence_proxy_async();
@@ -243,47 +283,69 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
           bulk_load(region + pend_slot[i] * slab_bytes, pend_src[i], slab_bytes, &T.full[pend_slot[i]]);
         npend = 0;
         passed = true;
+        TIMER_ADD(tm_pgrid, t0);
       };
-      const int nmax = max(n1[0] + n2[0], n1[1] + n2[1]);
-      for (int j = 0; j < nmax; ++j) {
-        for (int g = 0; g < 2; ++g) {
-          if (j >= n1[g] + n2[g]) continue;
-          const int slot = 2 * (j % per) + g, use = j / per;
-          const bool is2 = j >= n1[g];
-          if (use >= 1) {
-            // the previous occupant of this slot was an FC2 tile still waiting for its activations: open the gate first
-            if (!passed && (j - per) >= n1[g]) wait_grid();
-            if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_EMPTY;
-          }
+      int si = 0;           // ring position of this group (0..per-1)
+      uint32_t ph = 0;      // parity of the current pass over the ring
+      int j = 0;            // tiles issued
+      auto claim_slot = [&](bool prev_was_fc2_pending) -> int {
+        const int slot = 2 * si + grp;
+        if (j >= per) {
+          if (prev_was_fc2_pending) wait_grid();   // the previous occupant still waits for its activations: open the gate first
+          TIMER_START(t0);
+          if (!mbar_wait(&T.empty[slot], ph ^ 1u, &T.abort_flag)) *P.status = ST_TIMEOUT_EMPTY;
+          TIMER_ADD(tm_pwait, t0);
+        }
+        return slot;
+      };
+      auto advance = [&]() {
+        ++j;
+        if (++si == per) { si = 0; ph ^= 1u; }
+      };
+      // ---- FC1 tiles of this worker, in flat order (expert slot u, column block cb, K box kb)
+      if (n1 > 0) {
+        const int f0 = T.sb1[v];
+        int kb = f0 % KB1, q = f0 / KB1, cb = q % CB1, u = q / CB1;
+        for (int i = 0; i < n1; ++i) {
+          const int slot = claim_slot(false);
           uint8_t* st = ring + slot * kSlotBytes;
-          if (!is2) {
-            const int f = s1[g] + j;
-            const int kb = f % KB1, q = f / KB1, cb = q % CB1, u = q / CB1;
-            const int e = T.experts[u];
-            const int nkt = min(4, P.KT1 - 4 * kb);
-            const int up_row = 64 * cb, gate_row = P.I + 64 * cb;
-            mbar_expect_tx(&T.full[slot], kCodesBytes + 2 * nkt * 512);
-            tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + up_row, &T.full[slot], pol);
-            tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + gate_row, &T.full[slot], pol);
-            const uint8_t* sbase = P.s1 + (long long)e * P.s1_expert_stride;
-            bulk_load_hint(st + kCodesBytes, sbase + ((long long)(up_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
-            bulk_load_hint(st + kCodesBytes + 2048, sbase + ((long long)(gate_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
-          } else {
-            const int f = s2[g] + (j - n1[g]);
-            const int kb = f % KB2, q = f / KB2, u = q % U, nb = q / U;
-            const int e = T.experts[u];
-            const int nkt = min(4, P.KT2 - 4 * kb);
-            mbar_expect_tx(&T.full[slot], kCodesBytes + nkt * 512 + slab_bytes);
-            tma_load_2d_hint(st, &P.tm2, 128 * kb, e * P.H + 128 * nb, &T.full[slot], pol);
-            bulk_load_hint(st + kCodesBytes, P.s2 + (long long)e * P.s2_expert_stride + ((long long)nb * P.KT2 + 4 * kb) * 512,
-                           nkt * 512, &T.full[slot], pol);
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(P.actfrag) + ((long long)u * KB2 + kb) * slab_bytes;
-            if (passed) bulk_load(region + slot * slab_bytes, src, slab_bytes, &T.full[slot]);
-            else { pend_slot[npend] = slot; pend_src[npend] = src; ++npend; }
-          }
+          const int e = T.experts[u];
+          const int nkt = min(4, P.KT1 - 4 * kb);
+          const int up_row = 64 * cb, gate_row = P.I + 64 * cb;
+          mbar_expect_tx(&T.full[slot], kCodesBytes + 2 * nkt * 512);
+          tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + up_row, &T.full[slot], pol);
+          tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + gate_row, &T.full[slot], pol);
+          const uint8_t* sbase = P.s1 + (long long)e * P.s1_expert_stride;
+          bulk_load_hint(st + kCodesBytes, sbase + ((long long)(up_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+          bulk_load_hint(st + kCodesBytes + 2048, sbase + ((long long)(gate_row >> 7) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+          advance();
+          if (++kb == KB1) { kb = 0; if (++cb == CB1) { cb = 0; ++u; } }
+        }
+      }
+      // ---- FC2 tiles, in flat order (output block nb, expert slot u, K box kb); weights run ahead of the grid barrier
+      if (n2 > 0) {
+        const int f0 = T.sb2[v];
+        int kb = f0 % KB2, q = f0 / KB2, u = q % U, nb = q / U;
+        for (int i = 0; i < n2; ++i) {
+          const int slot = claim_slot(!passed && (j - per) >= n1);
+          uint8_t* st = ring + slot * kSlotBytes;
+          const int e = T.experts[u];
+          const int nkt = min(4, P.KT2 - 4 * kb);
+          mbar_expect_tx(&T.full[slot], kCodesBytes + nkt * 512 + slab_bytes);
+          tma_load_2d_hint(st, &P.tm2, 128 * kb, e * P.H + 128 * nb, &T.full[slot], pol);
+          bulk_load_hint(st + kCodesBytes, P.s2 + (long long)e * P.s2_expert_stride + ((long long)nb * P.KT2 + 4 * kb) * 512,
+                         nkt * 512, &T.full[slot], pol);
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(P.actfrag) + ((long long)u * KB2 + kb) * slab_bytes;
+          if (passed) bulk_load(region + slot * slab_bytes, src, slab_bytes, &T.full[slot]);
+          else { pend_slot[npend] = slot; pend_src[npend] = src; ++npend; }
+          advance();
+          if (++kb == KB2) { kb = 0; if (++u == U) { u = 0; ++nb; } }
         }
       }
       if (npend > 0) wait_grid();
+#ifdef B200_TIMERS
+      if (P.debug) { P.debug[v * 8 + 4] = tm_pwait; P.debug[v * 8 + 5] = tm_pgrid; P.debug[v * 8 + 6] = clock64() - tm_begin; }
+#endif
     }
     __syncwarp();
   } else {
@@ -292,9 +354,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
     const int v = 2 * blockIdx.x + grp;
     const int gtid = tid & (kGroupThreads - 1);
     const int g = lane >> 2, t = lane & 3;
-    const int per = NS / 2;
     const uint32_t ring_a = smem_u32(ring), region_a = smem_u32(region);
-    int j = 0;   // this group's tile sequence number (ring position)
+    int si = 0;
+    uint32_t ph = 0;
 
     if (do1) {
       // ---- stage x as f16 in fragment order (all 256 consumer threads), zero beyond M tokens / H columns
@@ -319,46 +381,62 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
       named_bar_sync(3, kConsumerWarps * 32);
 
       // ---- FC1 pieces of this worker
-      const int fs = share_begin(v, T1, V), fe = share_begin(v + 1, T1, V);
+      const int fs = T.sb1[v], fe = T.sb1[v + 1];
       int f = fs;
       while (f < fe) {
         const int q = f / KB1, cb = q % CB1, u = q / CB1;
         const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
         const int e = T.experts[u];
-        float acc[2][NB8][4];
+        float acc[2][2][NB8][4];
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
+        for (int pa = 0; pa < 2; ++pa)
 #pragma unroll
-          for (int n = 0; n < NB8; ++n)
+          for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
+            for (int n = 0; n < NB8; ++n)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[pa][a][n][i] = 0.f;
         const int rt_up = ((64 * cb) & 127) + 16 * w, rt_gate = ((P.I + 64 * cb) & 127) + 16 * w;
-        for (int kb = k0; kb < k1; ++kb, ++j) {
-          const int slot = 2 * (j % per) + grp, use = j / per;
-          if (!mbar_wait(&T.full[slot], use & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+        for (int kb = k0; kb < k1; ++kb) {
+          const int slot = 2 * si + grp;
+          TIMER_START(t0);
+          if (!mbar_wait(&T.full[slot], ph, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+          TIMER_ADD(tm_wait, t0);
+          TIMER_START(t1);
           const uint32_t st = ring_a + slot * kSlotBytes;
           mma_tile<NB8>(st, 16 * w, 64 + 16 * w, st + kCodesBytes, rt_up, st + kCodesBytes + 2048, rt_gate,
                         4 * kb + t < P.KT1, region_a + kb * (NB8 * 4096), lane, acc);
           __syncwarp();
           if (lane == 0) mbar_arrive(&T.empty[slot]);
+          if (++si == per) { si = 0; ph ^= 1u; }
+          TIMER_ADD(tm_mma, t1);
         }
+        TIMER_START(t2);
+        float r[8 * NB8];   // [rb][n][4]: rb 0 = up, rb 1 = gate
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int n = 0; n < NB8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r[(a * NB8 + n) * 4 + i] = acc[0][a][n][i] + acc[1][a][n][i];
+        const int piece_first = f;
         f += k1 - k0;
         // ---- finish the unit: directly when this piece covers all of K, else through the scratch and a last arriver
         bool finalize = true;
         if (!(k0 == 0 && k1 == KB1)) {
-          const int slot_id = (f - (k1 - k0)) == fs ? 0 : 1;
+          const int slot_id = piece_first == fs ? 0 : 1;
           float* mine = P.scratch + ((long long)(v * 2 + slot_id) * kGroupThreads + gtid) * 16;
 #pragma unroll
-          for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int n = 0; n < NB8; ++n)
-              *reinterpret_cast<float4*>(mine + (a * NB8 + n) * 4) = make_float4(acc[a][n][0], acc[a][n][1], acc[a][n][2], acc[a][n][3]);
+          for (int i = 0; i < 2 * NB8; ++i)
+            *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
           __threadfence();
           named_bar_sync(1 + grp, kGroupThreads);
           const int vlo = worker_of(q * KB1, T1, V), vhi = worker_of(q * KB1 + KB1 - 1, T1, V);
           if (gtid == 0) {
+            int nlive = 0;
+            for (int pv = vlo; pv <= vhi; ++pv) nlive += T.sb1[pv + 1] > T.sb1[pv];
             const unsigned old = atomicAdd(P.cnt1 + q, 1u);
-            const int last = old + 1u == (unsigned)live_workers(vlo, vhi, T1, V);
+            const int last = old + 1u == (unsigned)nlive;
             if (last) P.cnt1[q] = 0;
             T.last_flag[grp] = last;
           }
@@ -366,24 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
           finalize = T.last_flag[grp] != 0;
           if (finalize) {
             __threadfence();
-#pragma unroll
-            for (int a = 0; a < 2; ++a)
-#pragma unroll
-              for (int n = 0; n < NB8; ++n)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
-            for (int pv = vlo; pv <= vhi; ++pv) {   // pieces in worker order: a fixed summation order
-              if (share_begin(pv + 1, T1, V) == share_begin(pv, T1, V)) continue;
-              const int pslot = share_begin(pv, T1, V) < q * KB1 ? 1 : 0;   // a piece that starts the worker's share is slot 0
-              const float* src = P.scratch + ((long long)(pv * 2 + pslot) * kGroupThreads + gtid) * 16;
-#pragma unroll
-              for (int a = 0; a < 2; ++a)
-#pragma unroll
-                for (int n = 0; n < NB8; ++n) {
-                  const float4 pf = __ldcg(reinterpret_cast<const float4*>(src + (a * NB8 + n) * 4));
-                  acc[a][n][0] += pf.x, acc[a][n][1] += pf.y, acc[a][n][2] += pf.z, acc[a][n][3] += pf.w;
-                }
-            }
+            reduce_pieces<NB8>(P.scratch, T.sb1, q * KB1, vlo, vhi, gtid, r);
           }
           named_bar_sync(1 + grp, kGroupThreads);   // last_flag may be rewritten by the next unit only after all read it
         }
@@ -403,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
                   if (T.ids[tok * P.top_k + s] == e) pair = tok * P.top_k + s;
               float a = 0.f;
               if (pair >= 0) {
-                a = silu_mul(alpha * acc[1][n][i], alpha * acc[0][n][i]);
+                a = silu_mul(alpha * r[(NB8 + n) * 4 + i], alpha * r[n * 4 + i]);
                 a = fminf(fmaxf(a, -65504.f), 65504.f);
               }
               af[frag_index<NB8>(c, tok)] = __float2half_rn(a);
@@ -416,9 +477,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
               af[frag_index<NB8>(P.I + i / (8 * NB8), i % (8 * NB8))] = __float2half_rn(0.f);
           }
         }
+        TIMER_ADD(tm_fix, t2);
       }
       if (do2) {
-        // ---- publish FC1's results and arrive at the grid-wide barrier (the producer is the only waiter)
+        // ---- publish FC1's results and arrive at the grid-wide barrier (the producers are the only waiters)
         __threadfence();
         fence_proxy_async();
         named_bar_sync(1 + grp, kGroupThreads);
@@ -432,44 +494,50 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
         }
       }
     }
+#ifdef B200_TIMERS
+    const long long tm_phase1 = clock64() - tm_begin;
+#endif
 
     if (do2) {
       // ---- FC2 pieces of this worker: tiles ordered (output block nb, expert u, K box kb)
-      const int fs = share_begin(v, T2, V), fe = share_begin(v + 1, T2, V);
+      const int fs = T.sb2[v], fe = T.sb2[v + 1];
       const int per_nb = U * KB2;
       int f = fs;
       while (f < fe) {
         const int nb = f / per_nb;
         const int pe = min(fe, (nb + 1) * per_nb);   // end of this piece
-        float oacc[2][NB8][4];
+        float r[8 * NB8];   // [rb][n][4] running output sums of this piece
 #pragma unroll
-        for (int a = 0; a < 2; ++a)
-#pragma unroll
-          for (int n = 0; n < NB8; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) oacc[a][n][i] = 0.f;
+        for (int i = 0; i < 8 * NB8; ++i) r[i] = 0.f;
         const int piece_start = f;
+        int kb = f % KB2, u = (f / KB2) % U;
         while (f < pe) {
-          const int q = f / KB2, u = q % U;
-          const int k0 = f % KB2, k1 = min(KB2, k0 + (pe - f));
+          const int k1 = min(KB2, kb + (pe - f));
           const int e = T.experts[u];
-          float acc[2][NB8][4];
+          float acc[2][2][NB8][4];
 #pragma unroll
-          for (int a = 0; a < 2; ++a)
+          for (int pa = 0; pa < 2; ++pa)
 #pragma unroll
-            for (int n = 0; n < NB8; ++n)
+            for (int a = 0; a < 2; ++a)
 #pragma unroll
-              for (int i = 0; i < 4; ++i) acc[a][n][i] = 0.f;
-          for (int kb = k0; kb < k1; ++kb, ++j) {
-            const int slot = 2 * (j % per) + grp, use = j / per;
-            if (!mbar_wait(&T.full[slot], use & 1, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+              for (int n = 0; n < NB8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[pa][a][n][i] = 0.f;
+          f += k1 - kb;
+          for (; kb < k1; ++kb) {
+            const int slot = 2 * si + grp;
+            TIMER_START(t0);
+            if (!mbar_wait(&T.full[slot], ph, &T.abort_flag)) *P.status = ST_TIMEOUT_FULL;
+            TIMER_ADD(tm_wait, t0);
+            TIMER_START(t1);
             const uint32_t st = ring_a + slot * kSlotBytes;
             mma_tile<NB8>(st, 32 * w, 32 * w + 16, st + kCodesBytes, 32 * w, st + kCodesBytes, 32 * w + 16,
                           4 * kb + t < P.KT2, region_a + slot * slab_bytes, lane, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive(&T.empty[slot]);
+            if (++si == per) { si = 0; ph ^= 1u; }
+            TIMER_ADD(tm_mma, t1);
           }
-          f += k1 - k0;
           // routing weight x alpha2 for this lane's token columns, applied in fp32
           const float alpha = P.alpha2[e];
 #pragma unroll
@@ -484,26 +552,28 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
               sc *= alpha;
 #pragma unroll
               for (int a = 0; a < 2; ++a) {
-                oacc[a][n][c] += sc * acc[a][n][c];
-                oacc[a][n][2 + c] += sc * acc[a][n][2 + c];
+                r[(a * NB8 + n) * 4 + c] += sc * (acc[0][a][n][c] + acc[1][a][n][c]);
+                r[(a * NB8 + n) * 4 + 2 + c] += sc * (acc[0][a][n][2 + c] + acc[1][a][n][2 + c]);
               }
             }
+          if (kb == KB2) { kb = 0; ++u; }   // u wraps only at a piece boundary, where it is recomputed
         }
         // ---- every output block is shared by several workers: partial sums to the scratch, last arriver reduces
         {
+          TIMER_START(t2);
           const int slot_id = piece_start == fs ? 0 : 1;
           float* mine = P.scratch + ((long long)(v * 2 + slot_id) * kGroupThreads + gtid) * 16;
 #pragma unroll
-          for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int n = 0; n < NB8; ++n)
-              *reinterpret_cast<float4*>(mine + (a * NB8 + n) * 4) = make_float4(oacc[a][n][0], oacc[a][n][1], oacc[a][n][2], oacc[a][n][3]);
+          for (int i = 0; i < 2 * NB8; ++i)
+            *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
           __threadfence();
           named_bar_sync(1 + grp, kGroupThreads);
           const int vlo = worker_of(nb * per_nb, T2, V), vhi = worker_of((nb + 1) * per_nb - 1, T2, V);
           if (gtid == 0) {
+            int nlive = 0;
+            for (int pv = vlo; pv <= vhi; ++pv) nlive += T.sb2[pv + 1] > T.sb2[pv];
             const unsigned old = atomicAdd(P.cnt2 + nb, 1u);
-            const int last = old + 1u == (unsigned)live_workers(vlo, vhi, T2, V);
+            const int last = old + 1u == (unsigned)nlive;
             if (last) P.cnt2[nb] = 0;
             T.last_flag[grp] = last;
           }
@@ -511,24 +581,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
           const bool last = T.last_flag[grp] != 0;
           if (last) {
             __threadfence();
-#pragma unroll
-            for (int a = 0; a < 2; ++a)
-#pragma unroll
-              for (int n = 0; n < NB8; ++n)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) oacc[a][n][i] = 0.f;
-            for (int pv = vlo; pv <= vhi; ++pv) {
-              if (share_begin(pv + 1, T2, V) == share_begin(pv, T2, V)) continue;
-              const int pslot = share_begin(pv, T2, V) < nb * per_nb ? 1 : 0;
-              const float* src = P.scratch + ((long long)(pv * 2 + pslot) * kGroupThreads + gtid) * 16;
-#pragma unroll
-              for (int a = 0; a < 2; ++a)
-#pragma unroll
-                for (int n = 0; n < NB8; ++n) {
-                  const float4 pf = __ldcg(reinterpret_cast<const float4*>(src + (a * NB8 + n) * 4));
-                  oacc[a][n][0] += pf.x, oacc[a][n][1] += pf.y, oacc[a][n][2] += pf.z, oacc[a][n][3] += pf.w;
-                }
-            }
+            reduce_pieces<NB8>(P.scratch, T.sb2, nb * per_nb, vlo, vhi, gtid, r);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
 #pragma unroll
@@ -537,13 +590,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
                 for (int i = 0; i < 4; ++i) {
                   const int tok = 8 * n + 2 * t + (i & 1);
                   const int row = 128 * nb + 32 * w + 16 * a + g + ((i >> 1) << 3);
-                  if (tok < P.M) P.out[(long long)tok * P.H + row] = __float2bfloat16_rn(oacc[a][n][i]);
+                  if (tok < P.M) P.out[(long long)tok * P.H + row] = __float2bfloat16_rn(r[(a * NB8 + n) * 4 + i]);
                 }
           }
           named_bar_sync(1 + grp, kGroupThreads);
+          TIMER_ADD(tm_fix, t2);
         }
       }
     }
+#ifdef B200_TIMERS
+    if (P.debug && gtid == 0) {
+      P.debug[v * 8 + 0] = tm_wait; P.debug[v * 8 + 1] = tm_mma; P.debug[v * 8 + 2] = tm_fix; P.debug[v * 8 + 3] = tm_phase1;
+      P.debug[v * 8 + 7] = clock64() - tm_begin;
+    }
+#endif
   }
   // Every TMA copy this CTA issued has been consumed by a full-barrier wait above. If a bounded wait ran out (abort flag
   // set, status word written), give copies still in flight time to land before the CTA retires.

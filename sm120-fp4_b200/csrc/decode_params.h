@@ -25,6 +25,7 @@ struct DecodeParams {
   unsigned* cnt2;           // workspace: arrival counters per FC2 output block (self-resetting)
   unsigned* gridbar;        // workspace: [0] arrivals, [1] generation
   int* status;              // workspace: 0, or the code of the first bounded wait that ran out
+  long long* debug;         // workspace: per-worker cycle counters (written only by the timer build)
   int* experts_out;         // optional routing tables in the reference's padded form
   int* offsets_out;
   int* pairs_out;
