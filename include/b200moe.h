@@ -76,6 +76,13 @@ int b200moe_layer_route_tables(const b200moe_layer* layer, const void* workspace
 /* status word of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT or B200MOE_ERR_ARG (bad expert id) */
 int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void* stream);
 
+/* single-tile check of the tcgen05 building blocks (TMEM, descriptors, scale copies, kind::mxf4nvf4 MMA): d f32 [128, N]
+ * = dequant(a)[128, K] x dequant(b)[N, K]^T with 128x4-swizzled block scales; N % 16 == 0 <= 128, K % 256 == 0 <= 1024.
+ * knobs: null, or 8 host uint32 overriding the descriptor fields (unit-test use). The arithmetic it checks is the
+ * reference GEMM of sm120fp4/reference.py:133-137. */
+int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
+                       const unsigned* knobs, int* status_dev, void* stream);
+
 /* per-worker cycle counters of the last decode launch (8 int64 per worker: consumer wait, math, fix-up, phase-1 end,
  * producer wait, producer grid wait, producer end, consumer end). Filled only by a library built with -DB200_TIMERS (a
  * diagnostic build; the reference has no counterpart); returns the number of workers copied. Synchronises the stream. */

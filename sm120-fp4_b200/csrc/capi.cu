@@ -161,6 +161,10 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
   }
   p.s1_expert_stride = L->s1_stride, p.s2_expert_stride = L->s2_stride;
   p.M = M, p.E = L->E, p.H = L->H, p.I = L->I, p.top_k = L->top_k, p.phases = phases;
+  {
+    const char* c = getenv("B200MOE_COOPERATIVE");
+    p.cooperative = c && c[0] == '1';
+  }
   p.KB1 = L->KB1, p.KB2 = L->KB2, p.CB1 = L->CB1, p.NB2 = L->NB2, p.KT1 = L->KT1, p.KT2 = L->KT2;
   const int nb8 = M <= 8 ? 1 : 2;
   const int slab = nb8 * 4096;

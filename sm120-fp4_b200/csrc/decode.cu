@@ -39,6 +39,7 @@ struct Tables {
   int base[kMaxE];     // inclusive scan of cnt
   int uidx[kMaxE];     // inclusive scan of touched flags
   int experts[kMaxE];  // touched experts ascending
+  unsigned omask[kMaxE];  // per touched expert: bit n set when a token of octet n (tokens 8n..8n+7) is routed to it
   int sb1[kMaxWorkers + 1];   // first FC1 tile of every worker (stream-K shares); sb1[V] = T1
   int sb2[kMaxWorkers + 1];   // same for FC2
   int U;
@@ -66,7 +67,7 @@ __device__ __forceinline__ int worker_of(int f, int T, int V) { return (int)(((u
 // acc[parity][rb][n][4]: even and odd MMAs of a K run use separate accumulators to halve the dependent chain.
 template <int NB8>
 __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uint32_t sc0, int rt0, uint32_t sc1, int rt1,
-                                         bool kt_valid, uint32_t bfrag, int lane, float (&acc)[2][2][NB8][4]) {
+                                         bool kt_valid, uint32_t bfrag, int lane, unsigned octets, float (&acc)[2][2][NB8][4]) {
   const int g = lane >> 2, t = lane & 3;
   uint32_t sfw[2][2];
   {
@@ -82,7 +83,8 @@ __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uin
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj)
 #pragma unroll
-      for (int n = 0; n < NB8; ++n) bq[jj][n] = lds128(bfrag + ((((h * 4 + jj) * NB8 + n) * 32 + lane) << 4));
+      for (int n = 0; n < NB8; ++n)
+        if (NB8 == 1 || ((octets >> n) & 1u)) bq[jj][n] = lds128(bfrag + ((((h * 4 + jj) * NB8 + n) * 32 + lane) << 4));
 #pragma unroll
     for (int rb = 0; rb < 2; ++rb) {
       const int ra = (rb == 0 ? row0 : row1) + g;   // stage row of fragment row g; fragment row g+8 is ra+8
@@ -106,10 +108,11 @@ __device__ __forceinline__ void mma_tile(uint32_t codes, int row0, int row1, uin
           db[i] = hmul2_u32(db[i], s_b);
         }
 #pragma unroll
-        for (int n = 0; n < NB8; ++n) {
-          mma_f16_16816(acc[0][rb][n], da[0], db[0], da[1], db[1], bq[wd][n].x, bq[wd][n].y);
-          mma_f16_16816(acc[1][rb][n], da[2], db[2], da[3], db[3], bq[wd][n].z, bq[wd][n].w);
-        }
+        for (int n = 0; n < NB8; ++n)
+          if (NB8 == 1 || ((octets >> n) & 1u)) {   // warp-uniform: skip a token octet no token of which is routed here
+            mma_f16_16816(acc[0][rb][n], da[0], db[0], da[1], db[1], bq[wd][n].x, bq[wd][n].y);
+            mma_f16_16816(acc[1][rb][n], da[2], db[2], da[3], db[3], bq[wd][n].z, bq[wd][n].w);
+          }
       }
     }
   }
@@ -220,7 +223,14 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
   const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
   const int T1 = do1 ? U * CB1 * KB1 : 0;
   const int T2 = do2 ? NB2 * U * KB2 : 0;
-  if (tid < kMaxE && T.cnt[tid] > 0) T.experts[T.uidx[tid] - 1] = tid;
+  if (tid < kMaxE && T.cnt[tid] > 0) {
+    T.experts[T.uidx[tid] - 1] = tid;
+    unsigned m = 0;
+    for (int tok = 0; tok < P.M; ++tok)
+      for (int sidx = 0; sidx < P.top_k; ++sidx)
+        if (T.ids[tok * P.top_k + sidx] == tid) m |= 1u << (tok >> 3);
+    T.omask[T.uidx[tid] - 1] = m;
+  }
   for (int v = tid; v <= V; v += kThreads) {   // stream-K shares: worker v owns tiles [sb[v], sb[v+1])
     T.sb1[v] = (int)(((unsigned)v * (unsigned)T1) / (unsigned)V);
     T.sb2[v] = (int)(((unsigned)v * (unsigned)T2) / (unsigned)V);
@@ -397,6 +407,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
 #pragma unroll
               for (int i = 0; i < 4; ++i) acc[pa][a][n][i] = 0.f;
         const int rt_up = ((64 * cb) & 127) + 16 * w, rt_gate = ((P.I + 64 * cb) & 127) + 16 * w;
+        const unsigned octets = NB8 == 1 ? 1u : T.omask[u];
         for (int kb = k0; kb < k1; ++kb) {
           const int slot = 2 * si + grp;
           TIMER_START(t0);
@@ -405,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
           TIMER_START(t1);
           const uint32_t st = ring_a + slot * kSlotBytes;
           mma_tile<NB8>(st, 16 * w, 64 + 16 * w, st + kCodesBytes, rt_up, st + kCodesBytes + 2048, rt_gate,
-                        4 * kb + t < P.KT1, region_a + kb * (NB8 * 4096), lane, acc);
+                        4 * kb + t < P.KT1, region_a + kb * (NB8 * 4096), lane, octets, acc);
           __syncwarp();
           if (lane == 0) mbar_arrive(&T.empty[slot]);
           if (++si == per) { si = 0; ph ^= 1u; }
@@ -429,21 +440,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
 #pragma unroll
           for (int i = 0; i < 2 * NB8; ++i)
             *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-          __threadfence();
           named_bar_sync(1 + grp, kGroupThreads);
           const int vlo = worker_of(q * KB1, T1, V), vhi = worker_of(q * KB1 + KB1 - 1, T1, V);
           if (gtid == 0) {
+            __threadfence();   // cumulative: orders the group's stores (observed through the barrier) before the arrival
             int nlive = 0;
             for (int pv = vlo; pv <= vhi; ++pv) nlive += T.sb1[pv + 1] > T.sb1[pv];
             const unsigned old = atomicAdd(P.cnt1 + q, 1u);
             const int last = old + 1u == (unsigned)nlive;
-            if (last) P.cnt1[q] = 0;
+            if (last) { P.cnt1[q] = 0; __threadfence(); }
             T.last_flag[grp] = last;
           }
           named_bar_sync(1 + grp, kGroupThreads);
           finalize = T.last_flag[grp] != 0;
           if (finalize) {
-            __threadfence();
             reduce_pieces<NB8>(P.scratch, T.sb1, q * KB1, vlo, vhi, gtid, r);
           }
           named_bar_sync(1 + grp, kGroupThreads);   // last_flag may be rewritten by the next unit only after all read it
@@ -481,10 +491,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
       }
       if (do2) {
         // ---- publish FC1's results and arrive at the grid-wide barrier (the producers are the only waiters)
-        __threadfence();
         fence_proxy_async();
         named_bar_sync(1 + grp, kGroupThreads);
         if (gtid == 0) {
+          __threadfence();
           const unsigned old = atomicAdd(P.gridbar, 1u);
           if (old == (unsigned)(V - 1)) {
             P.gridbar[0] = 0;
@@ -524,6 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[pa][a][n][i] = 0.f;
           f += k1 - kb;
+          const unsigned octets = NB8 == 1 ? 1u : T.omask[u];
           for (; kb < k1; ++kb) {
             const int slot = 2 * si + grp;
             TIMER_START(t0);
@@ -532,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
             TIMER_START(t1);
             const uint32_t st = ring_a + slot * kSlotBytes;
             mma_tile<NB8>(st, 32 * w, 32 * w + 16, st + kCodesBytes, 32 * w, st + kCodesBytes, 32 * w + 16,
-                          4 * kb + t < P.KT2, region_a + slot * slab_bytes, lane, acc);
+                          4 * kb + t < P.KT2, region_a + slot * slab_bytes, lane, octets, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive(&T.empty[slot]);
             if (++si == per) { si = 0; ph ^= 1u; }
@@ -566,21 +577,20 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
 #pragma unroll
           for (int i = 0; i < 2 * NB8; ++i)
             *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-          __threadfence();
           named_bar_sync(1 + grp, kGroupThreads);
           const int vlo = worker_of(nb * per_nb, T2, V), vhi = worker_of((nb + 1) * per_nb - 1, T2, V);
           if (gtid == 0) {
+            __threadfence();
             int nlive = 0;
             for (int pv = vlo; pv <= vhi; ++pv) nlive += T.sb2[pv + 1] > T.sb2[pv];
             const unsigned old = atomicAdd(P.cnt2 + nb, 1u);
             const int last = old + 1u == (unsigned)nlive;
-            if (last) P.cnt2[nb] = 0;
+            if (last) { P.cnt2[nb] = 0; __threadfence(); }
             T.last_flag[grp] = last;
           }
           named_bar_sync(1 + grp, kGroupThreads);
           const bool last = T.last_flag[grp] != 0;
           if (last) {
-            __threadfence();
             reduce_pieces<NB8>(P.scratch, T.sb2, nb * per_nb, vlo, vhi, gtid, r);
 #pragma unroll
             for (int a = 0; a < 2; ++a)
@@ -649,7 +659,14 @@ int b200_decode_launch(const DecodeParams& p, int grid, int smem_bytes, cudaStre
     B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     configured[which] = smem_bytes;
   }
-  B200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, (size_t)smem_bytes, st));
+  // One CTA per SM (shared memory allows no second one), so on an otherwise idle device every CTA is resident and the
+  // grid-wide barrier inside the kernel can complete; its waits are bounded either way. A cooperative launch makes
+  // co-residency a launch-time guarantee at the price of a few microseconds between back-to-back launches.
+  if (p.cooperative) {
+    B200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, (size_t)smem_bytes, st));
+  } else {
+    B200_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kThreads), args, (size_t)smem_bytes, st));
+  }
   return B200MOE_OK;
 }
 

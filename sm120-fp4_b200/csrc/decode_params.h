@@ -32,6 +32,7 @@ struct DecodeParams {
   long long s1_expert_stride, s2_expert_stride;
   int M, E, H, I, top_k, Umax;
   int phases;               // bit 0: FC1, bit 1: FC2
+  int cooperative;          // launch with cudaLaunchCooperativeKernel
   int NS;                   // ring stages (even)
   int region_bytes;         // shared-memory region for x fragments / activation slabs
   int KB1, KB2;             // 256-code K boxes of FC1 (over H) and FC2 (over I)

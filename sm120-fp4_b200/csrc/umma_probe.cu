@@ -1,0 +1,111 @@
+// Single-tile check of the tcgen05 block-scaled FP4 MMA building blocks (TMEM allocation, shared-memory descriptors,
+// scale-factor copies, kind::mxf4nvf4 MMA, accumulator loads): D[128, N] = dequant(A)[128, K] * dequant(B)[N, K]^T.
+// One CTA, operands staged by ordinary stores in the layout a 128B-swizzled TMA box produces. It is the unit test of
+// tcgen05.cuh; the descriptor fields can be overridden from the host so a test can state which encoding is the live one.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+struct ProbeKnobs {
+  uint32_t op_lbo, op_sbo, op_layout;   // operand descriptor (bytes, bytes, layout type)
+  uint32_t sf_lbo, sf_sbo;              // scale-tile descriptor
+  uint32_t idesc;                       // 0: computed by idesc_mxf4nvf4
+  uint32_t k_step;                      // descriptor start-address increment per K=64 step, in 16-byte units
+  uint32_t sf_col_step;                 // TMEM columns per K=64 step of scale factors
+};
+
+__global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict__ a, const uint8_t* __restrict__ sfa,
+                                                       const uint8_t* __restrict__ b, const uint8_t* __restrict__ sfb, int N, int K,
+                                                       float* __restrict__ d, ProbeKnobs kn, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int nkb = K / 256;
+  uint8_t* sA = smem;                          // [nkb][128 rows][128 B], 128B swizzle
+  uint8_t* sB = sA + nkb * 16384;              // [nkb][128 rows][128 B] (rows >= N zero)
+  uint8_t* sSFA = sB + nkb * 16384;            // [nkb*4][512 B]
+  uint8_t* sSFB = sSFA + nkb * 2048;
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base, 256);
+    tmem_relinquish();
+  }
+  // stage the operands: element (row, byte c) of a 128-byte row goes to row*128 + ((c/16 ^ (row&7))*16) + c%16
+  const int row_bytes = K / 2;
+  for (int i = tid; i < nkb * 128 * 8; i += 128) {
+    const int kb = i / 1024, r = (i / 8) % 128, ch = i % 8;
+    const uint4 va = *reinterpret_cast<const uint4*>(a + (long long)r * row_bytes + kb * 128 + ch * 16);
+    uint4 vb = make_uint4(0u, 0u, 0u, 0u);
+    if (r < N) vb = *reinterpret_cast<const uint4*>(b + (long long)r * row_bytes + kb * 128 + ch * 16);
+    const int off = kb * 16384 + r * 128 + ((ch ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(sA + off) = va;
+    *reinterpret_cast<uint4*>(sB + off) = vb;
+  }
+  for (int i = tid; i < nkb * 2048 / 16; i += 128) {
+    reinterpret_cast<uint4*>(sSFA)[i] = reinterpret_cast<const uint4*>(sfa)[i];
+    reinterpret_cast<uint4*>(sSFB)[i] = reinterpret_cast<const uint4*>(sfb)[i];
+  }
+  fence_proxy_async();          // generic-proxy stores -> visible to the tensor-core (async) proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = tmem_base;
+  const uint32_t d_tmem = tb, sfa_tmem = tb + 128, sfb_tmem = tb + 192;
+  if (tid == 32) {              // one thread issues all tensor-core work
+    const uint32_t idesc = kn.idesc ? kn.idesc : idesc_mxf4nvf4(128, N);
+    for (int kb = 0; kb < nkb; ++kb)
+      for (int j = 0; j < 4; ++j) {
+        const int s = kb * 4 + j;
+        tmem_cp_sf(sfa_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFA + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
+        tmem_cp_sf(sfb_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFB + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
+        const uint64_t ad = smem_desc(smem_u32(sA + kb * 16384), kn.op_lbo, kn.op_sbo, kn.op_layout) + (uint64_t)(j * kn.k_step);
+        const uint64_t bd = smem_desc(smem_u32(sB + kb * 16384), kn.op_lbo, kn.op_sbo, kn.op_layout) + (uint64_t)(j * kn.k_step);
+        umma_mxf4nvf4(d_tmem, ad, bd, idesc, sfa_tmem + s * kn.sf_col_step, sfb_tmem + s * kn.sf_col_step, s != 0);
+      }
+    umma_commit(&bar);
+  }
+  if (!mbar_wait(&bar, 0, &abort_flag, 1u << 18)) *status = 1;
+  tc_fence_after();
+  if (!abort_flag) {
+    for (int c0 = 0; c0 < N; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(d_tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) d[(long long)tid * N + c0 + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// a u8 [128, K/2], sfa u8 128x4-swizzled over [128, K/16], b u8 [N, K/2], sfb u8 128x4-swizzled over [N -> 128, K/16],
+// d f32 [128, N]; N a multiple of 16 up to 128, K a multiple of 256 up to 1024. knobs: 8 uint32 on the host, or null
+// for the defaults the library itself uses.
+extern "C" int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
+                                  const unsigned* knobs, int* status_dev, void* stream) {
+  if (!a || !sfa || !b || !sfb || !d || !status_dev) return B200MOE_ERR_ARG;
+  if (N < 16 || N > 128 || N % 16 || K < 256 || K > 1024 || K % 256) return B200MOE_ERR_SHAPE;
+  ProbeKnobs kn = {16, 1024, 2, 0, 128, 0, 2, 4};
+  if (knobs) kn = {knobs[0], knobs[1], knobs[2], knobs[3], knobs[4], knobs[5], knobs[6], knobs[7]};
+  const int nkb = K / 256;
+  const int smem = 1024 + nkb * (16384 * 2 + 4096);
+  B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  k_umma_probe<<<1, 128, smem, (cudaStream_t)stream>>>((const uint8_t*)a, (const uint8_t*)sfa, (const uint8_t*)b, (const uint8_t*)sfb, N, K,
+                                                        d, kn, status_dev);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
