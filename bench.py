@@ -94,11 +94,8 @@ def build_layers(cfg, n_layers, device):
         parts = {}
         for name, rows, cols in (("1", 2 * i, h), ("2", h, i)):
             w = (torch.randn(e, rows, cols, generator=g, device=device) * 0.02).to(torch.bfloat16)
-            qs, ss, al = [], [], []
-            for ex in range(e):
-                q, s, gs = pkg.quantize_nvfp4(w[ex])
-                qs.append(q), ss.append(s), al.append(1.0 / gs)
-            parts[name] = (torch.stack(qs), pkg.to_128x4(torch.stack(ss)), torch.cat(al))
+            q, sw, gs = pkg.quantize_nvfp4_experts(w, swizzle=True)
+            parts[name] = (q, sw, 1.0 / gs)
             del w
         layers.append(Weights(parts["1"][0], parts["1"][1], parts["1"][2], parts["2"][0], parts["2"][1], parts["2"][2], k,
                               scale_layout="128x4"))

@@ -35,12 +35,15 @@ int b200moe_from_128x4(const void* sf_swizzled, void* sf_linear, int batch, int 
 
 /* ---- quantizer: sm120fp4/reference.py:68-71 (global_scale_for) and :74-90 (quantize_nvfp4). dtype 0 = bf16, 1 = f32.
  * b200moe_global_scale: gs_out[0] = 2688 / max(amax|x|, 1e-12) with the reference's rounding; amax_scratch_u32 is 4
- * bytes of device scratch. b200moe_quantize_nvfp4: destination row r quantises source row src_row[r] (null: r; negative:
+ * bytes of device scratch. b200moe_quantize_nvfp4: global_scale holds one value (gs_rows 0) or one per gs_rows
+ * destination rows (stacked experts); destination row r quantises source row src_row[r] (null: r; negative:
  * zero codes and scales); packed u8 [rows, K/2]; sf u8 row-major [rows, K/16] (sf_layout 0) or 128x4-swizzled over
  * [rows, K/16] (sf_layout 1; the caller sizes the buffer for the padded extent). Bit-exact with the reference. */
 int b200moe_global_scale(const void* x, int dtype, long long n, void* amax_scratch_u32, float* gs_out, void* stream);
+int b200moe_global_scale_grouped(const void* x, int dtype, int groups, long long group_elems, void* amax_scratch_u32,
+                                 float* gs_out, void* stream); /* one scale per group (per expert); scratch 4*groups bytes */
 int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_row, int rows, int K, const float* global_scale,
-                           void* packed, void* sf, int sf_layout, void* stream);
+                           int gs_rows, void* packed, void* sf, int sf_layout, void* stream);
 
 /* ---- router: sm120fp4/kernels/moe_w4a16.py:85-91 (route; padded form of k_route :48-83) and the torch router of
  * sm120fp4/kernels/fc1_w4a16.py:272-279. ids i32 [P] -> experts i32 [Umax] (ascending, -1 padding), offsets i32

@@ -6,5 +6,5 @@ Everything computes on the GPU through the C ABI of include/b200moe.h; there is 
 __version__ = "0.1.0"
 
 from .layouts import from_128x4, padded_sf_shape, to_128x4  # noqa: E402,F401
-from .quant import global_scale_for, quantize_nvfp4, quantize_nvfp4_128x4  # noqa: E402,F401
+from .quant import global_scale_for, quantize_nvfp4, quantize_nvfp4_128x4, quantize_nvfp4_experts  # noqa: E402,F401
 from .router import route, route_tables  # noqa: E402,F401

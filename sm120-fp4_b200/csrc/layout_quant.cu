@@ -119,11 +119,10 @@ __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], float 
 // sf_layout 0: row-major [rows, K/16]; 1: 128x4 swizzle over [rows, K/16] (rows padded by the caller's buffer).
 template <typename T>
 __global__ void __launch_bounds__(256) k_quantize_nvfp4(const T* __restrict__ x, const int* __restrict__ src_row, int rows,
-                                                        int K, const float* __restrict__ gs_ptr, uint8_t* __restrict__ packed,
-                                                        uint8_t* __restrict__ sf, int sf_layout) {
+                                                        int K, const float* __restrict__ gs_ptr, int gs_rows,
+                                                        uint8_t* __restrict__ packed, uint8_t* __restrict__ sf, int sf_layout) {
   const int bpr = K >> 4;
   const int nkt = (bpr + 3) >> 2;
-  const float gs = *gs_ptr;
   const long long total = (long long)rows * bpr;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / bpr), b = (int)(i % bpr);
@@ -133,7 +132,7 @@ __global__ void __launch_bounds__(256) k_quantize_nvfp4(const T* __restrict__ x,
     if (s >= 0) {
       float v[16];
       load16(x + (long long)s * K + b * 16, v);
-      sb = quantize_block16(v, gs, pk);
+      sb = quantize_block16(v, gs_ptr[gs_rows > 0 ? r / gs_rows : 0], pk);   // one global scale per gs_rows destination rows
     }
     *reinterpret_cast<uint2*>(packed + (long long)r * (K >> 1) + b * 8) = pk;
     if (sf_layout == 0) sf[(long long)r * bpr + b] = sb;
@@ -171,6 +170,43 @@ extern "C" int b200moe_from_128x4(const void* sf_swizzled, void* sf_linear, int 
   return B200MOE_OK;
 }
 
+// One global scale per group of `group_elems` consecutive elements: grid.y = group.
+template <typename T>
+__global__ void __launch_bounds__(256) k_amax_grouped(const T* __restrict__ x, long long group_elems, unsigned* __restrict__ amax_bits) {
+  const T* xg = x + (long long)blockIdx.y * group_elems;
+  float m = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < group_elems; i += (long long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf((float)xg[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, wm[w]);
+    atomicMax(amax_bits + blockIdx.y, __float_as_uint(m));
+  }
+}
+__global__ void k_global_scale_grouped(const unsigned* __restrict__ amax_bits, float* __restrict__ gs, int groups) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g < groups) gs[g] = __fmul_rn(__frcp_rn(fmaxf(__uint_as_float(amax_bits[g]), 1e-12f)), 2688.0f);
+}
+
+extern "C" int b200moe_global_scale_grouped(const void* x, int dtype, int groups, long long group_elems, void* amax_scratch_u32,
+                                            float* gs_out, void* stream) {
+  if (!x || !amax_scratch_u32 || !gs_out || groups <= 0 || groups > 65535 || group_elems <= 0) return B200MOE_ERR_ARG;
+  if (dtype != 0 && dtype != 1) return B200MOE_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  B200_CUDA_TRY(cudaMemsetAsync(amax_scratch_u32, 0, sizeof(unsigned) * groups, st));
+  dim3 grid(grid_for(group_elems, 256 * 8, 64), groups);
+  if (dtype == 0) k_amax_grouped<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, group_elems, (unsigned*)amax_scratch_u32);
+  else k_amax_grouped<<<grid, 256, 0, st>>>((const float*)x, group_elems, (unsigned*)amax_scratch_u32);
+  B200_LAUNCH_CHECK();
+  k_global_scale_grouped<<<(groups + 127) / 128, 128, 0, st>>>((const unsigned*)amax_scratch_u32, gs_out, groups);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
 extern "C" int b200moe_global_scale(const void* x, int dtype, long long n, void* amax_scratch_u32, float* gs_out, void* stream) {
   if (!x || !amax_scratch_u32 || !gs_out || n < 0) return B200MOE_ERR_ARG;
   if (dtype != 0 && dtype != 1) return B200MOE_ERR_ARG;
@@ -187,8 +223,8 @@ extern "C" int b200moe_global_scale(const void* x, int dtype, long long n, void*
 }
 
 extern "C" int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_row, int rows, int K, const float* global_scale,
-                                      void* packed, void* sf, int sf_layout, void* stream) {
-  if (!x || !global_scale || !packed || !sf || rows < 0) return B200MOE_ERR_ARG;
+                                      int gs_rows, void* packed, void* sf, int sf_layout, void* stream) {
+  if (!x || !global_scale || !packed || !sf || rows < 0 || gs_rows < 0) return B200MOE_ERR_ARG;
   if (K <= 0 || K % 16) return B200MOE_ERR_SHAPE;
   if ((dtype != 0 && dtype != 1) || (sf_layout != 0 && sf_layout != 1)) return B200MOE_ERR_ARG;
   if (((uintptr_t)x & 15) || ((uintptr_t)packed & 7)) return B200MOE_ERR_ARG;
@@ -196,9 +232,9 @@ extern "C" int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_r
   cudaStream_t st = (cudaStream_t)stream;
   const int g = grid_for((long long)rows * (K / 16), 256);
   if (dtype == 0)
-    k_quantize_nvfp4<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, src_row, rows, K, global_scale, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
+    k_quantize_nvfp4<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, src_row, rows, K, global_scale, gs_rows, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
   else
-    k_quantize_nvfp4<<<g, 256, 0, st>>>((const float*)x, src_row, rows, K, global_scale, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
+    k_quantize_nvfp4<<<g, 256, 0, st>>>((const float*)x, src_row, rows, K, global_scale, gs_rows, (uint8_t*)packed, (uint8_t*)sf, sf_layout);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }

@@ -101,6 +101,10 @@ extern "C" int b200moe_umma_probe(const void* a, const void* sfa, const void* b,
   if (N < 16 || N > 128 || N % 16 || K < 256 || K > 1024 || K % 256) return B200MOE_ERR_SHAPE;
   ProbeKnobs kn = {16, 1024, 2, 0, 128, 0, 2, 4};
   if (knobs) kn = {knobs[0], knobs[1], knobs[2], knobs[3], knobs[4], knobs[5], knobs[6], knobs[7]};
+  // a scale copy writes 4 TMEM columns and must start on a multiple of 4 (anything else is a misaligned-address fault);
+  // descriptor offsets are multiples of 16 bytes by construction
+  if (kn.sf_col_step % 4 || kn.sf_col_step > 8 || (kn.op_lbo & 15) || (kn.op_sbo & 15) || (kn.sf_lbo & 15) || (kn.sf_sbo & 15) || kn.op_layout > 6)
+    return B200MOE_ERR_ARG;
   const int nkb = K / 256;
   const int smem = 1024 + nkb * (16384 * 2 + 4096);
   B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

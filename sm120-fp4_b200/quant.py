@@ -47,7 +47,7 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor | None = None):
     m, k = x.shape
     packed = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
     sf = torch.empty(m, k // BLOCK, dtype=torch.uint8, device=x.device)
-    _lib.check(_lib.lib().b200moe_quantize_nvfp4(_lib.ptr(x), _dtype_code(x), 0, m, k, _lib.ptr(gs), _lib.ptr(packed), _lib.ptr(sf), 0,
+    _lib.check(_lib.lib().b200moe_quantize_nvfp4(_lib.ptr(x), _dtype_code(x), 0, m, k, _lib.ptr(gs), 0, _lib.ptr(packed), _lib.ptr(sf), 0,
                                                  _lib.stream_ptr()), "quantize_nvfp4")
     return packed, sf, gs
 
@@ -68,6 +68,36 @@ def quantize_nvfp4_128x4(x: torch.Tensor, global_scale: torch.Tensor, src_row: t
     sf = (torch.zeros if zero else torch.empty)(pr, pc, dtype=torch.uint8, device=x.device)
     if src_row is not None:
         src_row = src_row.to(device=x.device, dtype=torch.int32).contiguous()
-    _lib.check(_lib.lib().b200moe_quantize_nvfp4(_lib.ptr(x), _dtype_code(x), _lib.ptr(src_row), rows, k, _lib.ptr(gs), _lib.ptr(packed),
+    _lib.check(_lib.lib().b200moe_quantize_nvfp4(_lib.ptr(x), _dtype_code(x), _lib.ptr(src_row), rows, k, _lib.ptr(gs), 0, _lib.ptr(packed),
                                                  _lib.ptr(sf), 1, _lib.stream_ptr()), "quantize_nvfp4_128x4")
+    return packed, sf, gs
+
+
+def quantize_nvfp4_experts(w: torch.Tensor, swizzle: bool = False):
+    """Stacked expert matrices w [E, R, K] -> (packed u8 [E, R, K/2], sf u8 [E, R, K/16] row-major or [E, pad128(R),
+    pad4(K/16)] in the 128x4 swizzle, global_scale f32 [E]): each expert quantised with its own global scale
+    2688 / amax, exactly as E separate calls of the reference's quantize_nvfp4 would, in three launches."""
+    if w.dim() != 3 or w.shape[2] % BLOCK:
+        raise ValueError(f"expected [E, R, K] with K a multiple of {BLOCK}, got {tuple(w.shape)}")
+    if not w.is_cuda:
+        raise RuntimeError("quantize_nvfp4_experts runs on the GPU; there is no CPU path in this package")
+    w = w.contiguous()
+    e, r, k = w.shape
+    h = _lib.lib()
+    scratch = torch.empty(e, dtype=torch.int32, device=w.device)
+    gs = torch.empty(e, dtype=torch.float32, device=w.device)
+    _lib.check(h.b200moe_global_scale_grouped(_lib.ptr(w), _dtype_code(w), e, r * k, _lib.ptr(scratch), _lib.ptr(gs), _lib.stream_ptr()),
+               "quantize_nvfp4_experts")
+    packed = torch.empty(e, r, k // 2, dtype=torch.uint8, device=w.device)
+    if swizzle and r % 128 == 0 and (k // BLOCK) % 4 == 0:
+        sf = torch.empty(e, r, k // BLOCK, dtype=torch.uint8, device=w.device)   # pad-free: expert e starts at row e*R
+        _lib.check(h.b200moe_quantize_nvfp4(_lib.ptr(w), _dtype_code(w), 0, e * r, k, _lib.ptr(gs), r, _lib.ptr(packed), _lib.ptr(sf), 1,
+                                            _lib.stream_ptr()), "quantize_nvfp4_experts")
+        return packed, sf, gs
+    sf = torch.empty(e, r, k // BLOCK, dtype=torch.uint8, device=w.device)
+    _lib.check(h.b200moe_quantize_nvfp4(_lib.ptr(w), _dtype_code(w), 0, e * r, k, _lib.ptr(gs), r, _lib.ptr(packed), _lib.ptr(sf), 0,
+                                        _lib.stream_ptr()), "quantize_nvfp4_experts")
+    if swizzle:
+        from .layouts import to_128x4
+        sf = to_128x4(sf)
     return packed, sf, gs

@@ -15,14 +15,9 @@ def make_layer(experts, hidden, inter, top_k, seed=0, std=0.02, device="cuda", s
     from sm120fp4_b200.vllm_backend import Weights
 
     w13, w2 = synth.layer_weights_bf16(experts, hidden, inter, seed=seed, std=std)
-    q1, s1, a1, q2, s2, a2 = [], [], [], [], [], []
-    for e in range(experts):
-        q, s, gs = pkg.quantize_nvfp4(w13[e].to(device))
-        q1.append(q), s1.append(s), a1.append(1.0 / gs)
-        q, s, gs = pkg.quantize_nvfp4(w2[e].to(device))
-        q2.append(q), s2.append(s), a2.append(1.0 / gs)
-    q1, s1, a1 = torch.stack(q1), torch.stack(s1), torch.cat(a1)
-    q2, s2, a2 = torch.stack(q2), torch.stack(s2), torch.cat(a2)
+    q1, s1, g1 = pkg.quantize_nvfp4_experts(w13.to(device))
+    q2, s2, g2 = pkg.quantize_nvfp4_experts(w2.to(device))
+    a1, a2 = 1.0 / g1, 1.0 / g2
     if scale_layout == "128x4":
         w = Weights(q1, pkg.to_128x4(s1), a1, q2, pkg.to_128x4(s2), a2, top_k, scale_layout="128x4")
     else:

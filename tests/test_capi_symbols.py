@@ -27,7 +27,7 @@ def test_argument_errors_need_no_gpu():
     import sm120fp4_b200._lib as L
     h = L.lib()
     assert h.b200moe_to_128x4(None, None, 1, 1, 1, None) == L.ERR_ARG
-    assert h.b200moe_quantize_nvfp4(None, 0, None, 1, 16, None, None, None, 0, None) == L.ERR_ARG
+    assert h.b200moe_quantize_nvfp4(None, 0, None, 1, 16, None, 0, None, None, 0, None) == L.ERR_ARG
     assert h.b200moe_route(None, 5, 8, 0, None, None, None, None, 0, None) == L.ERR_ARG
     assert h.b200moe_route_workspace_bytes(100, 8) > 0
     assert h.b200moe_layer_workspace_bytes(None) == L.ERR_ARG
