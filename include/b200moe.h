@@ -62,6 +62,14 @@ void b200moe_layer_destroy(b200moe_layer* layer);
 long long b200moe_layer_workspace_bytes(const b200moe_layer* layer);
 int b200moe_layer_workspace_init(const b200moe_layer* layer, void* workspace, long long workspace_bytes, void* stream);
 int b200moe_layer_sm_count(const b200moe_layer* layer);
+/* tcgen05 decode path: kernel-native copies built once per layer into caller-owned device memory (the counterpart of the
+ * load-time re-layout in sm120fp4/vllm_backend.py:193-206). After prepack, b200moe_decode_forward runs the tcgen05 kernel;
+ * b200moe_layer_set_decode_impl picks 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel; b200moe_layer_set_act_scale
+ * sets the global scale of the first NVFP4 term of the FC1->FC2 activations (default 8). */
+long long b200moe_layer_prepack_bytes(const b200moe_layer* layer);
+int b200moe_layer_prepack(b200moe_layer* layer, void* buffer, long long buffer_bytes, void* stream);
+int b200moe_layer_set_decode_impl(b200moe_layer* layer, int impl);
+int b200moe_layer_set_act_scale(b200moe_layer* layer, float first_term_global_scale);
 
 /* forward: x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]; one launch
  * (routing + FC1 + SiLU*mul + FC2 + weighted combine). Replaces Weights._slice, sm120fp4/vllm_backend.py:174-190. */

@@ -28,6 +28,10 @@ SIGNATURES = {
     "b200moe_layer_workspace_bytes": (_LL, [_P]),
     "b200moe_layer_workspace_init": (_I, [_P, _P, _LL, _P]),
     "b200moe_layer_sm_count": (_I, [_P]),
+    "b200moe_layer_prepack_bytes": (_LL, [_P]),
+    "b200moe_layer_prepack": (_I, [_P, _P, _LL, _P]),
+    "b200moe_layer_set_decode_impl": (_I, [_P, _I]),
+    "b200moe_layer_set_act_scale": (_I, [_P, C.c_float]),
     "b200moe_decode_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc1": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc2": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),

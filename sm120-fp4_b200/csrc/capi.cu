@@ -22,6 +22,14 @@ static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 }
 
 // u8 matrix [rows, row_bytes] -> tensor map with a 128-byte x box_rows box, 128B shared-memory swizzle, zero OOB fill.
+__global__ void k_alpha_ref(const float* __restrict__ alpha, int E, float* __restrict__ out) {
+  float m = 0.f;
+  for (int e = 0; e < E; ++e) m = fmaxf(m, fabsf(alpha[e]));
+  m = fmaxf(m, 1e-30f);
+  out[0] = m;
+  out[1] = 1.0f / m;
+}
+
 static int make_codes_map(CUtensorMap* map, const void* base, long long rows, long long row_bytes, int box_rows) {
   auto enc = tensor_map_encoder();
   if (!enc) return B200MOE_ERR_DEVICE;
@@ -49,7 +57,16 @@ struct b200moe_layer {
   long long s1_stride, s2_stride;
   // workspace layout (byte offsets)
   long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, off_debug, ws_bytes;
+  long long off_xq, off_xsf, off_xscale, off_aq, off_asf;   // operands of the tcgen05 decode kernel
   int umax_cap;
+  // tcgen05 decode path: composed FC1 scale tiles + alpha2 reference in a caller-owned buffer (b200moe_layer_prepack)
+  const uint8_t* s1t;
+  const float* alpha2_ref;
+  long long prepack_bytes;
+  int decode_impl;      // 0 auto (tcgen05 when prepacked), 1 legacy mma.sync kernel, 2 tcgen05 kernel
+  float act_g1;
+  const void* maps_ws;  // workspace the cached operand tensor maps below were encoded for
+  CUtensorMap tmx[3], tma[3];
 };
 
 static inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
@@ -110,7 +127,14 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   L->off_tables = o, o = align_up(o + (long long)(2 * L->umax_cap + 1 + 16 * top_k) * 4, 256);
   L->off_actbf16 = o, o = align_up(o + (long long)16 * top_k * I * 2, 256);
   L->off_debug = o, o = align_up(o + (long long)V * 8 * 8, 256);
+  L->off_xq = o, o = align_up(o + 64LL * (H / 2), 256);
+  L->off_xsf = o, o = align_up(o + (long long)L->KT1 * 512, 256);
+  L->off_xscale = o, o += 256;
+  L->off_aq = o, o = align_up(o + (long long)L->umax_cap * 64 * (I / 2), 256);
+  L->off_asf = o, o = align_up(o + (long long)L->umax_cap * L->KT2 * 512, 256);
   L->ws_bytes = o;
+  L->prepack_bytes = align_up((long long)E * L->CB1 * L->KT1 * 512, 256) + 256;
+  L->act_g1 = 8.0f;
   *out = L;
   return B200MOE_OK;
 }
@@ -126,6 +150,89 @@ extern "C" int b200moe_layer_workspace_init(const b200moe_layer* L, void* ws, lo
   if (ws_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
   B200_CUDA_TRY(cudaMemsetAsync(ws, 0, (size_t)L->ws_bytes, (cudaStream_t)stream));
   return B200MOE_OK;
+}
+
+// ---- tcgen05 decode path -------------------------------------------------------------------------------------------
+extern "C" long long b200moe_layer_prepack_bytes(const b200moe_layer* L) { return L ? L->prepack_bytes : B200MOE_ERR_ARG; }
+
+// Build the kernel-native copies the tcgen05 decode kernel reads - FC1 scale tiles composed per (expert, 64-column block)
+// and the alpha2 normaliser - into `buffer` (caller-owned device memory of b200moe_layer_prepack_bytes bytes that must
+// outlive the handle). Once per layer, like the layout rotation the reference does at load (vllm_backend.py:193-206).
+extern "C" int b200moe_layer_prepack(b200moe_layer* L, void* buffer, long long buffer_bytes, void* stream) {
+  if (!L || !buffer) return B200MOE_ERR_ARG;
+  if (buffer_bytes < L->prepack_bytes) return B200MOE_ERR_WORKSPACE;
+  if ((uintptr_t)buffer & 255) return B200MOE_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = b200_compose_fc1_scales_launch(L->s1, buffer, L->E, L->I, L->KT1, L->s1_stride, st);
+  if (rc != B200MOE_OK) return rc;
+  float* ref = (float*)((uint8_t*)buffer + align_up((long long)L->E * L->CB1 * L->KT1 * 512, 256));
+  k_alpha_ref<<<1, 1, 0, st>>>(L->alpha2, L->E, ref);
+  B200_LAUNCH_CHECK();
+  L->s1t = (const uint8_t*)buffer;
+  L->alpha2_ref = ref;
+  return B200MOE_OK;
+}
+
+// 0: tcgen05 kernel when the layer is prepacked, else the mma.sync kernel; 1: mma.sync kernel; 2: tcgen05 kernel.
+extern "C" int b200moe_layer_set_decode_impl(b200moe_layer* L, int impl) {
+  if (!L || impl < 0 || impl > 2) return B200MOE_ERR_ARG;
+  if (impl == 2 && !L->s1t) return B200MOE_ERR_ARG;
+  L->decode_impl = impl;
+  return B200MOE_OK;
+}
+
+// Global scale of the first NVFP4 term of the FC1->FC2 activations (default 8; 1 / the checkpoint's w2 input scale is the
+// calibrated choice). Block maxima up to 2688 / scale are represented without saturation.
+extern "C" int b200moe_layer_set_act_scale(b200moe_layer* L, float g1) {
+  if (!L || !(g1 > 0.f)) return B200MOE_ERR_ARG;
+  L->act_g1 = g1;
+  return B200MOE_OK;
+}
+
+static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* ws, void* stream) {
+  uint8_t* w = (uint8_t*)ws;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nbv = M <= 4 ? 0 : M <= 8 ? 1 : 2;
+  const int N = 16 << nbv;
+  if (L->maps_ws != ws) {   // operand tensor maps point into the workspace: encode once per workspace
+    for (int i = 0; i < 3; ++i) {
+      const int n = 16 << i;
+      int rc = make_codes_map(&L->tmx[i], w + L->off_xq, n, L->H / 2, n);
+      if (rc == B200MOE_OK) rc = make_codes_map(&L->tma[i], w + L->off_aq, (long long)L->umax_cap * n, L->I / 2, n);
+      if (rc != B200MOE_OK) return rc;
+    }
+    L->maps_ws = ws;
+  }
+  int rc = b200_expand_x_launch(x, M, L->H, N, w + L->off_xq, w + L->off_xsf, (float*)(w + L->off_xscale), st);
+  if (rc != B200MOE_OK) return rc;
+  DecodeTcParams p;
+  memset(&p, 0, sizeof(p));
+  p.tm1 = L->tm1, p.tm2 = L->tm2, p.tmx = L->tmx[nbv], p.tma = L->tma[nbv];
+  p.s1t = L->s1t, p.s2 = (const uint8_t*)L->s2, p.alpha1 = L->alpha1, p.alpha2 = L->alpha2, p.alpha2_ref = L->alpha2_ref;
+  p.xsf = w + L->off_xsf, p.xscale = (const float*)(w + L->off_xscale);
+  p.aq = w + L->off_aq, p.asf = w + L->off_asf;
+  p.ids = ids, p.wts = wts, p.out = (__nv_bfloat16*)out;
+  p.scratch = (float*)(w + L->off_scratch);
+  p.cnt1 = (unsigned*)(w + L->off_cnt1), p.cnt2 = (unsigned*)(w + L->off_cnt2);
+  p.status = (int*)(w + L->off_status);
+  p.gridbar = (unsigned*)(w + L->off_status + 64);
+  p.experts_out = (int*)(w + L->off_tables);
+  p.offsets_out = p.experts_out + L->umax_cap;
+  p.pairs_out = p.offsets_out + L->umax_cap + 1;
+  p.s2_expert_stride = L->s2_stride;
+  p.act_g1 = L->act_g1;
+  p.M = M, p.E = L->E, p.H = L->H, p.I = L->I, p.top_k = L->top_k;
+  p.Umax = L->E < M * L->top_k ? L->E : M * L->top_k;
+  p.KB1 = L->KB1, p.KB2 = L->KB2, p.CB1 = L->CB1, p.NB2 = L->NB2, p.KT1 = L->KT1, p.KT2 = L->KT2;
+  const int xb = L->KB1 * N * 128 + L->KT1 * 512, slab = N * 128 + 2048;
+  int NS = 8;
+  for (; NS >= 2; --NS) {
+    const int region = (int)align_up(xb > NS * slab ? xb : NS * slab, 1024);
+    if (b200_decode_tc_smem_bytes(NS, region) <= 227 * 1024) { p.region_bytes = region; break; }
+  }
+  if (NS < 2) return B200MOE_ERR_SHAPE;
+  p.NS = NS;
+  return b200_decode_tc_launch(p, L->sms, b200_decode_tc_smem_bytes(NS, p.region_bytes), st);
 }
 
 static int decode_common(const b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* act_bf16,
@@ -183,6 +290,14 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
 // Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
 extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                                       int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
+  if (L && L->s1t && L->decode_impl != 1 && 2 * L->sms <= 512) {
+    if (!x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0) return B200MOE_ERR_ARG;
+    if (M > 16) return B200MOE_ERR_LIMIT;
+    if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
+    if (((uintptr_t)workspace & 255) || ((uintptr_t)x_bf16 & 15)) return B200MOE_ERR_ARG;
+    if (M == 0) return B200MOE_OK;
+    return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, stream);
+  }
   return decode_common(L, x_bf16, topk_ids, topk_weights, M, out_bf16, nullptr, 3, 1, workspace, workspace_bytes, stream);
 }
 

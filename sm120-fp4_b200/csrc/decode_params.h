@@ -40,8 +40,45 @@ struct DecodeParams {
   int KT1, KT2;             // 4-column scale tiles along K
 };
 
+// Parameter block of the tcgen05 decode kernel (k_moe_decode_tc).
+struct DecodeTcParams {
+  CUtensorMap tm1;   // FC1 codes [E*2I, H/2], box 128 B x 64 rows
+  CUtensorMap tm2;   // FC2 codes [E*H, I/2], box 128 B x 128 rows
+  CUtensorMap tmx;   // expanded x operand [N, H/2], box 128 B x N rows
+  CUtensorMap tma;   // expanded activation operand [Umax*N, I/2], box 128 B x N rows
+  const uint8_t* s1t;        // FC1 scale tiles composed per (expert, 64-column block): [E][I/64][KT1][512]
+  const uint8_t* s2;         // FC2 scales, 128x4 swizzle per expert
+  const float* alpha1;
+  const float* alpha2;
+  const float* alpha2_ref;   // [0] = max over experts of alpha2, [1] = its reciprocal
+  const uint8_t* xsf;        // scale tiles of the expanded x operand [KT1][512]
+  const float* xscale;       // 1 / g_t per column of the x operand [N]
+  uint8_t* aq;               // expanded activations (FC2 operand) [Umax][N][I/2]
+  uint8_t* asf;              // their scale tiles [Umax][KT2][512]
+  const int* ids;
+  const float* wts;
+  __nv_bfloat16* out;
+  float* scratch;
+  unsigned* cnt1;
+  unsigned* cnt2;
+  unsigned* gridbar;
+  int* status;
+  int* experts_out;
+  int* offsets_out;
+  int* pairs_out;
+  long long s2_expert_stride;
+  float act_g1;              // global scale of the first activation term
+  int M, E, H, I, top_k, Umax;
+  int NS, region_bytes;
+  int KB1, KB2, CB1, NB2, KT1, KT2;
+};
+
 }  // namespace b200
 
+int b200_decode_tc_smem_bytes(int NS, int region_bytes);
+int b200_expand_x_launch(const void* x, int M, int H, int N, void* xq, void* xsf, float* colscale, cudaStream_t st);
+int b200_compose_fc1_scales_launch(const void* s1, void* s1t, int E, int I, int KT, long long s1_stride, cudaStream_t st);
+int b200_decode_tc_launch(const b200::DecodeTcParams& p, int grid, int smem_bytes, cudaStream_t st);
 int b200_decode_smem_bytes(int NS, int region_bytes);
 int b200_decode_launch(const b200::DecodeParams& p, int grid, int smem_bytes, cudaStream_t st);
 int b200_act_to_frag_launch(const void* act, const int* ids, const int* experts, int Umax, int M, int top_k, int I, int KB2,

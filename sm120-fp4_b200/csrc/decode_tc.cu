@@ -1,0 +1,628 @@
+// The decode-regime MoE layer on the 5th-generation tensor cores: weights are consumed as FP4 straight from shared
+// memory by tcgen05.mma kind::mxf4nvf4 with their E4M3 block scales in TMEM - no CUDA-core dequantisation at all - so the
+// SMs only move bytes and the kernel is bound by HBM. It keeps the contract of the reference's decode kernels
+// (sm120fp4/kernels/{fc1_w4a16,fc1_mma,fc2_w4a16,fc2_mma_pf}.py: W4A16, fp32 accumulation, alpha in fp32, SiLU*mul,
+// weighted combine, bit-identical from call to call).
+//
+// W4A16 on an FP4 x FP4 instruction: a 16-bit activation vector is written as a short sum of NVFP4 vectors,
+//     x = q1*s1/g1 + q2*s2/g2 + q3*s3/g3 + q4*s4/g4 + r,   g_t = g1 * 6^(t-1),   |r| <= blockmax(x) * 6^-4 (about 2^-10.3),
+// each term the NVFP4 quantisation (E2M1 codes, E4M3 scale per 16 values) of the residual left by the terms before it.
+// The terms of a token are adjacent columns of the B operand; the epilogue adds the four accumulator columns with their
+// 1/g_t. Four terms carry more mantissa than bf16 for the values that decide a dot product and keep the layer's error
+// against the fp32 oracle below the bf16 output rounding.
+//
+// Structure: one CTA per SM = one stream-K worker. Warp 0: TMA producer (weight tiles into a shared-memory ring, FC2
+// tiles prefetched across the FC1->FC2 grid barrier). Warp 1: MMA issuer (scale tiles smem->TMEM with tcgen05.cp, four
+// K=64 MMAs per 256-code tile, tcgen05.commit frees the ring stage). Warps 2-5: epilogue (tcgen05.ld of a double-buffered
+// TMEM accumulator, term sums, SiLU*mul, re-expansion of the activations for FC2, fixed-order reduction of split units).
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include "decode_params.h"
+
+namespace b200 {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
+constexpr int kTerms = 4;
+constexpr int kTcMaxE = 256, kTcMaxP = 256, kTcMaxWorkers = 256;
+
+struct TcTables {
+  int ids[kTcMaxP];
+  float wts[kTcMaxP];
+  int cnt[kTcMaxE], base[kTcMaxE], uidx[kTcMaxE], experts[kTcMaxE];
+  int sb1[kTcMaxWorkers + 1], sb2[kTcMaxWorkers + 1];
+  float colscale[64];          // 1 / g_t of every B column of the FC1 operand (token-major, four terms per token)
+  int U;
+  unsigned gen0;
+  volatile int abort_flag;
+  int last_flag;
+  uint32_t tmem_base;
+  uint64_t full[8], empty[8];
+  uint64_t acc_full[2], acc_empty[2];
+  uint64_t xb_full;
+};
+
+__device__ __forceinline__ int tc_worker_of(int f, int T, int V) { return (int)(((unsigned)(f + 1) * (unsigned)V - 1u) / (unsigned)T); }
+__device__ __forceinline__ float tc_silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
+__device__ __forceinline__ uint32_t tc_e2m1(float v) {
+  const float m = fabsf(v);
+  const uint32_t c = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
+  return c | ((__float_as_uint(v) >> 31) << 3);
+}
+__device__ __forceinline__ float tc_e2m1_value(uint32_t code) {
+  const float mag = (code & 7u) < 2u ? 0.5f * (float)(code & 7u) : (float)(2u + ((code & 7u) & 1u)) * 0.5f * (float)(1u << (((code & 7u) >> 1) - 1u));
+  return (code & 8u) ? -mag : mag;
+}
+__device__ __forceinline__ uint8_t tc_e4m3(float v) {   // RNE, saturating at 448, subnormals kept
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
+  return (uint8_t)(r & 0xff);
+}
+__device__ __forceinline__ float tc_e4m3_value(uint8_t b) {
+  const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+  return e == 0 ? (float)m * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
+}
+
+// One 16-value block -> kTerms NVFP4 terms (residual expansion). g1: global scale of the first term; term t uses g1*6^t.
+// codes[t] = 8 packed bytes (element 2j in the low nibble), sf[t] = E4M3 scale byte.
+__device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (&codes)[kTerms], uint8_t (&sf)[kTerms]) {
+  float g = g1;
+#pragma unroll
+  for (int t = 0; t < kTerms; ++t) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
+    const uint8_t sb = tc_e4m3(fminf(amax * (1.0f / 6.0f) * g, 448.0f));
+    const float sv = tc_e4m3_value(sb);
+    const float scale = sv > 0.f ? g / sv : 0.f, back = sv > 0.f ? sv / g : 0.f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t c = tc_e2m1(r[i] * scale);
+      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
+      r[i] -= tc_e2m1_value(c) * back;
+    }
+    codes[t] = make_uint2(lo, hi);
+    sf[t] = sb;
+    g *= 6.0f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ x -> B operand
+// One block per token slot (N/4 slots): token amax, then every 16-value block expanded into four NVFP4 terms.
+// xq u8 [N, H/2] (row = token*4 + term), xsf: 128x4-swizzled over [128, H/16] (rows >= N zero), colscale f32 [N] = 1/g_t.
+__global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ xq,
+                                                  uint8_t* __restrict__ xsf, float* __restrict__ colscale) {
+  const int tok = blockIdx.x, tid = threadIdx.x;
+  const int nkt = (H / 16 + 3) / 4;
+  __shared__ float wm[8];
+  __shared__ float s_g1;
+  float m = 0.f;
+  if (tok < M)
+    for (int i = tid; i < H; i += 256) m = fmaxf(m, fabsf(__bfloat162float(x[(long long)tok * H + i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & 31) == 0) wm[tid >> 5] = m;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, wm[w]);
+    const float g1 = 2688.0f / fmaxf(m, 1e-30f);
+    s_g1 = g1;
+    float g = g1;
+    for (int t = 0; t < kTerms; ++t) { colscale[tok * kTerms + t] = tok < M ? 1.0f / g : 0.f; g *= 6.0f; }
+  }
+  __syncthreads();
+  const float g1 = s_g1;
+  for (int b = tid; b < H / 16; b += 256) {
+    uint2 codes[kTerms];
+    uint8_t sf[kTerms];
+    if (tok < M) {
+      float r[16];
+      const uint4 v0 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16 + 8);
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { r[2 * i] = __uint_as_float(w[i] << 16); r[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+      expand_block16(r, g1, codes, sf);
+    } else {
+#pragma unroll
+      for (int t = 0; t < kTerms; ++t) { codes[t] = make_uint2(0u, 0u); sf[t] = 0; }
+    }
+#pragma unroll
+    for (int t = 0; t < kTerms; ++t) {
+      const int n = tok * kTerms + t;
+      *reinterpret_cast<uint2*>(xq + (long long)n * (H / 2) + b * 8) = codes[t];
+      xsf[(long long)(b >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (b & 3)] = sf[t];
+    }
+  }
+  (void)nkt;
+}
+
+// ------------------------------------------------------------------------------------------------ FC1 scale tiles
+// FC1 multiplies 64 up rows and the 64 matching gate rows in one 128-row MMA; its scale tile must hold those 128 rows.
+// s1 (128x4 swizzle over the [2I, H/16] scales of one expert) -> s1t [E][I/64][KT][512]: rows 0..63 = up rows 64cb..,
+// rows 64..127 = gate rows I+64cb.., in the same 128x4 in-tile order. Done once when the layer is created.
+__global__ void __launch_bounds__(256) k_compose_fc1_scales(const uint8_t* __restrict__ s1, uint8_t* __restrict__ s1t, int E, int I,
+                                                            int KT, long long s1_expert_stride) {
+  const int CB = I / 64;
+  const long long total = (long long)E * CB * KT * 128;   // one thread per (tile, row): 4 bytes
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i % 128);
+    const int kt = (int)((i / 128) % KT);
+    const int cb = (int)((i / (128LL * KT)) % CB);
+    const int e = (int)(i / (128LL * KT * CB));
+    const int src_row = r < 64 ? 64 * cb + r : I + 64 * cb + (r - 64);
+    const uint8_t* src = s1 + e * s1_expert_stride + ((long long)(src_row >> 7) * KT + kt) * 512 + (src_row & 31) * 16 + ((src_row & 127) >> 5) * 4;
+    uint8_t* dst = s1t + (((long long)(e * CB + cb) * KT + kt) * 512) + (r & 31) * 16 + (r >> 5) * 4;
+    *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ the layer kernel
+template <int NB>   // N = 16 * NB columns of the B operand (tokens x four terms): NB = 1 (M<=4), 2 (M<=8), 4 (M<=16)
+__global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_constant__ DecodeTcParams P) {
+  constexpr int N = 16 * NB;
+  constexpr int kSlab = N * 128 + 2048;     // FC2 activation slab of one tile: N rows x 128 B codes + 4 scale tiles
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int NS = P.NS;
+  uint8_t* ring = smem;                                   // NS x [16 KB codes | 2 KB scales]
+  uint8_t* region = smem + NS * kTcStage;                 // FC1: resident x operand [KB1][N x 128 B] then its scale tiles;
+                                                          // FC2: NS activation slabs
+  TcTables& T = *reinterpret_cast<TcTables*>(region + P.region_bytes);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int npairs = P.M * P.top_k;
+  const int V = gridDim.x;
+  const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
+
+  // ---------------------------------------------------------------- prologue
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&T.acc_full[b], 1); mbar_init(&T.acc_empty[b], 4); }
+    mbar_init(&T.xb_full, 1);
+    T.abort_flag = 0;
+    T.last_flag = 0;
+    T.gen0 = ld_acquire_gpu(P.gridbar + 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
+    tmem_alloc(&T.tmem_base, 512);
+    tmem_relinquish();
+  }
+  for (int i = tid; i < kTcMaxE; i += kTcThreads) T.cnt[i] = 0;
+  __syncthreads();
+  for (int p = tid; p < npairs; p += kTcThreads) {
+    int e = P.ids[p];
+    if (e < 0 || e >= P.E) { *P.status = 4; e = 0; }
+    T.ids[p] = e;
+    T.wts[p] = P.wts[p];
+    atomicAdd(&T.cnt[e], 1);
+  }
+  for (int i = tid; i < N; i += kTcThreads) T.colscale[i] = P.xscale[i];
+  __syncthreads();
+  if (warp == 0) {
+    int c[8], f[8], sc = 0, sf = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { c[i] = T.cnt[lane * 8 + i]; f[i] = c[i] > 0; sc += c[i]; sf += f[i]; }
+    int ic = sc, iff = sf;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, iff, o);
+      if (lane >= o) { ic += a; iff += b; }
+    }
+    int rc = ic - sc, rf = iff - sf;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { rc += c[i]; rf += f[i]; T.base[lane * 8 + i] = rc; T.uidx[lane * 8 + i] = rf; }
+    if (lane == 31) T.U = iff;
+  }
+  __syncthreads();
+  const int U = T.U;
+  const int T1 = U * CB1 * KB1, T2 = NB2 * U * KB2;
+  for (int i = tid; i < kTcMaxE; i += kTcThreads)
+    if (T.cnt[i] > 0) T.experts[T.uidx[i] - 1] = i;
+  for (int v = tid; v <= V; v += kTcThreads) {
+    T.sb1[v] = (int)(((unsigned)v * (unsigned)T1) / (unsigned)V);
+    T.sb2[v] = (int)(((unsigned)v * (unsigned)T2) / (unsigned)V);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (blockIdx.x == 0 && P.experts_out) {
+    for (int e = tid; e < P.E; e += kTcThreads)
+      if (T.cnt[e] > 0) { P.experts_out[T.uidx[e] - 1] = e; P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e]; }
+    for (int u = U + tid; u < P.Umax; u += kTcThreads) { P.experts_out[u] = -1; P.offsets_out[u + 1] = npairs; }
+    if (tid == 0) P.offsets_out[U] = npairs;
+    for (int p = tid; p < npairs; p += kTcThreads) {
+      const int e = T.ids[p];
+      int r = 0;
+      for (int q = 0; q < p; ++q) r += T.ids[q] == e;
+      P.pairs_out[T.base[e] - T.cnt[e] + r] = p;
+    }
+  }
+  const int v = blockIdx.x;
+  const int n1 = T.sb1[v + 1] - T.sb1[v], n2 = T.sb2[v + 1] - T.sb2[v];
+  const uint32_t tmem = T.tmem_base;
+  const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // 2 x 64 | NS x 16 | up to 176 + (FC2: NS x 16)
+  uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
+
+  if (warp == 0) {
+    // ============================================================== TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&P.tm1);
+      prefetch_tensormap(&P.tm2);
+      const uint64_t pol = policy_evict_first();
+      // the resident B operand of FC1: x expanded into NVFP4 terms, one box per K box, and its scale tiles
+      if (n1 > 0) {
+        mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
+        for (int kb = 0; kb < KB1; ++kb) tma_load_2d(region + kb * (N * 128), &P.tmx, 128 * kb, 0, &T.xb_full);
+        bulk_load(xb_sf, P.xsf, P.KT1 * 512, &T.xb_full);
+      }
+      const unsigned gen0 = T.gen0;
+      bool passed = false;
+      int pend_slot[8], pend_u[8], pend_kb[8], npend = 0;
+      auto load_slab = [&](int slot, int u, int kb) {
+        uint8_t* dst = region + slot * kSlab;
+        tma_load_2d(dst, &P.tma, 128 * kb, u * N, &T.full[slot]);
+        const int nkt = min(4, P.KT2 - 4 * kb);
+        bulk_load(dst + N * 128, P.asf + ((long long)u * P.KT2 + 4 * kb) * 512, nkt * 512, &T.full[slot]);
+      };
+      auto wait_grid = [&]() {
+        if (passed) return;
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 24); ++it) {
+          if (ld_acquire_gpu(P.gridbar + 1) != gen0) { ok = true; break; }
+          if (T.abort_flag) break;
+          __nanosleep(64);
+        }
+        if (!ok) { T.abort_flag = 1; *P.status = 3; }
+        fence_proxy_async();
+        for (int i = 0; i < npend; ++i) load_slab(pend_slot[i], pend_u[i], pend_kb[i]);
+        npend = 0;
+        passed = true;
+      };
+      int si = 0, j = 0;
+      uint32_t ph = 0;
+      auto claim = [&](bool prev_pending) -> int {
+        if (j >= NS) {
+          if (prev_pending) wait_grid();
+          if (!mbar_wait(&T.empty[si], ph ^ 1u, &T.abort_flag)) *P.status = 2;
+        }
+        return si;
+      };
+      auto advance = [&]() { ++j; if (++si == NS) { si = 0; ph ^= 1u; } };
+      if (n1 > 0) {
+        const int f0 = T.sb1[v];
+        int kb = f0 % KB1, q = f0 / KB1, cb = q % CB1, u = q / CB1;
+        for (int i = 0; i < n1; ++i) {
+          const int slot = claim(false);
+          uint8_t* st = ring + slot * kTcStage;
+          const int e = T.experts[u];
+          const int nkt = min(4, P.KT1 - 4 * kb);
+          mbar_expect_tx(&T.full[slot], 16384 + nkt * 512);
+          tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + 64 * cb, &T.full[slot], pol);
+          tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + P.I + 64 * cb, &T.full[slot], pol);
+          bulk_load_hint(st + 16384, P.s1t + (((long long)e * CB1 + cb) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+          advance();
+          if (++kb == KB1) { kb = 0; if (++cb == CB1) { cb = 0; ++u; } }
+        }
+      }
+      if (n2 > 0) {
+        const int f0 = T.sb2[v];
+        int kb = f0 % KB2, q = f0 / KB2, u = q % U, nb = q / U;
+        for (int i = 0; i < n2; ++i) {
+          const int slot = claim(!passed && (j - NS) >= n1);
+          uint8_t* st = ring + slot * kTcStage;
+          const int e = T.experts[u];
+          const int nkt = min(4, P.KT2 - 4 * kb);
+          mbar_expect_tx(&T.full[slot], 16384 + nkt * 512 + N * 128 + nkt * 512);
+          tma_load_2d_hint(st, &P.tm2, 128 * kb, e * P.H + 128 * nb, &T.full[slot], pol);
+          bulk_load_hint(st + 16384, P.s2 + (long long)e * P.s2_expert_stride + ((long long)nb * P.KT2 + 4 * kb) * 512, nkt * 512,
+                         &T.full[slot], pol);
+          if (passed) load_slab(slot, u, kb);
+          else { pend_slot[npend] = slot; pend_u[npend] = u; pend_kb[npend] = kb; ++npend; }
+          advance();
+          if (++kb == KB2) { kb = 0; if (++u == U) { u = 0; ++nb; } }
+        }
+      }
+      if (npend > 0) wait_grid();
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ============================================================== MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = idesc_mxf4nvf4(128, N);
+      int si = 0;
+      uint32_t ph = 0;
+      int ab = 0;              // accumulator buffer of the current piece
+      uint32_t aph[2] = {0, 0};
+      int pieces = 0;
+      auto next_acc = [&]() {   // wait until the epilogue has drained the buffer we are about to overwrite
+        if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+        tc_fence_after();
+      };
+      auto acc_done = [&]() {
+        umma_commit(&T.acc_full[ab]);
+        aph[ab] ^= 1u;
+        ab ^= 1;
+        ++pieces;
+      };
+      if (n1 > 0) {
+        if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
+        tc_fence_after();
+        for (int kt = 0; kt < P.KT1; ++kt) tmem_cp_sf(tm_sfb + 4 * kt, smem_desc_sf_tile(smem_u32(xb_sf + kt * 512)));
+        int f = T.sb1[v];
+        const int fe = T.sb1[v + 1];
+        while (f < fe) {
+          const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
+          next_acc();
+          for (int kb = k0; kb < k1; ++kb) {
+            if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+            tc_fence_after();
+            const uint32_t st = smem_u32(ring + si * kTcStage);
+            const int nkt = min(4, P.KT1 - 4 * kb);
+            for (int jj = 0; jj < nkt; ++jj) {
+              tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
+              umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj,
+                            smem_desc_sw128_kmajor(smem_u32(region + kb * (N * 128))) + 2 * jj, idesc, tm_sfa + 16 * si + 4 * jj,
+                            tm_sfb + 4 * (4 * kb + jj), (kb > k0 || jj > 0) ? 1u : 0u);
+            }
+            umma_commit(&T.empty[si]);
+            if (++si == NS) { si = 0; ph ^= 1u; }
+          }
+          acc_done();
+          f += k1 - k0;
+        }
+      }
+      if (n2 > 0) {
+        const int per_nb = U * KB2;
+        int f = T.sb2[v];
+        const int fe = T.sb2[v + 1];
+        while (f < fe) {
+          const int nb = f / per_nb;
+          const int pe = min(fe, (nb + 1) * per_nb);
+          next_acc();
+          bool first = true;
+          int kb = f % KB2;
+          for (; f < pe; ++f) {
+            if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+            tc_fence_after();
+            const uint32_t st = smem_u32(ring + si * kTcStage), sl = smem_u32(region + si * kSlab);
+            const int nkt = min(4, P.KT2 - 4 * kb);
+            for (int jj = 0; jj < nkt; ++jj) {
+              tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
+              tmem_cp_sf(tm_sfb + 16 * si + 4 * jj, smem_desc_sf_tile(sl + N * 128 + jj * 512));
+              umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(sl) + 2 * jj, idesc,
+                            tm_sfa + 16 * si + 4 * jj, tm_sfb + 16 * si + 4 * jj, first ? 0u : 1u);
+              first = false;
+            }
+            umma_commit(&T.empty[si]);
+            if (++si == NS) { si = 0; ph ^= 1u; }
+            if (++kb == KB2) kb = 0;
+          }
+          acc_done();
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ============================================================== epilogue: 4 warps, thread = accumulator row
+    const int et = tid - 64;                       // 0..127
+    const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int row = quad * 32 + lane;              // accumulator row (MMA M index)
+    __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
+    int ab = 0;
+    uint32_t aph[2] = {0, 0};
+    auto load_terms = [&](float (&val)[16], const float* cs, bool per_column) {   // sum the four term columns of every token
+      if (!mbar_wait(&T.acc_full[ab], aph[ab], &T.abort_flag)) *P.status = 7;
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < N; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(tm_acc + 64 * ab + ((uint32_t)(quad * 32) << 16) + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int tk = 0; tk < 4; ++tk)
+        {
+          const int o = per_column ? c0 + 4 * tk : 0;
+          val[c0 / 4 + tk] = __uint_as_float(r[4 * tk]) * cs[o] + __uint_as_float(r[4 * tk + 1]) * cs[o + 1] +
+                             __uint_as_float(r[4 * tk + 2]) * cs[o + 2] + __uint_as_float(r[4 * tk + 3]) * cs[o + 3];
+        }
+      }
+#pragma unroll
+      for (int i = N / 4; i < 16; ++i) val[i] = 0.f;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&T.acc_empty[ab]);
+      aph[ab] ^= 1u;
+      ab ^= 1;
+    };
+    auto reduce = [&](const int* sb, int first, int vlo, int vhi, float (&val)[16]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) val[i] = 0.f;
+      for (int p0 = vlo; p0 <= vhi; p0 += 4) {
+        float4 tmp[4][4];
+        bool live[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int pv = p0 + b;
+          live[b] = pv <= vhi && sb[pv + 1] > sb[pv];
+          const int pslot = (live[b] && sb[pv] < first) ? 1 : 0;
+          const float* src = P.scratch + ((long long)((live[b] ? pv : vlo) * 2 + pslot) * 128 + et) * 16;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) tmp[b][i] = live[b] ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (live[b]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { val[4 * i] += tmp[b][i].x; val[4 * i + 1] += tmp[b][i].y; val[4 * i + 2] += tmp[b][i].z; val[4 * i + 3] += tmp[b][i].w; }
+          }
+      }
+    };
+    // publish this worker's partial of a split unit and learn whether it arrived last
+    auto publish = [&](const float (&val)[16], int slot_id, unsigned* counter, const int* sb, int vlo, int vhi) -> bool {
+      float* mine = P.scratch + ((long long)(v * 2 + slot_id) * 128 + et) * 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(val[4 * i], val[4 * i + 1], val[4 * i + 2], val[4 * i + 3]);
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        __threadfence();
+        int nlive = 0;
+        for (int pv = vlo; pv <= vhi; ++pv) nlive += sb[pv + 1] > sb[pv];
+        const unsigned old = atomicAdd(counter, 1u);
+        const int last = old + 1u == (unsigned)nlive;
+        if (last) { *counter = 0; __threadfence(); }
+        T.last_flag = last;
+      }
+      named_bar_sync(1, 128);
+      const bool last = T.last_flag != 0;
+      named_bar_sync(1, 128);
+      return last;
+    };
+
+    // ---- FC1 pieces
+    {
+      const int fs = T.sb1[v], fe = T.sb1[v + 1];
+      int f = fs;
+      while (f < fe) {
+        const int q = f / KB1, cb = q % CB1, u = q / CB1;
+        const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
+        const int e = T.experts[u];
+        float val[16];
+        load_terms(val, T.colscale, true);
+        const int piece_first = f;
+        f += k1 - k0;
+        bool finalize = true;
+        if (!(k0 == 0 && k1 == KB1)) {
+          const int vlo = tc_worker_of(q * KB1, T1, V), vhi = tc_worker_of(q * KB1 + KB1 - 1, T1, V);
+          finalize = publish(val, piece_first == fs ? 0 : 1, P.cnt1 + q, T.sb1, vlo, vhi);
+          if (finalize) reduce(T.sb1, q * KB1, vlo, vhi, val);
+        }
+        if (finalize) {
+          // rows 0..63 hold the up columns 64cb.., rows 64..127 the gate columns: exchange through shared memory
+          const float alpha = P.alpha1[e];
+          if (row >= 64) {
+#pragma unroll
+            for (int tk = 0; tk < 16; ++tk) s_ex[row - 64][tk] = val[tk] * alpha;
+          }
+          named_bar_sync(1, 128);
+          if (row < 64) {
+#pragma unroll
+            for (int tk = 0; tk < 16; ++tk) {
+              // routing weight of token tk on this expert (0: not routed), folded with alpha2 relative to the layer's largest
+              float wsum = 0.f;
+              if (tk < P.M)
+                for (int s = 0; s < P.top_k; ++s)
+                  if (T.ids[tk * P.top_k + s] == e) wsum += T.wts[tk * P.top_k + s];
+              const float a = wsum != 0.f ? tc_silu_mul(s_ex[row][tk], val[tk] * alpha) * (wsum * P.alpha2[e] * P.alpha2_ref[1]) : 0.f;
+              val[tk] = a;
+            }
+          }
+          named_bar_sync(1, 128);
+          if (row < 64) {
+#pragma unroll
+            for (int tk = 0; tk < 16; ++tk) s_ex[row][tk] = val[tk];
+          }
+          named_bar_sync(1, 128);
+          // re-expand: thread (token, 16-column block) -> four NVFP4 terms of the FC2 operand
+          if (et < 4 * (N / 4)) {
+            const int tk = et >> 2, blk = et & 3;
+            float r[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = s_ex[blk * 16 + i][tk];
+            uint2 codes[kTerms];
+            uint8_t sf[kTerms];
+            expand_block16(r, P.act_g1, codes, sf);
+#pragma unroll
+            for (int t = 0; t < kTerms; ++t) {
+              const int n = tk * kTerms + t;
+              *reinterpret_cast<uint2*>(P.aq + ((long long)u * N + n) * (P.I / 2) + (64 * cb + 16 * blk) / 2) = codes[t];
+              P.asf[((long long)u * P.KT2 + cb) * 512 + (n & 31) * 16 + (n >> 5) * 4 + blk] = sf[t];
+            }
+          }
+          named_bar_sync(1, 128);
+        }
+      }
+      // ---- publish FC1's results, arrive at the grid-wide barrier (the producers are the only waiters)
+      fence_proxy_async();
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(P.gridbar, 1u);
+        if (old == (unsigned)(V - 1)) {
+          P.gridbar[0] = 0;
+          __threadfence();
+          atomicAdd(P.gridbar + 1, 1u);
+        }
+      }
+    }
+    // ---- FC2 pieces: one accumulator per (worker, output block), all experts and K boxes summed inside the tensor core
+    {
+      const int fs = T.sb2[v], fe = T.sb2[v + 1];
+      const int per_nb = U * KB2;
+      int f = fs;
+      float cs[kTerms];   // 1 / g_t of the activation terms, times the alpha2 the operand was normalised by
+      {
+        float g = P.act_g1;
+        const float a2ref = P.alpha2_ref[0];
+#pragma unroll
+        for (int t = 0; t < kTerms; ++t) { cs[t] = a2ref / g; g *= 6.0f; }
+      }
+      while (f < fe) {
+        const int nb = f / per_nb;
+        const int pe = min(fe, (nb + 1) * per_nb);
+        float val[16];
+        load_terms(val, cs, false);
+        const int vlo = tc_worker_of(nb * per_nb, T2, V), vhi = tc_worker_of((nb + 1) * per_nb - 1, T2, V);
+        const bool last = publish(val, f == fs ? 0 : 1, P.cnt2 + nb, T.sb2, vlo, vhi);
+        if (last) {
+          reduce(T.sb2, nb * per_nb, vlo, vhi, val);
+#pragma unroll
+          for (int tk = 0; tk < 16; ++tk)
+            if (tk < P.M) P.out[(long long)tk * P.H + 128 * nb + row] = __float2bfloat16_rn(val[tk]);
+        }
+        f = pe;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (T.abort_flag)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+int b200_decode_tc_smem_bytes(int NS, int region_bytes) { return 1024 + NS * kTcStage + region_bytes + (int)sizeof(TcTables); }
+
+int b200_expand_x_launch(const void* x, int M, int H, int N, void* xq, void* xsf, float* colscale, cudaStream_t st) {
+  k_expand_x<<<N / kTerms, 256, 0, st>>>((const __nv_bfloat16*)x, M, H, (uint8_t*)xq, (uint8_t*)xsf, colscale);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+int b200_compose_fc1_scales_launch(const void* s1, void* s1t, int E, int I, int KT, long long s1_stride, cudaStream_t st) {
+  const long long total = (long long)E * (I / 64) * KT * 128;
+  long long g = (total + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  k_compose_fc1_scales<<<(int)g, 256, 0, st>>>((const uint8_t*)s1, (uint8_t*)s1t, E, I, KT, s1_stride);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+int b200_decode_tc_launch(const DecodeTcParams& p, int grid, int smem_bytes, cudaStream_t st) {
+  void* args[] = {(void*)&p};
+  const void* fn = p.M <= 4 ? (const void*)k_moe_decode_tc<1> : p.M <= 8 ? (const void*)k_moe_decode_tc<2> : (const void*)k_moe_decode_tc<4>;
+  static thread_local int configured[3] = {0, 0, 0};
+  const int which = p.M <= 4 ? 0 : p.M <= 8 ? 1 : 2;
+  if (configured[which] < smem_bytes) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    configured[which] = smem_bytes;
+  }
+  B200_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kTcThreads), args, (size_t)smem_bytes, st));
+  return B200MOE_OK;
+}

@@ -89,6 +89,11 @@ class Weights:
         dev = q1.device
         self.ws_bytes = int(h.b200moe_layer_workspace_bytes(self._h))
         self.workspace = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=dev)
+        # kernel-native copies for the tcgen05 decode kernel (FC1 scale tiles per 64-column block, alpha2 normaliser)
+        self.prepack = torch.empty(int(h.b200moe_layer_prepack_bytes(self._h)), dtype=torch.uint8, device=dev)
+        _lib.check(h.b200moe_layer_prepack(self._h, _lib.ptr(self.prepack), self.prepack.numel(), _lib.stream_ptr()), "prepack")
+        if os.environ.get("B200MOE_DECODE", "") == "mma":
+            self.set_decode_impl("mma")
         umax, pmax = min(e_n, MAXM * top_k), MAXM * top_k
         self.experts = torch.empty(umax, dtype=torch.int32, device=dev)
         self.offsets = torch.empty(umax + 1, dtype=torch.int32, device=dev)
@@ -147,6 +152,14 @@ class Weights:
         _lib.check(_lib.lib().b200moe_layer_route_tables(self._h, _lib.ptr(self.workspace), m, _lib.ptr(ex), _lib.ptr(off), _lib.ptr(pairs),
                                                          _lib.stream_ptr()), "route_tables")
         return ex, off, pairs
+
+    def set_decode_impl(self, impl: str) -> None:
+        """'auto' / 'tcgen05' (FP4 tensor-core kernel) or 'mma' (mma.sync kernel with in-register dequantisation)."""
+        code = {"auto": 0, "mma": 1, "tcgen05": 2}[impl]
+        _lib.check(_lib.lib().b200moe_layer_set_decode_impl(self._h, code), "set_decode_impl")
+
+    def set_act_scale(self, g1: float) -> None:
+        _lib.check(_lib.lib().b200moe_layer_set_act_scale(self._h, float(g1)), "set_act_scale")
 
     def status(self) -> None:
         """Synchronise and raise if a bounded device-side wait ran out or an expert id was out of range."""

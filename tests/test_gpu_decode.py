@@ -50,6 +50,27 @@ def test_small_layers_match_oracle(name, m):
     assert np.array_equal(ex.cpu().numpy(), wex) and np.array_equal(off.cpu().numpy(), woff) and np.array_equal(pairs.cpu().numpy(), wpairs)
 
 
+@pytest.mark.parametrize("name,m", [("tiny", 3), ("mid", 7), ("odd", 16), ("qwen", 16), ("gemma", 5)])
+def test_both_decode_kernels_meet_the_bar(name, m):
+    """The tcgen05 kernel (FP4 tensor cores, activations as a four-term NVFP4 expansion) and the mma.sync kernel
+    (in-register dequantisation) are two implementations of the same contract."""
+    cfg, w, ow = layer(name)
+    x, ids, wts = inputs(cfg, m, 300 + m)
+    want = O.moe_reference(x.float().numpy(), ow, ids.numpy(), wts.numpy())
+    errs = {}
+    try:
+        for impl in ("mma", "tcgen05"):
+            w.set_decode_impl(impl)
+            out = run(w, x, ids, wts)
+            errs[impl] = check_layer_output(out, want, f"{name} m={m} {impl}")
+            first = out.clone()
+            for _ in range(3):
+                assert torch.equal(run(w, x, ids, wts), first), f"{impl}: not bit-identical from call to call"
+    finally:
+        w.set_decode_impl("auto")
+    print(f"{name} m={m}: (max-abs/rms, normwise) {errs}")
+
+
 def test_tiny_layer_matches_golden_reference_outputs(golden):
     cfg, w, ow = layer("tiny")
     g = golden.load("layer_tiny")
