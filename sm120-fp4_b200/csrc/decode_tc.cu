@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int v = blockIdx.x;
   const int n1 = T.sb1[v + 1] - T.sb1[v], n2 = T.sb2[v + 1] - T.sb2[v];
   const uint32_t tmem = T.tmem_base;
-  const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // 2 x 64 | NS x 16 | up to 176 + (FC2: NS x 16)
+  const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
 
   if (warp == 0) {
@@ -330,78 +330,95 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     __syncwarp();
   } else if (warp == 1) {
     // ============================================================== MMA issuer
+    // Software-pipelined: the scale-tile copies of tile i+1 are issued before the MMAs of tile i, so an MMA never waits
+    // for a copy (tcgen05 operations of one thread run in order; copies and MMAs of different tiles overlap).
     if (lane == 0) {
       const uint32_t idesc = idesc_mxf4nvf4(128, N);
+      struct TileJob { int slot, nkt, acc, first_of_piece, last_of_piece; uint32_t b_addr; };
       int si = 0;
       uint32_t ph = 0;
-      int ab = 0;              // accumulator buffer of the current piece
+      int ab = 0;
       uint32_t aph[2] = {0, 0};
       int pieces = 0;
-      auto next_acc = [&]() {   // wait until the epilogue has drained the buffer we are about to overwrite
-        if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+      // tile iterator over this worker's FC1 then FC2 share
+      const int fe1 = T.sb1[v + 1], fe2 = T.sb2[v + 1], per_nb = U * KB2;
+      int f1 = T.sb1[v], f2 = T.sb2[v];
+      int kb1 = n1 > 0 ? f1 % KB1 : 0, kb2 = n2 > 0 ? f2 % KB2 : 0;
+      bool piece_open = false;
+      // claim the next tile: wait for its stage (or only test it when `blocking` is false), issue its scale copies.
+      // returns 1: claimed, 0: no tile left, -1: not landed yet (non-blocking only)
+      auto copies = [&](TileJob& jb, bool blocking) -> int {
+        const bool is1 = f1 < fe1;
+        if (!is1 && f2 >= fe2) return 0;
+        if (!blocking) {
+          if (!mbar_try_wait(&T.full[si], ph)) return -1;
+        } else if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) {
+          *P.status = 1;
+        }
         tc_fence_after();
+        const uint32_t st = smem_u32(ring + si * kTcStage);
+        jb.slot = si;
+        jb.first_of_piece = !piece_open;
+        uint32_t sfb_src;
+        if (is1) {
+          jb.nkt = min(4, P.KT1 - 4 * kb1);
+          jb.b_addr = smem_u32(region + kb1 * (N * 128));
+          sfb_src = smem_u32(xb_sf + 4 * kb1 * 512);
+          ++f1;
+          ++kb1;
+          jb.last_of_piece = (kb1 == KB1) || (f1 == fe1);
+          if (kb1 == KB1) kb1 = 0;
+        } else {
+          jb.nkt = min(4, P.KT2 - 4 * kb2);
+          jb.b_addr = smem_u32(region + si * kSlab);
+          sfb_src = jb.b_addr + N * 128;
+          ++f2;
+          if (++kb2 == KB2) kb2 = 0;
+          jb.last_of_piece = (f2 == fe2) || (f2 % per_nb == 0);
+        }
+        piece_open = !jb.last_of_piece;
+        for (int jj = 0; jj < jb.nkt; ++jj) {
+          tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
+          tmem_cp_sf(tm_sfb + 16 * si + 4 * jj, smem_desc_sf_tile(sfb_src + jj * 512));
+        }
+        if (++si == NS) { si = 0; ph ^= 1u; }
+        return 1;
       };
-      auto acc_done = [&]() {
-        umma_commit(&T.acc_full[ab]);
-        aph[ab] ^= 1u;
-        ab ^= 1;
-        ++pieces;
+      bool acc_flag = false;   // accumulate into the open piece
+      auto mmas = [&](const TileJob& jb) {
+        if (jb.first_of_piece) {   // wait until the epilogue has drained the accumulator buffer we are about to overwrite
+          if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+          tc_fence_after();
+          acc_flag = false;
+        }
+        const uint32_t st = smem_u32(ring + jb.slot * kTcStage);
+        for (int jj = 0; jj < jb.nkt; ++jj) {
+          umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(jb.b_addr) + 2 * jj, idesc,
+                        tm_sfa + 16 * jb.slot + 4 * jj, tm_sfb + 16 * jb.slot + 4 * jj, acc_flag ? 1u : 0u);
+          acc_flag = true;
+        }
+        umma_commit(&T.empty[jb.slot]);
+        if (jb.last_of_piece) {
+          umma_commit(&T.acc_full[ab]);
+          aph[ab] ^= 1u;
+          ab ^= 1;
+          ++pieces;
+        }
       };
       if (n1 > 0) {
         if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
         tc_fence_after();
-        for (int kt = 0; kt < P.KT1; ++kt) tmem_cp_sf(tm_sfb + 4 * kt, smem_desc_sf_tile(smem_u32(xb_sf + kt * 512)));
-        int f = T.sb1[v];
-        const int fe = T.sb1[v + 1];
-        while (f < fe) {
-          const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
-          next_acc();
-          for (int kb = k0; kb < k1; ++kb) {
-            if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
-            tc_fence_after();
-            const uint32_t st = smem_u32(ring + si * kTcStage);
-            const int nkt = min(4, P.KT1 - 4 * kb);
-            for (int jj = 0; jj < nkt; ++jj) {
-              tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
-              umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj,
-                            smem_desc_sw128_kmajor(smem_u32(region + kb * (N * 128))) + 2 * jj, idesc, tm_sfa + 16 * si + 4 * jj,
-                            tm_sfb + 4 * (4 * kb + jj), (kb > k0 || jj > 0) ? 1u : 0u);
-            }
-            umma_commit(&T.empty[si]);
-            if (++si == NS) { si = 0; ph ^= 1u; }
-          }
-          acc_done();
-          f += k1 - k0;
-        }
       }
-      if (n2 > 0) {
-        const int per_nb = U * KB2;
-        int f = T.sb2[v];
-        const int fe = T.sb2[v + 1];
-        while (f < fe) {
-          const int nb = f / per_nb;
-          const int pe = min(fe, (nb + 1) * per_nb);
-          next_acc();
-          bool first = true;
-          int kb = f % KB2;
-          for (; f < pe; ++f) {
-            if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
-            tc_fence_after();
-            const uint32_t st = smem_u32(ring + si * kTcStage), sl = smem_u32(region + si * kSlab);
-            const int nkt = min(4, P.KT2 - 4 * kb);
-            for (int jj = 0; jj < nkt; ++jj) {
-              tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
-              tmem_cp_sf(tm_sfb + 16 * si + 4 * jj, smem_desc_sf_tile(sl + N * 128 + jj * 512));
-              umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(sl) + 2 * jj, idesc,
-                            tm_sfa + 16 * si + 4 * jj, tm_sfb + 16 * si + 4 * jj, first ? 0u : 1u);
-              first = false;
-            }
-            umma_commit(&T.empty[si]);
-            if (++si == NS) { si = 0; ph ^= 1u; }
-            if (++kb == KB2) kb = 0;
-          }
-          acc_done();
-        }
+      // Never block on a future tile while MMAs of a landed tile are unissued: the first FC2 tile lands only after the
+      // grid barrier, which this CTA's own epilogue reaches only once the last FC1 accumulator has been committed.
+      TileJob cur, nxt;
+      int have = copies(cur, true);
+      while (have == 1) {
+        const int more = copies(nxt, false);
+        mmas(cur);
+        if (more == 1) cur = nxt;
+        else if (more == 0) have = 0;
+        else have = copies(cur, true);
       }
     }
     __syncwarp();
