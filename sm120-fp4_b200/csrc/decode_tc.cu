@@ -11,17 +11,19 @@
 // 1/g_t. Four terms carry more mantissa than bf16 for the values that decide a dot product and keep the layer's error
 // against the fp32 oracle below the bf16 output rounding.
 //
-// Structure: one CTA per SM = one stream-K worker. Warp 0: TMA producer (weight tiles into a shared-memory ring, FC2
-// tiles prefetched across the FC1->FC2 grid barrier). Warp 1: MMA issuer (scale tiles smem->TMEM with tcgen05.cp, four
-// K=64 MMAs per 256-code tile, tcgen05.commit frees the ring stage). Warps 2-5: epilogue (tcgen05.ld of a double-buffered
-// TMEM accumulator, term sums, SiLU*mul, re-expansion of the activations for FC2, fixed-order reduction of split units).
+// Structure: one CTA per SM = one stream-K worker. Warps 0-3: epilogue (tcgen05.ld of a double-buffered TMEM accumulator,
+// term sums, SiLU*mul, re-expansion of the activations for FC2, fixed-order reduction of split units). Warp 4: MMA issuer
+// (scale tiles smem->TMEM with tcgen05.cp, four K=64 MMAs per 256-code tile, tcgen05.commit frees the ring stage).
+// Warps 5-8: TMA producers, tile i of the worker's share belongs to producer i mod 4 (weight tiles into a shared-memory
+// ring, FC2 tiles prefetched across the FC1->FC2 grid barrier).
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "decode_params.h"
 
 namespace b200 {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcProducers = 4;    // TMA producer warps: one thread issues roughly one bulk operation per 100 cycles
+constexpr int kTcThreads = (4 + 1 + kTcProducers) * 32;   // epilogue warps 0-3, MMA warp 4, producer warps 5..
 constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
 constexpr int kTerms = 4;
 constexpr int kTcMaxE = 256, kTcMaxP = 256, kTcMaxWorkers = 256;
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     T.gen0 = ld_acquire_gpu(P.gridbar + 1);
     fence_mbar_init();
   }
-  if (warp == 1) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
+  if (warp == 4) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
     tmem_alloc(&T.tmem_base, 512);
     tmem_relinquish();
   }
@@ -246,21 +248,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
 
-  if (warp == 0) {
-    // ============================================================== TMA producer
+  if (warp >= 5) {
+    // ============================================================== TMA producers (one thread each)
     if (lane == 0) {
+      const int pw = warp - 5;
       prefetch_tensormap(&P.tm1);
       prefetch_tensormap(&P.tm2);
       const uint64_t pol = policy_evict_first();
       // the resident B operand of FC1: x expanded into NVFP4 terms, one box per K box, and its scale tiles
-      if (n1 > 0) {
+      if (pw == 0 && n1 > 0) {
         mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
         for (int kb = 0; kb < KB1; ++kb) tma_load_2d(region + kb * (N * 128), &P.tmx, 128 * kb, 0, &T.xb_full);
         bulk_load(xb_sf, P.xsf, P.KT1 * 512, &T.xb_full);
       }
       const unsigned gen0 = T.gen0;
       bool passed = false;
-      int pend_slot[8], pend_u[8], pend_kb[8], npend = 0;
+      int pend_slot[4], pend_u[4], pend_kb[4], npend = 0;
       auto load_slab = [&](int slot, int u, int kb) {
         uint8_t* dst = region + slot * kSlab;
         tma_load_2d(dst, &P.tma, 128 * kb, u * N, &T.full[slot]);
@@ -281,38 +284,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         npend = 0;
         passed = true;
       };
-      int si = 0, j = 0;
-      uint32_t ph = 0;
-      auto claim = [&](bool prev_pending) -> int {
-        if (j >= NS) {
-          if (prev_pending) wait_grid();
-          if (!mbar_wait(&T.empty[si], ph ^ 1u, &T.abort_flag)) *P.status = 2;
+      const int f1 = T.sb1[v], f2 = T.sb2[v];
+      for (int j = pw; j < n1 + n2; j += kTcProducers) {   // j: position in this worker's tile sequence; slot = j mod NS
+        const int slot = j % NS, use = j / NS;
+        const bool is2 = j >= n1;
+        if (use >= 1) {
+          // the previous occupant of the slot is an FC2 tile still waiting for its activations: open the gate first
+          if (!passed && (j - NS) >= n1) wait_grid();
+          if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = 2;
         }
-        return si;
-      };
-      auto advance = [&]() { ++j; if (++si == NS) { si = 0; ph ^= 1u; } };
-      if (n1 > 0) {
-        const int f0 = T.sb1[v];
-        int kb = f0 % KB1, q = f0 / KB1, cb = q % CB1, u = q / CB1;
-        for (int i = 0; i < n1; ++i) {
-          const int slot = claim(false);
-          uint8_t* st = ring + slot * kTcStage;
+        uint8_t* st = ring + slot * kTcStage;
+        if (!is2) {
+          const int f = f1 + j;
+          const int kb = f % KB1, q = f / KB1, cb = q % CB1, u = q / CB1;
           const int e = T.experts[u];
           const int nkt = min(4, P.KT1 - 4 * kb);
           mbar_expect_tx(&T.full[slot], 16384 + nkt * 512);
           tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + 64 * cb, &T.full[slot], pol);
           tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + P.I + 64 * cb, &T.full[slot], pol);
           bulk_load_hint(st + 16384, P.s1t + (((long long)e * CB1 + cb) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
-          advance();
-          if (++kb == KB1) { kb = 0; if (++cb == CB1) { cb = 0; ++u; } }
-        }
-      }
-      if (n2 > 0) {
-        const int f0 = T.sb2[v];
-        int kb = f0 % KB2, q = f0 / KB2, u = q % U, nb = q / U;
-        for (int i = 0; i < n2; ++i) {
-          const int slot = claim(!passed && (j - NS) >= n1);
-          uint8_t* st = ring + slot * kTcStage;
+        } else {
+          const int f = f2 + (j - n1);
+          const int kb = f % KB2, q = f / KB2, u = q % U, nb = q / U;
           const int e = T.experts[u];
           const int nkt = min(4, P.KT2 - 4 * kb);
           mbar_expect_tx(&T.full[slot], 16384 + nkt * 512 + N * 128 + nkt * 512);
@@ -321,20 +314,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
                          &T.full[slot], pol);
           if (passed) load_slab(slot, u, kb);
           else { pend_slot[npend] = slot; pend_u[npend] = u; pend_kb[npend] = kb; ++npend; }
-          advance();
-          if (++kb == KB2) { kb = 0; if (++u == U) { u = 0; ++nb; } }
         }
       }
       if (npend > 0) wait_grid();
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 4) {
     // ============================================================== MMA issuer
     // Software-pipelined: the scale-tile copies of tile i+1 are issued before the MMAs of tile i, so an MMA never waits
     // for a copy (tcgen05 operations of one thread run in order; copies and MMAs of different tiles overlap).
     if (lane == 0) {
       const uint32_t idesc = idesc_mxf4nvf4(128, N);
-      struct TileJob { int slot, nkt, acc, first_of_piece, last_of_piece; uint32_t b_addr; };
+      struct TileJob { int slot, nkt, acc, first_of_piece, last_of_piece; uint32_t b_addr, sfb; };
       int si = 0;
       uint32_t ph = 0;
       int ab = 0;
@@ -345,6 +336,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       int f1 = T.sb1[v], f2 = T.sb2[v];
       int kb1 = n1 > 0 ? f1 % KB1 : 0, kb2 = n2 > 0 ? f2 % KB2 : 0;
       bool piece_open = false;
+      unsigned long long xsf_done = 0;   // K boxes whose x-operand scale tiles are already in TMEM
       // claim the next tile: wait for its stage (or only test it when `blocking` is false), issue its scale copies.
       // returns 1: claimed, 0: no tile left, -1: not landed yet (non-blocking only)
       auto copies = [&](TileJob& jb, bool blocking) -> int {
@@ -359,11 +351,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         const uint32_t st = smem_u32(ring + si * kTcStage);
         jb.slot = si;
         jb.first_of_piece = !piece_open;
-        uint32_t sfb_src;
+        uint32_t sfb_src = 0;
         if (is1) {
           jb.nkt = min(4, P.KT1 - 4 * kb1);
           jb.b_addr = smem_u32(region + kb1 * (N * 128));
-          sfb_src = smem_u32(xb_sf + 4 * kb1 * 512);
+          jb.sfb = tm_sfb + 16 * kb1;
+          if (!((xsf_done >> kb1) & 1ull)) {
+            xsf_done |= 1ull << kb1;
+            for (int jj = 0; jj < jb.nkt; ++jj) tmem_cp_sf(jb.sfb + 4 * jj, smem_desc_sf_tile(smem_u32(xb_sf + (4 * kb1 + jj) * 512)));
+          }
           ++f1;
           ++kb1;
           jb.last_of_piece = (kb1 == KB1) || (f1 == fe1);
@@ -372,6 +368,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           jb.nkt = min(4, P.KT2 - 4 * kb2);
           jb.b_addr = smem_u32(region + si * kSlab);
           sfb_src = jb.b_addr + N * 128;
+          jb.sfb = tm_sfb + 16 * si;
           ++f2;
           if (++kb2 == KB2) kb2 = 0;
           jb.last_of_piece = (f2 == fe2) || (f2 % per_nb == 0);
@@ -379,7 +376,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         piece_open = !jb.last_of_piece;
         for (int jj = 0; jj < jb.nkt; ++jj) {
           tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
-          tmem_cp_sf(tm_sfb + 16 * si + 4 * jj, smem_desc_sf_tile(sfb_src + jj * 512));
+          if (sfb_src) tmem_cp_sf(jb.sfb + 4 * jj, smem_desc_sf_tile(sfb_src + jj * 512));
         }
         if (++si == NS) { si = 0; ph ^= 1u; }
         return 1;
@@ -394,7 +391,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         const uint32_t st = smem_u32(ring + jb.slot * kTcStage);
         for (int jj = 0; jj < jb.nkt; ++jj) {
           umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(jb.b_addr) + 2 * jj, idesc,
-                        tm_sfa + 16 * jb.slot + 4 * jj, tm_sfb + 16 * jb.slot + 4 * jj, acc_flag ? 1u : 0u);
+                        tm_sfa + 16 * jb.slot + 4 * jj, jb.sfb + 4 * jj, acc_flag ? 1u : 0u);
           acc_flag = true;
         }
         umma_commit(&T.empty[jb.slot]);
@@ -424,8 +421,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     __syncwarp();
   } else {
     // ============================================================== epilogue: 4 warps, thread = accumulator row
-    const int et = tid - 64;                       // 0..127
-    const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int et = tid;                            // 0..127
+    const int quad = warp;                     // TMEM lane quadrant this warp may read
     const int row = quad * 32 + lane;              // accumulator row (MMA M index)
     __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
     int ab = 0;
@@ -605,7 +602,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 4) tmem_dealloc(tmem, 512);
   if (T.abort_flag)
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
 }
