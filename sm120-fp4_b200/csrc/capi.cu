@@ -126,7 +126,7 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   L->off_actfrag = o, o = align_up(o + (long long)L->umax_cap * L->KB2 * 8192, 256);
   L->off_tables = o, o = align_up(o + (long long)(2 * L->umax_cap + 1 + 16 * top_k) * 4, 256);
   L->off_actbf16 = o, o = align_up(o + (long long)16 * top_k * I * 2, 256);
-  L->off_debug = o, o = align_up(o + (long long)V * 8 * 8, 256);
+  L->off_debug = o, o = align_up(o + (long long)V * 16 * 8, 256);
   L->off_xq = o, o = align_up(o + 64LL * (H / 2), 256);
   L->off_xsf = o, o = align_up(o + (long long)L->KT1 * 512, 256);
   L->off_xscale = o, o += 256;
@@ -220,6 +220,7 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   p.offsets_out = p.experts_out + L->umax_cap;
   p.pairs_out = p.offsets_out + L->umax_cap + 1;
   p.s2_expert_stride = L->s2_stride;
+  p.debug = (long long*)(w + L->off_debug);
   p.act_g1 = L->act_g1;
   p.M = M, p.E = L->E, p.H = L->H, p.I = L->I, p.top_k = L->top_k;
   p.Umax = L->E < M * L->top_k ? L->E : M * L->top_k;
@@ -357,7 +358,7 @@ extern "C" int b200moe_layer_status(const b200moe_layer* L, const void* workspac
 extern "C" int b200moe_layer_debug_counters(const b200moe_layer* L, const void* workspace, long long* out, int max_workers, void* stream) {
   if (!L || !workspace || !out) return B200MOE_ERR_ARG;
   const int n = 2 * L->sms < max_workers ? 2 * L->sms : max_workers;
-  B200_CUDA_TRY(cudaMemcpyAsync(out, (const uint8_t*)workspace + L->off_debug, (size_t)n * 64, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA_TRY(cudaMemcpyAsync(out, (const uint8_t*)workspace + L->off_debug, (size_t)n * 128, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
   return n;
 }

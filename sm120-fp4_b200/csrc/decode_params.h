@@ -67,6 +67,7 @@ struct DecodeTcParams {
   int* offsets_out;
   int* pairs_out;
   long long s2_expert_stride;
+  long long* debug;          // per-worker cycle counters (timer build only), 16 per worker
   float act_g1;              // global scale of the first activation term
   int M, E, H, I, top_k, Umax;
   int NS, region_bytes;

@@ -44,6 +44,14 @@ struct TcTables {
   uint64_t xb_full;
 };
 
+#ifdef B200_TIMERS
+#define TC_T0(var) long long var = clock64()
+#define TC_ADD(acc, var) acc += clock64() - var
+#else
+#define TC_T0(var)
+#define TC_ADD(acc, var)
+#endif
+
 __device__ __forceinline__ int tc_worker_of(int f, int T, int V) { return (int)(((unsigned)(f + 1) * (unsigned)V - 1u) / (unsigned)T); }
 __device__ __forceinline__ float tc_silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
@@ -66,8 +74,21 @@ __device__ __forceinline__ float tc_e4m3_value(uint8_t b) {
   return e == 0 ? (float)m * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
 }
 
+// 8 floats -> 8 E2M1 codes in one word (element 2j in the low nibble of byte j), hardware round-to-nearest-even, saturating
+__device__ __forceinline__ uint32_t cvt_f32x8_e2m1(const float* v) {
+  uint32_t d;
+  asm("{\n .reg .b8 b0, b1, b2, b3;\n"
+      " cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      " cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      " mov.b32 %0, {b0, b1, b2, b3};\n}\n"
+      : "=r"(d)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return d;
+}
+
 // One 16-value block -> kTerms NVFP4 terms (residual expansion). g1: global scale of the first term; term t uses g1*6^t.
-// codes[t] = 8 packed bytes (element 2j in the low nibble), sf[t] = E4M3 scale byte.
+// codes[t] = 8 packed bytes (element 2j in the low nibble), sf[t] = E4M3 scale byte. The residual is taken against the
+// codes actually emitted, so any rounding of the code conversion is absorbed by the next term.
 __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (&codes)[kTerms], uint8_t (&sf)[kTerms]) {
   float g = g1;
 #pragma unroll
@@ -78,12 +99,21 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
     const uint8_t sb = tc_e4m3(fminf(amax * (1.0f / 6.0f) * g, 448.0f));
     const float sv = tc_e4m3_value(sb);
     const float scale = sv > 0.f ? g / sv : 0.f, back = sv > 0.f ? sv / g : 0.f;
-    uint32_t lo = 0, hi = 0;
+    float sc[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t c = tc_e2m1(r[i] * scale);
-      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-      r[i] -= tc_e2m1_value(c) * back;
+    for (int i = 0; i < 16; ++i) sc[i] = r[i] * scale;
+    const uint32_t lo = cvt_f32x8_e2m1(sc), hi = cvt_f32x8_e2m1(sc + 8);
+    uint32_t dl[4], dh[4];
+    cvt_e2m1x8_f16x2(lo, dl);
+    cvt_e2m1x8_f16x2(hi, dh);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&dl[i]));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&dh[i]));
+      r[2 * i] -= a.x * back;
+      r[2 * i + 1] -= a.y * back;
+      r[8 + 2 * i] -= b.x * back;
+      r[8 + 2 * i + 1] -= b.y * back;
     }
     codes[t] = make_uint2(lo, hi);
     sf[t] = sb;
@@ -244,6 +274,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   const int v = blockIdx.x;
   const int n1 = T.sb1[v + 1] - T.sb1[v], n2 = T.sb2[v + 1] - T.sb2[v];
+#ifdef B200_TIMERS
+  long long tm_a = 0, tm_b = 0, tm_c = 0, tm_d = 0;
+  const long long tm_begin = clock64();
+#endif
   const uint32_t tmem = T.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
@@ -291,7 +325,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         if (use >= 1) {
           // the previous occupant of the slot is an FC2 tile still waiting for its activations: open the gate first
           if (!passed && (j - NS) >= n1) wait_grid();
+          TC_T0(t0);
           if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = 2;
+          TC_ADD(tm_a, t0);
         }
         uint8_t* st = ring + slot * kTcStage;
         if (!is2) {
@@ -317,6 +353,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         }
       }
       if (npend > 0) wait_grid();
+#ifdef B200_TIMERS
+      if (P.debug && pw == 0) { P.debug[v * 16 + 8] = tm_a; P.debug[v * 16 + 9] = clock64() - tm_begin; }
+#endif
     }
     __syncwarp();
   } else if (warp == 4) {
@@ -344,8 +383,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         if (!is1 && f2 >= fe2) return 0;
         if (!blocking) {
           if (!mbar_try_wait(&T.full[si], ph)) return -1;
-        } else if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) {
-          *P.status = 1;
+        } else {
+          TC_T0(t0);
+          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+          TC_ADD(tm_a, t0);
         }
         tc_fence_after();
         const uint32_t st = smem_u32(ring + si * kTcStage);
@@ -384,7 +425,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       bool acc_flag = false;   // accumulate into the open piece
       auto mmas = [&](const TileJob& jb) {
         if (jb.first_of_piece) {   // wait until the epilogue has drained the accumulator buffer we are about to overwrite
+          TC_T0(t0);
           if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+          TC_ADD(tm_b, t0);
           tc_fence_after();
           acc_flag = false;
         }
@@ -417,6 +460,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         else if (more == 0) have = 0;
         else have = copies(cur, true);
       }
+#ifdef B200_TIMERS
+      if (P.debug) { P.debug[v * 16 + 4] = tm_a; P.debug[v * 16 + 5] = tm_b; P.debug[v * 16 + 6] = clock64() - tm_begin; }
+#endif
     }
     __syncwarp();
   } else {
@@ -425,10 +471,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     const int quad = warp;                     // TMEM lane quadrant this warp may read
     const int row = quad * 32 + lane;              // accumulator row (MMA M index)
     __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
+    __shared__ float s_w[16];
     int ab = 0;
     uint32_t aph[2] = {0, 0};
     auto load_terms = [&](float (&val)[16], const float* cs, bool per_column) {   // sum the four term columns of every token
+      TC_T0(t0);
       if (!mbar_wait(&T.acc_full[ab], aph[ab], &T.abort_flag)) *P.status = 7;
+      TC_ADD(tm_a, t0);
       tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < N; c0 += 16) {
@@ -508,14 +557,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         const int piece_first = f;
         f += k1 - k0;
         bool finalize = true;
+        TC_T0(tfix);
         if (!(k0 == 0 && k1 == KB1)) {
           const int vlo = tc_worker_of(q * KB1, T1, V), vhi = tc_worker_of(q * KB1 + KB1 - 1, T1, V);
           finalize = publish(val, piece_first == fs ? 0 : 1, P.cnt1 + q, T.sb1, vlo, vhi);
           if (finalize) reduce(T.sb1, q * KB1, vlo, vhi, val);
         }
         if (finalize) {
-          // rows 0..63 hold the up columns 64cb.., rows 64..127 the gate columns: exchange through shared memory
+          // rows 0..63 hold the up columns 64cb.., rows 64..127 the gate columns: exchange through shared memory.
+          // s_w[tk]: routing weight of token tk on this expert folded with alpha2 (relative to the layer's largest), 0 when
+          // the token is not routed here - only routed tokens cost any arithmetic below.
           const float alpha = P.alpha1[e];
+          if (et < 16) {
+            float wsum = 0.f;
+            if (et < P.M)
+              for (int sidx = 0; sidx < P.top_k; ++sidx)
+                if (T.ids[et * P.top_k + sidx] == e) wsum += T.wts[et * P.top_k + sidx];
+            s_w[et] = wsum * P.alpha2[e] * P.alpha2_ref[1];
+          }
           if (row >= 64) {
 #pragma unroll
             for (int tk = 0; tk < 16; ++tk) s_ex[row - 64][tk] = val[tk] * alpha;
@@ -524,13 +583,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           if (row < 64) {
 #pragma unroll
             for (int tk = 0; tk < 16; ++tk) {
-              // routing weight of token tk on this expert (0: not routed), folded with alpha2 relative to the layer's largest
-              float wsum = 0.f;
-              if (tk < P.M)
-                for (int s = 0; s < P.top_k; ++s)
-                  if (T.ids[tk * P.top_k + s] == e) wsum += T.wts[tk * P.top_k + s];
-              const float a = wsum != 0.f ? tc_silu_mul(s_ex[row][tk], val[tk] * alpha) * (wsum * P.alpha2[e] * P.alpha2_ref[1]) : 0.f;
-              val[tk] = a;
+              const float wf = s_w[tk];
+              val[tk] = wf != 0.f ? tc_silu_mul(s_ex[row][tk], val[tk] * alpha) * wf : 0.f;
             }
           }
           named_bar_sync(1, 128);
@@ -539,25 +593,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             for (int tk = 0; tk < 16; ++tk) s_ex[row][tk] = val[tk];
           }
           named_bar_sync(1, 128);
-          // re-expand: thread (token, 16-column block) -> four NVFP4 terms of the FC2 operand
-          if (et < 4 * (N / 4)) {
+          // re-expand: thread (token, 16-column block) -> four NVFP4 terms of the FC2 operand; a token that is not routed
+          // here only gets zero scale bytes (a zero scale silences whatever codes the row holds)
+          if (et < N) {
             const int tk = et >> 2, blk = et & 3;
-            float r[16];
+            uint8_t* sfp = P.asf + ((long long)u * P.KT2 + cb) * 512 + blk;
+            if (s_w[tk] != 0.f) {
+              float r[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = s_ex[blk * 16 + i][tk];
-            uint2 codes[kTerms];
-            uint8_t sf[kTerms];
-            expand_block16(r, P.act_g1, codes, sf);
+              for (int i = 0; i < 16; ++i) r[i] = s_ex[blk * 16 + i][tk];
+              uint2 codes[kTerms];
+              uint8_t sf[kTerms];
+              expand_block16(r, P.act_g1, codes, sf);
 #pragma unroll
-            for (int t = 0; t < kTerms; ++t) {
-              const int n = tk * kTerms + t;
-              *reinterpret_cast<uint2*>(P.aq + ((long long)u * N + n) * (P.I / 2) + (64 * cb + 16 * blk) / 2) = codes[t];
-              P.asf[((long long)u * P.KT2 + cb) * 512 + (n & 31) * 16 + (n >> 5) * 4 + blk] = sf[t];
+              for (int t = 0; t < kTerms; ++t) {
+                const int n = tk * kTerms + t;
+                *reinterpret_cast<uint2*>(P.aq + ((long long)u * N + n) * (P.I / 2) + (64 * cb + 16 * blk) / 2) = codes[t];
+                sfp[(n & 31) * 16 + (n >> 5) * 4] = sf[t];
+              }
+            } else {
+#pragma unroll
+              for (int t = 0; t < kTerms; ++t) {
+                const int n = tk * kTerms + t;
+                sfp[(n & 31) * 16 + (n >> 5) * 4] = 0;
+              }
             }
           }
           named_bar_sync(1, 128);
         }
+        TC_ADD(tm_b, tfix);
       }
+#ifdef B200_TIMERS
+      tm_c = clock64() - tm_begin;
+#endif
       // ---- publish FC1's results, arrive at the grid-wide barrier (the producers are the only waiters)
       fence_proxy_async();
       named_bar_sync(1, 128);
@@ -588,6 +656,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         const int pe = min(fe, (nb + 1) * per_nb);
         float val[16];
         load_terms(val, cs, false);
+        TC_T0(tfix2);
         const int vlo = tc_worker_of(nb * per_nb, T2, V), vhi = tc_worker_of((nb + 1) * per_nb - 1, T2, V);
         const bool last = publish(val, f == fs ? 0 : 1, P.cnt2 + nb, T.sb2, vlo, vhi);
         if (last) {
@@ -597,8 +666,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             if (tk < P.M) P.out[(long long)tk * P.H + 128 * nb + row] = __float2bfloat16_rn(val[tk]);
         }
         f = pe;
+        TC_ADD(tm_d, tfix2);
       }
     }
+#ifdef B200_TIMERS
+    if (P.debug && et == 0) { P.debug[v * 16 + 0] = tm_a; P.debug[v * 16 + 1] = tm_b; P.debug[v * 16 + 2] = tm_c; P.debug[v * 16 + 3] = tm_d; P.debug[v * 16 + 7] = clock64() - tm_begin; }
+#endif
   }
   tc_fence_before();
   __syncthreads();
