@@ -95,8 +95,8 @@ int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void
                        const unsigned* knobs, int* status_dev, void* stream);
 
 /* issue-cost measurement of tcgen05 scale copies and MMAs (diagnostic; no counterpart in the reference): cycles_dev[0] =
- * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64}, cycles_dev[1] = cycles until all completed. */
-int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, long long* cycles_dev, void* stream);
+ * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64, ncommit commits}, cycles_dev[1] = cycles until all completed. */
+int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, int ncommit, long long* cycles_dev, void* stream);
 
 /* per-worker cycle counters of the last decode launch (8 int64 per worker: consumer wait, math, fix-up, phase-1 end,
  * producer wait, producer grid wait, producer end, consumer end). Filled only by a library built with -DB200_TIMERS (a

@@ -23,7 +23,7 @@
 namespace b200 {
 
 constexpr int kTcProducers = 4;    // TMA producer warps: one thread issues roughly one bulk operation per 100 cycles
-constexpr int kTcThreads = (4 + 1 + kTcProducers) * 32;   // epilogue warps 0-3, MMA warp 4, producer warps 5..
+constexpr int kTcThreads = (4 + 2 + kTcProducers) * 32;   // epilogue warps 0-3, MMA warp 4, scale-copy warp 5, producers 6..
 constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
 constexpr int kTerms = 4;
 constexpr int kTcMaxE = 256, kTcMaxP = 256, kTcMaxWorkers = 256;
@@ -39,7 +39,7 @@ struct TcTables {
   volatile int abort_flag;
   int last_flag;
   uint32_t tmem_base;
-  uint64_t full[8], empty[8];
+  uint64_t full[8], empty[8], sfr[8];   // stage landed / stage consumed / scale tiles of the stage are in TMEM
   uint64_t acc_full[2], acc_empty[2];
   uint64_t xb_full;
 };
@@ -74,15 +74,17 @@ __device__ __forceinline__ float tc_e4m3_value(uint8_t b) {
   return e == 0 ? (float)m * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
 }
 
-// 8 floats -> 8 E2M1 codes in one word (element 2j in the low nibble of byte j), hardware round-to-nearest-even, saturating
+// 8 floats -> 8 E2M1 codes in one word (element 2j in the low nibble of byte j), hardware round-to-nearest-even,
+// saturating. Each value is converted on both operands of the pair instruction, so the result does not depend on which
+// operand lands in which nibble.
 __device__ __forceinline__ uint32_t cvt_f32x8_e2m1(const float* v) {
-  uint32_t d;
-  asm("{\n .reg .b8 b0, b1, b2, b3;\n"
-      " cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
-      " cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
-      " mov.b32 %0, {b0, b1, b2, b3};\n}\n"
-      : "=r"(d)
-      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  uint32_t d = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t b;
+    asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %1;\n cvt.u32.u8 %0, t;\n}\n" : "=r"(b) : "f"(v[i]));
+    d |= (b & 0xFu) << (4 * i);
+  }
   return d;
 }
 
@@ -210,7 +212,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 
   // ---------------------------------------------------------------- prologue
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); }
+    for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); mbar_init(&T.sfr[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&T.acc_full[b], 1); mbar_init(&T.acc_empty[b], 4); }
     mbar_init(&T.xb_full, 1);
     T.abort_flag = 0;
@@ -282,10 +284,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
 
-  if (warp >= 5) {
+  if (warp >= 6) {
     // ============================================================== TMA producers (one thread each)
     if (lane == 0) {
-      const int pw = warp - 5;
+      const int pw = warp - 6;
       prefetch_tensormap(&P.tm1);
       prefetch_tensormap(&P.tm2);
       const uint64_t pol = policy_evict_first();
@@ -358,110 +360,98 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 #endif
     }
     __syncwarp();
-  } else if (warp == 4) {
-    // ============================================================== MMA issuer
-    // Software-pipelined: the scale-tile copies of tile i+1 are issued before the MMAs of tile i, so an MMA never waits
-    // for a copy (tcgen05 operations of one thread run in order; copies and MMAs of different tiles overlap).
+  } else if (warp == 4 || warp == 5) {
+    // ============================================================== scale copier (warp 5) and MMA issuer (warp 4)
+    // One thread can issue roughly one tcgen05 operation per 80-100 cycles, so the scale-tile copies (4-8 per tile) and the
+    // MMAs (4 per tile) are issued by two threads: the copier runs ahead, commits its copies to sfr[slot], the issuer waits
+    // for that barrier, issues the MMAs and commits them to empty[slot] (and to acc_full at the end of a piece).
     if (lane == 0) {
+      const bool copier = warp == 5;
       const uint32_t idesc = idesc_mxf4nvf4(128, N);
-      struct TileJob { int slot, nkt, acc, first_of_piece, last_of_piece; uint32_t b_addr, sfb; };
-      int si = 0;
-      uint32_t ph = 0;
-      int ab = 0;
-      uint32_t aph[2] = {0, 0};
-      int pieces = 0;
-      // tile iterator over this worker's FC1 then FC2 share
       const int fe1 = T.sb1[v + 1], fe2 = T.sb2[v + 1], per_nb = U * KB2;
       int f1 = T.sb1[v], f2 = T.sb2[v];
       int kb1 = n1 > 0 ? f1 % KB1 : 0, kb2 = n2 > 0 ? f2 % KB2 : 0;
-      bool piece_open = false;
+      int si = 0;
+      uint32_t ph = 0;
+      int ab = 0, pieces = 0;
+      uint32_t aph[2] = {0, 0};
+      bool piece_open = false, acc_flag = false;
       unsigned long long xsf_done = 0;   // K boxes whose x-operand scale tiles are already in TMEM
-      // claim the next tile: wait for its stage (or only test it when `blocking` is false), issue its scale copies.
-      // returns 1: claimed, 0: no tile left, -1: not landed yet (non-blocking only)
-      auto copies = [&](TileJob& jb, bool blocking) -> int {
-        const bool is1 = f1 < fe1;
-        if (!is1 && f2 >= fe2) return 0;
-        if (!blocking) {
-          if (!mbar_try_wait(&T.full[si], ph)) return -1;
-        } else {
-          TC_T0(t0);
-          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
-          TC_ADD(tm_a, t0);
-        }
-        tc_fence_after();
-        const uint32_t st = smem_u32(ring + si * kTcStage);
-        jb.slot = si;
-        jb.first_of_piece = !piece_open;
-        uint32_t sfb_src = 0;
-        if (is1) {
-          jb.nkt = min(4, P.KT1 - 4 * kb1);
-          jb.b_addr = smem_u32(region + kb1 * (N * 128));
-          jb.sfb = tm_sfb + 16 * kb1;
-          if (!((xsf_done >> kb1) & 1ull)) {
-            xsf_done |= 1ull << kb1;
-            for (int jj = 0; jj < jb.nkt; ++jj) tmem_cp_sf(jb.sfb + 4 * jj, smem_desc_sf_tile(smem_u32(xb_sf + (4 * kb1 + jj) * 512)));
-          }
-          ++f1;
-          ++kb1;
-          jb.last_of_piece = (kb1 == KB1) || (f1 == fe1);
-          if (kb1 == KB1) kb1 = 0;
-        } else {
-          jb.nkt = min(4, P.KT2 - 4 * kb2);
-          jb.b_addr = smem_u32(region + si * kSlab);
-          sfb_src = jb.b_addr + N * 128;
-          jb.sfb = tm_sfb + 16 * si;
-          ++f2;
-          if (++kb2 == KB2) kb2 = 0;
-          jb.last_of_piece = (f2 == fe2) || (f2 % per_nb == 0);
-        }
-        piece_open = !jb.last_of_piece;
-        for (int jj = 0; jj < jb.nkt; ++jj) {
-          tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
-          if (sfb_src) tmem_cp_sf(jb.sfb + 4 * jj, smem_desc_sf_tile(sfb_src + jj * 512));
-        }
-        if (++si == NS) { si = 0; ph ^= 1u; }
-        return 1;
-      };
-      bool acc_flag = false;   // accumulate into the open piece
-      auto mmas = [&](const TileJob& jb) {
-        if (jb.first_of_piece) {   // wait until the epilogue has drained the accumulator buffer we are about to overwrite
-          TC_T0(t0);
-          if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
-          TC_ADD(tm_b, t0);
-          tc_fence_after();
-          acc_flag = false;
-        }
-        const uint32_t st = smem_u32(ring + jb.slot * kTcStage);
-        for (int jj = 0; jj < jb.nkt; ++jj) {
-          umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(jb.b_addr) + 2 * jj, idesc,
-                        tm_sfa + 16 * jb.slot + 4 * jj, jb.sfb + 4 * jj, acc_flag ? 1u : 0u);
-          acc_flag = true;
-        }
-        umma_commit(&T.empty[jb.slot]);
-        if (jb.last_of_piece) {
-          umma_commit(&T.acc_full[ab]);
-          aph[ab] ^= 1u;
-          ab ^= 1;
-          ++pieces;
-        }
-      };
       if (n1 > 0) {
         if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
         tc_fence_after();
       }
-      // Never block on a future tile while MMAs of a landed tile are unissued: the first FC2 tile lands only after the
-      // grid barrier, which this CTA's own epilogue reaches only once the last FC1 accumulator has been committed.
-      TileJob cur, nxt;
-      int have = copies(cur, true);
-      while (have == 1) {
-        const int more = copies(nxt, false);
-        mmas(cur);
-        if (more == 1) cur = nxt;
-        else if (more == 0) have = 0;
-        else have = copies(cur, true);
+      while (f1 < fe1 || f2 < fe2) {
+        const bool is1 = f1 < fe1;
+        const uint32_t st = smem_u32(ring + si * kTcStage);
+        int nkt;
+        uint32_t b_addr, sfb;
+        bool last_of_piece;
+        const int kbx = kb1;
+        if (is1) {
+          nkt = min(4, P.KT1 - 4 * kb1);
+          b_addr = smem_u32(region + kb1 * (N * 128));
+          sfb = tm_sfb + 16 * kb1;
+          ++f1;
+          ++kb1;
+          last_of_piece = (kb1 == KB1) || (f1 == fe1);
+          if (kb1 == KB1) kb1 = 0;
+        } else {
+          nkt = min(4, P.KT2 - 4 * kb2);
+          b_addr = smem_u32(region + si * kSlab);
+          sfb = tm_sfb + 16 * si;
+          ++f2;
+          if (++kb2 == KB2) kb2 = 0;
+          last_of_piece = (f2 == fe2) || (f2 % per_nb == 0);
+        }
+        if (copier) {
+          TC_T0(t0);
+          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+          TC_ADD(tm_a, t0);
+          tc_fence_after();
+          TC_T0(tcp);
+          for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
+          if (!is1) {
+            for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(sfb + 4 * jj, smem_desc_sf_tile(b_addr + N * 128 + jj * 512));
+          } else if (!((xsf_done >> kbx) & 1ull)) {
+            xsf_done |= 1ull << kbx;
+            for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(sfb + 4 * jj, smem_desc_sf_tile(smem_u32(xb_sf + (4 * kbx + jj) * 512)));
+          }
+          umma_commit(&T.sfr[si]);
+          TC_ADD(tm_d, tcp);
+        } else {
+          if (!piece_open) {   // first tile of a piece: the epilogue must have drained the accumulator buffer
+            TC_T0(t0);
+            if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+            TC_ADD(tm_b, t0);
+            acc_flag = false;
+          }
+          TC_T0(t1);
+          if (!mbar_wait(&T.sfr[si], ph, &T.abort_flag)) *P.status = 8;
+          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+          TC_ADD(tm_a, t1);
+          tc_fence_after();
+          TC_T0(tmm);
+          for (int jj = 0; jj < nkt; ++jj) {
+            umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(b_addr) + 2 * jj, idesc,
+                          tm_sfa + 16 * si + 4 * jj, sfb + 4 * jj, acc_flag ? 1u : 0u);
+            acc_flag = true;
+          }
+          umma_commit(&T.empty[si]);
+          if (last_of_piece) {
+            umma_commit(&T.acc_full[ab]);
+            aph[ab] ^= 1u;
+            ab ^= 1;
+            ++pieces;
+          }
+          TC_ADD(tm_c, tmm);
+        }
+        piece_open = !last_of_piece;
+        if (++si == NS) { si = 0; ph ^= 1u; }
       }
 #ifdef B200_TIMERS
-      if (P.debug) { P.debug[v * 16 + 4] = tm_a; P.debug[v * 16 + 5] = tm_b; P.debug[v * 16 + 6] = clock64() - tm_begin; }
+      if (P.debug && !copier) { P.debug[v * 16 + 4] = tm_a; P.debug[v * 16 + 5] = tm_b; P.debug[v * 16 + 6] = clock64() - tm_begin; P.debug[v * 16 + 10] = tm_c; P.debug[v * 16 + 12] = n1 + n2; }
+      if (P.debug && copier) { P.debug[v * 16 + 11] = tm_d; P.debug[v * 16 + 13] = tm_a; }
 #endif
     }
     __syncwarp();

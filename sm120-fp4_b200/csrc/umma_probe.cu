@@ -91,15 +91,15 @@ __global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict
 
 // Issue-cost measurement of the tcgen05 operations the kernels use: `reps` rounds of {ncp scale copies, nmma MMAs of
 // shape 128 x N x 64}, optionally alternating between two accumulators, timed with clock64 around issue + commit + wait.
-__global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, long long* __restrict__ cycles) {
+__global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, int ncommit, long long* __restrict__ cycles) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, bar2;
   __shared__ uint32_t tmem_base;
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
   for (int i = tid; i < (32768 + 4096) / 16; i += 128) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (tid == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_mbar_init(); }
+  if (tid == 0) { mbar_init(&bar, 1); mbar_init(&bar2, 1); abort_flag = 0; fence_mbar_init(); }
   if (warp == 0) { tmem_alloc(&tmem_base, 512); tmem_relinquish(); }
   fence_proxy_async();
   tc_fence_before();
@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, 
       for (int m = 0; m < nmma; ++m)
         umma_mxf4nvf4(tb + (two_acc ? 128 * (m & 1) : 0), smem_desc_sw128_kmajor(sA) + 2 * (m & 3), smem_desc_sw128_kmajor(sB) + 2 * (m & 3), idesc,
                       tb + 256 + 4 * (m & 3), tb + 272 + 4 * (m & 3), 1u);
+      for (int c = 0; c < ncommit; ++c) umma_commit(&bar2);
     }
     const long long t1 = clock64();
     umma_commit(&bar);
@@ -133,11 +134,11 @@ __global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, 
 using namespace b200;
 
 // cycles_dev[0] = cycles to issue, cycles_dev[1] = cycles until everything completed (device int64 x 2)
-extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, long long* cycles_dev, void* stream) {
-  if (!cycles_dev || N < 16 || N > 128 || N % 16 || reps < 1 || reps > 4096 || ncp < 0 || ncp > 64 || nmma < 0 || nmma > 64) return B200MOE_ERR_ARG;
+extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, int ncommit, long long* cycles_dev, void* stream) {
+  if (!cycles_dev || N < 16 || N > 128 || N % 16 || reps < 1 || reps > 4096 || ncp < 0 || ncp > 64 || nmma < 0 || nmma > 64 || ncommit < 0 || ncommit > 8) return B200MOE_ERR_ARG;
   const int smem = 1024 + 32768 + 4096;
   B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_cost, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  k_umma_cost<<<1, 128, smem, (cudaStream_t)stream>>>(N, reps, ncp, nmma, two_acc, cycles_dev);
+  k_umma_cost<<<1, 128, smem, (cudaStream_t)stream>>>(N, reps, ncp, nmma, two_acc, ncommit, cycles_dev);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
