@@ -62,8 +62,10 @@ void b200moe_layer_destroy(b200moe_layer* layer);
 long long b200moe_layer_workspace_bytes(const b200moe_layer* layer);
 int b200moe_layer_workspace_init(const b200moe_layer* layer, void* workspace, long long workspace_bytes, void* stream);
 int b200moe_layer_sm_count(const b200moe_layer* layer);
-/* tcgen05 decode path: kernel-native copies built once per layer into caller-owned device memory (the counterpart of the
- * load-time re-layout in sm120fp4/vllm_backend.py:193-206). After prepack, b200moe_decode_forward runs the tcgen05 kernel;
+/* tcgen05 decode path: the kernel-native weight copy - every (expert, block, K box) tile as one contiguous 18 KB record of
+ * codes (shared-memory image) + scale tiles - built once per layer into caller-owned device memory of about the size of
+ * the weights (the counterpart of the load-time re-layout in sm120fp4/vllm_backend.py:193-206; the caller may drop the
+ * checkpoint-layout codes afterwards if it only decodes). After prepack, b200moe_decode_forward runs the tcgen05 kernel;
  * b200moe_layer_set_decode_impl picks 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel; b200moe_layer_set_act_scale
  * sets the global scale of the first NVFP4 term of the FC1->FC2 activations (default 8). */
 long long b200moe_layer_prepack_bytes(const b200moe_layer* layer);
@@ -93,6 +95,13 @@ int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void
  * reference GEMM of sm120fp4/reference.py:133-137. */
 int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
                        const unsigned* knobs, int* status_dev, void* stream);
+
+/* HBM streaming floor of the kernels' access patterns, no math (the reference's k_stream probe,
+ * sm120fp4/kernels/micro_floor.py:59-95): pattern 0 = 128-byte x box_rows TMA boxes from a row-major matrix of `pitch`
+ * bytes per row, pattern 1 = contiguous tiles of tile_bytes by 1-D bulk copies; `stages` ring slots, `producers` issuing
+ * threads per CTA, one CTA per SM. Time it with events around the call. */
+int b200moe_stream_probe(const void* buf, long long bytes, int pattern, int pitch, int box_rows, int tile_bytes, int stages,
+                         int producers, int* status_dev, void* stream);
 
 /* issue-cost measurement of tcgen05 scale copies and MMAs (diagnostic; no counterpart in the reference): cycles_dev[0] =
  * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64, ncommit commits}, cycles_dev[1] = cycles until all completed. */

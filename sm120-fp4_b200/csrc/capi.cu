@@ -57,16 +57,15 @@ struct b200moe_layer {
   long long s1_stride, s2_stride;
   // workspace layout (byte offsets)
   long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, off_debug, ws_bytes;
-  long long off_xq, off_xsf, off_xscale, off_aq, off_asf;   // operands of the tcgen05 decode kernel
+  long long off_xb, off_xscale, off_aslab;   // operands of the tcgen05 decode kernel
   int umax_cap;
   // tcgen05 decode path: composed FC1 scale tiles + alpha2 reference in a caller-owned buffer (b200moe_layer_prepack)
-  const uint8_t* s1t;
+  const uint8_t* w1t;
+  const uint8_t* w2t;
   const float* alpha2_ref;
   long long prepack_bytes;
   int decode_impl;      // 0 auto (tcgen05 when prepacked), 1 legacy mma.sync kernel, 2 tcgen05 kernel
   float act_g1;
-  const void* maps_ws;  // workspace the cached operand tensor maps below were encoded for
-  CUtensorMap tmx[3], tma[3];
 };
 
 static inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
@@ -127,13 +126,11 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   L->off_tables = o, o = align_up(o + (long long)(2 * L->umax_cap + 1 + 16 * top_k) * 4, 256);
   L->off_actbf16 = o, o = align_up(o + (long long)16 * top_k * I * 2, 256);
   L->off_debug = o, o = align_up(o + (long long)V * 16 * 8, 256);
-  L->off_xq = o, o = align_up(o + 64LL * (H / 2), 256);
-  L->off_xsf = o, o = align_up(o + (long long)L->KT1 * 512, 256);
+  L->off_xb = o, o = align_up(o + (long long)L->KB1 * 64 * 128 + (long long)L->KT1 * 512, 256);
   L->off_xscale = o, o += 256;
-  L->off_aq = o, o = align_up(o + (long long)L->umax_cap * 64 * (I / 2), 256);
-  L->off_asf = o, o = align_up(o + (long long)L->umax_cap * L->KT2 * 512, 256);
+  L->off_aslab = o, o = align_up(o + (long long)L->umax_cap * L->KB2 * (64 * 128 + 2048), 256);
   L->ws_bytes = o;
-  L->prepack_bytes = align_up((long long)E * L->CB1 * L->KT1 * 512, 256) + 256;
+  L->prepack_bytes = (long long)E * ((long long)L->CB1 * L->KB1 + (long long)L->NB2 * L->KB2) * 18432 + 256;
   L->act_g1 = 8.0f;
   *out = L;
   return B200MOE_OK;
@@ -155,20 +152,25 @@ extern "C" int b200moe_layer_workspace_init(const b200moe_layer* L, void* ws, lo
 // ---- tcgen05 decode path -------------------------------------------------------------------------------------------
 extern "C" long long b200moe_layer_prepack_bytes(const b200moe_layer* L) { return L ? L->prepack_bytes : B200MOE_ERR_ARG; }
 
-// Build the kernel-native copies the tcgen05 decode kernel reads - FC1 scale tiles composed per (expert, 64-column block)
-// and the alpha2 normaliser - into `buffer` (caller-owned device memory of b200moe_layer_prepack_bytes bytes that must
+// Build the kernel-native copy the tcgen05 decode kernel streams - every weight tile as one contiguous 18 KB record (codes
+// in their shared-memory image + scale tiles) - and the alpha2 normaliser into `buffer` (caller-owned device memory of b200moe_layer_prepack_bytes bytes that must
 // outlive the handle). Once per layer, like the layout rotation the reference does at load (vllm_backend.py:193-206).
 extern "C" int b200moe_layer_prepack(b200moe_layer* L, void* buffer, long long buffer_bytes, void* stream) {
   if (!L || !buffer) return B200MOE_ERR_ARG;
   if (buffer_bytes < L->prepack_bytes) return B200MOE_ERR_WORKSPACE;
   if ((uintptr_t)buffer & 255) return B200MOE_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = b200_compose_fc1_scales_launch(L->s1, buffer, L->E, L->I, L->KT1, L->s1_stride, st);
+  uint8_t* w1t = (uint8_t*)buffer;
+  uint8_t* w2t = w1t + (long long)L->E * L->CB1 * L->KB1 * 18432;
+  int rc = b200_pack_tiles_launch(L->q1, L->s1, w1t, L->E, 2 * L->I, L->H / 2, L->CB1, L->KB1, L->KT1, 1, L->I, L->s1_stride, st);
   if (rc != B200MOE_OK) return rc;
-  float* ref = (float*)((uint8_t*)buffer + align_up((long long)L->E * L->CB1 * L->KT1 * 512, 256));
+  rc = b200_pack_tiles_launch(L->q2, L->s2, w2t, L->E, L->H, L->I / 2, L->NB2, L->KB2, L->KT2, 0, L->I, L->s2_stride, st);
+  if (rc != B200MOE_OK) return rc;
+  float* ref = (float*)(w2t + (long long)L->E * L->NB2 * L->KB2 * 18432);
   k_alpha_ref<<<1, 1, 0, st>>>(L->alpha2, L->E, ref);
   B200_LAUNCH_CHECK();
-  L->s1t = (const uint8_t*)buffer;
+  L->w1t = w1t;
+  L->w2t = w2t;
   L->alpha2_ref = ref;
   return B200MOE_OK;
 }
@@ -176,7 +178,7 @@ extern "C" int b200moe_layer_prepack(b200moe_layer* L, void* buffer, long long b
 // 0: tcgen05 kernel when the layer is prepacked, else the mma.sync kernel; 1: mma.sync kernel; 2: tcgen05 kernel.
 extern "C" int b200moe_layer_set_decode_impl(b200moe_layer* L, int impl) {
   if (!L || impl < 0 || impl > 2) return B200MOE_ERR_ARG;
-  if (impl == 2 && !L->s1t) return B200MOE_ERR_ARG;
+  if (impl == 2 && !L->w1t) return B200MOE_ERR_ARG;
   L->decode_impl = impl;
   return B200MOE_OK;
 }
@@ -194,23 +196,13 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   cudaStream_t st = (cudaStream_t)stream;
   const int nbv = M <= 4 ? 0 : M <= 8 ? 1 : 2;
   const int N = 16 << nbv;
-  if (L->maps_ws != ws) {   // operand tensor maps point into the workspace: encode once per workspace
-    for (int i = 0; i < 3; ++i) {
-      const int n = 16 << i;
-      int rc = make_codes_map(&L->tmx[i], w + L->off_xq, n, L->H / 2, n);
-      if (rc == B200MOE_OK) rc = make_codes_map(&L->tma[i], w + L->off_aq, (long long)L->umax_cap * n, L->I / 2, n);
-      if (rc != B200MOE_OK) return rc;
-    }
-    L->maps_ws = ws;
-  }
-  int rc = b200_expand_x_launch(x, M, L->H, N, w + L->off_xq, w + L->off_xsf, (float*)(w + L->off_xscale), st);
+  int rc = b200_expand_x_launch(x, M, L->H, N, L->KB1, w + L->off_xb, (float*)(w + L->off_xscale), st);
   if (rc != B200MOE_OK) return rc;
   DecodeTcParams p;
   memset(&p, 0, sizeof(p));
-  p.tm1 = L->tm1, p.tm2 = L->tm2, p.tmx = L->tmx[nbv], p.tma = L->tma[nbv];
-  p.s1t = L->s1t, p.s2 = (const uint8_t*)L->s2, p.alpha1 = L->alpha1, p.alpha2 = L->alpha2, p.alpha2_ref = L->alpha2_ref;
-  p.xsf = w + L->off_xsf, p.xscale = (const float*)(w + L->off_xscale);
-  p.aq = w + L->off_aq, p.asf = w + L->off_asf;
+  p.w1t = L->w1t, p.w2t = L->w2t, p.alpha1 = L->alpha1, p.alpha2 = L->alpha2, p.alpha2_ref = L->alpha2_ref;
+  p.xb = w + L->off_xb, p.xscale = (const float*)(w + L->off_xscale);
+  p.aslab = w + L->off_aslab;
   p.ids = ids, p.wts = wts, p.out = (__nv_bfloat16*)out;
   p.scratch = (float*)(w + L->off_scratch);
   p.cnt1 = (unsigned*)(w + L->off_cnt1), p.cnt2 = (unsigned*)(w + L->off_cnt2);
@@ -219,7 +211,6 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   p.experts_out = (int*)(w + L->off_tables);
   p.offsets_out = p.experts_out + L->umax_cap;
   p.pairs_out = p.offsets_out + L->umax_cap + 1;
-  p.s2_expert_stride = L->s2_stride;
   p.debug = (long long*)(w + L->off_debug);
   p.act_g1 = L->act_g1;
   p.M = M, p.E = L->E, p.H = L->H, p.I = L->I, p.top_k = L->top_k;
@@ -291,7 +282,7 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
 // Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
 extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                                       int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
-  if (L && L->s1t && L->decode_impl != 1 && 2 * L->sms <= 512) {
+  if (L && L->w1t && L->decode_impl != 1 && L->sms <= 256) {
     if (!x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0) return B200MOE_ERR_ARG;
     if (M > 16) return B200MOE_ERR_LIMIT;
     if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;

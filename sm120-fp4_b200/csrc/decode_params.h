@@ -42,19 +42,14 @@ struct DecodeParams {
 
 // Parameter block of the tcgen05 decode kernel (k_moe_decode_tc).
 struct DecodeTcParams {
-  CUtensorMap tm1;   // FC1 codes [E*2I, H/2], box 128 B x 64 rows
-  CUtensorMap tm2;   // FC2 codes [E*H, I/2], box 128 B x 128 rows
-  CUtensorMap tmx;   // expanded x operand [N, H/2], box 128 B x N rows
-  CUtensorMap tma;   // expanded activation operand [Umax*N, I/2], box 128 B x N rows
-  const uint8_t* s1t;        // FC1 scale tiles composed per (expert, 64-column block): [E][I/64][KT1][512]
-  const uint8_t* s2;         // FC2 scales, 128x4 swizzle per expert
+  const uint8_t* w1t;        // FC1 tile records [E][I/64][KB1][18432]: codes image + scale tiles (k_pack_tiles)
+  const uint8_t* w2t;        // FC2 tile records [E][H/128][KB2][18432]
   const float* alpha1;
   const float* alpha2;
   const float* alpha2_ref;   // [0] = max over experts of alpha2, [1] = its reciprocal
-  const uint8_t* xsf;        // scale tiles of the expanded x operand [KT1][512]
+  const uint8_t* xb;         // expanded x operand: [KB1][N][128 B] images then [KT1][512] scale tiles
   const float* xscale;       // 1 / g_t per column of the x operand [N]
-  uint8_t* aq;               // expanded activations (FC2 operand) [Umax][N][I/2]
-  uint8_t* asf;              // their scale tiles [Umax][KT2][512]
+  uint8_t* aslab;            // expanded activations (FC2 operand): [Umax][KB2] slabs of N*128 + 2048 bytes
   const int* ids;
   const float* wts;
   __nv_bfloat16* out;
@@ -66,7 +61,6 @@ struct DecodeTcParams {
   int* experts_out;
   int* offsets_out;
   int* pairs_out;
-  long long s2_expert_stride;
   long long* debug;          // per-worker cycle counters (timer build only), 16 per worker
   float act_g1;              // global scale of the first activation term
   int M, E, H, I, top_k, Umax;
@@ -77,8 +71,9 @@ struct DecodeTcParams {
 }  // namespace b200
 
 int b200_decode_tc_smem_bytes(int NS, int region_bytes);
-int b200_expand_x_launch(const void* x, int M, int H, int N, void* xq, void* xsf, float* colscale, cudaStream_t st);
-int b200_compose_fc1_scales_launch(const void* s1, void* s1t, int E, int I, int KT, long long s1_stride, cudaStream_t st);
+int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, cudaStream_t st);
+int b200_pack_tiles_launch(const void* q, const void* sf, void* out, int E, int rows_per_expert, int row_bytes, int blocks, int KB, int KT,
+                           int fc1, int I, long long sf_stride, cudaStream_t st);
 int b200_decode_tc_launch(const b200::DecodeTcParams& p, int grid, int smem_bytes, cudaStream_t st);
 int b200_decode_smem_bytes(int NS, int region_bytes);
 int b200_decode_launch(const b200::DecodeParams& p, int grid, int smem_bytes, cudaStream_t st);

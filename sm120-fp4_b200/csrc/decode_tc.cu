@@ -22,7 +22,7 @@
 
 namespace b200 {
 
-constexpr int kTcProducers = 4;    // TMA producer warps: one thread issues roughly one bulk operation per 100 cycles
+constexpr int kTcProducers = 2;    // TMA producer warps: one thread issues only ~2.5 M bulk operations per second
 constexpr int kTcThreads = (4 + 2 + kTcProducers) * 32;   // epilogue warps 0-3, MMA warp 4, scale-copy warp 5, producers 6..
 constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
 constexpr int kTerms = 4;
@@ -125,11 +125,13 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
 
 // ------------------------------------------------------------------------------------------------ x -> B operand
 // One block per token slot (N/4 slots): token amax, then every 16-value block expanded into four NVFP4 terms.
-// xq u8 [N, H/2] (row = token*4 + term), xsf: 128x4-swizzled over [128, H/16] (rows >= N zero), colscale f32 [N] = 1/g_t.
-__global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, uint8_t* __restrict__ xq,
-                                                  uint8_t* __restrict__ xsf, float* __restrict__ colscale) {
+// xb: the FC1 B operand exactly as the kernel wants it in shared memory, so that ONE bulk copy brings it in:
+//   [KB1 boxes][N rows (token*4 + term)][128 B] in the 128-byte-swizzle image (16-byte chunk c of row n sits at chunk
+//   c ^ (n & 7)), followed by KT1 scale tiles of 512 B (128x4 order, rows >= N zero). colscale f32 [N] = 1/g_t.
+__global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
+                                                  float* __restrict__ colscale) {
   const int tok = blockIdx.x, tid = threadIdx.x;
-  const int nkt = (H / 16 + 3) / 4;
+  uint8_t* xsf = xb + (long long)KB1 * N * 128;
   __shared__ float wm[8];
   __shared__ float s_g1;
   float m = 0.f;
@@ -148,10 +150,10 @@ __global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restric
   }
   __syncthreads();
   const float g1 = s_g1;
-  for (int b = tid; b < H / 16; b += 256) {
+  for (int b = tid; b < KB1 * 16; b += 256) {   // 16-value blocks over the padded K (KB1 * 256 values)
     uint2 codes[kTerms];
     uint8_t sf[kTerms];
-    if (tok < M) {
+    if (tok < M && b * 16 < H) {
       float r[16];
       const uint4 v0 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16);
       const uint4 v1 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16 + 8);
@@ -163,33 +165,53 @@ __global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restric
 #pragma unroll
       for (int t = 0; t < kTerms; ++t) { codes[t] = make_uint2(0u, 0u); sf[t] = 0; }
     }
+    const int kb = b >> 4, chunk = (b & 15) >> 1, half = b & 1;   // 8 code bytes = half a 16-byte chunk
 #pragma unroll
     for (int t = 0; t < kTerms; ++t) {
       const int n = tok * kTerms + t;
-      *reinterpret_cast<uint2*>(xq + (long long)n * (H / 2) + b * 8) = codes[t];
-      xsf[(long long)(b >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (b & 3)] = sf[t];
+      *reinterpret_cast<uint2*>(xb + ((long long)kb * N + n) * 128 + ((chunk ^ (n & 7)) << 4) + half * 8) = codes[t];
+      if ((b >> 2) < (H / 16 + 3) / 4) xsf[(long long)(b >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (b & 3)] = sf[t];
     }
   }
-  (void)nkt;
 }
 
-// ------------------------------------------------------------------------------------------------ FC1 scale tiles
-// FC1 multiplies 64 up rows and the 64 matching gate rows in one 128-row MMA; its scale tile must hold those 128 rows.
-// s1 (128x4 swizzle over the [2I, H/16] scales of one expert) -> s1t [E][I/64][KT][512]: rows 0..63 = up rows 64cb..,
-// rows 64..127 = gate rows I+64cb.., in the same 128x4 in-tile order. Done once when the layer is created.
-__global__ void __launch_bounds__(256) k_compose_fc1_scales(const uint8_t* __restrict__ s1, uint8_t* __restrict__ s1t, int E, int I,
-                                                            int KT, long long s1_expert_stride) {
-  const int CB = I / 64;
-  const long long total = (long long)E * CB * KT * 128;   // one thread per (tile, row): 4 bytes
+// ------------------------------------------------------------------------------------------------ weight tiles
+// Kernel-native weight layout, built once per layer: every (expert, block, K box) tile is ONE contiguous 18 KB record =
+// the shared-memory image of its 128 rows x 128 B of codes (128-byte swizzle) followed by its four 512 B scale tiles, so
+// a single bulk copy per tile streams it at full HBM rate (one thread issues only ~2.5 M TMA operations per second,
+// whatever their size; 2-D boxes from the checkpoint layout need 3-4 operations per tile).
+//   FC1 record (e, cb, kb): rows 0..63 = up rows 64cb.., rows 64..127 = gate rows I+64cb..; scale rows likewise.
+//   FC2 record (e, nb, kb): rows = output rows 128nb...
+__global__ void __launch_bounds__(256) k_pack_tiles(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf, uint8_t* __restrict__ out,
+                                                    int E, int rows_per_expert, int row_bytes, int blocks, int KB, int KT, int fc1, int I,
+                                                    long long sf_expert_stride) {
+  const long long records = (long long)E * blocks * KB;
+  const long long total = records * (1024 + 128);   // 1024 code chunks of 16 B + 128 scale rows x 16 B
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i % 128);
-    const int kt = (int)((i / 128) % KT);
-    const int cb = (int)((i / (128LL * KT)) % CB);
-    const int e = (int)(i / (128LL * KT * CB));
-    const int src_row = r < 64 ? 64 * cb + r : I + 64 * cb + (r - 64);
-    const uint8_t* src = s1 + e * s1_expert_stride + ((long long)(src_row >> 7) * KT + kt) * 512 + (src_row & 31) * 16 + ((src_row & 127) >> 5) * 4;
-    uint8_t* dst = s1t + (((long long)(e * CB + cb) * KT + kt) * 512) + (r & 31) * 16 + (r >> 5) * 4;
-    *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+    const long long rec = i / 1152;
+    const int w = (int)(i % 1152);
+    const int kb = (int)(rec % KB), blk = (int)((rec / KB) % blocks), e = (int)(rec / ((long long)KB * blocks));
+    uint8_t* dst = out + rec * kTcStage;
+    if (w < 1024) {
+      const int r = w >> 3, c = w & 7;
+      const int src_row = fc1 ? (r < 64 ? 64 * blk + r : I + 64 * blk + (r - 64)) : 128 * blk + r;
+      const int byte = kb * 128 + c * 16;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (byte < row_bytes) v = *reinterpret_cast<const uint4*>(q + ((long long)e * rows_per_expert + src_row) * row_bytes + byte);
+      *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    } else {
+      const int r = w - 1024;   // scale row of the record: four K tiles x 4 bytes
+      const int src_row = fc1 ? (r < 64 ? 64 * blk + r : I + 64 * blk + (r - 64)) : 128 * blk + r;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kt = 4 * kb + j;
+        uint32_t v = 0;
+        if (kt < KT)
+          v = *reinterpret_cast<const uint32_t*>(sf + e * sf_expert_stride + ((long long)(src_row >> 7) * KT + kt) * 512 + (src_row & 31) * 16 +
+                                                 ((src_row & 127) >> 5) * 4);
+        *reinterpret_cast<uint32_t*>(dst + 16384 + j * 512 + (r & 31) * 16 + (r >> 5) * 4) = v;
+      }
+    }
   }
 }
 
@@ -282,29 +304,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 #endif
   const uint32_t tmem = T.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
-  uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand
+  uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand (same bulk copy)
 
   if (warp >= 6) {
     // ============================================================== TMA producers (one thread each)
     if (lane == 0) {
       const int pw = warp - 6;
-      prefetch_tensormap(&P.tm1);
-      prefetch_tensormap(&P.tm2);
       const uint64_t pol = policy_evict_first();
-      // the resident B operand of FC1: x expanded into NVFP4 terms, one box per K box, and its scale tiles
+      // the resident B operand of FC1 (x expanded into NVFP4 terms) and its scale tiles: one bulk copy
       if (pw == 0 && n1 > 0) {
         mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
-        for (int kb = 0; kb < KB1; ++kb) tma_load_2d(region + kb * (N * 128), &P.tmx, 128 * kb, 0, &T.xb_full);
-        bulk_load(xb_sf, P.xsf, P.KT1 * 512, &T.xb_full);
+        bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
       }
       const unsigned gen0 = T.gen0;
       bool passed = false;
-      int pend_slot[4], pend_u[4], pend_kb[4], npend = 0;
-      auto load_slab = [&](int slot, int u, int kb) {
-        uint8_t* dst = region + slot * kSlab;
-        tma_load_2d(dst, &P.tma, 128 * kb, u * N, &T.full[slot]);
-        const int nkt = min(4, P.KT2 - 4 * kb);
-        bulk_load(dst + N * 128, P.asf + ((long long)u * P.KT2 + 4 * kb) * 512, nkt * 512, &T.full[slot]);
+      int pend_slot[4], pend_idx[4], npend = 0;
+      auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
+        bulk_load(region + slot * kSlab, P.aslab + (long long)idx * kSlab, kSlab, &T.full[slot]);
       };
       auto wait_grid = [&]() {
         if (passed) return;
@@ -316,7 +332,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         }
         if (!ok) { T.abort_flag = 1; *P.status = 3; }
         fence_proxy_async();
-        for (int i = 0; i < npend; ++i) load_slab(pend_slot[i], pend_u[i], pend_kb[i]);
+        for (int i = 0; i < npend; ++i) load_slab(pend_slot[i], pend_idx[i]);
         npend = 0;
         passed = true;
       };
@@ -336,22 +352,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           const int f = f1 + j;
           const int kb = f % KB1, q = f / KB1, cb = q % CB1, u = q / CB1;
           const int e = T.experts[u];
-          const int nkt = min(4, P.KT1 - 4 * kb);
-          mbar_expect_tx(&T.full[slot], 16384 + nkt * 512);
-          tma_load_2d_hint(st, &P.tm1, 128 * kb, e * 2 * P.I + 64 * cb, &T.full[slot], pol);
-          tma_load_2d_hint(st + 8192, &P.tm1, 128 * kb, e * 2 * P.I + P.I + 64 * cb, &T.full[slot], pol);
-          bulk_load_hint(st + 16384, P.s1t + (((long long)e * CB1 + cb) * P.KT1 + 4 * kb) * 512, nkt * 512, &T.full[slot], pol);
+          mbar_expect_tx(&T.full[slot], kTcStage);
+          bulk_load_hint(st, P.w1t + (((long long)e * CB1 + cb) * KB1 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
         } else {
           const int f = f2 + (j - n1);
           const int kb = f % KB2, q = f / KB2, u = q % U, nb = q / U;
           const int e = T.experts[u];
-          const int nkt = min(4, P.KT2 - 4 * kb);
-          mbar_expect_tx(&T.full[slot], 16384 + nkt * 512 + N * 128 + nkt * 512);
-          tma_load_2d_hint(st, &P.tm2, 128 * kb, e * P.H + 128 * nb, &T.full[slot], pol);
-          bulk_load_hint(st + 16384, P.s2 + (long long)e * P.s2_expert_stride + ((long long)nb * P.KT2 + 4 * kb) * 512, nkt * 512,
-                         &T.full[slot], pol);
-          if (passed) load_slab(slot, u, kb);
-          else { pend_slot[npend] = slot; pend_u[npend] = u; pend_kb[npend] = kb; ++npend; }
+          mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
+          bulk_load_hint(st, P.w2t + (((long long)e * NB2 + nb) * KB2 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
+          if (passed) load_slab(slot, u * KB2 + kb);
+          else { pend_slot[npend] = slot; pend_idx[npend] = u * KB2 + kb; ++npend; }
         }
       }
       if (npend > 0) wait_grid();
@@ -381,6 +391,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
         tc_fence_after();
       }
+#ifdef B200_TIMERS
+      if (P.debug && !copier) P.debug[v * 16 + 14] = clock64() - tm_begin;   // x operand landed
+      bool first_stamp = true;
+#endif
       while (f1 < fe1 || f2 < fe2) {
         const bool is1 = f1 < fe1;
         const uint32_t st = smem_u32(ring + si * kTcStage);
@@ -431,6 +445,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
           TC_ADD(tm_a, t1);
           tc_fence_after();
+#ifdef B200_TIMERS
+          if (P.debug && first_stamp) { P.debug[v * 16 + 15] = clock64() - tm_begin; first_stamp = false; }   // first tile ready for MMA
+#endif
           TC_T0(tmm);
           for (int jj = 0; jj < nkt; ++jj) {
             umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(b_addr) + 2 * jj, idesc,
@@ -468,6 +485,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       TC_T0(t0);
       if (!mbar_wait(&T.acc_full[ab], aph[ab], &T.abort_flag)) *P.status = 7;
       TC_ADD(tm_a, t0);
+#ifdef B200_TIMERS
+      if (tm_d == 0) tm_d = clock64() - tm_begin;   // first accumulator ready
+#endif
       tc_fence_after();
 #pragma unroll
       for (int c0 = 0; c0 < N; c0 += 16) {
@@ -587,7 +607,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           // here only gets zero scale bytes (a zero scale silences whatever codes the row holds)
           if (et < N) {
             const int tk = et >> 2, blk = et & 3;
-            uint8_t* sfp = P.asf + ((long long)u * P.KT2 + cb) * 512 + blk;
+            uint8_t* slab = P.aslab + ((long long)u * KB2 + (cb >> 2)) * kSlab;   // slab of K box cb/4
+            uint8_t* sfp = slab + N * 128 + (cb & 3) * 512 + blk;
+            const int chunk = 2 * (cb & 3) + (blk >> 1);                        // 16-byte chunk of the row's 128 bytes
             if (s_w[tk] != 0.f) {
               float r[16];
 #pragma unroll
@@ -598,7 +620,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 #pragma unroll
               for (int t = 0; t < kTerms; ++t) {
                 const int n = tk * kTerms + t;
-                *reinterpret_cast<uint2*>(P.aq + ((long long)u * N + n) * (P.I / 2) + (64 * cb + 16 * blk) / 2) = codes[t];
+                *reinterpret_cast<uint2*>(slab + n * 128 + ((chunk ^ (n & 7)) << 4) + (blk & 1) * 8) = codes[t];
                 sfp[(n & 31) * 16 + (n >> 5) * 4] = sf[t];
               }
             } else {
@@ -646,7 +668,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         const int pe = min(fe, (nb + 1) * per_nb);
         float val[16];
         load_terms(val, cs, false);
-        TC_T0(tfix2);
         const int vlo = tc_worker_of(nb * per_nb, T2, V), vhi = tc_worker_of((nb + 1) * per_nb - 1, T2, V);
         const bool last = publish(val, f == fs ? 0 : 1, P.cnt2 + nb, T.sb2, vlo, vhi);
         if (last) {
@@ -656,7 +677,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             if (tk < P.M) P.out[(long long)tk * P.H + 128 * nb + row] = __float2bfloat16_rn(val[tk]);
         }
         f = pe;
-        TC_ADD(tm_d, tfix2);
       }
     }
 #ifdef B200_TIMERS
@@ -676,17 +696,20 @@ using namespace b200;
 
 int b200_decode_tc_smem_bytes(int NS, int region_bytes) { return 1024 + NS * kTcStage + region_bytes + (int)sizeof(TcTables); }
 
-int b200_expand_x_launch(const void* x, int M, int H, int N, void* xq, void* xsf, float* colscale, cudaStream_t st) {
-  k_expand_x<<<N / kTerms, 256, 0, st>>>((const __nv_bfloat16*)x, M, H, (uint8_t*)xq, (uint8_t*)xsf, colscale);
+int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, cudaStream_t st) {
+  k_expand_x<<<N / kTerms, 256, 0, st>>>((const __nv_bfloat16*)x, M, H, N, KB1, (uint8_t*)xb, colscale);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
 
-int b200_compose_fc1_scales_launch(const void* s1, void* s1t, int E, int I, int KT, long long s1_stride, cudaStream_t st) {
-  const long long total = (long long)E * (I / 64) * KT * 128;
+// q u8 [E, rows, row_bytes], sf = 128x4-swizzled scales per expert -> tile records (see k_pack_tiles)
+int b200_pack_tiles_launch(const void* q, const void* sf, void* out, int E, int rows_per_expert, int row_bytes, int blocks, int KB, int KT,
+                           int fc1, int I, long long sf_stride, cudaStream_t st) {
+  const long long total = (long long)E * blocks * KB * 1152;
   long long g = (total + 255) / 256;
-  if (g > 148 * 16) g = 148 * 16;
-  k_compose_fc1_scales<<<(int)g, 256, 0, st>>>((const uint8_t*)s1, (uint8_t*)s1t, E, I, KT, s1_stride);
+  if (g > 148 * 32) g = 148 * 32;
+  k_pack_tiles<<<(int)g, 256, 0, st>>>((const uint8_t*)q, (const uint8_t*)sf, (uint8_t*)out, E, rows_per_expert, row_bytes, blocks, KB, KT, fc1,
+                                       I, sf_stride);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
