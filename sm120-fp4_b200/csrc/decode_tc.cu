@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "decode_params.h"
+#include <string.h>
 
 namespace b200 {
 
@@ -39,7 +40,7 @@ struct TcTables {
   volatile int abort_flag;
   int last_flag;
   uint32_t tmem_base;
-  uint64_t full[8], empty[8], sfr[8];   // stage landed / stage consumed / scale tiles of the stage are in TMEM
+  uint64_t full[12], empty[12], sfr[12];   // stage landed / stage consumed / scale tiles of the stage are in TMEM
   uint64_t acc_full[2], acc_empty[2];
   uint64_t xb_full;
 };
@@ -131,6 +132,7 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
 __global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
                                                   float* __restrict__ colscale) {
   const int tok = blockIdx.x, tid = threadIdx.x;
+  grid_launch_dependents();   // the layer kernel may start its prologue and weight prefetch now; it waits before reading xb
   uint8_t* xsf = xb + (long long)KB1 * N * 128;
   __shared__ float wm[8];
   __shared__ float s_g1;
@@ -255,7 +257,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     T.wts[p] = P.wts[p];
     atomicAdd(&T.cnt[e], 1);
   }
-  for (int i = tid; i < N; i += kTcThreads) T.colscale[i] = P.xscale[i];
   __syncthreads();
   if (warp == 0) {
     int c[8], f[8], sc = 0, sf = 0;
@@ -278,7 +279,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   for (int i = tid; i < kTcMaxE; i += kTcThreads)
     if (T.cnt[i] > 0) T.experts[T.uidx[i] - 1] = i;
   for (int v = tid; v <= V; v += kTcThreads) {
-    T.sb1[v] = (int)(((unsigned)v * (unsigned)T1) / (unsigned)V);
+    // FC1 shares are whole units (an expert's 64-column block over all of K): no unit is split, so FC1 needs no cross-CTA
+    // reduction; the imbalance is at most one unit. FC2 output blocks are reduced over experts anyway: tile-granular shares.
+    T.sb1[v] = (int)(((unsigned)v * (unsigned)(U * CB1)) / (unsigned)V) * KB1;
     T.sb2[v] = (int)(((unsigned)v * (unsigned)T2) / (unsigned)V);
   }
   tc_fence_before();
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const long long tm_begin = clock64();
 #endif
   const uint32_t tmem = T.tmem_base;
-  const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 256;   // accumulators 2 x 64 | weight scales NS x 16 | operand scales NS x 16
+  const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 320;   // accumulators 2 x 64 | weight scales NS x 16 (<= 192) | operand scales (<= 192)
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand (same bulk copy)
 
   if (warp >= 6) {
@@ -313,12 +316,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       const uint64_t pol = policy_evict_first();
       // the resident B operand of FC1 (x expanded into NVFP4 terms) and its scale tiles: one bulk copy
       if (pw == 0 && n1 > 0) {
+        grid_dependency_wait();   // the x operand comes from the expansion kernel launched just before this one
         mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
         bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
       }
       const unsigned gen0 = T.gen0;
       bool passed = false;
-      int pend_slot[4], pend_idx[4], npend = 0;
+      int pend_slot[8], pend_idx[8], npend = 0;
       auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
         bulk_load(region + slot * kSlab, P.aslab + (long long)idx * kSlab, kSlab, &T.full[slot]);
       };
@@ -479,6 +483,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     const int row = quad * 32 + lane;              // accumulator row (MMA M index)
     __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
     __shared__ float s_w[16];
+    grid_dependency_wait();
+    if (et < N) T.colscale[et] = P.xscale[et];
+    named_bar_sync(1, 128);
     int ab = 0;
     uint32_t aph[2] = {0, 0};
     auto load_terms = [&](float (&val)[16], const float* cs, bool per_column) {   // sum the four term columns of every token
@@ -723,6 +730,14 @@ int b200_decode_tc_launch(const DecodeTcParams& p, int grid, int smem_bytes, cud
     B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     configured[which] = smem_bytes;
   }
-  B200_CUDA_TRY(cudaLaunchKernel(fn, dim3(grid), dim3(kTcThreads), args, (size_t)smem_bytes, st));
+  // programmatic dependent launch: this kernel's prologue and weight prefetch overlap the activation-expansion kernel
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kTcThreads), cfg.dynamicSmemBytes = (size_t)smem_bytes, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  B200_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, args));
   return B200MOE_OK;
 }

@@ -48,10 +48,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `abort_flag` (shared memory) lets one timed-out waiter release every other waiter of the block.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = (1u << 20)) {
   for (uint32_t it = 0; it < limit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;   // try_wait itself parks the thread until the phase flips or a hardware time-out
     if ((it & 63u) == 63u) {
       if (*abort_flag) return false;
-      __nanosleep(64);
+      if (it > 4096u) __nanosleep(64);
     }
   }
   *abort_flag = 1;
@@ -146,6 +146,10 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+
+// Programmatic dependent launch: wait for the kernel this one depends on / allow the dependent kernel to start.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
