@@ -220,7 +220,7 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   int NS = 12;
   for (; NS >= 2; --NS) {
     const int region = (int)align_up(xb > NS * slab ? xb : NS * slab, 1024);
-    if (b200_decode_tc_smem_bytes(NS, region) <= 227 * 1024) { p.region_bytes = region; break; }
+    if (b200_decode_tc_smem_bytes(NS, region) <= 227 * 1024 - 6144) { p.region_bytes = region; break; }   // room for static shared memory
   }
   if (NS < 2) return B200MOE_ERR_SHAPE;
   p.NS = NS;
@@ -282,7 +282,9 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
 // Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
 extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                                       int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
-  if (L && L->w1t && L->decode_impl != 1 && L->sms <= 256 && L->KB1 <= 12) {   // x scale tiles of 12 K boxes fit TMEM
+  // automatic choice (measured on B200, Qwen3-30B-A3B shape): the mma.sync kernel is ahead up to 8 tokens (shorter latency
+  // chain), the tcgen05 kernel from 9 tokens (no CUDA-core dequantisation)
+  if (L && L->w1t && (L->decode_impl == 2 || (L->decode_impl == 0 && M > 8)) && L->sms <= 256 && L->KB1 <= 12) {   // x scale tiles of 12 K boxes fit TMEM
     if (!x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0) return B200MOE_ERR_ARG;
     if (M > 16) return B200MOE_ERR_LIMIT;
     if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
