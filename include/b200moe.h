@@ -73,6 +73,16 @@ int b200moe_layer_prepack(b200moe_layer* layer, void* buffer, long long buffer_b
 int b200moe_layer_set_decode_impl(b200moe_layer* layer, int impl);
 int b200moe_layer_set_act_scale(b200moe_layer* layer, float first_term_global_scale);
 
+/* ---- W4A4 prefill for any M <= max_tokens: the layer's own tcgen05 kind::mxf4nvf4 grouped GEMM in place of the reference's
+ * hand-off to FlashInfer's CUTLASS MoE (sm120fp4/vllm_backend.py:123-145 enable_cutlass_prefill, :161-168 the call); the
+ * arithmetic is the reference's W4A4 oracle (sm120fp4/kernels/bench_moe_baseline.py:53-74, act_quant=True). Needs
+ * b200moe_layer_prepack. gs_x, gs_a: global scales of the two activation quantisations (1 / input scales). */
+long long b200moe_prefill_workspace_bytes(const b200moe_layer* layer, int max_tokens);
+int b200moe_prefill_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                            void* out_bf16, void* workspace, long long workspace_bytes, int max_tokens, float gs_x, float gs_a,
+                            void* stream);
+int b200moe_prefill_status(const b200moe_layer* layer, const void* workspace, int max_tokens, void* stream);
+
 /* forward: x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]; one launch
  * (routing + FC1 + SiLU*mul + FC2 + weighted combine). Replaces Weights._slice, sm120fp4/vllm_backend.py:174-190. */
 int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,

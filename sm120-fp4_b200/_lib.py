@@ -32,6 +32,9 @@ SIGNATURES = {
     "b200moe_layer_prepack": (_I, [_P, _P, _LL, _P]),
     "b200moe_layer_set_decode_impl": (_I, [_P, _I]),
     "b200moe_layer_set_act_scale": (_I, [_P, C.c_float]),
+    "b200moe_prefill_workspace_bytes": (_LL, [_P, _I]),
+    "b200moe_prefill_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, C.c_float, C.c_float, _P]),
+    "b200moe_prefill_status": (_I, [_P, _P, _I, _P]),
     "b200moe_decode_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc1": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc2": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),

@@ -356,4 +356,44 @@ extern "C" int b200moe_layer_debug_counters(const b200moe_layer* L, const void* 
   return n;
 }
 
+// ---- W4A4 prefill (any number of tokens up to the workspace's max_tokens): own tcgen05 grouped GEMM, replacing the
+// third-party CUTLASS hand-off of sm120fp4/vllm_backend.py:123-168. Needs b200moe_layer_prepack (weight tile records).
+long long b200_prefill_workspace_bytes(int E, int H, int I, int top_k, int max_tokens);
+int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const uint8_t* w2t, const float* alpha1, const float* alpha2,
+                         const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
+                         float gs_x, float gs_a, int sms, cudaStream_t st);
+int b200_prefill_status_offset(int E, int H, int I, int top_k, int max_tokens, long long* off);
+
+extern "C" long long b200moe_prefill_workspace_bytes(const b200moe_layer* L, int max_tokens) {
+  if (!L || max_tokens <= 0) return B200MOE_ERR_ARG;
+  return b200_prefill_workspace_bytes(L->E, L->H, L->I, L->top_k, max_tokens);
+}
+
+// x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]. gs_x / gs_a: global scales of the
+// NVFP4 quantisation of x and of the SiLU*mul activations (1 / the checkpoint's input scales; 1.0 reproduces the reference's
+// own W4A4 arithmetic). The workspace must have been sized for max_tokens >= M and zeroed once.
+extern "C" int b200moe_prefill_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                                       void* out_bf16, void* workspace, long long workspace_bytes, int max_tokens, float gs_x, float gs_a,
+                                       void* stream) {
+  if (!L || !x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0 || max_tokens <= 0) return B200MOE_ERR_ARG;
+  if (!L->w1t) return B200MOE_ERR_ARG;   // not prepacked
+  if (!(gs_x > 0.f) || !(gs_a > 0.f)) return B200MOE_ERR_ARG;
+  if (((uintptr_t)workspace & 255) || ((uintptr_t)x_bf16 & 15) || ((uintptr_t)out_bf16 & 15)) return B200MOE_ERR_ARG;
+  if (L->H % 128 || L->I % 64) return B200MOE_ERR_SHAPE;
+  if (M == 0) return B200MOE_OK;
+  return b200_prefill_forward(L->E, L->H, L->I, L->top_k, L->w1t, L->w2t, L->alpha1, L->alpha2, x_bf16, topk_ids, topk_weights, M, out_bf16,
+                              workspace, workspace_bytes, max_tokens, gs_x, gs_a, L->sms, (cudaStream_t)stream);
+}
+
+// status word of the prefill workspace; synchronises the stream
+extern "C" int b200moe_prefill_status(const b200moe_layer* L, const void* workspace, int max_tokens, void* stream) {
+  if (!L || !workspace) return B200MOE_ERR_ARG;
+  long long off = 0;
+  b200_prefill_status_offset(L->E, L->H, L->I, L->top_k, max_tokens, &off);
+  int st = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&st, (const uint8_t*)workspace + off, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  return st == 0 ? B200MOE_OK : B200MOE_ERR_TIMEOUT;
+}
+
 extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }

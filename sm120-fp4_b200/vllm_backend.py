@@ -109,6 +109,41 @@ class Weights:
         except Exception:  # noqa: BLE001 - interpreter shutdown
             pass
 
+    def enable_prefill(self, a1_scale: torch.Tensor | float | None = None, a2_scale: torch.Tensor | float | None = None,
+                       max_tokens: int = 8192) -> None:
+        """Above MAXM tokens, run the layer's own W4A4 tensor-core path (NVFP4 activations) instead of slices of MAXM.
+        a1_scale / a2_scale: the checkpoint's activation input scales of FC1 and FC2 (the largest over the experts is used,
+        as in the reference's enable_cutlass_prefill, sm120fp4/vllm_backend.py:123-145); None means 1.0, the global scale
+        of the reference's own W4A4 arithmetic."""
+        def one(a):
+            if a is None:
+                return 1.0
+            v = float(torch.as_tensor(a).float().max())
+            if not (v > 0 and v == v and v != float("inf")):
+                raise ValueError("the input scales must be finite and positive")
+            return v
+        h = _lib.lib()
+        nbytes = int(h.b200moe_prefill_workspace_bytes(self._h, int(max_tokens)))
+        if nbytes < 0:
+            _lib.check(nbytes, "enable_prefill")
+        self.prefill = SimpleNamespace(max_tokens=int(max_tokens), gs_x=1.0 / one(a1_scale), gs_a=1.0 / one(a2_scale),
+                                       workspace=torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device), forward=self._prefill_forward)
+
+    enable_cutlass_prefill = enable_prefill   # the reference's name for the same switch
+
+    def _prefill_forward(self, x, ids, wts, out):
+        pf = self.prefill
+        for s in range(0, x.shape[0], pf.max_tokens):
+            e = min(x.shape[0], s + pf.max_tokens)
+            _lib.check(_lib.lib().b200moe_prefill_forward(self._h, _lib.ptr(x[s:e]), _lib.ptr(ids[s:e]), _lib.ptr(wts[s:e]), e - s,
+                                                          _lib.ptr(out[s:e]), _lib.ptr(pf.workspace), pf.workspace.numel(), pf.max_tokens,
+                                                          pf.gs_x, pf.gs_a, _lib.stream_ptr()), "prefill forward")
+        return out
+
+    def prefill_status(self) -> None:
+        _lib.check(_lib.lib().b200moe_prefill_status(self._h, _lib.ptr(self.prefill.workspace), self.prefill.max_tokens, _lib.stream_ptr()),
+                   "prefill status")
+
     # ------------------------------------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
                 pdl: bool | None = None) -> torch.Tensor:
