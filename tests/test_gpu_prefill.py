@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import check_layer_output
+from helpers import check_w4a4_output as check_layer_output
 from oracle import nvfp4_oracle as O
 from test_gpu_decode import inputs, layer
 
