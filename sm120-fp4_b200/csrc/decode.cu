@@ -185,11 +185,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
   if (tid < kMaxE) T.cnt[tid] = 0;
   __syncthreads();
   for (int p = tid; p < npairs; p += kThreads) {
-    int e = P.ids[p];
-    if (e < 0 || e >= P.E) { *P.status = ST_BAD_ID; e = 0; }
+    int e = P.ids[p];   // a negative id marks an empty slot (expert-parallel shards mask the experts they do not own)
+    if (e >= P.E) { *P.status = ST_BAD_ID; e = -1; }
+    if (e < 0) e = -1;
     T.ids[p] = e;
     T.wts[p] = P.wts[p];
-    atomicAdd(&T.cnt[e], 1);
+    if (e >= 0) atomicAdd(&T.cnt[e], 1);
   }
   __syncthreads();
   if (warp == 0) {   // inclusive scans over kMaxE entries, 8 per lane
@@ -246,11 +247,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode(const __grid_constan
       }
     for (int u = U + tid; u < Umax; u += kThreads) {
       P.experts_out[u] = -1;
-      P.offsets_out[u + 1] = npairs;
+      P.offsets_out[u + 1] = T.base[kMaxE - 1];
     }
-    if (tid == 0) P.offsets_out[U] = npairs;
+    if (tid == 0) P.offsets_out[U] = T.base[kMaxE - 1];   // number of routed pairs (= npairs when no slot is empty)
     for (int p = tid; p < npairs; p += kThreads) {
       const int e = T.ids[p];
+      if (e < 0) continue;
       int r = 0;
       for (int q = 0; q < p; ++q) r += T.ids[q] == e;
       P.pairs_out[T.base[e] - T.cnt[e] + r] = p;

@@ -251,11 +251,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   for (int i = tid; i < kTcMaxE; i += kTcThreads) T.cnt[i] = 0;
   __syncthreads();
   for (int p = tid; p < npairs; p += kTcThreads) {
-    int e = P.ids[p];
-    if (e < 0 || e >= P.E) { *P.status = 4; e = 0; }
+    int e = P.ids[p];   // a negative id marks an empty slot (expert-parallel shards mask the experts they do not own)
+    if (e >= P.E) { *P.status = 4; e = -1; }
+    if (e < 0) e = -1;
     T.ids[p] = e;
     T.wts[p] = P.wts[p];
-    atomicAdd(&T.cnt[e], 1);
+    if (e >= 0) atomicAdd(&T.cnt[e], 1);
   }
   __syncthreads();
   if (warp == 0) {
@@ -290,10 +291,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   if (blockIdx.x == 0 && P.experts_out) {
     for (int e = tid; e < P.E; e += kTcThreads)
       if (T.cnt[e] > 0) { P.experts_out[T.uidx[e] - 1] = e; P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e]; }
-    for (int u = U + tid; u < P.Umax; u += kTcThreads) { P.experts_out[u] = -1; P.offsets_out[u + 1] = npairs; }
-    if (tid == 0) P.offsets_out[U] = npairs;
+    for (int u = U + tid; u < P.Umax; u += kTcThreads) { P.experts_out[u] = -1; P.offsets_out[u + 1] = T.base[kTcMaxE - 1]; }
+    if (tid == 0) P.offsets_out[U] = T.base[kTcMaxE - 1];
     for (int p = tid; p < npairs; p += kTcThreads) {
       const int e = T.ids[p];
+      if (e < 0) continue;
       int r = 0;
       for (int q = 0; q < p; ++q) r += T.ids[q] == e;
       P.pairs_out[T.base[e] - T.cnt[e] + r] = p;

@@ -289,6 +289,7 @@ __global__ void __launch_bounds__(256) k_prefill_combine(const __nv_bfloat16* __
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < top_k; ++j) {
       const int r = dst_row[tok * top_k + j];
+      if (r < 0) continue;   // empty slot
       const uint4 v = *reinterpret_cast<const uint4*>(y + (long long)r * H + c * 8);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -374,6 +375,7 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   int* status = (int*)(w + L.status);
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
+  B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
   const int max_tiles = P / 128 + Umax;
   k_prefill_plan<<<1, 1024, 2 * max_tiles * sizeof(int), st>>>(experts, offsets, pairs, Umax, P, top_k, max_tiles, ntiles, tile_expert, src_tok,
                                                                 row_pair, dst_row);

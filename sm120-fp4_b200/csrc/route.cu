@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(128) k_route_hist(const int* __restrict__ ids,
   const int p0 = blockIdx.x * ROUTE_CHUNK, p1 = min(P, p0 + ROUTE_CHUNK);
   for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) {
     const int e = ids[p];
-    if (e < 0 || e >= E) { *bad = 1; continue; }
+    if (e < 0) continue;                 // empty slot
+    if (e >= E) { *bad = 1; continue; }
     atomicAdd(&sh[e], 1);
   }
   __syncthreads();
@@ -54,6 +55,7 @@ __global__ void __launch_bounds__(1024) k_route_scan(int* __restrict__ hist, int
     __syncthreads();
   }
   const int U = uidx[ROUTE_MAXE - 1];
+  const int routed = base[ROUTE_MAXE - 1];   // pairs with a non-negative id (= P when no slot is empty)
   if (t < E) {
     expert_base[t] = base[t] - c;
     if (c > 0 && uidx[t] - 1 < Umax) {
@@ -63,10 +65,10 @@ __global__ void __launch_bounds__(1024) k_route_scan(int* __restrict__ hist, int
   }
   for (int u = U + t; u < Umax; u += blockDim.x) {
     experts[u] = -1;
-    offsets[u + 1] = P;
+    offsets[u + 1] = routed;
   }
   if (t == 0) {
-    if (U <= Umax) offsets[U] = P;
+    if (U <= Umax) offsets[U] = routed;
     if (num_touched) *num_touched = U;
   }
 }

@@ -1,0 +1,117 @@
+"""Expert-parallel layer on GPUs: the single-rank path (dispatch / masked slots / combine around the real kernels) always,
+and a two-rank NCCL run when the box has two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+from helpers import check_layer_output
+from oracle import nvfp4_oracle as O
+from test_gpu_decode import inputs, layer
+
+pytestmark = pytest.mark.gpu
+
+
+def test_masked_slots_are_skipped():
+    """ids of -1 mark slots another rank owns: the kernels must skip them (decode kernels and the prefill path)."""
+    cfg, w, ow = layer("mid")
+    for m in (6, 16, 40):
+        x, ids, wts = inputs(cfg, m, 900 + m)
+        masked = ids.clone()
+        masked[:, 1] = -1
+        masked[0, :] = -1                       # a row with no local expert at all -> zero output row
+        wz = wts.clone()
+        wz[masked < 0] = 0
+        for impl in ("mma", "tcgen05"):
+            w.set_decode_impl(impl)
+            out = w.forward(x.cuda(), masked.cuda(), wz.cuda())
+            w.status()
+            # oracle: the masked slots contribute nothing
+            ref_ids = ids.clone()
+            want = O.moe_reference(x.float().numpy(), ow, ref_ids.numpy(), wz.numpy())
+            check_layer_output(out, want, f"masked m={m} {impl}")
+            assert float(out[0].float().abs().max()) == 0.0
+        w.set_decode_impl("auto")
+    x, ids, wts = inputs(cfg, 150, 77)
+    masked = ids.clone()
+    masked[::3, 2] = -1
+    wz = wts.clone()
+    wz[masked < 0] = 0
+    w.enable_prefill(max_tokens=256)
+    out = w.forward(x.cuda(), masked.cuda(), wz.cuda())
+    w.prefill_status()
+    from helpers import check_w4a4_output
+    check_w4a4_output(out, O.moe_reference(x.float().numpy(), ow, ids.numpy(), wz.numpy(), act_quant=True), "masked prefill")
+    w.prefill = None
+
+
+def test_single_rank_expert_parallel_wrapper_equals_the_layer():
+    from sm120fp4_b200.ep import ExpertParallelMoE
+    cfg, w, ow = layer("mid")
+    x, ids, wts = inputs(cfg, 12, 55)
+    base = w.forward(x.cuda(), ids.cuda(), wts.cuda())
+    for cap in (None, 16):
+        ep = ExpertParallelMoE(w.forward, cfg["experts"], cfg["top_k"], capacity=cap)
+        out = ep.forward(x.cuda(), ids.cuda(), wts.cuda())
+        assert torch.equal(out, base), f"capacity={cap}"
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import sm120fp4_b200 as pkg
+        from sm120fp4_b200 import synth
+        from sm120fp4_b200.ep import ExpertParallelMoE, shard_range
+        from sm120fp4_b200.vllm_backend import Weights
+        cfg = dict(experts=16, hidden=512, inter=192, top_k=4)
+        w13, w2 = synth.layer_weights_bf16(cfg["experts"], cfg["hidden"], cfg["inter"], seed=21)
+        q1, s1, g1 = pkg.quantize_nvfp4_experts(w13.cuda())
+        q2, s2, g2 = pkg.quantize_nvfp4_experts(w2.cuda())
+        lo, hi = shard_range(cfg["experts"], rank, world)
+        local = Weights(q1[lo:hi].contiguous(), s1[lo:hi].contiguous(), (1 / g1)[lo:hi].contiguous(), q2[lo:hi].contiguous(),
+                        s2[lo:hi].contiguous(), (1 / g2)[lo:hi].contiguous(), cfg["top_k"])
+        full = O.ExpertWeights(q1.cpu().numpy(), s1.cpu().numpy(), (1 / g1).cpu().numpy(), q2.cpu().numpy(), s2.cpu().numpy(), (1 / g2).cpu().numpy())
+        res = []
+        for cap, m in ((None, 7 + rank), (16, 16), (None, 40)):
+            x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 300 + rank + m)
+            ep = ExpertParallelMoE(local.forward, cfg["experts"], cfg["top_k"], capacity=cap)
+            out = ep.forward(x.cuda(), ids.cuda(), wts.cuda())
+            out2 = ep.forward(x.cuda(), ids.cuda(), wts.cuda())
+            local.status()
+            want = O.moe_reference(x.float().numpy(), full, ids.numpy(), wts.numpy())
+            res.append((float(np.abs(out.float().cpu().numpy() - want).max()), float(np.sqrt((want ** 2).mean())), bool(torch.equal(out, out2))))
+        q.put((rank, res))
+    except Exception as ex:  # noqa: BLE001
+        import traceback
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_expert_parallel_matches_the_full_layer():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    for r in res:
+        assert r[1] != "error", r[2]
+        for err, rms, same in r[1]:
+            assert err <= 3e-2 * rms and same, r
