@@ -82,7 +82,7 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_layers(cfg, n_layers, device):
+def build_layers(cfg, n_layers, device, shard=None):
     """n_layers independently seeded layers; weights drawn on the GPU as bf16 N(0, 0.02) and quantised by the library's
     own (bit-exact) quantizer with one global scale per expert, scales kept in the 128x4 swizzle."""
     import sm120fp4_b200 as pkg
@@ -94,6 +94,8 @@ def build_layers(cfg, n_layers, device):
         parts = {}
         for name, rows, cols in (("1", 2 * i, h), ("2", h, i)):
             w = (torch.randn(e, rows, cols, generator=g, device=device) * 0.02).to(torch.bfloat16)
+            if shard is not None:   # expert-parallel: this rank keeps experts [lo, hi) of the same seeded layer
+                w = w[shard[0]:shard[1]].contiguous()
             q, sw, gs = pkg.quantize_nvfp4_experts(w, swizzle=True)
             parts[name] = (q, sw, 1.0 / gs)
             del w
@@ -124,6 +126,7 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
     from sm120fp4_b200 import synth
     cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
+    from sm120fp4_b200.ep import shard_range
     layers = build_layers(cfg, a.layers, dev)
     cs = cases(cfg, set(a.cases.split(",")) if a.cases else None)
     for c in cs:
@@ -210,6 +213,18 @@ def run_ours(a):
         t = torch.tensor([step_ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         step_ms, e2e_ms = float(t[0]), float(t[1])
+    extras = {}
+    if not a.no_extras:
+        with torch.cuda.stream(stream):
+            if world == 1:
+                extras["prefill"] = prefill_numbers(cfg, layers[:2], dev)
+                extras["ep"] = ep_stack(cfg, layers, None, 1, 0, dev, stack=a.ep_layers)
+            else:
+                del graphs
+                layers.clear()
+                torch.cuda.empty_cache()
+                sharded = build_layers(cfg, a.layers, dev, shard=shard_range(cfg["experts"], rank, world))
+                extras["ep"] = ep_stack(cfg, sharded, dist, world, rank, dev, stack=a.ep_layers)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -247,9 +262,83 @@ def run_ours(a):
                 "d2h_bytes_per_step": int(sum(c["x"].numel() * 2 for c in cs) * a.layers)},
         "gpu_launches": launches, "clocks": clocks, "cpu_baseline": cpu,
     }
+    line.update(extras)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def prefill_numbers(cfg, layers, dev, reps=5):
+    """W4A4 prefill (own tcgen05 grouped GEMM): us per layer call and TFLOP/s on 6*M*k*I*H flop at M = 256 .. 8192."""
+    from sm120fp4_b200 import synth
+    ws = None
+    for w in layers:
+        w.enable_prefill(max_tokens=8192, workspace=ws)
+        ws = w.prefill.workspace
+    rows = []
+    for m in (256, 1024, 4096, 8192):
+        x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 9000 + m)
+        xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
+        out = torch.empty_like(xd)
+        for _ in range(2):
+            for w in layers:
+                w.forward(xd, idd, wd, out=out)
+        ts = []
+        for _ in range(reps):
+            ts.append(time_region(lambda: [w.forward(xd, idd, wd, out=out) for w in layers], torch.cuda.synchronize) / len(layers))
+        ts.sort()
+        t = ts[len(ts) // 2]
+        flop = 6.0 * m * cfg["top_k"] * cfg["inter"] * cfg["hidden"]
+        rows.append({"m": m, "us_per_layer": round(t * 1e3, 1), "tflops": round(flop / t / 1e9, 1),
+                     "frac_of_dense_fp4_nominal": round(flop / t / 1e9 / 9000.0, 4)})
+    layers[0].prefill_status()
+    for w in layers:
+        w.prefill = None
+    return rows
+
+
+def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, prefill_tokens=4096, reps=3):
+    """The expert-parallel stack of BASELINE configs[4]: `stack` layer calls (cycling over the resident layer objects, each
+    holding E / world experts), decode with 16 tokens per GPU (fixed-capacity dispatch, no host sync) and prefill with 4096
+    tokens per GPU (variable-size dispatch, W4A4 path). Device-timed, max over ranks. Returns tokens/s and per-layer us."""
+    from sm120fp4_b200 import synth
+    from sm120fp4_b200.ep import ExpertParallelMoE
+    e, k = cfg["experts"], cfg["top_k"]
+    res = {}
+    for name, m, cap in (("decode", decode_tokens, decode_tokens), ("prefill", prefill_tokens, None)):
+        ws = None
+        if name == "prefill":
+            for w in layers:
+                w.enable_prefill(max_tokens=prefill_tokens * world, workspace=ws)
+                ws = w.prefill.workspace
+        eps = [ExpertParallelMoE(w.forward, e, k, capacity=cap) for w in layers]
+        x, ids, wts = synth.decode_inputs(m, e, cfg["hidden"], k, 7000 + 13 * rank + m)
+        xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
+
+        def run():
+            for li in range(stack):
+                eps[li % len(eps)].forward(xd, idd, wd)
+
+        def sync():
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+                torch.cuda.synchronize()
+        run()
+        ts = [time_region(run, sync) for _ in range(reps)]
+        t = torch.tensor([sorted(ts)[len(ts) // 2]], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        res[name] = {"tokens_per_gpu": m, "tokens_per_s": round(world * m / (ms * 1e-3), 1), "us_per_layer": round(ms * 1e3 / stack, 1),
+                     "rows_dispatched_per_layer_per_gpu": eps[0].last_sent_rows, "row_bytes": cfg["hidden"] * 2}
+        if name == "prefill":
+            for w in layers:
+                w.prefill = None
+        for w in layers:
+            w.status()
+    res["stack_layers"] = stack
+    return res
 
 
 def host_layer(cfg, seed=0):
@@ -345,6 +434,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cases", default="", help="subset of the sweep for profiling, e.g. 16:random,1:fixed8 (default: all ten)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill and expert-parallel stack measurements")
+    ap.add_argument("--ep-layers", type=int, default=48, help="layer calls in the expert-parallel stack")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)

@@ -110,11 +110,12 @@ class Weights:
             pass
 
     def enable_prefill(self, a1_scale: torch.Tensor | float | None = None, a2_scale: torch.Tensor | float | None = None,
-                       max_tokens: int = 8192) -> None:
+                       max_tokens: int = 8192, workspace: torch.Tensor | None = None) -> None:
         """Above MAXM tokens, run the layer's own W4A4 tensor-core path (NVFP4 activations) instead of slices of MAXM.
         a1_scale / a2_scale: the checkpoint's activation input scales of FC1 and FC2 (the largest over the experts is used,
         as in the reference's enable_cutlass_prefill, sm120fp4/vllm_backend.py:123-145); None means 1.0, the global scale
-        of the reference's own W4A4 arithmetic."""
+        of the reference's own W4A4 arithmetic. `workspace`: a zeroed uint8 tensor to share between the layers of a stack
+        (it only holds transient data of one call); allocated here when None."""
         def one(a):
             if a is None:
                 return 1.0
@@ -126,8 +127,12 @@ class Weights:
         nbytes = int(h.b200moe_prefill_workspace_bytes(self._h, int(max_tokens)))
         if nbytes < 0:
             _lib.check(nbytes, "enable_prefill")
+        if workspace is None:
+            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device)
+        elif workspace.numel() < nbytes or workspace.dtype != torch.uint8:
+            raise ValueError(f"the shared prefill workspace needs {nbytes} bytes of uint8")
         self.prefill = SimpleNamespace(max_tokens=int(max_tokens), gs_x=1.0 / one(a1_scale), gs_a=1.0 / one(a2_scale),
-                                       workspace=torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device), forward=self._prefill_forward)
+                                       workspace=workspace, forward=self._prefill_forward)
 
     enable_cutlass_prefill = enable_prefill   # the reference's name for the same switch
 
