@@ -52,6 +52,14 @@ long long b200moe_route_workspace_bytes(int P, int E);
 int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* workspace,
                   long long workspace_bytes, void* stream);
 
+/* Router for hosts that cannot provide scratch memory (no counterpart in the reference). Identical tables to b200moe_route,
+ * but the intermediate histograms sit in a fixed array inside the library (about 129 KiB per GPU that loads it), so the call
+ * allocates nothing and takes no workspace. Meant for callers with no allocator of their own: a server that froze its
+ * memory budget after start-up, a plugin that only receives its input and output buffers. Limits: P <= 65536, E <= 256
+ * (B200MOE_ERR_LIMIT beyond). The first call on each device looks up the array's device address - issue it before any
+ * stream capture. Calls on one device share the array: do not let two of them overlap on the GPU. */
+int b200moe_route_static(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* stream);
+
 /* ---- decode layer (M <= 16 tokens, W4A16): sm120fp4/vllm_backend.py:95-121 (Weights) and :147-190 (forward/_slice).
  * q1 u8 [E, 2I, H/2] rows [up ; gate]; s1 u8 [E, pad128(2I) * pad4(H/16)] 128x4-swizzled per expert; q2 u8 [E, H, I/2];
  * s2 u8 [E, pad128(H) * pad4(I/16)] 128x4-swizzled per expert; alpha f32 [E] (weight_scale_2). H % 128 == 0,

@@ -23,6 +23,7 @@ SIGNATURES = {
     "b200moe_quantize_nvfp4": (_I, [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _P]),
     "b200moe_route_workspace_bytes": (_LL, [_I, _I]),
     "b200moe_route": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _LL, _P]),
+    "b200moe_route_static": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "b200moe_layer_create": (_I, [C.POINTER(_P), _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_layer_destroy": (None, [_P]),
     "b200moe_layer_workspace_bytes": (_LL, [_P]),

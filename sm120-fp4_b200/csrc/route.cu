@@ -138,3 +138,68 @@ extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* expert
   }
   return B200MOE_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Router for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library own no allocator: an inference server that has finished its memory-profiling pass and
+// forbids any further device allocation, or a plugin that is only ever given its input and output buffers. For them the
+// chunk histograms and expert bases of the router live in a fixed device array inside the library image instead of a
+// caller-provided workspace. Every GPU that loads the library carries these kRouteStaticInts * 4 bytes (about 129 KiB)
+// until the process exits.
+constexpr int kRouteStaticMaxPairs = 65536;   // 8192 tokens x top-8
+constexpr int kRouteStaticMaxExperts = 256;
+constexpr int kRouteStaticInts = (kRouteStaticMaxPairs / b200::ROUTE_CHUNK) * kRouteStaticMaxExperts + kRouteStaticMaxExperts + 2;
+static __device__ __align__(256) int g_route_static[kRouteStaticInts];
+
+// In host code `g_route_static` is only a handle for the symbol, not an address a kernel can use: the device address is
+// looked up per device with cudaGetSymbolAddress, with that device current, the first time the entry point runs there.
+static int route_static_address(int** out) {
+  constexpr int kMaxDevices = 64;
+  static int* addr[kMaxDevices] = {};
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return B200MOE_ERR_DEVICE;
+  if (!addr[dev]) {
+    int* p = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_route_static));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return B200MOE_OK;
+}
+
+// Same tables as b200moe_route, with no workspace argument and no allocation of any kind inside the call.
+//  * limits: P <= 65536 pairs and E <= 256 experts, otherwise B200MOE_ERR_LIMIT.
+//  * the first call on a device resolves the address of the built-in scratch (a synchronous runtime query), so make that
+//    first call before starting a stream capture on that device.
+//  * all calls on a device share the one scratch array: two calls whose kernels may overlap on the GPU (different streams)
+//    race on it. The array keeps what the previous call left; the cells that must start from zero (the bad-id flag and the
+//    touched-expert count) are cleared on the stream at the start of every call, the rest is fully rewritten.
+extern "C" int b200moe_route_static(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* stream) {
+  if (!offsets || P < 0 || Umax < 0) return B200MOE_ERR_ARG;
+  if ((P > 0 && (!ids || !pairs)) || (Umax > 0 && !experts)) return B200MOE_ERR_ARG;
+  if (E <= 0) return B200MOE_ERR_SHAPE;
+  if (P > kRouteStaticMaxPairs || E > kRouteStaticMaxExperts) return B200MOE_ERR_LIMIT;
+  int* scratch = nullptr;
+  const int rc = route_static_address(&scratch);
+  if (rc != B200MOE_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nchunks = (P + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  int* hist = scratch;
+  int* expert_base = hist + (long long)nchunks * E;
+  int* bad = expert_base + E;
+  int* num_touched = bad + 1;
+  B200_CUDA_TRY(cudaMemsetAsync(bad, 0, 2 * sizeof(int), st));
+  if (nchunks > 0) {
+    k_route_hist<<<nchunks, 128, E * sizeof(int), st>>>(ids, P, E, hist, bad);
+    B200_LAUNCH_CHECK();
+  }
+  k_route_scan<<<1, 1024, 0, st>>>(hist, nchunks, P, E, Umax, experts, offsets, expert_base, num_touched);
+  B200_LAUNCH_CHECK();
+  if (nchunks > 0) {
+    k_route_place<<<nchunks, 32, E * sizeof(int), st>>>(ids, P, E, hist, expert_base, pairs);
+    B200_LAUNCH_CHECK();
+  }
+  return B200MOE_OK;
+}
