@@ -1,0 +1,105 @@
+"""The vLLM config and MoE method of this backend, at module level so vLLM can pickle the config into its engine-core process
+(the reason the reference keeps them in their own module, sm120fp4/vllm_classes.py:1-7).
+
+Same surface as the reference: `ModelOptNvFp4FusedMoESM120` (alias `SM120Fp4MoEMethod`) with `fits`,
+`process_weights_after_loading`, `apply`; `SM120Fp4Config.get_quant_method`. Differences, all widening: any hidden size
+that is a multiple of 128 and intermediate size that is a multiple of 64 fit (the reference: 2048 x {768, 1024},
+vllm_classes.py:41-45); batches above 16 tokens run the layer's own W4A4 kernels when the checkpoint carries activation
+input scales. Expert parallelism is still declined here: the engine-side expert map is not wired to `ep.ExpertParallelMoE`.
+"""
+from __future__ import annotations
+
+import torch
+
+try:  # vLLM moved RoutedExperts between releases: try the reference's import path first, then the package-level one
+    from vllm.model_executor.layers.fused_moe.routed_experts import RoutedExperts
+except ImportError:  # pragma: no cover - depends on the installed vLLM
+    from vllm.model_executor.layers.fused_moe import RoutedExperts
+from vllm.model_executor.layers.fused_moe.activation import MoEActivation
+from vllm.model_executor.layers.fused_moe.fused_moe_method_base import FusedMoEMethodBase
+from vllm.model_executor.layers.quantization.modelopt import ModelOptNvFp4Config, ModelOptNvFp4FusedMoE
+
+from .vllm_backend import Weights, _log, prefill_explicit, prefill_mode, weights_from_vllm_layout
+
+
+class ModelOptNvFp4FusedMoESM120(ModelOptNvFp4FusedMoE):
+    """vLLM's NVFP4 MoE method with this package's layer in place of the Marlin repack and kernel. The class name keeps
+    "ModelOpt" in it: vLLM's weight loader branches on the method's class name (sm120fp4/vllm_classes.py:22-26)."""
+
+    def __init__(self, quant_config, moe_config) -> None:
+        FusedMoEMethodBase.__init__(self, moe_config)   # not the parent's: it would select a vLLM backend that never runs
+        self.quant_config = quant_config
+        self.use_a16 = True
+        self.use_global_sf = False
+        self.nvfp4_backend, self.experts_cls = None, None
+        self.weights: Weights | None = None
+
+    @staticmethod
+    def fits(moe_config) -> tuple[bool, str]:
+        """Whether the layer described by a FusedMoEConfig can run on the kernels; (False, reason) otherwise."""
+        if not getattr(moe_config, "is_act_and_mul", False) or moe_config.activation != MoEActivation.SILU:
+            return False, f"activation {moe_config.activation!r} is not gated SiLU"
+        if moe_config.hidden_dim % 128:
+            return False, f"hidden size {moe_config.hidden_dim} (kernels take multiples of 128)"
+        if moe_config.intermediate_size_per_partition % 64:
+            return False, f"intermediate size {moe_config.intermediate_size_per_partition} (kernels take multiples of 64)"
+        if moe_config.moe_parallel_config.use_ep:
+            return False, "expert parallelism (the engine's expert map is not wired to this backend)"
+        if moe_config.in_dtype != torch.bfloat16:
+            return False, f"activations {moe_config.in_dtype} (kernels take bf16)"
+        return True, ""
+
+    @property
+    def is_monolithic(self) -> bool:
+        return False
+
+    @property
+    def supports_eplb(self) -> bool:
+        return False
+
+    def get_fused_moe_quant_config(self, layer):
+        return None
+
+    def process_weights_after_loading(self, layer) -> None:
+        self.weights = weights_from_vllm_layout(layer.w13_weight.data, layer.w13_weight_scale.data, layer.w13_weight_scale_2.data,
+                                                layer.w2_weight.data, layer.w2_weight_scale.data, layer.w2_weight_scale_2.data,
+                                                int(layer.top_k))
+        w = self.weights
+        if prefill_mode() != "slices":
+            if getattr(layer, "w13_input_scale", None) is None or getattr(layer, "w2_input_scale", None) is None:
+                if prefill_explicit():
+                    raise ValueError("SM120FP4_PREFILL=cutlass needs the checkpoint's w13_input_scale and w2_input_scale")
+                _log("no activation input scales in this checkpoint: batches above 16 tokens run as slices")
+            else:
+                w.enable_prefill(layer.w13_input_scale.data, layer.w2_input_scale.data)
+        for name, t in (("w13_weight", w.q1), ("w13_weight_scale", w.s1_linear.view(torch.float8_e4m3fn)), ("w13_weight_scale_2", w.alpha1),
+                        ("w2_weight", w.q2), ("w2_weight_scale", w.s2_linear.view(torch.float8_e4m3fn)), ("w2_weight_scale_2", w.alpha2)):
+            layer.register_parameter(name, torch.nn.Parameter(t, requires_grad=False))
+        for name in ("w13_input_scale", "w2_input_scale"):
+            if hasattr(layer, name):
+                layer.register_parameter(name, None)
+
+    def apply(self, layer, x, topk_weights, topk_ids, shared_experts, shared_experts_input):
+        assert self.weights is not None, "process_weights_after_loading has not run"
+        if shared_experts is not None:
+            raise NotImplementedError("shared experts are not run by this backend")
+        if getattr(layer, "apply_router_weight_on_input", False):
+            raise NotImplementedError("apply_router_weight_on_input")
+        if getattr(layer, "expert_map", None) is not None:
+            raise NotImplementedError("expert map (expert parallelism)")
+        return self.weights.forward(x, topk_ids, topk_weights)
+
+
+class SM120Fp4Config(ModelOptNvFp4Config):
+    """vLLM's ModelOpt NVFP4 config, routing the routed-experts layers the kernels fit to the method above."""
+
+    def get_quant_method(self, layer, prefix: str):
+        if isinstance(layer, RoutedExperts) and not self.is_layer_excluded(prefix):
+            ok, why = ModelOptNvFp4FusedMoESM120.fits(layer.moe_config)
+            if ok:
+                return ModelOptNvFp4FusedMoESM120(quant_config=self, moe_config=layer.moe_config)
+            _log(f"layer {prefix} stays on vLLM's path: {why}")
+        return super().get_quant_method(layer, prefix)
+
+
+SM120Fp4MoEMethod = ModelOptNvFp4FusedMoESM120  # the short name the reference's tests and docs use
