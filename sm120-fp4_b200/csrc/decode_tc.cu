@@ -12,10 +12,12 @@
 // against the fp32 oracle below the bf16 output rounding.
 //
 // Structure: one CTA per SM = one stream-K worker. Warps 0-3: epilogue (tcgen05.ld of a double-buffered TMEM accumulator,
-// term sums, SiLU*mul, re-expansion of the activations for FC2, fixed-order reduction of split units). Warp 4: MMA issuer
-// (scale tiles smem->TMEM with tcgen05.cp, four K=64 MMAs per 256-code tile, tcgen05.commit frees the ring stage).
-// Warps 5-8: TMA producers, tile i of the worker's share belongs to producer i mod 4 (weight tiles into a shared-memory
-// ring, FC2 tiles prefetched across the FC1->FC2 grid barrier).
+// term sums, SiLU*mul, re-expansion of the activations for FC2, fixed-order reduction of split units). Warps 4-7: scale
+// warps, one per TMEM lane quadrant (scale tiles of a landed stage shared memory -> registers -> TMEM). Warp 8: MMA issuer
+// (converged warp, one elected lane: four K=64 MMAs per 256-code tile, tcgen05.commit frees the ring stage). Warps 9-10:
+// TMA producers (one bulk copy per 18 KB tile record into a shared-memory ring, FC2 tiles prefetched across the
+// FC1->FC2 grid barrier). The per-tile loops of the single-thread roles are kept free of divisions: at 148 tiles per
+// microsecond per GPU a role has only a few hundred cycles per tile.
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "decode_params.h"
@@ -24,7 +26,7 @@
 namespace b200 {
 
 constexpr int kTcProducers = 2;    // TMA producer warps: one thread issues only ~2.5 M bulk operations per second
-constexpr int kTcThreads = (4 + 2 + kTcProducers) * 32;   // epilogue warps 0-3, MMA warp 4, scale-copy warp 5, producers 6..
+constexpr int kTcThreads = (4 + 4 + 1 + kTcProducers) * 32;   // epilogue warps 0-3, scale warps 4-7, MMA warp 8, producers 9..
 constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
 constexpr int kTerms = 4;
 constexpr int kTcMaxE = 256, kTcMaxP = 256, kTcMaxWorkers = 256;
@@ -48,7 +50,9 @@ struct TcTables {
 #ifdef B200_TIMERS
 #define TC_T0(var) long long var = clock64()
 #define TC_ADD(acc, var) acc += clock64() - var
+#define TC_TRACE(j, k) do { if (P.debug && v == 5 && (threadIdx.x & 31) == 0 && (j) < 128) P.debug[148 * 16 + (j) * 8 + (k)] = clock64() - tm_begin; } while (0)
 #else
+#define TC_TRACE(j, k)
 #define TC_T0(var)
 #define TC_ADD(acc, var)
 #endif
@@ -236,7 +240,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 
   // ---------------------------------------------------------------- prologue
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); mbar_init(&T.sfr[s], 1); }
+    for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); mbar_init(&T.sfr[s], 4); }
     for (int b = 0; b < 2; ++b) { mbar_init(&T.acc_full[b], 1); mbar_init(&T.acc_empty[b], 4); }
     mbar_init(&T.xb_full, 1);
     T.abort_flag = 0;
@@ -244,7 +248,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     T.gen0 = ld_acquire_gpu(P.gridbar + 1);
     fence_mbar_init();
   }
-  if (warp == 4) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
+  if (warp == 8) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
     tmem_alloc(&T.tmem_base, 512);
     tmem_relinquish();
   }
@@ -311,10 +315,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 320;   // accumulators 2 x 64 | weight scales NS x 16 (<= 192) | operand scales (<= 192)
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand (same bulk copy)
 
-  if (warp >= 6) {
+  if (warp >= 9) {
     // ============================================================== TMA producers (one thread each)
+    // Both producers walk the worker's whole tile sequence with incremental indices (no divisions in the loop) and
+    // issue the tiles whose position is theirs (position mod kTcProducers).
     if (lane == 0) {
-      const int pw = warp - 6;
+      const int pw = warp - 9;
       const uint64_t pol = policy_evict_first();
       // the resident B operand of FC1 (x expanded into NVFP4 terms) and its scale tiles: one bulk copy
       if (pw == 0 && n1 > 0) {
@@ -342,142 +348,177 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         npend = 0;
         passed = true;
       };
-      const int f1 = T.sb1[v], f2 = T.sb2[v];
-      for (int j = pw; j < n1 + n2; j += kTcProducers) {   // j: position in this worker's tile sequence; slot = j mod NS
-        const int slot = j % NS, use = j / NS;
-        const bool is2 = j >= n1;
+      int slot = 0, use = 0, mine = pw == 0 ? 0 : kTcProducers - pw;   // `mine` counts down to this producer's next tile
+      auto acquire = [&](bool over_fc2) {   // the ring slot of the current position, free of its previous occupant
         if (use >= 1) {
-          // the previous occupant of the slot is an FC2 tile still waiting for its activations: open the gate first
-          if (!passed && (j - NS) >= n1) wait_grid();
-          TC_T0(t0);
+          if (over_fc2) wait_grid();        // that occupant is an FC2 tile still waiting for its activations: open the gate first
           if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = 2;
-          TC_ADD(tm_a, t0);
         }
-        uint8_t* st = ring + slot * kTcStage;
-        if (!is2) {
-          const int f = f1 + j;
-          const int kb = f % KB1, q = f / KB1, cb = q % CB1, u = q / CB1;
-          const int e = T.experts[u];
-          mbar_expect_tx(&T.full[slot], kTcStage);
-          bulk_load_hint(st, P.w1t + (((long long)e * CB1 + cb) * KB1 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
-        } else {
-          const int f = f2 + (j - n1);
-          const int kb = f % KB2, q = f / KB2, u = q % U, nb = q / U;
-          const int e = T.experts[u];
-          mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
-          bulk_load_hint(st, P.w2t + (((long long)e * NB2 + nb) * KB2 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
-          if (passed) load_slab(slot, u * KB2 + kb);
-          else { pend_slot[npend] = slot; pend_idx[npend] = u * KB2 + kb; ++npend; }
+      };
+      auto advance = [&]() {
+        if (++slot == NS) { slot = 0; ++use; }
+        mine = mine == 0 ? kTcProducers - 1 : mine - 1;
+      };
+      // ---- FC1 tiles: whole units (expert, 64-column block) x KB1 boxes; the records of one expert are contiguous
+      if (n1 > 0) {
+        const int q0 = T.sb1[v] / KB1;
+        int u = q0 / CB1;
+        int left_e = (CB1 - q0 % CB1) * KB1;   // tiles left in this expert
+        const uint8_t* src = P.w1t + ((long long)T.experts[u] * CB1 + q0 % CB1) * KB1 * kTcStage;
+        for (int j = 0; j < n1; ++j) {
+          if (left_e == 0) {
+            ++u;
+            src = P.w1t + (long long)T.experts[u] * CB1 * KB1 * kTcStage;
+            left_e = CB1 * KB1;
+          }
+          if (mine == 0) {
+            acquire(false);
+            TC_TRACE(j, 0);
+            mbar_expect_tx(&T.full[slot], kTcStage);
+            bulk_load_hint(ring + slot * kTcStage, src, kTcStage, &T.full[slot], pol);
+          }
+          src += kTcStage;
+          --left_e;
+          advance();
+        }
+      }
+      // ---- FC2 tiles: position f = (nb * U + u) * KB2 + kb; weights (expert of u, nb, kb), activation slab (u, kb)
+      if (n2 > 0) {
+        const int f0 = T.sb2[v];
+        int kb = f0 % KB2, u = (f0 / KB2) % U, nb = (f0 / KB2) / U;
+        const uint8_t* src = P.w2t + (((long long)T.experts[u] * NB2 + nb) * KB2 + kb) * kTcStage;
+        for (int j = 0; j < n2; ++j) {
+          if (mine == 0) {
+            acquire(!passed && (n1 + j - NS) >= n1);
+            TC_TRACE(n1 + j, 0);
+            mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
+            bulk_load_hint(ring + slot * kTcStage, src, kTcStage, &T.full[slot], pol);
+            if (passed) load_slab(slot, u * KB2 + kb);
+            else { pend_slot[npend] = slot; pend_idx[npend] = u * KB2 + kb; ++npend; }
+          }
+          src += kTcStage;
+          if (++kb == KB2) {
+            kb = 0;
+            if (++u == U) { u = 0; ++nb; }
+            if (nb < NB2) src = P.w2t + ((long long)T.experts[u] * NB2 + nb) * KB2 * kTcStage;
+          }
+          advance();
         }
       }
       if (npend > 0) wait_grid();
 #ifdef B200_TIMERS
-      if (P.debug && pw == 0) { P.debug[v * 16 + 8] = tm_a; P.debug[v * 16 + 9] = clock64() - tm_begin; }
+      if (P.debug && pw == 0) P.debug[v * 16 + 9] = clock64() - tm_begin;
 #endif
     }
     __syncwarp();
-  } else if (warp == 4 || warp == 5) {
-    // ============================================================== scale copier (warp 5) and MMA issuer (warp 4)
-    // One thread can issue roughly one tcgen05 operation per 80-100 cycles, so the scale-tile copies (4-8 per tile) and the
-    // MMAs (4 per tile) are issued by two threads: the copier runs ahead, commits its copies to sfr[slot], the issuer waits
-    // for that barrier, issues the MMAs and commits them to empty[slot] (and to acc_full at the end of a piece).
-    if (lane == 0) {
-      const bool copier = warp == 5;
-      const uint32_t idesc = idesc_mxf4nvf4(128, N);
-      const int fe1 = T.sb1[v + 1], fe2 = T.sb2[v + 1], per_nb = U * KB2;
-      int f1 = T.sb1[v], f2 = T.sb2[v];
-      int kb1 = n1 > 0 ? f1 % KB1 : 0, kb2 = n2 > 0 ? f2 % KB2 : 0;
-      int si = 0;
-      uint32_t ph = 0;
-      int ab = 0, pieces = 0;
-      uint32_t aph[2] = {0, 0};
-      bool piece_open = false, acc_flag = false;
-      unsigned long long xsf_done = 0;   // K boxes whose x-operand scale tiles are already in TMEM
-      if (n1 > 0) {
-        if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
-        tc_fence_after();
+  } else if (warp >= 4 && warp < 8) {
+    // ============================================================== scale warps: one per TMEM lane quadrant
+    // The E4M3 scale tiles of a landed stage go shared memory -> registers -> TMEM (tcgen05.st): lane l of every quadrant
+    // holds row l of each 512-byte tile (16 bytes = 4 columns). Four warps in parallel replace the 4-8 tcgen05.cp per
+    // tile that a single thread would have to issue one after the other.
+    const uint32_t lane_base = (uint32_t)((warp - 4) * 32) << 16;
+    const uint32_t ring_u = smem_u32(ring) + 16384 + lane * 16, region_u = smem_u32(region);
+    const uint32_t xsf_u = smem_u32(xb_sf) + lane * 16;
+    int si = 0;
+    uint32_t ph = 0;
+    auto put = [&](uint32_t src, uint32_t dst_col, int ntiles) {   // up to four consecutive 512-byte tiles -> 16 columns
+      uint32_t r[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 t4 = make_uint4(0u, 0u, 0u, 0u);
+        if (j < ntiles) t4 = lds128(src + j * 512);
+        r[4 * j] = t4.x, r[4 * j + 1] = t4.y, r[4 * j + 2] = t4.z, r[4 * j + 3] = t4.w;
       }
-#ifdef B200_TIMERS
-      if (P.debug && !copier) P.debug[v * 16 + 14] = clock64() - tm_begin;   // x operand landed
-      bool first_stamp = true;
-#endif
-      while (f1 < fe1 || f2 < fe2) {
-        const bool is1 = f1 < fe1;
-        const uint32_t st = smem_u32(ring + si * kTcStage);
-        int nkt;
-        uint32_t b_addr, sfb;
-        bool last_of_piece;
-        const int kbx = kb1;
-        if (is1) {
-          nkt = min(4, P.KT1 - 4 * kb1);
-          b_addr = smem_u32(region + kb1 * (N * 128));
-          sfb = tm_sfb + 16 * kb1;
-          ++f1;
-          ++kb1;
-          last_of_piece = (kb1 == KB1) || (f1 == fe1);
-          if (kb1 == KB1) kb1 = 0;
-        } else {
-          nkt = min(4, P.KT2 - 4 * kb2);
-          b_addr = smem_u32(region + si * kSlab);
-          sfb = tm_sfb + 16 * si;
-          ++f2;
-          if (++kb2 == KB2) kb2 = 0;
-          last_of_piece = (f2 == fe2) || (f2 % per_nb == 0);
+      tmem_st_32x32b_x16(dst_col + lane_base, r);
+    };
+    auto publish_sf = [&]() {
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&T.sfr[si]);
+      if (++si == NS) { si = 0; ph ^= 1u; }
+    };
+    if (n1 > 0 && !mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
+    for (int j = 0, kb = 0; j < n1; ++j) {
+      if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+      TC_TRACE(j, 1);
+      put(ring_u + si * kTcStage, tm_sfa + 16 * si, 4);
+      if (j < KB1) put(xsf_u + kb * 2048, tm_sfb + 16 * kb, min(4, P.KT1 - 4 * kb));   // the x operand's scales: once per K box
+      publish_sf();
+      TC_TRACE(j, 2);
+      if (++kb == KB1) kb = 0;
+    }
+    for (int j = 0; j < n2; ++j) {
+      if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
+      TC_TRACE(n1 + j, 1);
+      put(ring_u + si * kTcStage, tm_sfa + 16 * si, 4);
+      put(region_u + si * kSlab + N * 128 + lane * 16, tm_sfb + 16 * si, 4);
+      publish_sf();
+      TC_TRACE(n1 + j, 2);
+    }
+  } else if (warp == 8) {
+    // ============================================================== MMA issuer: the whole warp stays converged
+    // Every lane runs the loop with warp-uniform values and one elected lane issues, so descriptors and TMEM addresses
+    // can live in uniform registers (issuing from a single diverged lane costs about twice as many cycles per operation).
+    const uint32_t el = elect_one();
+    const uint32_t idesc = idesc_mxf4nvf4(128, N);
+    const uint64_t desc0 = smem_desc_sw128_kmajor(0);
+    const uint32_t ring16 = smem_u32(ring) >> 4, region16 = smem_u32(region) >> 4;
+    const int nkt_last1 = P.KT1 - 4 * (KB1 - 1), nkt_last2 = P.KT2 - 4 * (KB2 - 1);
+    int si = 0, ab = 0, pieces = 0;
+    uint32_t ph = 0;
+    uint32_t aph[2] = {0, 0};
+    auto issue = [&](uint32_t b16, uint32_t sfb, int nkt, bool fresh) {   // the MMAs of the tile in ring slot si
+      if (!mbar_wait(&T.sfr[si], ph, &T.abort_flag)) *P.status = 8;     // scale warps arrive after they saw the stage land
+      tc_fence_after();
+      const uint64_t ad = desc0 | (uint64_t)(ring16 + si * (kTcStage >> 4)), bd = desc0 | (uint64_t)b16;
+      const uint32_t acc = tm_acc + 64 * ab, sfa = tm_sfa + 16 * si;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+        if (jj < nkt) umma_mxf4nvf4_p(acc, ad + 2 * jj, bd + 2 * jj, idesc, sfa + 4 * jj, sfb + 4 * jj, (fresh && jj == 0) ? 0u : 1u, el);
+      umma_commit_p(&T.empty[si], el);
+    };
+    auto open_piece = [&]() {   // first tile of a piece: the epilogue must have drained this accumulator buffer
+      if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
+    };
+    auto close_piece = [&]() {
+      umma_commit_p(&T.acc_full[ab], el);
+      aph[ab] ^= 1u;
+      ab ^= 1;
+      ++pieces;
+    };
+    if (n1 > 0) {
+      if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
+      tc_fence_after();
+    }
+    for (int j = 0, kb = 0; j < n1; ++j) {
+      if (kb == 0) open_piece();
+      issue(region16 + kb * ((N * 128) >> 4), tm_sfb + 16 * kb, kb == KB1 - 1 ? nkt_last1 : 4, kb == 0);
+      TC_TRACE(j, 4);
+      if (++kb == KB1) { kb = 0; close_piece(); }
+      if (++si == NS) { si = 0; ph ^= 1u; }
+    }
+    if (n2 > 0) {
+      const int per_nb = U * KB2;
+      int left = per_nb - T.sb2[v] % per_nb, kb = T.sb2[v] % KB2;
+      bool open = false;
+      for (int j = 0; j < n2; ++j) {
+        const bool fresh = !open;
+        if (fresh) { open_piece(); open = true; }
+        issue(region16 + si * (kSlab >> 4), tm_sfb + 16 * si, kb == KB2 - 1 ? nkt_last2 : 4, fresh);
+        TC_TRACE(n1 + j, 4);
+        if (++kb == KB2) kb = 0;
+        if (--left == 0 || j == n2 - 1) {
+          close_piece();
+          open = false;
+          if (left == 0) left = per_nb;
         }
-        if (copier) {
-          TC_T0(t0);
-          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
-          TC_ADD(tm_a, t0);
-          tc_fence_after();
-          TC_T0(tcp);
-          for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(tm_sfa + 16 * si + 4 * jj, smem_desc_sf_tile(st + 16384 + jj * 512));
-          if (!is1) {
-            for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(sfb + 4 * jj, smem_desc_sf_tile(b_addr + N * 128 + jj * 512));
-          } else if (!((xsf_done >> kbx) & 1ull)) {
-            xsf_done |= 1ull << kbx;
-            for (int jj = 0; jj < nkt; ++jj) tmem_cp_sf(sfb + 4 * jj, smem_desc_sf_tile(smem_u32(xb_sf + (4 * kbx + jj) * 512)));
-          }
-          umma_commit(&T.sfr[si]);
-          TC_ADD(tm_d, tcp);
-        } else {
-          if (!piece_open) {   // first tile of a piece: the epilogue must have drained the accumulator buffer
-            TC_T0(t0);
-            if (pieces >= 2 && !mbar_wait(&T.acc_empty[ab], aph[ab] ^ 1u, &T.abort_flag)) *P.status = 5;
-            TC_ADD(tm_b, t0);
-            acc_flag = false;
-          }
-          TC_T0(t1);
-          if (!mbar_wait(&T.sfr[si], ph, &T.abort_flag)) *P.status = 8;
-          if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
-          TC_ADD(tm_a, t1);
-          tc_fence_after();
-#ifdef B200_TIMERS
-          if (P.debug && first_stamp) { P.debug[v * 16 + 15] = clock64() - tm_begin; first_stamp = false; }   // first tile ready for MMA
-#endif
-          TC_T0(tmm);
-          for (int jj = 0; jj < nkt; ++jj) {
-            umma_mxf4nvf4(tm_acc + 64 * ab, smem_desc_sw128_kmajor(st) + 2 * jj, smem_desc_sw128_kmajor(b_addr) + 2 * jj, idesc,
-                          tm_sfa + 16 * si + 4 * jj, sfb + 4 * jj, acc_flag ? 1u : 0u);
-            acc_flag = true;
-          }
-          umma_commit(&T.empty[si]);
-          if (last_of_piece) {
-            umma_commit(&T.acc_full[ab]);
-            aph[ab] ^= 1u;
-            ab ^= 1;
-            ++pieces;
-          }
-          TC_ADD(tm_c, tmm);
-        }
-        piece_open = !last_of_piece;
         if (++si == NS) { si = 0; ph ^= 1u; }
       }
-#ifdef B200_TIMERS
-      if (P.debug && !copier) { P.debug[v * 16 + 4] = tm_a; P.debug[v * 16 + 5] = tm_b; P.debug[v * 16 + 6] = clock64() - tm_begin; P.debug[v * 16 + 10] = tm_c; P.debug[v * 16 + 12] = n1 + n2; }
-      if (P.debug && copier) { P.debug[v * 16 + 11] = tm_d; P.debug[v * 16 + 13] = tm_a; }
-#endif
     }
-    __syncwarp();
+#ifdef B200_TIMERS
+    if (P.debug && lane == 0) { P.debug[v * 16 + 6] = clock64() - tm_begin; P.debug[v * 16 + 12] = n1 + n2; }
+#endif
   } else {
     // ============================================================== epilogue: 4 warps, thread = accumulator row
     const int et = tid;                            // 0..127
@@ -694,7 +735,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, 512);
+  if (warp == 8) tmem_dealloc(tmem, 512);
   if (T.abort_flag)
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
 }

@@ -57,6 +57,30 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------- issue (whole warp)
+// The same operations for a warp that stays converged: every lane executes the surrounding code with warp-uniform
+// values, and `pred` (from elect_one) lets exactly one lane issue. Uniform operands can then live in uniform registers,
+// which makes the issue much cheaper than from a single diverged lane.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred;
+}
+__device__ __forceinline__ void umma_mxf4nvf4_p(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                                uint32_t sfb_tmem, uint32_t accumulate, uint32_t pred) {
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.b32 p, %4, 0;\n setp.ne.b32 q, %7, 0;\n"
+      " @q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_p(uint32_t taddr, uint64_t sdesc, uint32_t pred) {
+  asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %2, 0;\n @q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n}\n" ::"r"(taddr), "l"(sdesc), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void umma_commit_p(uint64_t* bar, uint32_t pred) {
+  asm volatile("{\n .reg .pred q;\n setp.ne.b32 q, %1, 0;\n @q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(smem_u32(bar)), "r"(pred) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------------- accumulator loads
 // 32 lanes (this warp's quadrant) x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -80,6 +104,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+// 16 registers per thread -> 16 consecutive columns of this warp's lane quadrant (thread = lane).
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace b200

@@ -9,7 +9,8 @@ namespace b200 {
 
 struct ProbeKnobs {
   uint32_t op_lbo, op_sbo, op_layout;   // operand descriptor (bytes, bytes, layout type)
-  uint32_t sf_lbo, sf_sbo;              // scale-tile descriptor
+  uint32_t sf_lbo, sf_sbo;              // scale-tile descriptor; sf_sbo == 0: no tcgen05.cp - the four warps move the scale
+                                        // tiles shared memory -> registers -> TMEM (tcgen05.st), each into its own lane quadrant
   uint32_t idesc;                       // 0: computed by idesc_mxf4nvf4
   uint32_t k_step;                      // descriptor start-address increment per K=64 step, in 16-byte units
   uint32_t sf_col_step;                 // TMEM columns per K=64 step of scale factors
@@ -59,13 +60,35 @@ __global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict
   tc_fence_after();
   const uint32_t tb = tmem_base;
   const uint32_t d_tmem = tb, sfa_tmem = tb + 128, sfb_tmem = tb + 192;
+  const bool sf_by_st = kn.sf_sbo == 0;
+  if (sf_by_st) {               // lane l of every quadrant holds row l of each 512-byte tile: 16 bytes = 4 columns
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int kb = 0; kb < nkb; ++kb) {
+      uint32_t ra[16], rb[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 va = lds128(smem_u32(sSFA + (kb * 4 + j) * 512 + (tid & 31) * 16));
+        const uint4 vb = lds128(smem_u32(sSFB + (kb * 4 + j) * 512 + (tid & 31) * 16));
+        ra[4 * j] = va.x, ra[4 * j + 1] = va.y, ra[4 * j + 2] = va.z, ra[4 * j + 3] = va.w;
+        rb[4 * j] = vb.x, rb[4 * j + 1] = vb.y, rb[4 * j + 2] = vb.z, rb[4 * j + 3] = vb.w;
+      }
+      tmem_st_32x32b_x16(sfa_tmem + 16 * kb + lane_base, ra);
+      tmem_st_32x32b_x16(sfb_tmem + 16 * kb + lane_base, rb);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
   if (tid == 32) {              // one thread issues all tensor-core work
     const uint32_t idesc = kn.idesc ? kn.idesc : idesc_mxf4nvf4(128, N);
     for (int kb = 0; kb < nkb; ++kb)
       for (int j = 0; j < 4; ++j) {
         const int s = kb * 4 + j;
-        tmem_cp_sf(sfa_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFA + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
-        tmem_cp_sf(sfb_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFB + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
+        if (!sf_by_st) {
+          tmem_cp_sf(sfa_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFA + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
+          tmem_cp_sf(sfb_tmem + s * kn.sf_col_step, smem_desc(smem_u32(sSFB + s * 512), kn.sf_lbo, kn.sf_sbo, 0));
+        }
         const uint64_t ad = smem_desc(smem_u32(sA + kb * 16384), kn.op_lbo, kn.op_sbo, kn.op_layout) + (uint64_t)(j * kn.k_step);
         const uint64_t bd = smem_desc(smem_u32(sB + kb * 16384), kn.op_lbo, kn.op_sbo, kn.op_layout) + (uint64_t)(j * kn.k_step);
         umma_mxf4nvf4(d_tmem, ad, bd, idesc, sfa_tmem + s * kn.sf_col_step, sfb_tmem + s * kn.sf_col_step, s != 0);
@@ -90,39 +113,86 @@ __global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict
 
 
 // Issue-cost measurement of the tcgen05 operations the kernels use: `reps` rounds of {ncp scale copies, nmma MMAs of
-// shape 128 x N x 64}, optionally alternating between two accumulators, timed with clock64 around issue + commit + wait.
-__global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, int ncommit, long long* __restrict__ cycles) {
+// shape 128 x N x 64, ncommit commits}, timed with clock64 around issue and around issue + completion.
+// flags: 1 = alternate between two accumulators; 2 = every round also waits on an mbarrier whose phase completed long
+// ago; 4 = every round executes tcgen05.fence::after_thread_sync; 8 = every round waits for its own commit (commit ->
+// arrive latency; needs ncommit >= 1); 16 = the copies are issued by a second thread in another warp, concurrently with
+// the MMAs of the first (cycles[2], cycles[3] are the second thread's issue and completion times); 32 = the issuing
+// warps stay converged and one elected lane issues (predicated instructions) instead of a single diverged thread.
+__global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, int nmma, int flags, int ncommit, long long* __restrict__ cycles) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t bar, bar2;
+  __shared__ uint64_t bar, bar2, bar_done, bar_b, bar_b2;
   __shared__ uint32_t tmem_base;
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
   for (int i = tid; i < (32768 + 4096) / 16; i += 128) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
-  if (tid == 0) { mbar_init(&bar, 1); mbar_init(&bar2, 1); abort_flag = 0; fence_mbar_init(); }
+  if (tid == 0) {
+    mbar_init(&bar, 1); mbar_init(&bar2, 1); mbar_init(&bar_done, 1); mbar_init(&bar_b, 1); mbar_init(&bar_b2, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+    mbar_arrive(&bar_done);   // phase 0 of this barrier is complete from here on
+  }
   if (warp == 0) { tmem_alloc(&tmem_base, 512); tmem_relinquish(); }
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tb = tmem_base;
-  if (tid == 32) {
+  const bool split = (flags & 16) != 0;
+  if ((flags & 32) && (warp == 1 || (split && warp == 2))) {
+    const bool second = warp == 2;
+    const uint32_t el = elect_one();
     const uint32_t idesc = idesc_mxf4nvf4(128, N);
     const uint32_t sA = smem_u32(smem), sB = smem_u32(smem + 16384), sS = smem_u32(smem + 32768);
+    uint64_t* round_bar = second ? &bar_b2 : &bar2;
+    uint64_t* end_bar = second ? &bar_b : &bar;
+    const int my_cp = split ? (second ? ncp : 0) : ncp, my_mma = second ? 0 : nmma;
+    uint32_t ph = 0;
     const long long t0 = clock64();
     for (int r = 0; r < reps; ++r) {
-      for (int c = 0; c < ncp; ++c) tmem_cp_sf(tb + 256 + 4 * (c & 31), smem_desc_sf_tile(sS + (c & 7) * 512));
-      for (int m = 0; m < nmma; ++m)
-        umma_mxf4nvf4(tb + (two_acc ? 128 * (m & 1) : 0), smem_desc_sw128_kmajor(sA) + 2 * (m & 3), smem_desc_sw128_kmajor(sB) + 2 * (m & 3), idesc,
-                      tb + 256 + 4 * (m & 3), tb + 272 + 4 * (m & 3), 1u);
-      for (int c = 0; c < ncommit; ++c) umma_commit(&bar2);
+      if (flags & 2) mbar_wait(&bar_done, 0, &abort_flag, 1u << 16);
+      if (flags & 4) tc_fence_after();
+      for (int c = 0; c < my_cp; ++c) tmem_cp_sf_p(tb + 256 + 4 * (c & 31), smem_desc_sf_tile(sS + (c & 7) * 512), el);
+      for (int m = 0; m < my_mma; ++m)
+        umma_mxf4nvf4_p(tb + ((flags & 1) ? 128 * (m & 1) : 0), smem_desc_sw128_kmajor(sA) + 2 * (m & 3), smem_desc_sw128_kmajor(sB) + 2 * (m & 3), idesc,
+                        tb + 256 + 4 * (m & 3), tb + 272 + 4 * (m & 3), 1u, el);
+      for (int c = 0; c < ncommit; ++c) umma_commit_p(round_bar, el);
+      if ((flags & 8) && ncommit == 1) { mbar_wait(round_bar, ph, &abort_flag, 1u << 20); ph ^= 1u; }
     }
     const long long t1 = clock64();
-    umma_commit(&bar);
-    mbar_wait(&bar, 0, &abort_flag, 1u << 22);
+    umma_commit_p(end_bar, el);
+    mbar_wait(end_bar, 0, &abort_flag, 1u << 22);
     const long long t2 = clock64();
-    cycles[0] = t1 - t0;
-    cycles[1] = t2 - t0;
+    if ((tid & 31) == 0) {
+      cycles[second ? 2 : 0] = t1 - t0;
+      cycles[second ? 3 : 1] = t2 - t0;
+    }
+  } else if (!(flags & 32) && (tid == 32 || (split && tid == 64))) {
+    const bool second = tid == 64;
+    const uint32_t idesc = idesc_mxf4nvf4(128, N);
+    const uint32_t sA = smem_u32(smem), sB = smem_u32(smem + 16384), sS = smem_u32(smem + 32768);
+    uint64_t* round_bar = second ? &bar_b2 : &bar2;
+    uint64_t* end_bar = second ? &bar_b : &bar;
+    const int my_cp = split ? (second ? ncp : 0) : ncp, my_mma = second ? 0 : nmma;
+    uint32_t ph = 0;
+    const long long t0 = clock64();
+    for (int r = 0; r < reps; ++r) {
+      if (flags & 2) mbar_wait(&bar_done, 0, &abort_flag, 1u << 16);
+      if (flags & 4) tc_fence_after();
+      for (int c = 0; c < my_cp; ++c) tmem_cp_sf(tb + 256 + 4 * (c & 31), smem_desc_sf_tile(sS + (c & 7) * 512));
+      for (int m = 0; m < my_mma; ++m)
+        umma_mxf4nvf4(tb + ((flags & 1) ? 128 * (m & 1) : 0), smem_desc_sw128_kmajor(sA) + 2 * (m & 3), smem_desc_sw128_kmajor(sB) + 2 * (m & 3), idesc,
+                      tb + 256 + 4 * (m & 3), tb + 272 + 4 * (m & 3), 1u);
+      for (int c = 0; c < ncommit; ++c) umma_commit(round_bar);
+      if ((flags & 8) && ncommit == 1) { mbar_wait(round_bar, ph, &abort_flag, 1u << 20); ph ^= 1u; }
+    }
+    const long long t1 = clock64();
+    umma_commit(end_bar);
+    mbar_wait(end_bar, 0, &abort_flag, 1u << 22);
+    const long long t2 = clock64();
+    cycles[second ? 2 : 0] = t1 - t0;
+    cycles[second ? 3 : 1] = t2 - t0;
   }
   tc_fence_before();
   __syncthreads();
@@ -133,12 +203,12 @@ __global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, 
 
 using namespace b200;
 
-// cycles_dev[0] = cycles to issue, cycles_dev[1] = cycles until everything completed (device int64 x 2)
-extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int two_acc, int ncommit, long long* cycles_dev, void* stream) {
-  if (!cycles_dev || N < 16 || N > 128 || N % 16 || reps < 1 || reps > 4096 || ncp < 0 || ncp > 64 || nmma < 0 || nmma > 64 || ncommit < 0 || ncommit > 8) return B200MOE_ERR_ARG;
+// cycles_dev: device int64 x 4 = {issue, completion} cycles of the first and (flags & 16) of the second issuing thread
+extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int flags, int ncommit, long long* cycles_dev, void* stream) {
+  if (!cycles_dev || N < 16 || N > 128 || N % 16 || reps < 1 || reps > 4096 || ncp < 0 || ncp > 64 || nmma < 0 || nmma > 64 || ncommit < 0 || ncommit > 8 || flags < 0 || flags > 63) return B200MOE_ERR_ARG;
   const int smem = 1024 + 32768 + 4096;
   B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_cost, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  k_umma_cost<<<1, 128, smem, (cudaStream_t)stream>>>(N, reps, ncp, nmma, two_acc, ncommit, cycles_dev);
+  k_umma_cost<<<1, 128, smem, (cudaStream_t)stream>>>(N, reps, ncp, nmma, flags, ncommit, cycles_dev);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
@@ -154,7 +224,7 @@ extern "C" int b200moe_umma_probe(const void* a, const void* sfa, const void* b,
   if (knobs) kn = {knobs[0], knobs[1], knobs[2], knobs[3], knobs[4], knobs[5], knobs[6], knobs[7]};
   // a scale copy writes 4 TMEM columns and must start on a multiple of 4 (anything else is a misaligned-address fault);
   // descriptor offsets are multiples of 16 bytes by construction
-  if (kn.sf_col_step % 4 || kn.sf_col_step > 8 || (kn.op_lbo & 15) || (kn.op_sbo & 15) || (kn.sf_lbo & 15) || (kn.sf_sbo & 15) || kn.op_layout > 6)
+  if ((kn.sf_sbo == 0 && kn.sf_col_step != 4) || kn.sf_col_step % 4 || kn.sf_col_step > 8 || (kn.op_lbo & 15) || (kn.op_sbo & 15) || (kn.sf_lbo & 15) || (kn.sf_sbo & 15) || kn.op_layout > 6)
     return B200MOE_ERR_ARG;
   const int nkb = K / 256;
   const int smem = 1024 + nkb * (16384 * 2 + 4096);

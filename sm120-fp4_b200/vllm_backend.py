@@ -92,8 +92,8 @@ class Weights:
         # kernel-native copies for the tcgen05 decode kernel (FC1 scale tiles per 64-column block, alpha2 normaliser)
         self.prepack = torch.empty(int(h.b200moe_layer_prepack_bytes(self._h)), dtype=torch.uint8, device=dev)
         _lib.check(h.b200moe_layer_prepack(self._h, _lib.ptr(self.prepack), self.prepack.numel(), _lib.stream_ptr()), "prepack")
-        if os.environ.get("B200MOE_DECODE", "") == "mma":
-            self.set_decode_impl("mma")
+        if os.environ.get("B200MOE_DECODE", "") in ("mma", "tcgen05"):   # force one decode kernel (default: chosen by batch size)
+            self.set_decode_impl(os.environ["B200MOE_DECODE"])
         umax, pmax = min(e_n, MAXM * top_k), MAXM * top_k
         self.experts = torch.empty(umax, dtype=torch.int32, device=dev)
         self.offsets = torch.empty(umax + 1, dtype=torch.int32, device=dev)

@@ -38,3 +38,16 @@ def test_block_scaled_fp4_tile_matches_oracle(n, k):
     assert np.isfinite(got).all()
     err = np.abs(got - want).max()
     assert err <= 1e-3 * np.abs(want).max() + 1e-4, f"max err {err} vs max |D| {np.abs(want).max()}"
+
+
+@pytest.mark.parametrize("n,k", [(64, 256), (16, 1024), (128, 512)])
+def test_scales_through_registers_match_the_copy_path(n, k):
+    """The decode kernel moves scale tiles shared memory -> registers -> TMEM (tcgen05.st by four warps, one per lane
+    quadrant) instead of tcgen05.cp; descriptor knob sf_sbo = 0 selects that path in the probe."""
+    rng = np.random.default_rng(n * 77 + k)
+    a = rng.standard_normal((128, k)).astype(np.float32) * 2
+    b = rng.standard_normal((n, k)).astype(np.float32)
+    got_cp, want = probe(a, b)
+    got_st, _ = probe(a, b, knobs=(16, 1024, 2, 0, 0, 0, 2, 4))
+    assert np.array_equal(got_cp, got_st)
+    assert np.abs(got_st - want).max() <= 1e-3 * np.abs(want).max() + 1e-4
