@@ -284,7 +284,9 @@ extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16
                                       int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
   // automatic choice (measured on B200, Qwen3-30B-A3B shape): the mma.sync kernel is ahead up to 8 tokens (shorter latency
   // chain), the tcgen05 kernel from 9 tokens (no CUDA-core dequantisation)
-  if (L && L->w1t && (L->decode_impl == 2 || (L->decode_impl == 0 && M > 8)) && L->sms <= 256 && L->KB1 <= 12) {   // x scale tiles of 12 K boxes fit TMEM
+  // the tcgen05 kernel whenever the tile records exist and the shape fits it: x scale tiles of <= 12 K boxes in TMEM, one
+  // worker group per 128-row output block
+  if (L && L->w1t && L->decode_impl != 1 && L->sms <= 256 && L->KB1 <= 12 && L->NB2 <= L->sms) {
     if (!x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0) return B200MOE_ERR_ARG;
     if (M > 16) return B200MOE_ERR_LIMIT;
     if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;

@@ -29,16 +29,16 @@ constexpr int kTcProducers = 2;    // TMA producer warps: one thread issues only
 constexpr int kTcThreads = (4 + 4 + 1 + kTcProducers) * 32;   // epilogue warps 0-3, scale warps 4-7, MMA warp 8, producers 9..
 constexpr int kTcStage = 18432;   // 16 KB codes + 2 KB scale tiles
 constexpr int kTerms = 4;
-constexpr int kTcMaxE = 256, kTcMaxP = 256, kTcMaxWorkers = 256;
+constexpr int kTcMaxE = 256, kTcMaxP = 256;
 
 struct TcTables {
   int ids[kTcMaxP];
   float wts[kTcMaxP];
   int cnt[kTcMaxE], base[kTcMaxE], uidx[kTcMaxE], experts[kTcMaxE];
-  int sb1[kTcMaxWorkers + 1], sb2[kTcMaxWorkers + 1];
   float colscale[64];          // 1 / g_t of every B column of the FC1 operand (token-major, four terms per token)
+  float a1[kTcMaxE], a2n[kTcMaxE];   // per touched expert (unit index): alpha1, alpha2 relative to the layer's largest alpha2
   int U;
-  unsigned gen0;
+  unsigned gen0[2];           // generation words of the two FC1 gates as found at kernel entry
   volatile int abort_flag;
   int last_flag;
   uint32_t tmem_base;
@@ -57,7 +57,6 @@ struct TcTables {
 #define TC_ADD(acc, var)
 #endif
 
-__device__ __forceinline__ int tc_worker_of(int f, int T, int V) { return (int)(((unsigned)(f + 1) * (unsigned)V - 1u) / (unsigned)T); }
 __device__ __forceinline__ float tc_silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
 
 __device__ __forceinline__ uint32_t tc_e2m1(float v) {
@@ -234,6 +233,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
                                                           // FC2: NS activation slabs
   TcTables& T = *reinterpret_cast<TcTables*>(region + P.region_bytes);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef B200_TIMERS
+  if (tid == 0 && P.debug) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); P.debug[blockIdx.x * 16 + 13] = (long long)g; }
+#endif
   const int npairs = P.M * P.top_k;
   const int V = gridDim.x;
   const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
@@ -245,7 +247,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     mbar_init(&T.xb_full, 1);
     T.abort_flag = 0;
     T.last_flag = 0;
-    T.gen0 = ld_acquire_gpu(P.gridbar + 1);
+    T.gen0[0] = ld_acquire_gpu(P.gridbar + 1);
+    T.gen0[1] = ld_acquire_gpu(P.gridbar + 3);
     fence_mbar_init();
   }
   if (warp == 8) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
@@ -280,14 +283,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   __syncthreads();
   const int U = T.U;
-  const int T1 = U * CB1 * KB1, T2 = NB2 * U * KB2;
-  for (int i = tid; i < kTcMaxE; i += kTcThreads)
-    if (T.cnt[i] > 0) T.experts[T.uidx[i] - 1] = i;
-  for (int v = tid; v <= V; v += kTcThreads) {
-    // FC1 shares are whole units (an expert's 64-column block over all of K): no unit is split, so FC1 needs no cross-CTA
-    // reduction; the imbalance is at most one unit. FC2 output blocks are reduced over experts anyway: tile-granular shares.
-    T.sb1[v] = (int)(((unsigned)v * (unsigned)(U * CB1)) / (unsigned)V) * KB1;
-    T.sb2[v] = (int)(((unsigned)v * (unsigned)T2) / (unsigned)V);
+  {
+    const float a2inv = P.alpha2_ref[1];
+    for (int i = tid; i < kTcMaxE; i += kTcThreads)
+      if (T.cnt[i] > 0) {
+        const int u = T.uidx[i] - 1;
+        T.experts[u] = i;
+        T.a1[u] = P.alpha1[i];
+        T.a2n[u] = P.alpha2[i] * a2inv;
+      }
   }
   tc_fence_before();
   __syncthreads();
@@ -305,11 +309,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       P.pairs_out[T.base[e] - T.cnt[e] + r] = p;
     }
   }
+  // ---------------------------------------------------------------- work split (closed form, the same on every worker)
+  // FC1: units q = (touched expert u, 64-column block cb), u-major; worker v takes q = v, v + V, ...: whole units (no
+  // cross-CTA reduction), and all workers move through the experts in the same order, so the experts below uA (group A)
+  // are finished grid-wide about half way through FC1. Gate A opens when every worker has finished its units of group A,
+  // gate B when all of FC1 is done.
+  // FC2: the workers are split into NB2 groups, one per 128-row output block; inside a group, worker r takes the items
+  // i = (u, kb) = r, r + W, ... in ascending order, accumulates them in one TMEM accumulator, and the group's partials are
+  // added in worker order by whoever arrives last. A worker's first items belong to group A: they run while the tail of
+  // FC1, gate B and the fetch of the remaining activation slabs are still in flight elsewhere.
   const int v = blockIdx.x;
-  const int n1 = T.sb1[v + 1] - T.sb1[v], n2 = T.sb2[v + 1] - T.sb2[v];
+  const int Q1 = U * CB1;
+  const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
+  const int n1 = nu1 * KB1;
+  const int uA = U / 2, qA = uA * CB1;
+  const int nuA = v < qA ? (qA - v + V - 1) / V : 0;   // this worker's units of group A (its first ones)
+  const int Wb = V / NB2, Wx = V % NB2;                // groups 0..Wx-1 have Wb + 1 workers
+  int nb2, r2, W2, vlo2;
+  if (v < Wx * (Wb + 1)) { nb2 = v / (Wb + 1); r2 = v - nb2 * (Wb + 1); W2 = Wb + 1; vlo2 = nb2 * (Wb + 1); }
+  else { const int vv = v - Wx * (Wb + 1); nb2 = Wx + vv / Wb; r2 = vv % Wb; W2 = Wb; vlo2 = Wx * (Wb + 1) + (nb2 - Wx) * Wb; }
+  const int I2 = U * KB2;
+  const int n2 = r2 < I2 ? (I2 - r2 + W2 - 1) / W2 : 0;
+  const int live2 = W2 < I2 ? W2 : I2;                 // workers of the group that hold a partial: ranks 0..live2-1
+  const int dU2 = W2 / KB2, dK2 = W2 % KB2;            // item step W2 as (experts, K boxes)
 #ifdef B200_TIMERS
   long long tm_a = 0, tm_b = 0, tm_c = 0, tm_d = 0;
   const long long tm_begin = clock64();
+  if (tid == 0 && P.debug) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); P.debug[blockIdx.x * 16 + 15] = (long long)g; }
 #endif
   const uint32_t tmem = T.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 320;   // accumulators 2 x 64 | weight scales NS x 16 (<= 192) | operand scales (<= 192)
@@ -328,30 +354,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
         bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
       }
-      const unsigned gen0 = T.gen0;
-      bool passed = false;
-      int pend_slot[8], pend_idx[8], npend = 0;
+      bool passed[2] = {false, false};
+      int pend_slot[16], pend_idx[16], pend_g[16], npend = 0, pend_head = 0;   // ring of 16: at most NS (<= 12) entries wait at a time
+      int slot_g[12];                                                          // gate of the FC2 tile in each ring slot
       auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
         bulk_load(region + slot * kSlab, P.aslab + (long long)idx * kSlab, kSlab, &T.full[slot]);
       };
-      auto wait_grid = [&]() {
-        if (passed) return;
-        bool ok = false;
-        for (uint32_t it = 0; it < (1u << 24); ++it) {
-          if (ld_acquire_gpu(P.gridbar + 1) != gen0) { ok = true; break; }
-          if (T.abort_flag) break;
-          __nanosleep(64);
+      auto open_gate = [&](int g) {   // wait until gate g (and every gate before it) is open; issue the slab loads that waited for it
+        for (int gg = 0; gg <= g; ++gg) {
+          if (passed[gg]) continue;
+          bool ok = false;
+          for (uint32_t it = 0; it < (1u << 24); ++it) {
+            if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) { ok = true; break; }
+            if (T.abort_flag) break;
+          }
+          if (!ok) { T.abort_flag = 1; *P.status = 3; }
+          fence_proxy_async();
+          while (pend_head < npend && pend_g[pend_head & 15] <= gg) { load_slab(pend_slot[pend_head & 15], pend_idx[pend_head & 15]); ++pend_head; }
+          passed[gg] = true;
         }
-        if (!ok) { T.abort_flag = 1; *P.status = 3; }
-        fence_proxy_async();
-        for (int i = 0; i < npend; ++i) load_slab(pend_slot[i], pend_idx[i]);
-        npend = 0;
-        passed = true;
       };
       int slot = 0, use = 0, mine = pw == 0 ? 0 : kTcProducers - pw;   // `mine` counts down to this producer's next tile
-      auto acquire = [&](bool over_fc2) {   // the ring slot of the current position, free of its previous occupant
+      auto acquire = [&](int gate) {   // the ring slot of the current position, free of its previous occupant
         if (use >= 1) {
-          if (over_fc2) wait_grid();        // that occupant is an FC2 tile still waiting for its activations: open the gate first
+          if (gate >= 0) open_gate(gate);   // that occupant may be an FC2 tile still waiting for its activations
           if (!mbar_wait(&T.empty[slot], (use - 1) & 1, &T.abort_flag)) *P.status = 2;
         }
       };
@@ -359,53 +385,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         if (++slot == NS) { slot = 0; ++use; }
         mine = mine == 0 ? kTcProducers - 1 : mine - 1;
       };
-      // ---- FC1 tiles: whole units (expert, 64-column block) x KB1 boxes; the records of one expert are contiguous
-      if (n1 > 0) {
-        const int q0 = T.sb1[v] / KB1;
-        int u = q0 / CB1;
-        int left_e = (CB1 - q0 % CB1) * KB1;   // tiles left in this expert
-        const uint8_t* src = P.w1t + ((long long)T.experts[u] * CB1 + q0 % CB1) * KB1 * kTcStage;
-        for (int j = 0; j < n1; ++j) {
-          if (left_e == 0) {
-            ++u;
-            src = P.w1t + (long long)T.experts[u] * CB1 * KB1 * kTcStage;
-            left_e = CB1 * KB1;
-          }
+      // ---- FC1 tiles: units v, v + V, ... x KB1 boxes; the KB1 records of a unit are contiguous
+      for (int t = 0, j = 0; t < nu1; ++t) {
+        const int q = v + t * V, u = q / CB1, cb = q - u * CB1;
+        const uint8_t* src = P.w1t + ((long long)T.experts[u] * CB1 + cb) * KB1 * kTcStage;
+        for (int kb = 0; kb < KB1; ++kb, ++j) {
           if (mine == 0) {
-            acquire(false);
+            acquire(-1);
             TC_TRACE(j, 0);
             mbar_expect_tx(&T.full[slot], kTcStage);
-            bulk_load_hint(ring + slot * kTcStage, src, kTcStage, &T.full[slot], pol);
+            bulk_load_hint(ring + slot * kTcStage, src + (long long)kb * kTcStage, kTcStage, &T.full[slot], pol);
           }
-          src += kTcStage;
-          --left_e;
           advance();
         }
       }
-      // ---- FC2 tiles: position f = (nb * U + u) * KB2 + kb; weights (expert of u, nb, kb), activation slab (u, kb)
-      if (n2 > 0) {
-        const int f0 = T.sb2[v];
-        int kb = f0 % KB2, u = (f0 / KB2) % U, nb = (f0 / KB2) / U;
-        const uint8_t* src = P.w2t + (((long long)T.experts[u] * NB2 + nb) * KB2 + kb) * kTcStage;
+      // ---- FC2 tiles: items (u, kb) = r2, r2 + W2, ... of output block nb2; weights (expert of u, nb2, kb), slab (u, kb)
+      {
+        int u = r2 / KB2, kb = r2 % KB2;
         for (int j = 0; j < n2; ++j) {
+          const int g = u < uA ? 0 : 1;
+          const int prev_g = j >= NS ? slot_g[slot] : -1;   // gate of the FC2 tile that holds this slot now, if any
+          slot_g[slot] = g;
           if (mine == 0) {
-            acquire(!passed && (n1 + j - NS) >= n1);
+            acquire(prev_g);
             TC_TRACE(n1 + j, 0);
             mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
-            bulk_load_hint(ring + slot * kTcStage, src, kTcStage, &T.full[slot], pol);
-            if (passed) load_slab(slot, u * KB2 + kb);
-            else { pend_slot[npend] = slot; pend_idx[npend] = u * KB2 + kb; ++npend; }
+            bulk_load_hint(ring + slot * kTcStage, P.w2t + (((long long)T.experts[u] * NB2 + nb2) * KB2 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
+            if (passed[g]) load_slab(slot, u * KB2 + kb);
+            else { pend_slot[npend & 15] = slot; pend_idx[npend & 15] = u * KB2 + kb; pend_g[npend & 15] = g; ++npend; }
           }
-          src += kTcStage;
-          if (++kb == KB2) {
-            kb = 0;
-            if (++u == U) { u = 0; ++nb; }
-            if (nb < NB2) src = P.w2t + ((long long)T.experts[u] * NB2 + nb) * KB2 * kTcStage;
-          }
+          kb += dK2, u += dU2;
+          if (kb >= KB2) { kb -= KB2; ++u; }
           advance();
         }
       }
-      if (npend > 0) wait_grid();
+      if (pend_head < npend) open_gate(1);
 #ifdef B200_TIMERS
       if (P.debug && pw == 0) P.debug[v * 16 + 9] = clock64() - tm_begin;
 #endif
@@ -498,23 +512,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       if (++kb == KB1) { kb = 0; close_piece(); }
       if (++si == NS) { si = 0; ph ^= 1u; }
     }
-    if (n2 > 0) {
-      const int per_nb = U * KB2;
-      int left = per_nb - T.sb2[v] % per_nb, kb = T.sb2[v] % KB2;
-      bool open = false;
-      for (int j = 0; j < n2; ++j) {
-        const bool fresh = !open;
-        if (fresh) { open_piece(); open = true; }
-        issue(region16 + si * (kSlab >> 4), tm_sfb + 16 * si, kb == KB2 - 1 ? nkt_last2 : 4, fresh);
+    if (n2 > 0) {   // one piece: all of this worker's items of output block nb2 go into one accumulator
+      open_piece();
+      for (int j = 0, kb = r2 % KB2; j < n2; ++j) {
+        issue(region16 + si * (kSlab >> 4), tm_sfb + 16 * si, kb == KB2 - 1 ? nkt_last2 : 4, j == 0);
         TC_TRACE(n1 + j, 4);
-        if (++kb == KB2) kb = 0;
-        if (--left == 0 || j == n2 - 1) {
-          close_piece();
-          open = false;
-          if (left == 0) left = per_nb;
-        }
+        kb += dK2;
+        if (kb >= KB2) kb -= KB2;
         if (++si == NS) { si = 0; ph ^= 1u; }
       }
+      close_piece();
     }
 #ifdef B200_TIMERS
     if (P.debug && lane == 0) { P.debug[v * 16 + 6] = clock64() - tm_begin; P.debug[v * 16 + 12] = n1 + n2; }
@@ -560,80 +567,82 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       aph[ab] ^= 1u;
       ab ^= 1;
     };
-    auto reduce = [&](const int* sb, int first, int vlo, int vhi, float (&val)[16]) {
+    // Sum of the partials of workers vlo..vhi in worker order (a fixed order: bit-identical from call to call). A partial
+    // holds N/4 floats per row; kRedBatch workers are loaded at once so that the L2 round trips overlap.
+    constexpr int kRedBatch = NB == 4 ? 6 : 12;
+    auto reduce = [&](int vlo, int nlive, float (&val)[16]) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) val[i] = 0.f;
-      for (int p0 = vlo; p0 <= vhi; p0 += 4) {
-        float4 tmp[4][4];
-        bool live[4];
+      for (int p0 = 0; p0 < nlive; p0 += kRedBatch) {
+        float4 tmp[kRedBatch][NB];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const int pv = p0 + b;
-          live[b] = pv <= vhi && sb[pv + 1] > sb[pv];
-          const int pslot = (live[b] && sb[pv] < first) ? 1 : 0;
-          const float* src = P.scratch + ((long long)((live[b] ? pv : vlo) * 2 + pslot) * 128 + et) * 16;
+        for (int b = 0; b < kRedBatch; ++b) {
+          const bool live = p0 + b < nlive;
+          const float* src = P.scratch + ((long long)((vlo + (live ? p0 + b : 0)) * 2) * 128 + et) * 16;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) tmp[b][i] = live[b] ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i = 0; i < NB; ++i) tmp[b][i] = live ? __ldcg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (live[b]) {
+        for (int b = 0; b < kRedBatch; ++b)
+          if (p0 + b < nlive) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { val[4 * i] += tmp[b][i].x; val[4 * i + 1] += tmp[b][i].y; val[4 * i + 2] += tmp[b][i].z; val[4 * i + 3] += tmp[b][i].w; }
+            for (int i = 0; i < NB; ++i) { val[4 * i] += tmp[b][i].x; val[4 * i + 1] += tmp[b][i].y; val[4 * i + 2] += tmp[b][i].z; val[4 * i + 3] += tmp[b][i].w; }
           }
       }
     };
-    // publish this worker's partial of a split unit and learn whether it arrived last
-    auto publish = [&](const float (&val)[16], int slot_id, unsigned* counter, const int* sb, int vlo, int vhi) -> bool {
-      float* mine = P.scratch + ((long long)(v * 2 + slot_id) * 128 + et) * 16;
+    // publish this worker's partial of its output block and learn whether it arrived last of the `nlive` holders
+    auto publish = [&](const float (&val)[16], unsigned* counter, int nlive) -> bool {
+      float* mine = P.scratch + ((long long)(v * 2) * 128 + et) * 16;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(val[4 * i], val[4 * i + 1], val[4 * i + 2], val[4 * i + 3]);
+      for (int i = 0; i < NB; ++i) *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(val[4 * i], val[4 * i + 1], val[4 * i + 2], val[4 * i + 3]);
       named_bar_sync(1, 128);
       if (et == 0) {
         __threadfence();
-        int nlive = 0;
-        for (int pv = vlo; pv <= vhi; ++pv) nlive += sb[pv + 1] > sb[pv];
         const unsigned old = atomicAdd(counter, 1u);
         const int last = old + 1u == (unsigned)nlive;
         if (last) { *counter = 0; __threadfence(); }
         T.last_flag = last;
       }
       named_bar_sync(1, 128);
-      const bool last = T.last_flag != 0;
+      return T.last_flag != 0;   // the next write of last_flag is behind at least one more barrier of these 128 threads
+    };
+    // arrive at gate g of FC1: everything this worker wrote for the experts of the gate's group is visible to the TMA
+    // loads of every worker that sees the gate open (the producers are the only waiters)
+    auto arrive_gate = [&](int g) {
+      fence_proxy_async();
       named_bar_sync(1, 128);
-      return last;
+      if (et == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(P.gridbar + 2 * g, 1u);
+        if (old == (unsigned)(V - 1)) {
+          P.gridbar[2 * g] = 0;
+          __threadfence();
+          atomicAdd(P.gridbar + 2 * g + 1, 1u);
+        }
+      }
     };
 
     // ---- FC1 pieces
     {
-      const int fs = T.sb1[v], fe = T.sb1[v + 1];
-      int f = fs;
-      while (f < fe) {
-        const int q = f / KB1, cb = q % CB1, u = q / CB1;
-        const int k0 = f % KB1, k1 = min(KB1, k0 + (fe - f));
+      if (nuA == 0) arrive_gate(0);
+      if (nu1 == 0) arrive_gate(1);
+      for (int t = 0; t < nu1; ++t) {
+        const int q = v + t * V, u = q / CB1, cb = q - u * CB1;   // a whole unit: K boxes 0..KB1-1 of (expert u, block cb)
         const int e = T.experts[u];
         float val[16];
         load_terms(val, T.colscale, true);
-        const int piece_first = f;
-        f += k1 - k0;
-        bool finalize = true;
         TC_T0(tfix);
-        if (!(k0 == 0 && k1 == KB1)) {
-          const int vlo = tc_worker_of(q * KB1, T1, V), vhi = tc_worker_of(q * KB1 + KB1 - 1, T1, V);
-          finalize = publish(val, piece_first == fs ? 0 : 1, P.cnt1 + q, T.sb1, vlo, vhi);
-          if (finalize) reduce(T.sb1, q * KB1, vlo, vhi, val);
-        }
-        if (finalize) {
+        {
           // rows 0..63 hold the up columns 64cb.., rows 64..127 the gate columns: exchange through shared memory.
           // s_w[tk]: routing weight of token tk on this expert folded with alpha2 (relative to the layer's largest), 0 when
           // the token is not routed here - only routed tokens cost any arithmetic below.
-          const float alpha = P.alpha1[e];
+          const float alpha = T.a1[u];
           if (et < 16) {
             float wsum = 0.f;
             if (et < P.M)
               for (int sidx = 0; sidx < P.top_k; ++sidx)
                 if (T.ids[et * P.top_k + sidx] == e) wsum += T.wts[et * P.top_k + sidx];
-            s_w[et] = wsum * P.alpha2[e] * P.alpha2_ref[1];
+            s_w[et] = wsum * T.a2n[u];
           }
           if (row >= 64) {
 #pragma unroll
@@ -644,13 +653,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 #pragma unroll
             for (int tk = 0; tk < 16; ++tk) {
               const float wf = s_w[tk];
-              val[tk] = wf != 0.f ? tc_silu_mul(s_ex[row][tk], val[tk] * alpha) * wf : 0.f;
+              s_ex[row][tk] = wf != 0.f ? tc_silu_mul(s_ex[row][tk], val[tk] * alpha) * wf : 0.f;   // only this thread reads that gate value
             }
-          }
-          named_bar_sync(1, 128);
-          if (row < 64) {
-#pragma unroll
-            for (int tk = 0; tk < 16; ++tk) s_ex[row][tk] = val[tk];
           }
           named_bar_sync(1, 128);
           // re-expand: thread (token, 16-column block) -> four NVFP4 terms of the FC2 operand; a token that is not routed
@@ -684,28 +688,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           named_bar_sync(1, 128);
         }
         TC_ADD(tm_b, tfix);
+        if (t == nuA - 1) arrive_gate(0);
+        if (t == nu1 - 1) arrive_gate(1);
       }
 #ifdef B200_TIMERS
       tm_c = clock64() - tm_begin;
 #endif
-      // ---- publish FC1's results, arrive at the grid-wide barrier (the producers are the only waiters)
-      fence_proxy_async();
-      named_bar_sync(1, 128);
-      if (et == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(P.gridbar, 1u);
-        if (old == (unsigned)(V - 1)) {
-          P.gridbar[0] = 0;
-          __threadfence();
-          atomicAdd(P.gridbar + 1, 1u);
-        }
-      }
     }
-    // ---- FC2 pieces: one accumulator per (worker, output block), all experts and K boxes summed inside the tensor core
-    {
-      const int fs = T.sb2[v], fe = T.sb2[v + 1];
-      const int per_nb = U * KB2;
-      int f = fs;
+    // ---- FC2: this worker's items of output block nb2, summed over experts and K boxes inside the tensor core
+    if (n2 > 0) {
       float cs[kTerms];   // 1 / g_t of the activation terms, times the alpha2 the operand was normalised by
       {
         float g = P.act_g1;
@@ -713,21 +704,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 #pragma unroll
         for (int t = 0; t < kTerms; ++t) { cs[t] = a2ref / g; g *= 6.0f; }
       }
-      while (f < fe) {
-        const int nb = f / per_nb;
-        const int pe = min(fe, (nb + 1) * per_nb);
-        float val[16];
-        load_terms(val, cs, false);
-        const int vlo = tc_worker_of(nb * per_nb, T2, V), vhi = tc_worker_of((nb + 1) * per_nb - 1, T2, V);
-        const bool last = publish(val, f == fs ? 0 : 1, P.cnt2 + nb, T.sb2, vlo, vhi);
-        if (last) {
-          reduce(T.sb2, nb * per_nb, vlo, vhi, val);
+      float val[16];
+      load_terms(val, cs, false);
+      if (publish(val, P.cnt2 + nb2, live2)) {
+        reduce(vlo2, live2, val);
 #pragma unroll
-          for (int tk = 0; tk < 16; ++tk)
-            if (tk < P.M) P.out[(long long)tk * P.H + 128 * nb + row] = __float2bfloat16_rn(val[tk]);
-        }
-        f = pe;
+        for (int tk = 0; tk < 16; ++tk)
+          if (tk < P.M) P.out[(long long)tk * P.H + 128 * nb2 + row] = __float2bfloat16_rn(val[tk]);
       }
+    } else if (I2 == 0 && r2 == 0) {   // every slot of the batch is empty: the layer's output is zero
+      for (int tk = 0; tk < P.M; ++tk) P.out[(long long)tk * P.H + 128 * nb2 + row] = __float2bfloat16_rn(0.f);
     }
 #ifdef B200_TIMERS
     if (P.debug && et == 0) { P.debug[v * 16 + 0] = tm_a; P.debug[v * 16 + 1] = tm_b; P.debug[v * 16 + 2] = tm_c; P.debug[v * 16 + 3] = tm_d; P.debug[v * 16 + 7] = clock64() - tm_begin; }
@@ -735,6 +721,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   tc_fence_before();
   __syncthreads();
+#ifdef B200_TIMERS
+  if (tid == 0 && P.debug) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); P.debug[blockIdx.x * 16 + 14] = (long long)g; }
+#endif
   if (warp == 8) tmem_dealloc(tmem, 512);
   if (T.abort_flag)
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
