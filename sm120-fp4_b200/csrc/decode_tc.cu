@@ -44,7 +44,7 @@ struct TcTables {
   uint32_t tmem_base;
   uint64_t full[12], empty[12], sfr[12];   // stage landed / stage consumed / scale tiles of the stage are in TMEM
   uint64_t acc_full[2], acc_empty[2];
-  uint64_t xb_full;
+  uint64_t xb_full, fc1_done;   // x operand landed / this worker's FC1 MMAs are complete
 };
 
 #ifdef B200_TIMERS
@@ -57,7 +57,7 @@ struct TcTables {
 #define TC_ADD(acc, var)
 #endif
 
-__device__ __forceinline__ float tc_silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+__device__ __forceinline__ float tc_silu_mul(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
 
 __device__ __forceinline__ uint32_t tc_e2m1(float v) {
   const float m = fabsf(v);
@@ -79,32 +79,32 @@ __device__ __forceinline__ float tc_e4m3_value(uint8_t b) {
 }
 
 // 8 floats -> 8 E2M1 codes in one word (element 2j in the low nibble of byte j), hardware round-to-nearest-even,
-// saturating. Each value is converted on both operands of the pair instruction, so the result does not depend on which
-// operand lands in which nibble.
+// saturating. cvt.rn.satfinite.e2m1x2.f32 d, a, b puts a into the high and b into the low nibble of d.
 __device__ __forceinline__ uint32_t cvt_f32x8_e2m1(const float* v) {
-  uint32_t d = 0;
+  uint32_t b[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t b;
-    asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %1;\n cvt.u32.u8 %0, t;\n}\n" : "=r"(b) : "f"(v[i]));
-    d |= (b & 0xFu) << (4 * i);
-  }
-  return d;
+  for (int i = 0; i < 4; ++i)
+    asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n cvt.u32.u8 %0, t;\n}\n" : "=r"(b[i]) : "f"(v[2 * i + 1]), "f"(v[2 * i]));
+  return (b[0] | (b[1] << 8)) | ((b[2] << 16) | (b[3] << 24));
 }
 
 // One 16-value block -> kTerms NVFP4 terms (residual expansion). g1: global scale of the first term; term t uses g1*6^t.
 // codes[t] = 8 packed bytes (element 2j in the low nibble), sf[t] = E4M3 scale byte. The residual is taken against the
-// codes actually emitted, so any rounding of the code conversion is absorbed by the next term.
+// codes and the scale actually emitted, so any rounding on the way (approximate reciprocal included) is absorbed by the
+// next term.
 __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (&codes)[kTerms], uint8_t (&sf)[kTerms]) {
-  float g = g1;
+  float g = g1, ginv = __frcp_rn(g1);
 #pragma unroll
   for (int t = 0; t < kTerms; ++t) {
-    float amax = 0.f;
+    float m[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
+    for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(r[i]), fabsf(r[i + 8]));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], m[i + 4]);
+    const float amax = fmaxf(fmaxf(m[0], m[2]), fmaxf(m[1], m[3]));
     const uint8_t sb = tc_e4m3(fminf(amax * (1.0f / 6.0f) * g, 448.0f));
     const float sv = tc_e4m3_value(sb);
-    const float scale = sv > 0.f ? g / sv : 0.f, back = sv > 0.f ? sv / g : 0.f;
+    const float scale = sv > 0.f ? g * __frcp_rn(sv) : 0.f, back = sv * ginv;
     float sc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) sc[i] = r[i] * scale;
@@ -124,6 +124,7 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
     codes[t] = make_uint2(lo, hi);
     sf[t] = sb;
     g *= 6.0f;
+    ginv *= (1.0f / 6.0f);
   }
 }
 
@@ -241,14 +242,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int KB1 = P.KB1, KB2 = P.KB2, CB1 = P.CB1, NB2 = P.NB2;
 
   // ---------------------------------------------------------------- prologue
+  // Every global load of the prologue is issued at entry, each by a thread of its own, so that their latencies overlap
+  // one another and the barrier / TMEM set-up: pair p is thread p's (npairs <= 256 < threads).
+  int my_e = -1;
+  float my_w = 0.f, my_a1 = 0.f, my_a2 = 0.f;
+  if (tid < npairs) { my_e = P.ids[tid]; my_w = P.wts[tid]; }
+  const float a2inv = P.alpha2_ref[1];
+  unsigned my_gen = 0;
+  if (tid == 9 * 32) my_gen = ld_acquire_gpu(P.gridbar + 1);    // generation words of the two FC1 gates as this launch finds them
+  if (tid == 10 * 32) my_gen = ld_acquire_gpu(P.gridbar + 3);
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); mbar_init(&T.sfr[s], 4); }
     for (int b = 0; b < 2; ++b) { mbar_init(&T.acc_full[b], 1); mbar_init(&T.acc_empty[b], 4); }
     mbar_init(&T.xb_full, 1);
+    mbar_init(&T.fc1_done, 1);
     T.abort_flag = 0;
     T.last_flag = 0;
-    T.gen0[0] = ld_acquire_gpu(P.gridbar + 1);
-    T.gen0[1] = ld_acquire_gpu(P.gridbar + 3);
     fence_mbar_init();
   }
   if (warp == 8) {                       // the MMA warp owns the TMEM allocation (all 512 columns: one CTA per SM)
@@ -256,14 +265,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     tmem_relinquish();
   }
   for (int i = tid; i < kTcMaxE; i += kTcThreads) T.cnt[i] = 0;
+  if (tid < npairs) {   // a negative id marks an empty slot (expert-parallel shards mask the experts they do not own)
+    if (my_e >= P.E) { *P.status = 4; my_e = -1; }
+    if (my_e < 0) my_e = -1;
+    if (my_e >= 0) { my_a1 = P.alpha1[my_e]; my_a2 = P.alpha2[my_e]; }   // in flight across the next two barriers
+  }
   __syncthreads();
-  for (int p = tid; p < npairs; p += kTcThreads) {
-    int e = P.ids[p];   // a negative id marks an empty slot (expert-parallel shards mask the experts they do not own)
-    if (e >= P.E) { *P.status = 4; e = -1; }
-    if (e < 0) e = -1;
-    T.ids[p] = e;
-    T.wts[p] = P.wts[p];
-    if (e >= 0) atomicAdd(&T.cnt[e], 1);
+  if (tid < npairs) {
+    T.ids[tid] = my_e;
+    T.wts[tid] = my_w;
+    if (my_e >= 0) atomicAdd(&T.cnt[my_e], 1);
   }
   __syncthreads();
   if (warp == 0) {
@@ -283,37 +294,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   }
   __syncthreads();
   const int U = T.U;
-  {
-    const float a2inv = P.alpha2_ref[1];
-    for (int i = tid; i < kTcMaxE; i += kTcThreads)
-      if (T.cnt[i] > 0) {
-        const int u = T.uidx[i] - 1;
-        T.experts[u] = i;
-        T.a1[u] = P.alpha1[i];
-        T.a2n[u] = P.alpha2[i] * a2inv;
-      }
+  if (tid < npairs && my_e >= 0) {   // the pairs of one expert all write the same values
+    const int u = T.uidx[my_e] - 1;
+    T.experts[u] = my_e;
+    T.a1[u] = my_a1;
+    T.a2n[u] = my_a2 * a2inv;
   }
+  if (tid == 9 * 32) T.gen0[0] = my_gen;
+  if (tid == 10 * 32) T.gen0[1] = my_gen;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (blockIdx.x == 0 && P.experts_out) {
-    for (int e = tid; e < P.E; e += kTcThreads)
-      if (T.cnt[e] > 0) { P.experts_out[T.uidx[e] - 1] = e; P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e]; }
-    for (int u = U + tid; u < P.Umax; u += kTcThreads) { P.experts_out[u] = -1; P.offsets_out[u + 1] = T.base[kTcMaxE - 1]; }
-    if (tid == 0) P.offsets_out[U] = T.base[kTcMaxE - 1];
-    for (int p = tid; p < npairs; p += kTcThreads) {
-      const int e = T.ids[p];
-      if (e < 0) continue;
-      int r = 0;
-      for (int q = 0; q < p; ++q) r += T.ids[q] == e;
-      P.pairs_out[T.base[e] - T.cnt[e] + r] = p;
-    }
-  }
   // ---------------------------------------------------------------- work split (closed form, the same on every worker)
   // FC1: units q = (touched expert u, 64-column block cb), u-major; worker v takes q = v, v + V, ...: whole units (no
-  // cross-CTA reduction), and all workers move through the experts in the same order, so the experts below uA (group A)
-  // are finished grid-wide about half way through FC1. Gate A opens when every worker has finished its units of group A,
-  // gate B when all of FC1 is done.
+  // cross-CTA reduction), and all workers move through the experts in the same order, so the experts below uA (group A,
+  // three quarters of them) are finished grid-wide three quarters of the way through FC1. Gate A opens when every worker
+  // has finished its units of group A, gate B when all of FC1 is done; a worker's FC2 items of group A keep it busy
+  // while gate B and the last slabs are still on their way.
   // FC2: the workers are split into NB2 groups, one per 128-row output block; inside a group, worker r takes the items
   // i = (u, kb) = r, r + W, ... in ascending order, accumulates them in one TMEM accumulator, and the group's partials are
   // added in worker order by whoever arrives last. A worker's first items belong to group A: they run while the tail of
@@ -322,7 +319,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
   const int n1 = nu1 * KB1;
-  const int uA = U / 2, qA = uA * CB1;
+  const int uA = (3 * U) / 4, qA = uA * CB1;
   const int nuA = v < qA ? (qA - v + V - 1) / V : 0;   // this worker's units of group A (its first ones)
   const int Wb = V / NB2, Wx = V % NB2;                // groups 0..Wx-1 have Wb + 1 workers
   int nb2, r2, W2, vlo2;
@@ -360,7 +357,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
         bulk_load(region + slot * kSlab, P.aslab + (long long)idx * kSlab, kSlab, &T.full[slot]);
       };
-      auto open_gate = [&](int g) {   // wait until gate g (and every gate before it) is open; issue the slab loads that waited for it
+      // An activation slab may land only when (a) the gate of its expert group is open and (b) this worker's own FC1 MMAs
+      // are complete: the slabs share their shared memory with the resident x operand, and their scale columns in TMEM
+      // with the x operand's. Weight tiles of FC2 are prefetched regardless; only the slab loads wait.
+      bool local_ok = n1 == 0;
+      auto flush = [&]() {
+        if (pend_head < npend && local_ok && passed[pend_g[pend_head & 15]]) {
+          fence_proxy_async();
+          while (pend_head < npend && passed[pend_g[pend_head & 15]]) { load_slab(pend_slot[pend_head & 15], pend_idx[pend_head & 15]); ++pend_head; }
+        }
+      };
+      auto open_gate = [&](int g) {   // blocking: wait for (b) and for gate g and every gate before it; issue what waited for them
+        if (!local_ok) {
+          if (!mbar_wait(&T.fc1_done, 0, &T.abort_flag)) *P.status = 9;
+          local_ok = true;
+        }
         for (int gg = 0; gg <= g; ++gg) {
           if (passed[gg]) continue;
           bool ok = false;
@@ -369,10 +380,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             if (T.abort_flag) break;
           }
           if (!ok) { T.abort_flag = 1; *P.status = 3; }
-          fence_proxy_async();
-          while (pend_head < npend && pend_g[pend_head & 15] <= gg) { load_slab(pend_slot[pend_head & 15], pend_idx[pend_head & 15]); ++pend_head; }
           passed[gg] = true;
         }
+        flush();
+      };
+      auto peek_gate = [&](int g) {   // one look, no waiting: gates usually opened long before the tile that needs them is issued
+        if (!local_ok && mbar_test_wait(&T.fc1_done, 0)) local_ok = true;
+        for (int gg = 0; gg <= g && !passed[gg]; ++gg)
+          if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) passed[gg] = true;
+          else break;
+        flush();
       };
       int slot = 0, use = 0, mine = pw == 0 ? 0 : kTcProducers - pw;   // `mine` counts down to this producer's next tile
       auto acquire = [&](int gate) {   // the ring slot of the current position, free of its previous occupant
@@ -411,7 +428,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             TC_TRACE(n1 + j, 0);
             mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
             bulk_load_hint(ring + slot * kTcStage, P.w2t + (((long long)T.experts[u] * NB2 + nb2) * KB2 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
-            if (passed[g]) load_slab(slot, u * KB2 + kb);
+            peek_gate(g);
+            if (local_ok && passed[g]) { fence_proxy_async(); load_slab(slot, u * KB2 + kb); }
             else { pend_slot[npend & 15] = slot; pend_idx[npend & 15] = u * KB2 + kb; pend_g[npend & 15] = g; ++npend; }
           }
           kb += dK2, u += dU2;
@@ -470,6 +488,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       publish_sf();
       TC_TRACE(n1 + j, 2);
     }
+    // The routing tables in the router's padded form, for callers that ask for them: written by these four warps of the
+    // last worker (the one with the least FC1 work) once their tiles are through, off every critical path.
+    if (blockIdx.x == V - 1 && P.experts_out) {
+      const int t4 = tid - 128;
+      for (int e = t4; e < P.E; e += 128)
+        if (T.cnt[e] > 0) { P.experts_out[T.uidx[e] - 1] = e; P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e]; }
+      for (int u = U + t4; u < P.Umax; u += 128) { P.experts_out[u] = -1; P.offsets_out[u + 1] = T.base[kTcMaxE - 1]; }
+      if (t4 == 0) P.offsets_out[U] = T.base[kTcMaxE - 1];
+      for (int p = t4; p < npairs; p += 128) {
+        const int e = T.ids[p];
+        if (e < 0) continue;
+        int r = 0;
+        for (int q = 0; q < p; ++q) r += T.ids[q] == e;
+        P.pairs_out[T.base[e] - T.cnt[e] + r] = p;
+      }
+    }
   } else if (warp == 8) {
     // ============================================================== MMA issuer: the whole warp stays converged
     // Every lane runs the loop with warp-uniform values and one elected lane issues, so descriptors and TMEM addresses
@@ -512,6 +546,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       if (++kb == KB1) { kb = 0; close_piece(); }
       if (++si == NS) { si = 0; ph ^= 1u; }
     }
+    if (n1 > 0) umma_commit_p(&T.fc1_done, el);   // the x operand's shared memory and scale columns may be reused from here on
     if (n2 > 0) {   // one piece: all of this worker's items of output block nb2 go into one accumulator
       open_piece();
       for (int j = 0, kb = r2 % KB2; j < n2; ++j) {
@@ -597,10 +632,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       for (int i = 0; i < NB; ++i) *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(val[4 * i], val[4 * i + 1], val[4 * i + 2], val[4 * i + 3]);
       named_bar_sync(1, 128);
       if (et == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(counter, 1u);
+        const unsigned old = atom_add_acq_rel_gpu(counter, 1u);   // releases the partial (barrier above), acquires the others'
         const int last = old + 1u == (unsigned)nlive;
-        if (last) { *counter = 0; __threadfence(); }
+        if (last) *counter = 0;   // nobody touches the counter again before the next launch
         T.last_flag = last;
       }
       named_bar_sync(1, 128);
@@ -612,12 +646,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       fence_proxy_async();
       named_bar_sync(1, 128);
       if (et == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(P.gridbar + 2 * g, 1u);
+        const unsigned old = atom_add_acq_rel_gpu(P.gridbar + 2 * g, 1u);
         if (old == (unsigned)(V - 1)) {
           P.gridbar[2 * g] = 0;
-          __threadfence();
-          atomicAdd(P.gridbar + 2 * g + 1, 1u);
+          atom_add_acq_rel_gpu(P.gridbar + 2 * g + 1, 1u);   // opens the gate; ordered after every arrival it acquired
         }
       }
     };

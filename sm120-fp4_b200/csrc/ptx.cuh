@@ -161,4 +161,12 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
   return v;
 }
 
+// fetch-add that releases this thread's earlier writes (and, by cumulativity, those it observed through a barrier) and
+// acquires the writes released by the earlier arrivals: one round trip instead of fence + atomic
+__device__ __forceinline__ unsigned atom_add_acq_rel_gpu(unsigned* p, unsigned v) {
+  unsigned old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 }  // namespace b200
