@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   // ---------------------------------------------------------------- work split (closed form, the same on every worker)
   // FC1: units q = (touched expert u, 64-column block cb), u-major; worker v takes q = v, v + V, ...: whole units (no
   // cross-CTA reduction), and all workers move through the experts in the same order, so the experts below uA (group A,
-  // three quarters of them) are finished grid-wide three quarters of the way through FC1. Gate A opens when every worker
+  // seven eighths of them) are finished grid-wide seven eighths of the way through FC1. Gate A opens when every worker
   // has finished its units of group A, gate B when all of FC1 is done; a worker's FC2 items of group A keep it busy
   // while gate B and the last slabs are still on their way.
   // FC2: the workers are split into NB2 groups, one per 128-row output block; inside a group, worker r takes the items
@@ -319,20 +319,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
   const int n1 = nu1 * KB1;
-  const int uA = (3 * U) / 4, qA = uA * CB1;
+  const int uA = (7 * U) / 8, qA = uA * CB1;
   const int nuA = v < qA ? (qA - v + V - 1) / V : 0;   // this worker's units of group A (its first ones)
+  const int I2 = U * KB2;
   const int Wb = V / NB2, Wx = V % NB2;                // groups 0..Wx-1 have Wb + 1 workers
   int nb2, r2, W2, vlo2;
   if (v < Wx * (Wb + 1)) { nb2 = v / (Wb + 1); r2 = v - nb2 * (Wb + 1); W2 = Wb + 1; vlo2 = nb2 * (Wb + 1); }
   else { const int vv = v - Wx * (Wb + 1); nb2 = Wx + vv / Wb; r2 = vv % Wb; W2 = Wb; vlo2 = Wx * (Wb + 1) + (nb2 - Wx) * Wb; }
-  const int I2 = U * KB2;
   const int n2 = r2 < I2 ? (I2 - r2 + W2 - 1) / W2 : 0;
   const int live2 = W2 < I2 ? W2 : I2;                 // workers of the group that hold a partial: ranks 0..live2-1
   const int dU2 = W2 / KB2, dK2 = W2 % KB2;            // item step W2 as (experts, K boxes)
 #ifdef B200_TIMERS
   long long tm_a = 0, tm_b = 0, tm_c = 0, tm_d = 0;
   const long long tm_begin = clock64();
-  if (tid == 0 && P.debug) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); P.debug[blockIdx.x * 16 + 15] = (long long)g; }
+  if (tid == 0 && P.debug) { unsigned long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); P.debug[blockIdx.x * 16 + 15] = (long long)g;
+    unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); P.debug[blockIdx.x * 16 + 11] = sm; }
 #endif
   const uint32_t tmem = T.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 320;   // accumulators 2 x 64 | weight scales NS x 16 (<= 192) | operand scales (<= 192)
@@ -361,11 +362,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       // are complete: the slabs share their shared memory with the resident x operand, and their scale columns in TMEM
       // with the x operand's. Weight tiles of FC2 are prefetched regardless; only the slab loads wait.
       bool local_ok = n1 == 0;
-      auto flush = [&]() {
-        if (pend_head < npend && local_ok && passed[pend_g[pend_head & 15]]) {
-          fence_proxy_async();
-          while (pend_head < npend && passed[pend_g[pend_head & 15]]) { load_slab(pend_slot[pend_head & 15], pend_idx[pend_head & 15]); ++pend_head; }
-        }
+      auto flush = [&]() {   // issue the parked slab loads whose conditions hold now
+        while (pend_head < npend && local_ok && passed[pend_g[pend_head & 15]]) { load_slab(pend_slot[pend_head & 15], pend_idx[pend_head & 15]); ++pend_head; }
       };
       auto open_gate = [&](int g) {   // blocking: wait for (b) and for gate g and every gate before it; issue what waited for them
         if (!local_ok) {
@@ -381,13 +379,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           }
           if (!ok) { T.abort_flag = 1; *P.status = 3; }
           passed[gg] = true;
+          fence_proxy_async();   // the slabs were written through the generic proxy and are read by bulk copies
         }
         flush();
       };
       auto peek_gate = [&](int g) {   // one look, no waiting: gates usually opened long before the tile that needs them is issued
         if (!local_ok && mbar_test_wait(&T.fc1_done, 0)) local_ok = true;
         for (int gg = 0; gg <= g && !passed[gg]; ++gg)
-          if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) passed[gg] = true;
+          if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) { passed[gg] = true; fence_proxy_async(); }
           else break;
         flush();
       };
@@ -429,7 +428,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
             mbar_expect_tx(&T.full[slot], kTcStage + kSlab);
             bulk_load_hint(ring + slot * kTcStage, P.w2t + (((long long)T.experts[u] * NB2 + nb2) * KB2 + kb) * kTcStage, kTcStage, &T.full[slot], pol);
             peek_gate(g);
-            if (local_ok && passed[g]) { fence_proxy_async(); load_slab(slot, u * KB2 + kb); }
+            if (local_ok && passed[g]) load_slab(slot, u * KB2 + kb);
             else { pend_slot[npend & 15] = slot; pend_idx[npend & 15] = u * KB2 + kb; pend_g[npend & 15] = g; ++npend; }
           }
           kb += dK2, u += dU2;
