@@ -22,6 +22,7 @@
 #include "tcgen05.cuh"
 #include "decode_params.h"
 #include <string.h>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -129,26 +130,29 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
 }
 
 // ------------------------------------------------------------------------------------------------ x -> B operand
-// One block per token slot (N/4 slots): token amax, then every 16-value block expanded into four NVFP4 terms.
+// One block of 128 threads per token slot (N/4 slots): token amax, then every 16-value block expanded into four NVFP4
+// terms. The block is small enough (registers, shared memory) to be resident next to a block of the layer kernel.
 // xb: the FC1 B operand exactly as the kernel wants it in shared memory, so that ONE bulk copy brings it in:
 //   [KB1 boxes][N rows (token*4 + term)][128 B] in the 128-byte-swizzle image (16-byte chunk c of row n sits at chunk
 //   c ^ (n & 7)), followed by KT1 scale tiles of 512 B (128x4 order, rows >= N zero). colscale f32 [N] = 1/g_t.
-__global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
+__global__ void __launch_bounds__(128) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
                                                   float* __restrict__ colscale) {
   const int tok = blockIdx.x, tid = threadIdx.x;
   grid_launch_dependents();   // the layer kernel may start its prologue and weight prefetch now; it waits before reading xb
+  grid_dependency_wait();     // this kernel is itself launched programmatically: x (and the workspace it writes) belong to
+                              // whatever ran before it in the stream until that has completed
   uint8_t* xsf = xb + (long long)KB1 * N * 128;
-  __shared__ float wm[8];
+  __shared__ float wm[4];
   __shared__ float s_g1;
   float m = 0.f;
   if (tok < M)
-    for (int i = tid; i < H; i += 256) m = fmaxf(m, fabsf(__bfloat162float(x[(long long)tok * H + i])));
+    for (int i = tid; i < H; i += 128) m = fmaxf(m, fabsf(__bfloat162float(x[(long long)tok * H + i])));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & 31) == 0) wm[tid >> 5] = m;
   __syncthreads();
   if (tid == 0) {
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, wm[w]);
+    for (int w = 1; w < 4; ++w) m = fmaxf(m, wm[w]);
     const float g1 = 2688.0f / fmaxf(m, 1e-30f);
     s_g1 = g1;
     float g = g1;
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(256) k_expand_x(const __nv_bfloat16* __restric
   }
   __syncthreads();
   const float g1 = s_g1;
-  for (int b = tid; b < KB1 * 16; b += 256) {   // 16-value blocks over the padded K (KB1 * 256 values)
+  for (int b = tid; b < KB1 * 16; b += 128) {   // 16-value blocks over the padded K (KB1 * 256 values)
     uint2 codes[kTerms];
     uint8_t sf[kTerms];
     if (tok < M && b * 16 < H) {
@@ -315,6 +319,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   // i = (u, kb) = r, r + W, ... in ascending order, accumulates them in one TMEM accumulator, and the group's partials are
   // added in worker order by whoever arrives last. A worker's first items belong to group A: they run while the tail of
   // FC1, gate B and the fetch of the remaining activation slabs are still in flight elsewhere.
+  // The kernel after this one in the stream, if it was launched programmatically (the activation expansion of the next
+  // layer call is), may be scheduled from here on: its blocks start as SMs free up and wait for this grid's completion
+  // before they touch anything this grid reads or writes.
+  grid_launch_dependents();
   const int v = blockIdx.x;
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
@@ -766,9 +774,25 @@ using namespace b200;
 
 int b200_decode_tc_smem_bytes(int NS, int region_bytes) { return 1024 + NS * kTcStage + region_bytes + (int)sizeof(TcTables); }
 
+static bool pdl_chain_enabled() {   // B200MOE_PDL_CHAIN=0: launch the expansion kernel as an ordinary stream-ordered kernel
+  static const bool on = [] { const char* c = getenv("B200MOE_PDL_CHAIN"); return !(c && c[0] == '0'); }();
+  return on;
+}
+
 int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, cudaStream_t st) {
-  k_expand_x<<<N / kTerms, 256, 0, st>>>((const __nv_bfloat16*)x, M, H, N, KB1, (uint8_t*)xb, colscale);
-  B200_LAUNCH_CHECK();
+  // programmatic launch: the blocks may be scheduled while the previous kernel of the stream drains (if that kernel
+  // allows it, as this library's layer kernel does); griddepcontrol.wait at their top keeps stream order for all data
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(N / kTerms), cfg.blockDim = dim3(128), cfg.dynamicSmemBytes = 0, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = pdl_chain_enabled() ? 1 : 0;
+  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+  uint8_t* xbp = (uint8_t*)xb;
+  void* args[] = {(void*)&xp, (void*)&M, (void*)&H, (void*)&N, (void*)&KB1, (void*)&xbp, (void*)&colscale};
+  B200_CUDA_TRY(cudaLaunchKernelExC(&cfg, (const void*)k_expand_x, args));
   return B200MOE_OK;
 }
 
