@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
       }
       bool passed[2] = {false, false};
-      int pend_slot[16], pend_idx[16], pend_g[16], npend = 0, pend_head = 0;   // ring of 16: at most NS (<= 12) entries wait at a time
+      int pend_slot[16], pend_idx[16], pend_g[16] = {0}, npend = 0, pend_head = 0;   // ring of 16: at most NS (<= 12) entries wait at a time
       int slot_g[12];                                                          // gate of the FC2 tile in each ring slot
       auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
         bulk_load(region + slot * kSlab, P.aslab + (long long)idx * kSlab, kSlab, &T.full[slot]);

@@ -1,6 +1,7 @@
 // NVFP4 quantisation arithmetic in the exact operation order of sm120fp4/reference.py:28-90 (bit-exact with the reference's
 // CPU code): block amax / 6 (IEEE division) * gs, clamp 448, E4M3 round-to-nearest-even; scale = gs / sf (IEEE division);
-// E2M1 codes by thresholds with ties to the even code and the sign bit kept on zero.
+// E2M1 codes rounded to nearest with ties to the even code, saturating at 6, the sign bit kept on zero - which is exactly
+// the hardware conversion cvt.rn.satfinite.e2m1x2.f32 (the threshold form below states the same rule in plain C).
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
@@ -34,21 +35,32 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
   }
 }
 
+// 8 floats -> 8 E2M1 codes in one word (element 2j in the low nibble of byte j). cvt.rn.satfinite.e2m1x2.f32 d, a, b puts
+// a into the high and b into the low nibble of d.
+__device__ __forceinline__ uint32_t e2m1x8_rn(const float* v) {
+  uint32_t b[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    asm("{\n .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n cvt.u32.u8 %0, t;\n}\n" : "=r"(b[i]) : "f"(v[2 * i + 1]), "f"(v[2 * i]));
+  return (b[0] | (b[1] << 8)) | ((b[2] << 16) | (b[3] << 24));
+}
+
 // Quantize one 16-element block: returns the E4M3 scale byte, writes 8 packed bytes.
 __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], float gs, uint2& packed) {
-  float amax = 0.f;
+  float m[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(v[i]), fabsf(v[i + 8]));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], m[i + 4]);
+  const float amax = fmaxf(fmaxf(m[0], m[2]), fmaxf(m[1], m[3]));
   const float sf_f = fminf(__fmul_rn(__fdiv_rn(amax, 6.0f), gs), 448.0f);
   const __nv_fp8_storage_t sfb = __nv_cvt_float_to_fp8(sf_f, __NV_SATFINITE, __NV_E4M3);  // RNE, subnormals kept
   const float sf_val = __half2float(__half(__nv_cvt_fp8_to_halfraw(sfb, __NV_E4M3)));
   const float scale = sf_val > 0.f ? __fdiv_rn(gs, sf_val) : 0.f;
-  uint32_t lo = 0, hi = 0;
+  float sc[16];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) lo |= e2m1_code(__fmul_rn(v[i], scale)) << (4 * i);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) hi |= e2m1_code(__fmul_rn(v[8 + i], scale)) << (4 * i);
-  packed = make_uint2(lo, hi);
+  for (int i = 0; i < 16; ++i) sc[i] = __fmul_rn(v[i], scale);
+  packed = make_uint2(e2m1x8_rn(sc), e2m1x8_rn(sc + 8));
   return (uint8_t)sfb;
 }
 

@@ -17,6 +17,7 @@
 #include "tcgen05.cuh"
 #include "nvfp4_math.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -25,44 +26,35 @@ constexpr int kPfStages = 5;         // ring stages of two records (A, B) each
 constexpr int kPfThreads = 256;      // warps 0-3 epilogue, 4 MMA issuer, 5 scale copier, 6-7 TMA producers
 
 // ------------------------------------------------------------------------------------------------ plan
-// experts/offsets/pairs: the router's tables. Output: ntiles[0] = number of 128-row tiles, tile_expert[t], and for every
-// padded row: src_tok (token index or -1) and row_pair (pair index or -1); dst_row[pair] = padded row of the pair.
-__global__ void __launch_bounds__(1024) k_prefill_plan(const int* __restrict__ experts, const int* __restrict__ offsets,
-                                                       const int* __restrict__ pairs, int Umax, int P, int top_k, int max_tiles,
-                                                       int* __restrict__ ntiles, int* __restrict__ tile_expert, int* __restrict__ src_tok,
-                                                       int* __restrict__ row_pair, int* __restrict__ dst_row) {
-  extern __shared__ int sh[];   // tile_u[max_tiles], tile_first[max_tiles]
-  int* tile_u = sh;
-  int* tile_first = sh + max_tiles;
-  __shared__ int s_nt;
-  if (threadIdx.x == 0) {
-    int nt = 0;
-    for (int u = 0; u < Umax && experts[u] >= 0; ++u) {
-      const int cnt = offsets[u + 1] - offsets[u];
-      for (int j = 0; j * 128 < cnt && nt < max_tiles; ++j) {
-        tile_u[nt] = u;
-        tile_first[nt] = offsets[u] + j * 128;
-        ++nt;
-      }
-    }
-    s_nt = nt;
-    ntiles[0] = nt;
+// experts/offsets: the router's tables. One thread per touched expert: its rows are cut into 128-row tiles, the tiles of
+// all experts are numbered in expert order by a block-wide scan. Output: ntiles[0], and per tile its expert and the range
+// [tile_first, tile_end) of the expert's rows in `pairs` that it holds (the last tile of an expert is partly empty).
+__global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ experts, const int* __restrict__ offsets, int Umax, int max_tiles,
+                                                      int* __restrict__ ntiles, int* __restrict__ tile_expert, int* __restrict__ tile_first,
+                                                      int* __restrict__ tile_end) {
+  __shared__ int wsum[8];
+  const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
+  int e = -1, lo = 0, hi = 0;
+  if (u < Umax) {
+    e = experts[u];
+    if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
   }
+  const int mine = (hi - lo + 127) >> 7;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += a;
+  }
+  if (lane == 31) wsum[warp] = inc;
   __syncthreads();
-  const int nt = s_nt;
-  for (int t = threadIdx.x; t < nt; t += blockDim.x) tile_expert[t] = experts[tile_u[t]];
-  for (int i = threadIdx.x; i < nt * 128; i += blockDim.x) {
-    const int t = i >> 7, r = i & 127;
-    const int u = tile_u[t];
-    const int j = tile_first[t] + r;
-    int tok = -1, pr = -1;
-    if (j < offsets[u + 1]) {
-      pr = pairs[j];
-      tok = pr / top_k;
-      dst_row[pr] = i;
-    }
-    src_tok[i] = tok;
-    row_pair[i] = pr;
+  int base = inc - mine;
+  for (int w2 = 0; w2 < warp; ++w2) base += wsum[w2];
+  if (u == 255) ntiles[0] = min(base + mine, max_tiles);
+  for (int j = 0; j < mine && base + j < max_tiles; ++j) {
+    tile_expert[base + j] = e;
+    tile_first[base + j] = lo + j * 128;
+    tile_end[base + j] = hi;
   }
 }
 
@@ -71,22 +63,31 @@ __device__ __forceinline__ int rec_code_offset(int r, int b16) { return r * 128 
 __device__ __forceinline__ int rec_scale_offset(int r, int b16) { return 16384 + (b16 >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b16 & 3); }
 
 // ------------------------------------------------------------------------------------------------ x -> records
-// One thread per 16-value block of a padded row. rec [ntiles][KB][18432]; K padded to KB*256 with zero codes/scales.
-__global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_tok,
-                                                          const int* __restrict__ ntiles, int H, int KB, const float* __restrict__ gs_ptr,
-                                                          uint8_t* __restrict__ rec) {
+// One thread per 16-value block of a padded row. rec [ntiles][KB][18432]; K padded to KB*256 with zero codes/scales. The
+// thread of a row's first block also records the row's pair (row_pair, -1 for padding) and the pair's row (dst_row).
+__global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pairs,
+                                                          const int* __restrict__ tile_first, const int* __restrict__ tile_end,
+                                                          const int* __restrict__ ntiles, int H, int KB, int top_k,
+                                                          const float* __restrict__ gs_ptr, uint8_t* __restrict__ rec,
+                                                          int* __restrict__ row_pair, int* __restrict__ dst_row) {
   const float gs = *gs_ptr;
-  const long long total = (long long)ntiles[0] * 128 * KB * 16;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int b = (int)(i % (KB * 16));
-    const long long row = i / (KB * 16);
+  const unsigned per_row = (unsigned)KB * 16u;
+  const unsigned total = (unsigned)ntiles[0] * 128u * per_row;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned row = i / per_row, b = i - row * per_row;
     const int t = (int)(row >> 7), r = (int)(row & 127);
-    const int tok = src_tok[row];
+    const int j = tile_first[t] + r;
+    int pr = -1;
+    if (j < tile_end[t]) pr = pairs[j];
+    if (b == 0) {
+      row_pair[row] = pr;
+      if (pr >= 0) dst_row[pr] = (int)row;
+    }
     uint2 pk = make_uint2(0u, 0u);
     uint8_t sb = 0;
-    if (tok >= 0 && b * 16 < H) {
+    if (pr >= 0 && (int)b * 16 < H) {
       float v[16];
-      load16(x + (long long)tok * H + b * 16, v);
+      load16(x + (long long)(pr / top_k) * H + b * 16, v);
       sb = quantize_block16(v, gs, pk);
     }
     uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kRec;
@@ -110,6 +111,7 @@ struct PrefillParams {
   __nv_bfloat16* y;           // PHASE 2: weighted rows [ntiles*128][H]
   int* status;
   int NBLK, KB, KT, KB2, H;
+  int dbg;                    // experiments only (B200MOE_PF_DEBUG): 1 epilogue without math, 2 no MMAs, 4 no scale moves
 };
 
 struct PfShared {
@@ -278,6 +280,229 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(const __grid_con
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
 }
 
+// ------------------------------------------------------------------------------------------------ grouped GEMM, A resident
+// The same GEMM with the activation tile kept in shared memory: a CTA takes a contiguous range of (row tile, column
+// block) items, so the KB records of a row tile are fetched once and only the weight records stream (one 18 KB record
+// per K box through a ring of NSB stages). That halves the L2 traffic per flop of the kernel above, which re-reads the
+// activation record with every weight record. The next row tile's records replace the current ones box by box as the
+// last column block of the tile releases them, so there is no drain between row tiles.
+// Warps 0-7: epilogue (two per TMEM lane quadrant, each half of the columns); 8-11: scale warps (scale tiles shared
+// memory -> registers -> TMEM, one warp per lane quadrant); 12: MMA issuer (converged warp, one elected lane);
+// 13: producer of activation records; 14: producer of weight records.
+constexpr int kPrThreads = 15 * 32;
+
+struct PrShared {
+  uint64_t a_full[12], a_empty[12], a_sfr[12];   // per K box of the resident activation tile
+  uint64_t b_full[12], b_empty[12], b_sfr[12];   // per ring stage of weight records
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+template <int PHASE>
+__global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_constant__ PrefillParams P, int NSB) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int KB = P.KB, NBLK = P.NBLK;
+  uint8_t* abuf = smem;                      // KB records of the current row tile
+  uint8_t* ring = smem + KB * kRec;          // NSB weight records
+  PrShared& S = *reinterpret_cast<PrShared*>(ring + NSB * kRec);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int k = 0; k < KB; ++k) { mbar_init(&S.a_full[k], 1); mbar_init(&S.a_empty[k], 1); mbar_init(&S.a_sfr[k], 4); }
+    for (int s = 0; s < NSB; ++s) { mbar_init(&S.b_full[s], 1); mbar_init(&S.b_empty[s], 1); mbar_init(&S.b_sfr[s], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 8); }
+    S.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 12) { tmem_alloc(&S.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = S.tmem_base;
+  const uint32_t tm_acc = tmem, tm_sfa = tmem + 256, tm_sfb = tmem + 256 + 16 * KB;   // 2 x 128 | KB x 16 | NSB x 16
+  // this CTA's items: w = t * NBLK + n, a contiguous range
+  const int total = P.ntiles[0] * NBLK;
+  const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int w0 = min(total, (int)blockIdx.x * per), w1 = min(total, w0 + per);
+  const int t0 = w0 / NBLK, n0 = w0 - t0 * NBLK;
+  const int nkt_last = P.KT - 4 * (KB - 1);
+
+  if (warp == 13) {
+    // ============================================================== activation records: once per row tile, box by box
+    if (lane == 0 && w0 < w1) {
+      const int tl = (w1 - 1) / NBLK;
+      for (int t = t0, ti = 0; t <= tl; ++t, ++ti)
+        for (int kb = 0; kb < KB; ++kb) {
+          if (ti >= 1 && !mbar_wait(&S.a_empty[kb], (uint32_t)((ti - 1) & 1), &S.abort_flag)) *P.status = 2;
+          mbar_expect_tx(&S.a_full[kb], kRec);
+          bulk_load(abuf + kb * kRec, P.arec + ((long long)t * KB + kb) * kRec, kRec, &S.a_full[kb]);
+        }
+    }
+    __syncwarp();
+  } else if (warp == 14) {
+    // ============================================================== weight records: one per (item, K box)
+    if (lane == 0) {
+      int slot = 0, use = 0;
+      for (int w = w0, t = t0, n = n0; w < w1; ++w) {
+        const uint8_t* src = P.wrec + ((long long)P.tile_expert[t] * NBLK + n) * KB * kRec;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
+          mbar_expect_tx(&S.b_full[slot], kRec);
+          bulk_load(ring + slot * kRec, src + (long long)kb * kRec, kRec, &S.b_full[slot]);
+          if (++slot == NSB) { slot = 0; ++use; }
+        }
+        if (++n == NBLK) { n = 0; ++t; }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 8 && warp < 12) {
+    // ============================================================== scale warps
+    const uint32_t lane_base = (uint32_t)((warp - 8) * 32) << 16;
+    const uint32_t a_u = smem_u32(abuf) + 16384 + lane * 16, b_u = smem_u32(ring) + 16384 + lane * 16;
+    auto put = [&](uint32_t src, uint32_t dst_col) {   // four 512-byte scale tiles -> 16 TMEM columns of this quadrant
+      uint32_t r[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 t4 = lds128(src + j * 512);
+        r[4 * j] = t4.x, r[4 * j + 1] = t4.y, r[4 * j + 2] = t4.z, r[4 * j + 3] = t4.w;
+      }
+      tmem_st_32x32b_x16(dst_col + lane_base, r);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+    };
+    int slot = 0, ti = -1;
+    uint32_t ph = 0;
+    for (int w = w0, n = n0; w < w1; ++w) {
+      const bool first = w == w0 || n == 0;
+      if (first) ++ti;
+      for (int kb = 0; kb < KB; ++kb) {
+        if (first) {
+          if (!mbar_wait(&S.a_full[kb], (uint32_t)(ti & 1), &S.abort_flag)) *P.status = 1;
+          put(a_u + kb * kRec, tm_sfa + 16 * kb);
+          if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
+        }
+        if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
+        if (!(P.dbg & 4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
+        if (lane == 0) mbar_arrive(&S.b_sfr[slot]);
+        if (++slot == NSB) { slot = 0; ph ^= 1u; }
+      }
+      if (++n == NBLK) n = 0;
+    }
+  } else if (warp == 12) {
+    // ============================================================== MMA issuer
+    const uint32_t el = elect_one();
+    const uint32_t idesc = idesc_mxf4nvf4(128, 128);
+    const uint64_t desc0 = smem_desc_sw128_kmajor(0);
+    const uint32_t a16 = smem_u32(abuf) >> 4, b16 = smem_u32(ring) >> 4;
+    int slot = 0, ab = 0, works = 0, ti = -1;
+    uint32_t ph = 0;
+    uint32_t aph[2] = {0, 0};
+    for (int w = w0, n = n0; w < w1; ++w) {
+      const bool first = w == w0 || n == 0, last = w == w1 - 1 || n == NBLK - 1;
+      if (first) ++ti;
+      if (works >= 2 && !mbar_wait(&S.acc_empty[ab], aph[ab] ^ 1u, &S.abort_flag)) *P.status = 5;
+      for (int kb = 0; kb < KB; ++kb) {
+        if (first && !mbar_wait(&S.a_sfr[kb], (uint32_t)(ti & 1), &S.abort_flag)) *P.status = 8;
+        if (!mbar_wait(&S.b_sfr[slot], ph, &S.abort_flag)) *P.status = 8;
+        tc_fence_after();
+        const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kRec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
+        const int nkt = kb == KB - 1 ? nkt_last : 4;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          if (jj < nkt && !(P.dbg & 2))
+            umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
+                            (kb > 0 || jj > 0) ? 1u : 0u, el);
+        umma_commit_p(&S.b_empty[slot], el);
+        if (last) umma_commit_p(&S.a_empty[kb], el);   // the next row tile's record of this box may land
+        if (++slot == NSB) { slot = 0; ph ^= 1u; }
+      }
+      umma_commit_p(&S.acc_full[ab], el);
+      aph[ab] ^= 1u;
+      ab ^= 1;
+      ++works;
+      if (++n == NBLK) n = 0;
+    }
+  } else {
+    // ============================================================== epilogue: thread = accumulator row, warp pair = column halves
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;
+    int ab = 0;
+    uint32_t aph[2] = {0, 0};
+    const float gs_in = *P.gs_in;
+    const float gs_out = PHASE == 1 ? *P.gs_out : 0.f;
+    float s = 0.f;   // per row tile: FC1 alpha / gs_in; FC2 that times the row's routing weight (0 on padding rows)
+    int pr = -1;
+    for (int w = w0, t = t0, n = n0; w < w1; ++w) {
+      if (w == w0 || n == 0) {   // a new row tile: its expert and (FC2) this row's pair, fetched once
+        s = P.alpha[P.tile_expert[t]] / gs_in;
+        if (PHASE == 2) {
+          pr = P.row_pair[(long long)t * 128 + row];
+          s = pr >= 0 ? s * P.wts[pr] : 0.f;
+        }
+      }
+      if (!mbar_wait(&S.acc_full[ab], aph[ab], &S.abort_flag)) *P.status = 7;
+      tc_fence_after();
+      const uint32_t taddr = tm_acc + 128 * ab + ((uint32_t)(quad * 32) << 16);
+      if (P.dbg & 1) {
+      } else if (PHASE == 1) {
+        // columns 0..63 = up, 64..127 = gate of intermediate columns 64*n..; SiLU*mul, re-quantise blocks of 16
+        uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
+        uint32_t sfw = 0;
+#pragma unroll
+        for (int bb = 0; bb < 2; ++bb) {
+          const int blk = 2 * half + bb;
+          uint32_t up[16], gt[16];
+          tmem_ld_32x32b_x16(taddr + 16 * blk, up);
+          tmem_ld_32x32b_x16(taddr + 64 + 16 * blk, gt);
+          tmem_ld_wait();
+          float a[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float g = __uint_as_float(gt[i]) * s, u = __uint_as_float(up[i]) * s;
+            a[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+          }
+          uint2 pk;
+          const uint8_t sb = quantize_block16(a, gs_out, pk);
+          *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = pk;
+          sfw |= (uint32_t)sb << (8 * bb);
+        }
+        *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+      } else {
+        __nv_bfloat16* yrow = P.y + ((long long)t * 128 + row) * P.H + 128 * n + 64 * half;
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + 64 * half + c0, r);
+          tmem_ld_wait();
+          if (pr >= 0) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * s, __uint_as_float(r[2 * i + 1]) * s);
+              o[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(yrow + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(yrow + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.acc_empty[ab]);
+      aph[ab] ^= 1u;
+      ab ^= 1;
+      if (++n == NBLK) { n = 0; ++t; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tmem, 512);
+  if (S.abort_flag)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+}
+
 // ------------------------------------------------------------------------------------------------ combine
 // out[tok, :] = sum_j y[dst_row[tok*k + j], :] in slot order, fp32 accumulation, one bf16 rounding.
 __global__ void __launch_bounds__(256) k_prefill_combine(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dst_row, int M, int top_k,
@@ -377,12 +602,15 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   if (rc != B200MOE_OK) return rc;
   B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
   const int max_tiles = P / 128 + Umax;
-  k_prefill_plan<<<1, 1024, 2 * max_tiles * sizeof(int), st>>>(experts, offsets, pairs, Umax, P, top_k, max_tiles, ntiles, tile_expert, src_tok,
-                                                                row_pair, dst_row);
+  int* tile_first = src_tok;              // two tables of max_tiles entries
+  int* tile_end = src_tok + max_tiles;
+  if (Umax > 256) return B200MOE_ERR_LIMIT;
+  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, ntiles, tile_expert, tile_first, tile_end);
   B200_LAUNCH_CHECK();
   k_set2<<<1, 1, 0, st>>>(gs, gs_x, gs_a);
   B200_LAUNCH_CHECK();
-  k_quantize_records<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)x, src_tok, ntiles, H, KB1, gs, w + L.xrec);
+  k_quantize_records<<<sms * 16, 256, 0, st>>>((const __nv_bfloat16*)x, pairs, tile_first, tile_end, ntiles, H, KB1, top_k, gs, w + L.xrec,
+                                               row_pair, dst_row);
   B200_LAUNCH_CHECK();
   const int smem = 1024 + kPfStages * 2 * kRec + (int)sizeof(PfShared);
   static thread_local bool configured = false;
@@ -394,17 +622,46 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = status, p.H = H;
+  p.dbg = getenv("B200MOE_PF_DEBUG") ? atoi(getenv("B200MOE_PF_DEBUG")) : 0;
+  // per GEMM: the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit in shared memory and
+  // the scale columns fit in TMEM; otherwise the kernel that streams both operands
+  auto launch = [&](int phase, int KB) -> int {
+    int nsb = (227 * 1024 - 1024 - (int)sizeof(PrShared) - 256 - KB * kRec) / kRec;
+    const int tmem_cap = (512 - 256 - 16 * KB) / 16;
+    if (nsb > tmem_cap) nsb = tmem_cap;
+    if (nsb > 12) nsb = 12;
+    if (KB <= 12 && nsb >= 3 && !(getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1')) {
+      const int sm_r = 1024 + (KB + nsb) * kRec + (int)sizeof(PrShared);
+      const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : (const void*)k_prefill_gemm_r<2>;
+      static thread_local int configured_r[2] = {0, 0};
+      if (configured_r[phase - 1] < sm_r) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, sm_r));
+        configured_r[phase - 1] = sm_r;
+      }
+      if (phase == 1) k_prefill_gemm_r<1><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+      else k_prefill_gemm_r<2><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+    } else {
+      if (phase == 1) k_prefill_gemm<1><<<sms, kPfThreads, smem, st>>>(p);
+      else k_prefill_gemm<2><<<sms, kPfThreads, smem, st>>>(p);
+    }
+    B200_LAUNCH_CHECK();
+    return B200MOE_OK;
+  };
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.gs_in = gs, p.gs_out = gs + 1, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
-  k_prefill_gemm<1><<<sms, kPfThreads, smem, st>>>(p);
-  B200_LAUNCH_CHECK();
+  {
+    const int rc1 = launch(1, KB1);
+    if (rc1 != B200MOE_OK) return rc1;
+  }
   // FC2
   p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.gs_in = gs + 1, p.gs_out = nullptr, p.orec = nullptr;
   p.wts = wts, p.y = (__nv_bfloat16*)(w + L.y);
   p.NBLK = H / 128, p.KB = KB2, p.KT = KT2;
-  k_prefill_gemm<2><<<sms, kPfThreads, smem, st>>>(p);
-  B200_LAUNCH_CHECK();
+  {
+    const int rc2 = launch(2, KB2);
+    if (rc2 != B200MOE_OK) return rc2;
+  }
   k_prefill_combine<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)(w + L.y), dst_row, M, top_k, H, (__nv_bfloat16*)out);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;

@@ -33,17 +33,21 @@ __global__ void __launch_bounds__(1024) k_route_scan(int* __restrict__ hist, int
                                                      int* __restrict__ experts, int* __restrict__ offsets,
                                                      int* __restrict__ expert_base /* [E], start of expert e in pairs */,
                                                      int* __restrict__ num_touched) {
-  __shared__ int cnt[ROUTE_MAXE], base[ROUTE_MAXE], uidx[ROUTE_MAXE];
+  __shared__ int base[ROUTE_MAXE], uidx[ROUTE_MAXE];
   const int t = threadIdx.x;
   int c = 0;
   if (t < E) {
-    for (int b = 0; b < nchunks; ++b) {
-      const int v = hist[(long long)b * E + t];
-      hist[(long long)b * E + t] = c;
-      c += v;
+    for (int b0 = 0; b0 < nchunks; b0 += 8) {   // eight independent loads in flight, then their running sums
+      int v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = b0 + i < nchunks ? hist[(long long)(b0 + i) * E + t] : 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (b0 + i < nchunks) hist[(long long)(b0 + i) * E + t] = c;
+        c += v[i];
+      }
     }
   }
-  cnt[t] = c;
   base[t] = c;
   uidx[t] = c > 0 ? 1 : 0;
   __syncthreads();
