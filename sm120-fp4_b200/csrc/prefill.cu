@@ -299,6 +299,8 @@ struct PrShared {
   volatile int abort_flag;
 };
 
+static_assert(sizeof(PrShared) <= 1024, "the epilogue's store patches start 1024 bytes after the barriers");
+
 template <int PHASE>
 __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_constant__ PrefillParams P, int NSB) {
   extern __shared__ uint8_t smem_raw[];
@@ -307,6 +309,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   uint8_t* abuf = smem;                      // KB records of the current row tile
   uint8_t* ring = smem + KB * kRec;          // NSB weight records
   PrShared& S = *reinterpret_cast<PrShared*>(ring + NSB * kRec);
+  uint8_t* stage = ring + NSB * kRec + 1024;   // PHASE 2: eight 32-row x 144-byte patches for the epilogue's transposed stores
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int k = 0; k < KB; ++k) { mbar_init(&S.a_full[k], 1); mbar_init(&S.a_empty[k], 1); mbar_init(&S.a_sfr[k], 4); }
@@ -344,8 +347,13 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     // ============================================================== weight records: one per (item, K box)
     if (lane == 0) {
       int slot = 0, use = 0;
+      int e = 0, e_next = w0 < w1 ? P.tile_expert[t0] : 0;
       for (int w = w0, t = t0, n = n0; w < w1; ++w) {
-        const uint8_t* src = P.wrec + ((long long)P.tile_expert[t] * NBLK + n) * KB * kRec;
+        if (w == w0 || n == 0) {   // a new row tile: its expert was fetched a tile ahead
+          e = e_next;
+          if ((long long)(t + 1) * NBLK < w1) e_next = P.tile_expert[t + 1];
+        }
+        const uint8_t* src = P.wrec + ((long long)e * NBLK + n) * KB * kRec;
         for (int kb = 0; kb < KB; ++kb) {
           if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
           mbar_expect_tx(&S.b_full[slot], kRec);
@@ -470,23 +478,35 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         }
         *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
       } else {
-        __nv_bfloat16* yrow = P.y + ((long long)t * 128 + row) * P.H + 128 * n + 64 * half;
+        // This thread holds 64 bf16 of its row (128 bytes); the warp transposes its 32 x 128-byte block through its own
+        // patch of shared memory so that every store instruction writes whole 128-byte row segments (four rows per
+        // instruction) instead of 32 scattered 16-byte pieces.
+        uint32_t r[4][16];
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld_32x32b_x16(taddr + 64 * half + c0, r);
-          tmem_ld_wait();
-          if (pr >= 0) {
-            uint32_t o[8];
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
+        tmem_ld_wait();
+        uint8_t* patch = stage + warp * (32 * 144);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * s, __uint_as_float(r[2 * i + 1]) * s);
-              o[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(yrow + c0) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(yrow + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[c][2 * i]) * s, __uint_as_float(r[c][2 * i + 1]) * s);
+            o[i] = *reinterpret_cast<const uint32_t*>(&h);
           }
+          *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c + 16) = make_uint4(o[4], o[5], o[6], o[7]);
         }
+        __syncwarp();
+        const unsigned valid = __ballot_sync(0xffffffffu, pr >= 0);   // bit l: row quad*32 + l holds a pair
+        __nv_bfloat16* ybase = P.y + ((long long)t * 128 + quad * 32) * P.H + 128 * n + 64 * half;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int rr = 4 * j + (lane >> 3);   // row of the warp's block this lane stores a 16-byte chunk of
+          const uint4 v4 = *reinterpret_cast<const uint4*>(patch + rr * 144 + (lane & 7) * 16);
+          if ((valid >> rr) & 1u) *reinterpret_cast<uint4*>(ybase + (long long)rr * P.H + (lane & 7) * 8) = v4;
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -626,12 +646,13 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   // per GEMM: the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit in shared memory and
   // the scale columns fit in TMEM; otherwise the kernel that streams both operands
   auto launch = [&](int phase, int KB) -> int {
-    int nsb = (227 * 1024 - 1024 - (int)sizeof(PrShared) - 256 - KB * kRec) / kRec;
+    const int tail = 1024 + (phase == 2 ? 8 * 32 * 144 : 0);   // barriers (+ the FC2 epilogue's store patches)
+    int nsb = (227 * 1024 - 1024 - tail - 256 - KB * kRec) / kRec;
     const int tmem_cap = (512 - 256 - 16 * KB) / 16;
     if (nsb > tmem_cap) nsb = tmem_cap;
     if (nsb > 12) nsb = 12;
     if (KB <= 12 && nsb >= 3 && !(getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1')) {
-      const int sm_r = 1024 + (KB + nsb) * kRec + (int)sizeof(PrShared);
+      const int sm_r = 1024 + (KB + nsb) * kRec + tail;
       const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : (const void*)k_prefill_gemm_r<2>;
       static thread_local int configured_r[2] = {0, 0};
       if (configured_r[phase - 1] < sm_r) {

@@ -87,10 +87,15 @@ __global__ void __launch_bounds__(32) k_route_place(const int* __restrict__ ids,
   for (int e = lane; e < E; e += 32) run[e] = expert_base[e] + hist[(long long)blockIdx.x * E + e];
   __syncwarp();
   const int p0 = blockIdx.x * ROUTE_CHUNK, p1 = min(P, p0 + ROUTE_CHUNK);
-  for (int s = p0; s < p1; s += 32) {
+  int mine[ROUTE_CHUNK / 32];   // this lane's ids of the chunk, all loads in flight at once
+#pragma unroll
+  for (int k = 0; k < ROUTE_CHUNK / 32; ++k) mine[k] = p0 + 32 * k + lane < p1 ? ids[p0 + 32 * k + lane] : -1;
+#pragma unroll
+  for (int k = 0; k < ROUTE_CHUNK / 32; ++k) {
+    const int s = p0 + 32 * k;
+    if (s >= p1) break;
     const int p = s + lane;
-    const bool live = p < p1;
-    int e = live ? ids[p] : -1;
+    int e = mine[k];
     if (e < 0 || e >= E) e = -1;
     const unsigned active = __ballot_sync(0xffffffffu, e >= 0);
     if (e >= 0) {
