@@ -121,6 +121,14 @@ int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void
 int b200moe_stream_probe(const void* buf, long long bytes, int pattern, int pitch, int box_rows, int tile_bytes, int stages,
                          int producers, int* status_dev, void* stream);
 
+/* expert-parallel fixed-capacity dispatch and combine (no counterpart in the reference: it declines expert parallelism,
+ * sm120fp4/vllm_classes.py:46-47). dispatch: x bf16 [m, h], ids int32 [m, k] (global ids, negative = empty slot), wts f32
+ * [m, k] -> sx bf16 [world, cap, h] and meta int32 [world, cap, 2k] (local ids, then the weights' float bits); block d is
+ * what rank d receives. combine: y bf16 [world, cap, h] -> out bf16 [m, h], summed in rank order in fp32. */
+int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
+                        void* sx, int* meta, void* stream);
+int b200moe_ep_combine(const void* y, int m, int h, int world, int cap, void* out, void* stream);
+
 /* issue-cost measurement of tcgen05 scale copies and MMAs (diagnostic; no counterpart in the reference): cycles_dev[0] =
  * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64, ncommit commits}, cycles_dev[1] = cycles until all completed
  * (device int64 x 4; [2], [3] = the same for the second issuing thread). flags: 1 two accumulators, 2 wait on a completed

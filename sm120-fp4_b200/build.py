@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libb200moe.so"
-SOURCES = ["capi.cu", "layout_quant.cu", "route.cu", "decode.cu", "decode_tc.cu", "prefill.cu", "umma_probe.cu", "stream_probe.cu"]
+SOURCES = ["capi.cu", "layout_quant.cu", "route.cu", "decode.cu", "decode_tc.cu", "prefill.cu", "ep.cu", "umma_probe.cu", "stream_probe.cu"]
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

@@ -67,6 +67,9 @@ class ExpertParallelMoE:
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         if self.capacity is not None:
             return self.forward_fixed(x, topk_ids, topk_weights)
+        if self.world == 1:   # one rank owns every expert: nothing to dispatch
+            self.last_sent_rows = 0
+            return self.local_forward(x, topk_ids, topk_weights)
         m, h = x.shape
         ids = topk_ids.to(torch.int64)
         wts = topk_weights.to(torch.float32)
@@ -105,17 +108,62 @@ class ExpertParallelMoE:
     # -------------------------------------------------------------------------------------------- fixed-capacity exchange
     def forward_fixed(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """Every (source, destination) block holds exactly `capacity` rows (>= the tokens of a rank's batch): row t of the
-        block is token t, its slots masked to -1 when the destination owns none of its experts. No host synchronisation."""
+        block is token t, its slots masked to -1 when the destination owns none of its experts. No host synchronisation and
+        no allocation after the first call of a shape: the call can be captured into a CUDA graph. On a CUDA device the
+        dispatch and the combine are one library kernel each; on the CPU (gloo tests) the same arithmetic runs in torch."""
         m, h = x.shape
         c = self.capacity
         if m > c:
             raise ValueError(f"batch of {m} tokens exceeds the dispatch capacity {c}")
         per = self.E // self.world
+        self.last_sent_rows = self.world * c
+        if not x.is_cuda:
+            return self._forward_fixed_torch(x, topk_ids, topk_weights)
+        from . import _lib
+        lib = _lib.lib()
+        b = self._buffers(h, x.device, x.dtype)
+        ids = topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights.to(torch.float32).contiguous()
+        _lib.check(lib.b200moe_ep_dispatch(_lib.ptr(x.contiguous()), _lib.ptr(ids), _lib.ptr(wts), m, h, self.k, self.world, per, c,
+                                           _lib.ptr(b.sx), _lib.ptr(b.smeta), _lib.stream_ptr()), "ep dispatch")
+        if self.world == 1:
+            rx, rmeta = b.sx, b.smeta
+        else:
+            dist.all_to_all_single(b.rx.view(-1, h), b.sx.view(-1, h), group=self.group)
+            dist.all_to_all_single(b.rmeta.view(-1, 2 * self.k), b.smeta.view(-1, 2 * self.k), group=self.group)
+            rx, rmeta = b.rx, b.rmeta
+        rid = rmeta[:, :, :self.k].reshape(-1, self.k)
+        rw = rmeta[:, :, self.k:].reshape(-1, self.k).view(torch.float32)
+        yl = self.local_forward(rx.view(-1, h), rid, rw)
+        if self.world == 1:
+            y = yl
+        else:
+            dist.all_to_all_single(b.y.view(-1, h), yl.contiguous().view(-1, h), group=self.group)
+            y = b.y
+        out = torch.empty(m, h, dtype=x.dtype, device=x.device)
+        _lib.check(lib.b200moe_ep_combine(_lib.ptr(y), m, h, self.world, c, _lib.ptr(out), _lib.stream_ptr()), "ep combine")
+        return out
+
+    def _buffers(self, h: int, device, dtype):
+        key = (h, str(device), dtype)
+        if getattr(self, "_buf_key", None) != key:
+            from types import SimpleNamespace
+            w, c, k = self.world, self.capacity, self.k
+            mk = lambda *shape, dt: torch.zeros(*shape, dtype=dt, device=device)  # noqa: E731
+            self._buf = SimpleNamespace(sx=mk(w, c, h, dt=dtype), rx=mk(w, c, h, dt=dtype), y=mk(w, c, h, dt=dtype),
+                                        smeta=mk(w, c, 2 * k, dt=torch.int32), rmeta=mk(w, c, 2 * k, dt=torch.int32))
+            self._buf_key = key
+        return self._buf
+
+    def _forward_fixed_torch(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        m, h = x.shape
+        c = self.capacity
+        per = self.E // self.world
         ids = topk_ids.to(torch.int64)
         wts = topk_weights.to(torch.float32)
         dest = torch.div(ids, per, rounding_mode="floor")
         ranks = torch.arange(self.world, device=x.device)
-        own = dest[None, :, :] == ranks[:, None, None]                                     # [world, m, k]
+        own = (dest[None, :, :] == ranks[:, None, None]) & (ids[None] >= 0)                # [world, m, k]
         lid = torch.where(own, ids[None] - (ranks * per)[:, None, None], torch.full_like(ids[None].expand(self.world, -1, -1), -1))
         sw = torch.where(own, wts[None].expand(self.world, -1, -1), torch.zeros((), device=x.device))
         sx = torch.zeros(self.world, c, h, dtype=x.dtype, device=x.device)
@@ -124,7 +172,6 @@ class ExpertParallelMoE:
         sx[:, :m] = x[None]
         sid[:, :m] = lid.to(torch.int32)
         swt[:, :m] = sw
-        self.last_sent_rows = self.world * c
         if self.world == 1:
             y = self.local_forward(sx.view(-1, h), sid.view(-1, self.k), swt.view(-1, self.k)).view(1, c, h)
         else:
