@@ -319,10 +319,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   // i = (u, kb) = r, r + W, ... in ascending order, accumulates them in one TMEM accumulator, and the group's partials are
   // added in worker order by whoever arrives last. A worker's first items belong to group A: they run while the tail of
   // FC1, gate B and the fetch of the remaining activation slabs are still in flight elsewhere.
-  // The kernel after this one in the stream, if it was launched programmatically (the activation expansion of the next
-  // layer call is), may be scheduled from here on: its blocks start as SMs free up and wait for this grid's completion
-  // before they touch anything this grid reads or writes.
-  grid_launch_dependents();
   const int v = blockIdx.x;
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
@@ -445,6 +441,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         }
       }
       if (pend_head < npend) open_gate(1);
+      if (pw == 0) {
+        // The kernel after this one in the stream, if it was launched programmatically (the activation expansion of the
+        // next layer call is), may be scheduled once every worker has seen gate B open: its blocks start as SMs free up
+        // and wait for this grid's completion before they touch any data. Not earlier: a next call on the same workspace
+        // reads the gate words at its entry, and they are final only when the last gate of this launch has opened.
+        open_gate(1);
+        grid_launch_dependents();
+      }
 #ifdef B200_TIMERS
       if (P.debug && pw == 0) P.debug[v * 16 + 9] = clock64() - tm_begin;
 #endif

@@ -178,3 +178,19 @@ def test_gemma_shape(m, routing):
     cfg, w, ow = layer("gemma")
     x, ids, wts = inputs(cfg, m, 2000 + m, routing)
     check_layer_output(run(w, x, ids, wts), O.moe_reference(x.float().numpy(), ow, ids.numpy(), wts.numpy()), f"gemma m={m} {routing}")
+
+
+@pytest.mark.parametrize("name,m", [("mid", 48), ("tiny", 40), ("qwen", 40)])
+def test_back_to_back_launches_on_one_workspace(name, m):
+    """Batches above 16 tokens run as consecutive launches on the same workspace, and each launch lets the next one be
+    scheduled before it has finished (programmatic dependent launch). Some workers of a launch finish before its last
+    FC1 gate opens; the next launch must still find the gate words final. Every slice is checked against the oracle and
+    the whole sequence must repeat bit for bit."""
+    cfg, w, ow = layer(name)
+    x, ids, wts = inputs(cfg, m, 4000 + m)
+    first = run(w, x, ids, wts).clone()
+    check_layer_output(first, O.moe_reference(x.float().numpy(), ow, ids.numpy(), wts.numpy()), f"{name} m={m} in slices")
+    xd, idd, wd = x.cuda(), ids.cuda(), wts.cuda()
+    for _ in range(20):
+        assert torch.equal(w.forward(xd, idd, wd), first)
+    w.status()
