@@ -324,44 +324,50 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   tc_fence_after();
   const uint32_t tmem = S.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 256, tm_sfb = tmem + 256 + 16 * KB;   // 2 x 128 | KB x 16 | NSB x 16
-  // this CTA's items: w = t * NBLK + n, a contiguous range
-  const int total = P.ntiles[0] * NBLK;
-  const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int w0 = min(total, (int)blockIdx.x * per), w1 = min(total, w0 + per);
-  const int t0 = w0 / NBLK, n0 = w0 - t0 * NBLK;
+  // This CTA's work: segments (row tile t, column blocks [n0, n1)). Whole tiles are dealt round-robin for as many full
+  // rounds as there are (tiles t and t + 1 of one expert then run on neighbouring CTAs at the same time and in the same
+  // block order, so the second reader of a weight record finds it in L2); the tiles left over are cut into equal ranges
+  // of column blocks so that every CTA gets a share of them.
+  const int NT = P.ntiles[0], G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int rounds = NT / G, T0 = rounds * G;
+  const int rem = (NT - T0) * NBLK, per = (rem + G - 1) / G;
+  const int ra = min(rem, cta * per), rb = min(rem, ra + per);
+  auto for_each_segment = [&](auto&& body) {   // body(t, n0, n1, ordinal)
+    int ord = 0;
+    for (int r = 0; r < rounds; ++r) body(r * G + cta, 0, NBLK, ord++);
+    for (int a2 = ra; a2 < rb;) {
+      const int t = T0 + a2 / NBLK, n0 = a2 % NBLK, n1 = min(NBLK, n0 + (rb - a2));
+      body(t, n0, n1, ord++);
+      a2 += n1 - n0;
+    }
+  };
   const int nkt_last = P.KT - 4 * (KB - 1);
 
   if (warp == 13) {
-    // ============================================================== activation records: once per row tile, box by box
-    if (lane == 0 && w0 < w1) {
-      const int tl = (w1 - 1) / NBLK;
-      for (int t = t0, ti = 0; t <= tl; ++t, ++ti)
+    // ============================================================== activation records: once per segment, box by box
+    if (lane == 0) {
+      for_each_segment([&](int t, int, int, int ord) {
         for (int kb = 0; kb < KB; ++kb) {
-          if (ti >= 1 && !mbar_wait(&S.a_empty[kb], (uint32_t)((ti - 1) & 1), &S.abort_flag)) *P.status = 2;
+          if (ord >= 1 && !mbar_wait(&S.a_empty[kb], (uint32_t)((ord - 1) & 1), &S.abort_flag)) *P.status = 2;
           mbar_expect_tx(&S.a_full[kb], kRec);
           bulk_load(abuf + kb * kRec, P.arec + ((long long)t * KB + kb) * kRec, kRec, &S.a_full[kb]);
         }
+      });
     }
     __syncwarp();
   } else if (warp == 14) {
     // ============================================================== weight records: one per (item, K box)
     if (lane == 0) {
       int slot = 0, use = 0;
-      int e = 0, e_next = w0 < w1 ? P.tile_expert[t0] : 0;
-      for (int w = w0, t = t0, n = n0; w < w1; ++w) {
-        if (w == w0 || n == 0) {   // a new row tile: its expert was fetched a tile ahead
-          e = e_next;
-          if ((long long)(t + 1) * NBLK < w1) e_next = P.tile_expert[t + 1];
-        }
-        const uint8_t* src = P.wrec + ((long long)e * NBLK + n) * KB * kRec;
-        for (int kb = 0; kb < KB; ++kb) {
+      for_each_segment([&](int t, int n0, int n1, int) {
+        const uint8_t* src = P.wrec + ((long long)P.tile_expert[t] * NBLK + n0) * KB * kRec;
+        for (int i = 0; i < (n1 - n0) * KB; ++i) {   // the records of consecutive column blocks of an expert are contiguous
           if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
           mbar_expect_tx(&S.b_full[slot], kRec);
-          bulk_load(ring + slot * kRec, src + (long long)kb * kRec, kRec, &S.b_full[slot]);
+          bulk_load(ring + slot * kRec, src + (long long)i * kRec, kRec, &S.b_full[slot]);
           if (++slot == NSB) { slot = 0; ++use; }
         }
-        if (++n == NBLK) { n = 0; ++t; }
-      }
+      });
     }
     __syncwarp();
   } else if (warp >= 8 && warp < 12) {
@@ -380,58 +386,56 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
       tc_fence_before();
       __syncwarp();
     };
-    int slot = 0, ti = -1;
+    int slot = 0;
     uint32_t ph = 0;
-    for (int w = w0, n = n0; w < w1; ++w) {
-      const bool first = w == w0 || n == 0;
-      if (first) ++ti;
-      for (int kb = 0; kb < KB; ++kb) {
-        if (first) {
-          if (!mbar_wait(&S.a_full[kb], (uint32_t)(ti & 1), &S.abort_flag)) *P.status = 1;
-          put(a_u + kb * kRec, tm_sfa + 16 * kb);
-          if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
+    for_each_segment([&](int, int n0, int n1, int ord) {
+      for (int n = n0; n < n1; ++n)
+        for (int kb = 0; kb < KB; ++kb) {
+          if (n == n0) {
+            if (!mbar_wait(&S.a_full[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 1;
+            put(a_u + kb * kRec, tm_sfa + 16 * kb);
+            if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
+          }
+          if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
+          if (!(P.dbg & 4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
+          if (lane == 0) mbar_arrive(&S.b_sfr[slot]);
+          if (++slot == NSB) { slot = 0; ph ^= 1u; }
         }
-        if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
-        if (!(P.dbg & 4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
-        if (lane == 0) mbar_arrive(&S.b_sfr[slot]);
-        if (++slot == NSB) { slot = 0; ph ^= 1u; }
-      }
-      if (++n == NBLK) n = 0;
-    }
+    });
   } else if (warp == 12) {
     // ============================================================== MMA issuer
     const uint32_t el = elect_one();
     const uint32_t idesc = idesc_mxf4nvf4(128, 128);
     const uint64_t desc0 = smem_desc_sw128_kmajor(0);
     const uint32_t a16 = smem_u32(abuf) >> 4, b16 = smem_u32(ring) >> 4;
-    int slot = 0, ab = 0, works = 0, ti = -1;
+    int slot = 0, ab = 0, works = 0;
     uint32_t ph = 0;
     uint32_t aph[2] = {0, 0};
-    for (int w = w0, n = n0; w < w1; ++w) {
-      const bool first = w == w0 || n == 0, last = w == w1 - 1 || n == NBLK - 1;
-      if (first) ++ti;
-      if (works >= 2 && !mbar_wait(&S.acc_empty[ab], aph[ab] ^ 1u, &S.abort_flag)) *P.status = 5;
-      for (int kb = 0; kb < KB; ++kb) {
-        if (first && !mbar_wait(&S.a_sfr[kb], (uint32_t)(ti & 1), &S.abort_flag)) *P.status = 8;
-        if (!mbar_wait(&S.b_sfr[slot], ph, &S.abort_flag)) *P.status = 8;
-        tc_fence_after();
-        const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kRec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
-        const int nkt = kb == KB - 1 ? nkt_last : 4;
+    for_each_segment([&](int, int n0, int n1, int ord) {
+      for (int n = n0; n < n1; ++n) {
+        const bool first = n == n0, last = n == n1 - 1;
+        if (works >= 2 && !mbar_wait(&S.acc_empty[ab], aph[ab] ^ 1u, &S.abort_flag)) *P.status = 5;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (first && !mbar_wait(&S.a_sfr[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 8;
+          if (!mbar_wait(&S.b_sfr[slot], ph, &S.abort_flag)) *P.status = 8;
+          tc_fence_after();
+          const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kRec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
+          const int nkt = kb == KB - 1 ? nkt_last : 4;
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          if (jj < nkt && !(P.dbg & 2))
-            umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
-                            (kb > 0 || jj > 0) ? 1u : 0u, el);
-        umma_commit_p(&S.b_empty[slot], el);
-        if (last) umma_commit_p(&S.a_empty[kb], el);   // the next row tile's record of this box may land
-        if (++slot == NSB) { slot = 0; ph ^= 1u; }
+          for (int jj = 0; jj < 4; ++jj)
+            if (jj < nkt && !(P.dbg & 2))
+              umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
+                              (kb > 0 || jj > 0) ? 1u : 0u, el);
+          umma_commit_p(&S.b_empty[slot], el);
+          if (last) umma_commit_p(&S.a_empty[kb], el);   // the next segment's record of this box may land
+          if (++slot == NSB) { slot = 0; ph ^= 1u; }
+        }
+        umma_commit_p(&S.acc_full[ab], el);
+        aph[ab] ^= 1u;
+        ab ^= 1;
+        ++works;
       }
-      umma_commit_p(&S.acc_full[ab], el);
-      aph[ab] ^= 1u;
-      ab ^= 1;
-      ++works;
-      if (++n == NBLK) n = 0;
-    }
+    });
   } else {
     // ============================================================== epilogue: thread = accumulator row, warp pair = column halves
     const int quad = warp & 3, half = warp >> 2;
@@ -440,81 +444,80 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     uint32_t aph[2] = {0, 0};
     const float gs_in = *P.gs_in;
     const float gs_out = PHASE == 1 ? *P.gs_out : 0.f;
-    float s = 0.f;   // per row tile: FC1 alpha / gs_in; FC2 that times the row's routing weight (0 on padding rows)
-    int pr = -1;
-    for (int w = w0, t = t0, n = n0; w < w1; ++w) {
-      if (w == w0 || n == 0) {   // a new row tile: its expert and (FC2) this row's pair, fetched once
-        s = P.alpha[P.tile_expert[t]] / gs_in;
-        if (PHASE == 2) {
-          pr = P.row_pair[(long long)t * 128 + row];
-          s = pr >= 0 ? s * P.wts[pr] : 0.f;
-        }
+    for_each_segment([&](int t, int n0, int n1, int) {
+      // per segment: the tile's expert and (FC2) this row's pair, fetched once
+      float s = P.alpha[P.tile_expert[t]] / gs_in;   // FC1: alpha / gs_in; FC2: that times the row's routing weight (0 on padding rows)
+      int pr = -1;
+      if (PHASE == 2) {
+        pr = P.row_pair[(long long)t * 128 + row];
+        s = pr >= 0 ? s * P.wts[pr] : 0.f;
       }
-      if (!mbar_wait(&S.acc_full[ab], aph[ab], &S.abort_flag)) *P.status = 7;
-      tc_fence_after();
-      const uint32_t taddr = tm_acc + 128 * ab + ((uint32_t)(quad * 32) << 16);
-      if (P.dbg & 1) {
-      } else if (PHASE == 1) {
-        // columns 0..63 = up, 64..127 = gate of intermediate columns 64*n..; SiLU*mul, re-quantise blocks of 16
-        uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
-        uint32_t sfw = 0;
+      for (int n = n0; n < n1; ++n) {
+        if (!mbar_wait(&S.acc_full[ab], aph[ab], &S.abort_flag)) *P.status = 7;
+        tc_fence_after();
+        const uint32_t taddr = tm_acc + 128 * ab + ((uint32_t)(quad * 32) << 16);
+        if (P.dbg & 1) {
+        } else if (PHASE == 1) {
+          // columns 0..63 = up, 64..127 = gate of intermediate columns 64*n..; SiLU*mul, re-quantise blocks of 16
+          uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
+          uint32_t sfw = 0;
 #pragma unroll
-        for (int bb = 0; bb < 2; ++bb) {
-          const int blk = 2 * half + bb;
-          uint32_t up[16], gt[16];
-          tmem_ld_32x32b_x16(taddr + 16 * blk, up);
-          tmem_ld_32x32b_x16(taddr + 64 + 16 * blk, gt);
+          for (int bb = 0; bb < 2; ++bb) {
+            const int blk = 2 * half + bb;
+            uint32_t up[16], gt[16];
+            tmem_ld_32x32b_x16(taddr + 16 * blk, up);
+            tmem_ld_32x32b_x16(taddr + 64 + 16 * blk, gt);
+            tmem_ld_wait();
+            float a[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g = __uint_as_float(gt[i]) * s, u = __uint_as_float(up[i]) * s;
+              a[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+            }
+            uint2 pk;
+            const uint8_t sb = quantize_block16(a, gs_out, pk);
+            *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = pk;
+            sfw |= (uint32_t)sb << (8 * bb);
+          }
+          *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+        } else {
+          // This thread holds 64 bf16 of its row (128 bytes); the warp transposes its 32 x 128-byte block through its own
+          // patch of shared memory so that every store instruction writes whole 128-byte row segments (four rows per
+          // instruction) instead of 32 scattered 16-byte pieces.
+          uint32_t r[4][16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
           tmem_ld_wait();
-          float a[16];
+          uint8_t* patch = stage + warp * (32 * 144);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float g = __uint_as_float(gt[i]) * s, u = __uint_as_float(up[i]) * s;
-            a[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[c][2 * i]) * s, __uint_as_float(r[c][2 * i + 1]) * s);
+              o[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c + 16) = make_uint4(o[4], o[5], o[6], o[7]);
           }
-          uint2 pk;
-          const uint8_t sb = quantize_block16(a, gs_out, pk);
-          *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = pk;
-          sfw |= (uint32_t)sb << (8 * bb);
-        }
-        *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
-      } else {
-        // This thread holds 64 bf16 of its row (128 bytes); the warp transposes its 32 x 128-byte block through its own
-        // patch of shared memory so that every store instruction writes whole 128-byte row segments (four rows per
-        // instruction) instead of 32 scattered 16-byte pieces.
-        uint32_t r[4][16];
+          __syncwarp();
+          const unsigned valid = __ballot_sync(0xffffffffu, pr >= 0);   // bit l: row quad*32 + l holds a pair
+          __nv_bfloat16* ybase = P.y + ((long long)t * 128 + quad * 32) * P.H + 128 * n + 64 * half;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
-        tmem_ld_wait();
-        uint8_t* patch = stage + warp * (32 * 144);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[c][2 * i]) * s, __uint_as_float(r[c][2 * i + 1]) * s);
-            o[i] = *reinterpret_cast<const uint32_t*>(&h);
+          for (int j = 0; j < 8; ++j) {
+            const int rr = 4 * j + (lane >> 3);   // row of the warp's block this lane stores a 16-byte chunk of
+            const uint4 v4 = *reinterpret_cast<const uint4*>(patch + rr * 144 + (lane & 7) * 16);
+            if ((valid >> rr) & 1u) *reinterpret_cast<uint4*>(ybase + (long long)rr * P.H + (lane & 7) * 8) = v4;
           }
-          *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c) = make_uint4(o[0], o[1], o[2], o[3]);
-          *reinterpret_cast<uint4*>(patch + lane * 144 + 32 * c + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+          __syncwarp();
         }
+        tc_fence_before();
         __syncwarp();
-        const unsigned valid = __ballot_sync(0xffffffffu, pr >= 0);   // bit l: row quad*32 + l holds a pair
-        __nv_bfloat16* ybase = P.y + ((long long)t * 128 + quad * 32) * P.H + 128 * n + 64 * half;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int rr = 4 * j + (lane >> 3);   // row of the warp's block this lane stores a 16-byte chunk of
-          const uint4 v4 = *reinterpret_cast<const uint4*>(patch + rr * 144 + (lane & 7) * 16);
-          if ((valid >> rr) & 1u) *reinterpret_cast<uint4*>(ybase + (long long)rr * P.H + (lane & 7) * 8) = v4;
-        }
-        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.acc_empty[ab]);
+        aph[ab] ^= 1u;
+        ab ^= 1;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.acc_empty[ab]);
-      aph[ab] ^= 1u;
-      ab ^= 1;
-      if (++n == NBLK) { n = 0; ++t; }
-    }
+    });
   }
   tc_fence_before();
   __syncthreads();
