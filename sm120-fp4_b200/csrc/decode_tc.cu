@@ -135,7 +135,7 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
 // xb: the FC1 B operand exactly as the kernel wants it in shared memory, so that ONE bulk copy brings it in:
 //   [KB1 boxes][N rows (token*4 + term)][128 B] in the 128-byte-swizzle image (16-byte chunk c of row n sits at chunk
 //   c ^ (n & 7)), followed by KT1 scale tiles of 512 B (128x4 order, rows >= N zero). colscale f32 [N] = 1/g_t.
-__global__ void __launch_bounds__(128) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
+__global__ void __launch_bounds__(128, 10) k_expand_x(const __nv_bfloat16* __restrict__ x, int M, int H, int N, int KB1, uint8_t* __restrict__ xb,
                                                   float* __restrict__ colscale) {
   const int tok = blockIdx.x, tid = threadIdx.x;
   grid_launch_dependents();   // the layer kernel may start its prologue and weight prefetch now; it waits before reading xb
@@ -144,30 +144,42 @@ __global__ void __launch_bounds__(128) k_expand_x(const __nv_bfloat16* __restric
   uint8_t* xsf = xb + (long long)KB1 * N * 128;
   __shared__ float wm[4];
   __shared__ float s_g1;
+  // each thread keeps its (at most two) 16-value blocks in registers: one pass over x serves the token amax and the expansion
+  const int nblk = KB1 * 16;                 // blocks over the padded K (KB1 * 256 values); nblk <= 256
+  uint4 raw[2][2];
   float m = 0.f;
-  if (tok < M)
-    for (int i = tid; i < H; i += 128) m = fmaxf(m, fabsf(__bfloat162float(x[(long long)tok * H + i])));
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int b = tid + 128 * j;
+    raw[j][0] = raw[j][1] = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < M && b < nblk && b * 16 < H) {
+      raw[j][0] = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16);
+      raw[j][1] = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16 + 8);
+      const uint32_t w[8] = {raw[j][0].x, raw[j][0].y, raw[j][0].z, raw[j][0].w, raw[j][1].x, raw[j][1].y, raw[j][1].z, raw[j][1].w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[i] << 16)), fabsf(__uint_as_float(w[i] & 0xffff0000u))));
+    }
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & 31) == 0) wm[tid >> 5] = m;
   __syncthreads();
-  if (tid == 0) {
-    for (int w = 1; w < 4; ++w) m = fmaxf(m, wm[w]);
-    const float g1 = 2688.0f / fmaxf(m, 1e-30f);
-    s_g1 = g1;
+  m = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+  const float g1 = 2688.0f / fmaxf(m, 1e-30f);
+  if (tid < kTerms) {
     float g = g1;
-    for (int t = 0; t < kTerms; ++t) { colscale[tok * kTerms + t] = tok < M ? 1.0f / g : 0.f; g *= 6.0f; }
+    for (int t = 0; t < tid; ++t) g *= 6.0f;
+    colscale[tok * kTerms + tid] = tok < M ? 1.0f / g : 0.f;
   }
-  __syncthreads();
-  const float g1 = s_g1;
-  for (int b = tid; b < KB1 * 16; b += 128) {   // 16-value blocks over the padded K (KB1 * 256 values)
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int b = tid + 128 * j;
+    if (b >= nblk) break;
     uint2 codes[kTerms];
     uint8_t sf[kTerms];
     if (tok < M && b * 16 < H) {
       float r[16];
-      const uint4 v0 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16);
-      const uint4 v1 = *reinterpret_cast<const uint4*>(x + (long long)tok * H + b * 16 + 8);
-      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      const uint32_t w[8] = {raw[j][0].x, raw[j][0].y, raw[j][0].z, raw[j][0].w, raw[j][1].x, raw[j][1].y, raw[j][1].z, raw[j][1].w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) { r[2 * i] = __uint_as_float(w[i] << 16); r[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
       expand_block16(r, g1, codes, sf);
