@@ -177,14 +177,10 @@ def run_ours(a):
         for idx in range(len(cs)):
             run_case(idx)
 
-    def e2e_step():
+    def e2e_step():   # the C-ABI call with host buffers: copies in, layer, copy out, all inside the timed region
         for c in cs:
             for w in layers:
-                xd = c["hx"].to(dev, non_blocking=True)
-                idd = c["hid"].to(dev, non_blocking=True)
-                wd = c["hw"].to(dev, non_blocking=True)
-                o = w.forward(xd, idd, wd)
-                c["hout"].copy_(o, non_blocking=True)
+                w.forward_host(c["hx"], c["hid"], c["hw"], c["hout"])
 
     with torch.cuda.stream(stream):
         for _ in range(a.warmup):

@@ -95,6 +95,14 @@ int b200moe_prefill_status(const b200moe_layer* layer, const void* workspace, in
  * (routing + FC1 + SiLU*mul + FC2 + weighted combine). Replaces Weights._slice, sm120fp4/vllm_backend.py:174-190. */
 int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                            int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream);
+/* b200moe_decode_forward for a caller whose tensors live in host memory: x bf16 [M, H], ids int32 [M, top_k], weights f32
+ * [M, top_k] in, out bf16 [M, H] back. Page-locked buffers are read and written by the kernels directly across the host
+ * link (no copy is enqueued); pageable buffers go through staging buffers inside the workspace. Everything is enqueued on
+ * `stream`, nothing synchronises. M <= 16. Replaces the same call
+ * site as b200moe_decode_forward (sm120fp4/vllm_backend.py:174-190) for hosts that do not hold device tensors. */
+int b200moe_decode_forward_host(const b200moe_layer* layer, const void* x_host, const int* ids_host, const float* wts_host, int M,
+                                void* out_host, void* workspace, long long workspace_bytes, void* stream);
+
 /* FC1 alone -> act bf16 [M*top_k, I], row = pair index: sm120fp4/kernels/fc1_w4a16.py:251-262, fc1_mma.py:266-282. */
 int b200moe_decode_fc1(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
                        void* act_bf16, void* workspace, long long workspace_bytes, void* stream);
@@ -128,6 +136,16 @@ int b200moe_stream_probe(const void* buf, long long bytes, int pattern, int pitc
 int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
                         void* sx, int* meta, void* stream);
 int b200moe_ep_combine(const void* y, int m, int h, int world, int cap, void* out, void* stream);
+/* variable-size exchange (prefill batches; no counterpart in the reference either). plan: counts int32 [world], offsets int32
+ * [world + 1], pos int32 [m, world] (row of token t in the send buffer for destination d, or -1), send_tok int32 [rows]
+ * (destination-major, token order within a destination). gather: the rows of the send buffer (sx bf16 [rows, h], meta int32
+ * [rows, 2k]); max_rows >= offsets[world] bounds the grid. combine_rows: out[t] = sum over destinations, in rank order, of
+ * the partial row that came back for (t, d), fp32, one rounding. */
+int b200moe_ep_plan(const int* ids, int m, int k, int world, int experts_per_rank, int* counts, int* offsets, int* pos, int* send_tok,
+                    void* stream);
+int b200moe_ep_gather(const void* x, const int* ids, const float* wts, const int* send_tok, const int* offsets, int h, int k, int world,
+                      int experts_per_rank, int max_rows, void* sx, int* meta, void* stream);
+int b200moe_ep_combine_rows(const void* back, const int* pos, int m, int h, int world, void* out, void* stream);
 
 /* issue-cost measurement of tcgen05 scale copies and MMAs (diagnostic; no counterpart in the reference): cycles_dev[0] =
  * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64, ncommit commits}, cycles_dev[1] = cycles until all completed

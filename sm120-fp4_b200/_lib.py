@@ -37,6 +37,7 @@ SIGNATURES = {
     "b200moe_prefill_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, C.c_float, C.c_float, _P]),
     "b200moe_prefill_status": (_I, [_P, _P, _I, _P]),
     "b200moe_decode_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
+    "b200moe_decode_forward_host": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc1": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc2": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_layer_route_tables": (_I, [_P, _P, _I, _P, _P, _P, _P]),
@@ -46,6 +47,9 @@ SIGNATURES = {
     "b200moe_umma_cost": (_I, [_I, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_ep_dispatch": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _I, _I, _I, _P, _P]),
+    "b200moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "b200moe_ep_gather": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "b200moe_ep_combine_rows": (_I, [_P, _P, _I, _I, _I, _P, _P]),
     "b200moe_umma_probe": (_I, [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P]),
 }
 

@@ -56,7 +56,7 @@ struct b200moe_layer {
   int KB1, KB2, CB1, NB2, KT1, KT2;
   long long s1_stride, s2_stride;
   // workspace layout (byte offsets)
-  long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, off_debug, ws_bytes;
+  long long off_status, off_cnt1, off_cnt2, off_scratch, off_actfrag, off_tables, off_actbf16, off_debug, off_hstage, ws_bytes;
   long long off_xb, off_xscale, off_aslab;   // operands of the tcgen05 decode kernel
   int umax_cap;
   // tcgen05 decode path: composed FC1 scale tiles + alpha2 reference in a caller-owned buffer (b200moe_layer_prepack)
@@ -64,6 +64,7 @@ struct b200moe_layer {
   const uint8_t* w2t;
   const float* alpha2_ref;
   long long prepack_bytes;
+  int device;           // CUDA device the layer was created on
   int decode_impl;      // 0 auto (tcgen05 when prepacked), 1 legacy mma.sync kernel, 2 tcgen05 kernel
   float act_g1;
 };
@@ -104,7 +105,7 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   b200moe_layer* L = new (std::nothrow) b200moe_layer;
   if (!L) return B200MOE_ERR_ARG;
   memset(L, 0, sizeof(*L));
-  L->E = E, L->H = H, L->I = I, L->top_k = top_k, L->sms = prop.multiProcessorCount;
+  L->E = E, L->H = H, L->I = I, L->top_k = top_k, L->sms = prop.multiProcessorCount, L->device = dev;
   L->q1 = q1, L->s1 = s1_128x4, L->q2 = q2, L->s2 = s2_128x4, L->alpha1 = alpha1, L->alpha2 = alpha2;
   L->KB1 = (H + 255) / 256, L->KB2 = (I + 255) / 256;
   L->CB1 = I / 64, L->NB2 = H / 128;
@@ -129,6 +130,7 @@ extern "C" int b200moe_layer_create(b200moe_layer** out, int E, int H, int I, in
   L->off_xb = o, o = align_up(o + (long long)L->KB1 * 64 * 128 + (long long)L->KT1 * 512, 256);
   L->off_xscale = o, o += 256;
   L->off_aslab = o, o = align_up(o + (long long)L->umax_cap * L->KB2 * (64 * 128 + 2048), 256);
+  L->off_hstage = o, o = align_up(o + 2LL * 16 * H * 2 + 2LL * 16 * top_k * 4, 256);   // device copies of host-side inputs / output
   L->ws_bytes = o;
   L->prepack_bytes = (long long)E * ((long long)L->CB1 * L->KB1 + (long long)L->NB2 * L->KB2) * 18432 + 256;
   L->act_g1 = 8.0f;
@@ -282,8 +284,6 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
 // Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
 extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                                       int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
-  // automatic choice (measured on B200, Qwen3-30B-A3B shape): the mma.sync kernel is ahead up to 8 tokens (shorter latency
-  // chain), the tcgen05 kernel from 9 tokens (no CUDA-core dequantisation)
   // the tcgen05 kernel whenever the tile records exist and the shape fits it: x scale tiles of <= 12 K boxes in TMEM, one
   // worker group per 128-row output block
   if (L && L->w1t && L->decode_impl != 1 && L->sms <= 256 && L->KB1 <= 12 && L->NB2 <= L->sms) {
@@ -295,6 +295,49 @@ extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16
     return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, stream);
   }
   return decode_common(L, x_bf16, topk_ids, topk_weights, M, out_bf16, nullptr, 3, 1, workspace, workspace_bytes, stream);
+}
+
+// The same call for a host that keeps its tensors in host memory. Page-locked buffers (cudaHostAlloc, cudaHostRegister,
+// torch's pin_memory) are addressable from the device: the kernels then read x, ids and weights and write the output
+// straight across the host link - no copy is enqueued and the transfer overlaps the layer's own work. Pageable buffers are
+// copied through staging buffers inside the workspace. Everything is enqueued on `stream`; nothing synchronises.
+static void* device_view(const void* host_ptr) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, host_ptr) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (at.type == cudaMemoryTypeHost || at.type == cudaMemoryTypeManaged || at.type == cudaMemoryTypeDevice) return at.devicePointer;
+  return nullptr;
+}
+
+extern "C" int b200moe_decode_forward_host(const b200moe_layer* L, const void* x_host, const int* ids_host, const float* wts_host, int M,
+                                           void* out_host, void* workspace, long long workspace_bytes, void* stream) {
+  if (!L || !x_host || !ids_host || !wts_host || !out_host || !workspace || M < 0) return B200MOE_ERR_ARG;
+  if (M > 16) return B200MOE_ERR_LIMIT;
+  if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
+  if (M == 0) return B200MOE_OK;
+  struct DeviceGuard {   // the call may come from a thread whose current device is another one
+    int prev = -1;
+    explicit DeviceGuard(int want) { if (cudaGetDevice(&prev) == cudaSuccess && prev != want) cudaSetDevice(want); else prev = -1; }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+  } guard(L->device);
+  void* vx = device_view(x_host);
+  void* vi = device_view(ids_host);
+  void* vw = device_view(wts_host);
+  void* vo = device_view(out_host);
+  if (vx && vi && vw && vo && !((uintptr_t)vx & 15))
+    return b200moe_decode_forward(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, stream);
+  uint8_t* w = (uint8_t*)workspace;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* dx = w + L->off_hstage;
+  uint8_t* dout = dx + 16LL * L->H * 2;
+  int* dids = (int*)(dout + 16LL * L->H * 2);
+  float* dwts = (float*)(dids + 16 * L->top_k);
+  B200_CUDA_TRY(cudaMemcpyAsync(dx, x_host, (size_t)M * L->H * 2, cudaMemcpyHostToDevice, st));
+  B200_CUDA_TRY(cudaMemcpyAsync(dids, ids_host, (size_t)M * L->top_k * 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA_TRY(cudaMemcpyAsync(dwts, wts_host, (size_t)M * L->top_k * 4, cudaMemcpyHostToDevice, st));
+  const int rc = b200moe_decode_forward(L, dx, dids, dwts, M, dout, workspace, workspace_bytes, stream);
+  if (rc != B200MOE_OK) return rc;
+  B200_CUDA_TRY(cudaMemcpyAsync(out_host, dout, (size_t)M * L->H * 2, cudaMemcpyDeviceToHost, st));
+  return B200MOE_OK;
 }
 
 // FC1 alone (sm120fp4/kernels/fc1_w4a16.py:251-262, fc1_mma.py:266-282): act[M*top_k, I] bf16, row = pair index.

@@ -71,6 +71,8 @@ class ExpertParallelMoE:
             self.last_sent_rows = 0
             return self.local_forward(x, topk_ids, topk_weights)
         m, h = x.shape
+        if x.is_cuda:
+            return self._forward_variable_cuda(x, topk_ids, topk_weights)
         ids = topk_ids.to(torch.int64)
         wts = topk_weights.to(torch.float32)
         send_tok, counts, local_ids, own = dispatch_plan(ids, self.E, self.world)
@@ -93,6 +95,47 @@ class ExpertParallelMoE:
         back = torch.empty(int(sum(s_split)), h, dtype=x.dtype, device=x.device)
         dist.all_to_all_single(back, y.contiguous(), s_split, r_split, group=self.group)
         return self._combine(back, send_tok, counts, m, x.dtype)
+
+    def _forward_variable_cuda(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """The variable-size exchange on a CUDA device: plan, gather and combine are one library kernel each; the only host
+        synchronisation is the read of the split sizes (own counts and, after a tiny all-to-all, the peers')."""
+        from . import _lib
+        lib = _lib.lib()
+        m, h = x.shape
+        k, world, per, dev = self.k, self.world, self.E // self.world, x.device
+        ids = topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights.to(torch.float32).contiguous()
+        x = x.contiguous()
+        max_rows = m * min(world, k)
+        plan = torch.empty(2 * world + 1 + m * world + max_rows, dtype=torch.int32, device=dev)
+        counts, offsets = plan[:world], plan[world:2 * world + 1]
+        pos, send_tok = plan[2 * world + 1:2 * world + 1 + m * world], plan[2 * world + 1 + m * world:]
+        st = _lib.stream_ptr()
+        _lib.check(lib.b200moe_ep_plan(_lib.ptr(ids), m, k, world, per, _lib.ptr(counts), _lib.ptr(offsets), _lib.ptr(pos), _lib.ptr(send_tok), st),
+                   "ep plan")
+        both = torch.empty(2, world, dtype=torch.int32, device=dev)
+        both[0] = counts
+        dist.all_to_all_single(both[1], counts, group=self.group)
+        s_split, r_split = both.tolist()                                   # the one host synchronisation of the call
+        s_total, r_total = int(sum(s_split)), int(sum(r_split))
+        self.last_sent_rows = s_total
+        sx = torch.empty(max(s_total, 1), h, dtype=x.dtype, device=dev)
+        smeta = torch.empty(max(s_total, 1), 2 * k, dtype=torch.int32, device=dev)
+        _lib.check(lib.b200moe_ep_gather(_lib.ptr(x), _lib.ptr(ids), _lib.ptr(wts), _lib.ptr(send_tok), _lib.ptr(offsets), h, k, world, per,
+                                         s_total, _lib.ptr(sx), _lib.ptr(smeta), st), "ep gather")
+        rx = torch.empty(r_total, h, dtype=x.dtype, device=dev)
+        rmeta = torch.empty(r_total, 2 * k, dtype=torch.int32, device=dev)
+        dist.all_to_all_single(rx, sx[:s_total], r_split, s_split, group=self.group)
+        dist.all_to_all_single(rmeta, smeta[:s_total], r_split, s_split, group=self.group)
+        if r_total:
+            y = self.local_forward(rx, rmeta[:, :k].contiguous(), rmeta[:, k:].contiguous().view(torch.float32))
+        else:
+            y = rx
+        back = torch.empty(max(s_total, 1), h, dtype=x.dtype, device=dev)
+        dist.all_to_all_single(back[:s_total], y.contiguous(), s_split, r_split, group=self.group)
+        out = torch.empty(m, h, dtype=x.dtype, device=dev)
+        _lib.check(lib.b200moe_ep_combine_rows(_lib.ptr(back), _lib.ptr(pos), m, h, world, _lib.ptr(out), _lib.stream_ptr()), "ep combine")
+        return out
 
     def _combine(self, rows: torch.Tensor, send_tok: torch.Tensor, counts: torch.Tensor, m: int, dtype) -> torch.Tensor:
         """out[t] = sum over destinations (rank order) of the partial row that came back for t; fp32, one rounding."""

@@ -100,6 +100,9 @@ class Weights:
         self.pairs = torch.empty(pmax, dtype=torch.int32, device=dev)
         self.act = torch.empty(pmax, self.I, dtype=torch.bfloat16, device=dev)
         self.prefill = None   # set by enable_prefill: the W4A4 path above MAXM tokens
+        self._host_checked: set = set()   # (addresses, tokens) of host tensor sets forward_host has validated
+        self._fwd_host = h.b200moe_decode_forward_host
+        self._ws_ptr = self.workspace.data_ptr()
 
     def __del__(self):
         try:
@@ -153,7 +156,8 @@ class Weights:
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
                 pdl: bool | None = None) -> torch.Tensor:
         """The MoE forward for a batch of any size (sm120fp4/vllm_backend.py:147-172). `pdl` is accepted for signature
-        compatibility; the decode layer is a single launch, so there is no dependent launch to toggle."""
+        compatibility: the two launches of a decode call are always programmatic (B200MOE_PDL_CHAIN=0 in the environment
+        makes the first of them an ordinary stream-ordered launch)."""
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.H:
             raise TypeError(f"x must be bf16 [tokens, {self.H}]")
         m = x.shape[0]
@@ -169,6 +173,37 @@ class Weights:
         for s in range(0, m, MAXM):
             e = min(m, s + MAXM)
             self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e])
+        return out
+
+    def forward_host(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """The forward for tensors in host memory: x bf16 [tokens, H], ids int32 and weights f32 [tokens, top_k], out bf16
+        [tokens, H], all on the CPU. One library call per 16 tokens enqueues everything on the current stream of the layer's
+        device (page-locked tensors are read and written by the kernels directly, pageable ones are copied); nothing
+        synchronises - read `out` after synchronising the stream. A set of tensors is validated once and then recognised by
+        its addresses, so that a serving loop that reuses its buffers pays for one foreign-function call only."""
+        m = x.shape[0]
+        key = (x.data_ptr(), topk_ids.data_ptr(), topk_weights.data_ptr(), out.data_ptr(), m)
+        if key not in self._host_checked:
+            if x.is_cuda or topk_ids.is_cuda or topk_weights.is_cuda or out.is_cuda:
+                raise TypeError("forward_host takes host tensors; use forward for device tensors")
+            if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float32:
+                raise TypeError("x/out bf16, topk_ids int32, topk_weights float32")
+            if tuple(x.shape) != (m, self.H) or tuple(out.shape) != (m, self.H) or tuple(topk_ids.shape) != (m, self.k) \
+                    or tuple(topk_weights.shape) != (m, self.k):
+                raise ValueError("x/out [tokens, H], topk_ids/topk_weights [tokens, top_k]")
+            if not (x.is_contiguous() and out.is_contiguous() and topk_ids.is_contiguous() and topk_weights.is_contiguous()):
+                raise ValueError("contiguous host tensors expected")
+            if len(self._host_checked) > 4096:
+                self._host_checked.clear()
+            self._host_checked.add(key)
+        st = torch.cuda.current_stream(self.q1.device).cuda_stream
+        fn = self._fwd_host
+        px, pi, pw, po = key[0], key[1], key[2], key[3]
+        for s in range(0, m, MAXM):
+            n = min(m, s + MAXM) - s
+            rc = fn(self._h, px + s * self.H * 2, pi + s * self.k * 4, pw + s * self.k * 4, n, po + s * self.H * 2, self._ws_ptr, self.ws_bytes, st)
+            if rc:
+                _lib.check(rc, "forward_host")
         return out
 
     def _slice(self, x, ids, wts, out) -> None:

@@ -196,3 +196,26 @@ def test_back_to_back_launches_on_one_workspace(name, m):
     for _ in range(20):
         assert torch.equal(w.forward(xd, idd, wd), first)
     w.status()
+
+
+@pytest.mark.parametrize("m", [1, 16, 37])
+def test_host_buffer_entry_point_equals_the_device_call(m):
+    """b200moe_decode_forward_host: pinned host tensors in, pinned host tensor out, same bits as the device-tensor call."""
+    cfg, w, ow = layer("mid")
+    x, ids, wts = inputs(cfg, m, 6000 + m)
+    want = run(w, x, ids, wts).cpu()
+    hx, hid, hw = x.pin_memory(), ids.pin_memory(), wts.pin_memory()
+    hout = torch.empty_like(x).pin_memory()
+    for _ in range(2):
+        hout.zero_()
+        w.forward_host(hx, hid, hw, hout)
+        torch.cuda.synchronize()
+        assert torch.equal(hout, want)
+    # pageable host memory takes the staged-copy route of the same entry point
+    pout = torch.zeros_like(x)
+    w.forward_host(x.clone(), ids.clone(), wts.clone(), pout)
+    torch.cuda.synchronize()
+    assert torch.equal(pout, want)
+    w.status()
+    with pytest.raises(TypeError):
+        w.forward_host(hx.cuda(), hid, hw, hout)

@@ -115,3 +115,51 @@ def test_two_rank_expert_parallel_matches_the_full_layer():
         assert r[1] != "error", r[2]
         for err, rms, same in r[1]:
             assert err <= 3e-2 * rms and same, r
+
+
+@pytest.mark.parametrize("m,world,k,experts", [(37, 4, 4, 16), (4096, 8, 8, 128), (5, 2, 2, 8), (1500, 16, 8, 128)])
+def test_variable_exchange_kernels_match_the_torch_plan(m, world, k, experts):
+    """b200moe_ep_plan / _gather / _combine_rows against the torch formulation used on CPU ranks (ep.dispatch_plan,
+    ExpertParallelMoE._combine): same rows in the same order, same masked slots, same sums."""
+    import sm120fp4_b200._lib as L
+    from sm120fp4_b200.ep import dispatch_plan
+    lib = L.lib()
+    g = torch.Generator().manual_seed(m * 31 + world)
+    h, per = 64, experts // world
+    ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(m)]).to(torch.int32)
+    ids[::7, 0] = -1                                                   # some empty slots
+    wts = torch.rand(m, k, generator=g)
+    x = torch.randn(m, h, generator=g).to(torch.bfloat16)
+    idd, wd, xd = ids.cuda(), wts.cuda(), x.cuda()
+    # torch plan on the non-empty slots (an empty slot belongs to no rank)
+    safe = torch.where(idd >= 0, idd.long(), torch.full_like(idd.long(), experts * 2))
+    send_tok_ref, counts_ref, local_ref, own_ref = dispatch_plan(safe, experts, world)
+    max_rows = m * min(world, k)
+    counts = torch.empty(world, dtype=torch.int32, device="cuda")
+    offsets = torch.empty(world + 1, dtype=torch.int32, device="cuda")
+    pos = torch.empty(m, world, dtype=torch.int32, device="cuda")
+    send_tok = torch.full((max_rows,), -7, dtype=torch.int32, device="cuda")
+    L.check(lib.b200moe_ep_plan(L.ptr(idd), m, k, world, per, L.ptr(counts), L.ptr(offsets), L.ptr(pos), L.ptr(send_tok), L.stream_ptr()), "plan")
+    total = int(offsets[-1])
+    assert torch.equal(counts.long(), counts_ref.long()) and total == int(counts_ref.sum())
+    assert torch.equal(send_tok[:total].long(), send_tok_ref)
+    sx = torch.zeros(max(total, 1), h, dtype=torch.bfloat16, device="cuda")
+    meta = torch.zeros(max(total, 1), 2 * k, dtype=torch.int32, device="cuda")
+    L.check(lib.b200moe_ep_gather(L.ptr(xd), L.ptr(idd), L.ptr(wd), L.ptr(send_tok), L.ptr(offsets), h, k, world, per, total, L.ptr(sx), L.ptr(meta),
+                                  L.stream_ptr()), "gather")
+    assert torch.equal(sx[:total], xd[send_tok_ref])
+    assert torch.equal(meta[:total, :k], local_ref)
+    want_w = torch.where(own_ref, wd[send_tok_ref], torch.zeros((), device="cuda"))
+    assert torch.equal(meta[:total, k:].contiguous().view(torch.float32), want_w)
+    # combine: every (token, destination) row exactly once, summed in rank order
+    back = torch.randn(max(total, 1), h, generator=torch.Generator(device="cuda").manual_seed(1), device="cuda").to(torch.bfloat16)
+    out = torch.empty(m, h, dtype=torch.bfloat16, device="cuda")
+    L.check(lib.b200moe_ep_combine_rows(L.ptr(back), L.ptr(pos), m, h, world, L.ptr(out), L.stream_ptr()), "combine")
+    ref = torch.zeros(m, h, dtype=torch.float32, device="cuda")
+    ends = torch.cumsum(counts_ref, 0).tolist()
+    start = 0
+    for end in ends:
+        if end > start:
+            ref.index_add_(0, send_tok_ref[start:end], back[start:end].float())
+        start = end
+    assert torch.equal(out, ref.to(torch.bfloat16))
