@@ -319,10 +319,11 @@ extern "C" int b200moe_decode_forward_host(const b200moe_layer* L, const void* x
     explicit DeviceGuard(int want) { if (cudaGetDevice(&prev) == cudaSuccess && prev != want) cudaSetDevice(want); else prev = -1; }
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
   } guard(L->device);
-  void* vx = device_view(x_host);
-  void* vi = device_view(ids_host);
-  void* vw = device_view(wts_host);
-  void* vo = device_view(out_host);
+  static const bool in_place = [] { const char* c = getenv("B200MOE_HOST_IN_PLACE"); return !(c && c[0] == '0'); }();
+  void* vx = in_place ? device_view(x_host) : nullptr;
+  void* vi = in_place ? device_view(ids_host) : nullptr;
+  void* vw = in_place ? device_view(wts_host) : nullptr;
+  void* vo = in_place ? device_view(out_host) : nullptr;
   if (vx && vi && vw && vo && !((uintptr_t)vx & 15))
     return b200moe_decode_forward(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, stream);
   uint8_t* w = (uint8_t*)workspace;

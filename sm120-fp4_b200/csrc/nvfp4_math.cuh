@@ -64,4 +64,29 @@ __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], float 
   return (uint8_t)sfb;
 }
 
+// The same with the second division looked up: `table[b]` = gs / value(E4M3 byte b) for b = 0..127 (0 for b = 0), filled once
+// per thread block by fill_scale_table with the very division the function above performs, so the results are identical.
+__device__ __forceinline__ void fill_scale_table(float* table, float gs, int tid, int nthreads) {
+  for (int b = tid; b < 128; b += nthreads) {
+    const float sf_val = __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
+    table[b] = sf_val > 0.f && sf_val == sf_val ? __fdiv_rn(gs, sf_val) : 0.f;
+  }
+}
+__device__ __forceinline__ uint8_t quantize_block16_t(const float (&v)[16], float gs, const float* __restrict__ table, uint2& packed) {
+  float m[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(v[i]), fabsf(v[i + 8]));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], m[i + 4]);
+  const float amax = fmaxf(fmaxf(m[0], m[2]), fmaxf(m[1], m[3]));
+  const float sf_f = fminf(__fmul_rn(__fdiv_rn(amax, 6.0f), gs), 448.0f);
+  const __nv_fp8_storage_t sfb = __nv_cvt_float_to_fp8(sf_f, __NV_SATFINITE, __NV_E4M3);
+  const float scale = table[sfb & 127];
+  float sc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) sc[i] = __fmul_rn(v[i], scale);
+  packed = make_uint2(e2m1x8_rn(sc), e2m1x8_rn(sc + 8));
+  return (uint8_t)sfb;
+}
+
 }  // namespace b200

@@ -71,6 +71,9 @@ __global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* _
                                                           const float* __restrict__ gs_ptr, uint8_t* __restrict__ rec,
                                                           int* __restrict__ row_pair, int* __restrict__ dst_row) {
   const float gs = *gs_ptr;
+  __shared__ float s_scale[128];   // gs / (E4M3 value) for every scale byte: one division per table entry instead of one per block
+  fill_scale_table(s_scale, gs, threadIdx.x, blockDim.x);
+  __syncthreads();
   const unsigned per_row = (unsigned)KB * 16u;
   const unsigned total = (unsigned)ntiles[0] * 128u * per_row;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* _
     if (pr >= 0 && (int)b * 16 < H) {
       float v[16];
       load16(x + (long long)(pr / top_k) * H + b * 16, v);
-      sb = quantize_block16(v, gs, pk);
+      sb = quantize_block16_t(v, gs, s_scale, pk);
     }
     uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kRec;
     *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b & 15)) = pk;
