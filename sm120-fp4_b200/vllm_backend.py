@@ -102,6 +102,7 @@ class Weights:
         self.prefill = None   # set by enable_prefill: the W4A4 path above MAXM tokens
         self._host_checked: set = set()   # (addresses, tokens) of host tensor sets forward_host has validated
         self._fwd_host = h.b200moe_decode_forward_host
+        self._fwd = h.b200moe_decode_forward
         self._ws_ptr = self.workspace.data_ptr()
 
     def __del__(self):
@@ -163,12 +164,20 @@ class Weights:
         m = x.shape[0]
         if tuple(topk_ids.shape) != (m, self.k) or tuple(topk_weights.shape) != (m, self.k):
             raise ValueError("topk_ids and topk_weights must be [tokens, top_k]")
-        x = x.contiguous()
-        ids = topk_ids.to(torch.int32).contiguous()
-        wts = topk_weights.to(torch.float32).contiguous()
+        if not x.is_contiguous():
+            x = x.contiguous()
+        ids = topk_ids if topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() else topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights if topk_weights.dtype == torch.float32 and topk_weights.is_contiguous() else topk_weights.to(torch.float32).contiguous()
         if out is None:
             out = torch.empty_like(x)
-        if m > MAXM and self.prefill is not None and prefill_mode() != "slices":
+        if m <= MAXM:   # the decode call: one foreign-function call, no slicing
+            if m:
+                rc = self._fwd(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(), self._ws_ptr, self.ws_bytes,
+                               torch.cuda.current_stream(x.device).cuda_stream)
+                if rc:
+                    _lib.check(rc, "forward")
+            return out
+        if self.prefill is not None and prefill_mode() != "slices":
             return self.prefill.forward(x, ids, wts, out)
         for s in range(0, m, MAXM):
             e = min(m, s + MAXM)
