@@ -307,6 +307,11 @@ def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, pr
             for w in layers:
                 w.enable_prefill(max_tokens=prefill_tokens * world, workspace=ws)
                 ws = w.prefill.workspace
+        if name == "decode" and world > 1:   # a rank receives 16 rows from every peer: one W4A16 call instead of `world` slices
+            for w in layers:
+                w.enable_mid(max_tokens=world * decode_tokens, workspace=ws)
+                ws = w.mid.workspace
+            ws = None
         eps = [ExpertParallelMoE(w.forward, e, k, capacity=cap) for w in layers]
         x, ids, wts = synth.decode_inputs(m, e, cfg["hidden"], k, 7000 + 13 * rank + m)
         xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
@@ -341,10 +346,9 @@ def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, pr
         ms = float(t[0])
         res[name] = {"tokens_per_gpu": m, "tokens_per_s": round(world * m / (ms * 1e-3), 1), "us_per_layer": round(ms * 1e3 / stack, 1),
                      "rows_dispatched_per_layer_per_gpu": eps[0].last_sent_rows, "row_bytes": cfg["hidden"] * 2, "graph_replay": graphed}
-        if name == "prefill":
-            for w in layers:
-                w.prefill = None
         for w in layers:
+            w.prefill = None
+            w.mid = None
             w.status()
     res["stack_layers"] = stack
     return res

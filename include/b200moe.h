@@ -129,6 +129,16 @@ int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void
 int b200moe_stream_probe(const void* buf, long long bytes, int pattern, int pitch, int box_rows, int tile_bytes, int stages,
                          int producers, int* status_dev, void* stream);
 
+/* W4A16 layer call for mid-sized batches (17 tokens up to a few hundred): the arithmetic of b200moe_decode_forward as a
+ * grouped GEMM over per-expert gathered rows (four NVFP4 terms per token-expert pair), one pass over the touched experts'
+ * weights instead of one per 16-token slice (the reference runs slices of 16, sm120fp4/vllm_backend.py:147-172). Needs
+ * b200moe_layer_prepack and H, I <= 2304 (b200moe_mid_workspace_bytes returns the shape error otherwise); the workspace
+ * (zeroed once) holds transient data of one call and can be shared by the layers of a stack. */
+long long b200moe_mid_workspace_bytes(const b200moe_layer* layer, int max_tokens);
+int b200moe_mid_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                        void* out_bf16, void* workspace, long long workspace_bytes, int max_tokens, void* stream);
+int b200moe_mid_status(const b200moe_layer* layer, const void* workspace, int max_tokens, void* stream);
+
 /* expert-parallel fixed-capacity dispatch and combine (no counterpart in the reference: it declines expert parallelism,
  * sm120fp4/vllm_classes.py:46-47). dispatch: x bf16 [m, h], ids int32 [m, k] (global ids, negative = empty slot), wts f32
  * [m, k] -> sx bf16 [world, cap, h] and meta int32 [world, cap, 2k] (local ids, then the weights' float bits); block d is

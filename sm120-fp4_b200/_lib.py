@@ -45,6 +45,9 @@ SIGNATURES = {
     "b200moe_layer_debug_counters": (_I, [_P, _P, _P, _I, _P]),
     "b200moe_stream_probe": (_I, [_P, _LL, _I, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_umma_cost": (_I, [_I, _I, _I, _I, _I, _I, _P, _P]),
+    "b200moe_mid_workspace_bytes": (_LL, [_P, _I]),
+    "b200moe_mid_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, _P]),
+    "b200moe_mid_status": (_I, [_P, _P, _I, _P]),
     "b200moe_ep_dispatch": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "b200moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),

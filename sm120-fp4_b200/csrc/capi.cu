@@ -442,4 +442,43 @@ extern "C" int b200moe_prefill_status(const b200moe_layer* L, const void* worksp
   return st == 0 ? B200MOE_OK : B200MOE_ERR_TIMEOUT;
 }
 
+// ---- W4A16 layer call for mid-sized batches (17 tokens up to a few hundred): the decode kernels' arithmetic as a grouped
+// GEMM over per-expert gathered rows, one pass over the touched experts' weights. The reference runs such batches as slices
+// of 16 through its decode kernels (sm120fp4/vllm_backend.py:147-172). Needs b200moe_layer_prepack.
+long long b200_mid_workspace_bytes(int E, int H, int I, int top_k, int max_tokens);
+int b200_mid_status_offset(int E, int H, int I, int top_k, int max_tokens, long long* off);
+int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const uint8_t* w2t, const float* alpha1, const float* alpha2,
+                     const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
+                     float act_g1, int sms, cudaStream_t st);
+
+extern "C" long long b200moe_mid_workspace_bytes(const b200moe_layer* L, int max_tokens) {
+  if (!L || max_tokens <= 0) return B200MOE_ERR_ARG;
+  if (L->KB1 > 9 || L->KB2 > 9) return B200MOE_ERR_SHAPE;   // the operand tile (KB records) plus three weight stages must fit in shared memory
+  return b200_mid_workspace_bytes(L->E, L->H, L->I, L->top_k, max_tokens);
+}
+
+// x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]; M <= max_tokens of the (zeroed)
+// workspace. Same arithmetic as b200moe_decode_forward (W4A16, fp32 accumulation).
+extern "C" int b200moe_mid_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,
+                                   void* out_bf16, void* workspace, long long workspace_bytes, int max_tokens, void* stream) {
+  if (!L || !x_bf16 || !topk_ids || !topk_weights || !out_bf16 || !workspace || M < 0 || max_tokens <= 0) return B200MOE_ERR_ARG;
+  if (!L->w1t) return B200MOE_ERR_ARG;   // not prepacked
+  if (((uintptr_t)workspace & 255) || ((uintptr_t)x_bf16 & 15) || ((uintptr_t)out_bf16 & 15)) return B200MOE_ERR_ARG;
+  if (L->H % 128 || L->I % 64) return B200MOE_ERR_SHAPE;
+  if (M == 0) return B200MOE_OK;
+  return b200_mid_forward(L->E, L->H, L->I, L->top_k, L->w1t, L->w2t, L->alpha1, L->alpha2, x_bf16, topk_ids, topk_weights, M, out_bf16,
+                          workspace, workspace_bytes, max_tokens, L->act_g1, L->sms, (cudaStream_t)stream);
+}
+
+// status word of the mid-batch workspace; synchronises the stream
+extern "C" int b200moe_mid_status(const b200moe_layer* L, const void* workspace, int max_tokens, void* stream) {
+  if (!L || !workspace) return B200MOE_ERR_ARG;
+  long long off = 0;
+  b200_mid_status_offset(L->E, L->H, L->I, L->top_k, max_tokens, &off);
+  int st = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&st, (const uint8_t*)workspace + off, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  return st == 0 ? B200MOE_OK : B200MOE_ERR_TIMEOUT;
+}
+
 extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }

@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "nvfp4_math.cuh"
+#include "expand.cuh"
 #include <string.h>
 #include <stdlib.h>
 
@@ -26,12 +27,13 @@ constexpr int kPfStages = 5;         // ring stages of two records (A, B) each
 constexpr int kPfThreads = 256;      // warps 0-3 epilogue, 4 MMA issuer, 5 scale copier, 6-7 TMA producers
 
 // ------------------------------------------------------------------------------------------------ plan
-// experts/offsets: the router's tables. One thread per touched expert: its rows are cut into 128-row tiles, the tiles of
+// experts/offsets: the router's tables. One thread per touched expert: its rows are cut into tiles of rows_per_tile rows
+// (128 for the W4A4 GEMM; 32 for the W4A16 GEMM, whose tile holds four term rows per token-expert pair), the tiles of
 // all experts are numbered in expert order by a block-wide scan. Output: ntiles[0], and per tile its expert and the range
 // [tile_first, tile_end) of the expert's rows in `pairs` that it holds (the last tile of an expert is partly empty).
 __global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ experts, const int* __restrict__ offsets, int Umax, int max_tiles,
-                                                      int* __restrict__ ntiles, int* __restrict__ tile_expert, int* __restrict__ tile_first,
-                                                      int* __restrict__ tile_end) {
+                                                      int rows_per_tile, int* __restrict__ ntiles, int* __restrict__ tile_expert,
+                                                      int* __restrict__ tile_first, int* __restrict__ tile_end) {
   __shared__ int wsum[8];
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   int e = -1, lo = 0, hi = 0;
@@ -39,7 +41,7 @@ __global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ ex
     e = experts[u];
     if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
   }
-  const int mine = (hi - lo + 127) >> 7;
+  const int mine = (hi - lo + rows_per_tile - 1) / rows_per_tile;
   int inc = mine;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -53,7 +55,7 @@ __global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ ex
   if (u == 255) ntiles[0] = min(base + mine, max_tiles);
   for (int j = 0; j < mine && base + j < max_tiles; ++j) {
     tile_expert[base + j] = e;
-    tile_first[base + j] = lo + j * 128;
+    tile_first[base + j] = lo + j * rows_per_tile;
     tile_end[base + j] = hi;
   }
 }
@@ -99,6 +101,74 @@ __global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------------------------------------------------ x -> W4A16 records
+// Mid-sized batches (17 tokens up to a few hundred) keep the decode path's W4A16 arithmetic but run as a grouped GEMM over
+// per-expert gathered rows: a tile of 128 operand rows holds 32 token-expert pairs x four NVFP4 terms of the pair's token
+// row (row 4p + t = term t of pair p), so that an expert's weight records are streamed once for all of its pairs.
+__global__ void __launch_bounds__(128) k_token_amax(const __nv_bfloat16* __restrict__ x, int H, float* __restrict__ amax) {
+  __shared__ float wm[4];
+  const int tok = blockIdx.x, tid = threadIdx.x;
+  float m = 0.f;
+  for (int i = tid * 8; i < H; i += 128 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)tok * H + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[q] << 16)), fabsf(__uint_as_float(w[q] & 0xffff0000u))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & 31) == 0) wm[tid >> 5] = m;
+  __syncthreads();
+  if (tid == 0) amax[tok] = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+}
+
+// One thread per 16-value block of a pair row: the block's four terms go to rows 4p..4p+3 of the tile's record. The thread
+// of a pair's first block also records the pair of the four rows (row_pair), their 1 / g_t (rowscale) and the pair's row in
+// the output of FC2 (dst_row = tile * 32 + p).
+__global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __restrict__ x, const float* __restrict__ tok_amax,
+                                                        const int* __restrict__ pairs, const int* __restrict__ tile_first,
+                                                        const int* __restrict__ tile_end, const int* __restrict__ ntiles, int H, int KB,
+                                                        int top_k, uint8_t* __restrict__ rec, int* __restrict__ row_pair,
+                                                        float* __restrict__ rowscale, int* __restrict__ dst_row) {
+  const unsigned per_row = (unsigned)KB * 16u;
+  const unsigned total = (unsigned)ntiles[0] * 32u * per_row;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const unsigned prow = i / per_row, b = i - prow * per_row;
+    const int t = (int)(prow >> 5), p = (int)(prow & 31);
+    const int j = tile_first[t] + p;
+    int pr = -1;
+    if (j < tile_end[t]) pr = pairs[j];
+    const int tok = pr >= 0 ? pr / top_k : 0;
+    const float g1 = pr >= 0 ? 2688.0f / fmaxf(tok_amax[tok], 1e-30f) : 0.f;
+    if (b == 0) {
+      float g = g1;
+#pragma unroll
+      for (int q = 0; q < kTerms; ++q) {
+        row_pair[t * 128 + 4 * p + q] = pr;
+        rowscale[t * 128 + 4 * p + q] = pr >= 0 ? 1.0f / g : 0.f;
+        g *= 6.0f;
+      }
+      if (pr >= 0) dst_row[pr] = t * 32 + p;
+    }
+    uint2 codes[kTerms];
+    uint8_t sf[kTerms];
+    if (pr >= 0 && (int)b * 16 < H) {
+      float v[16];
+      load16(x + (long long)tok * H + b * 16, v);
+      expand_block16(v, g1, codes, sf);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kTerms; ++q) { codes[q] = make_uint2(0u, 0u); sf[q] = 0; }
+    }
+    uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kRec;
+#pragma unroll
+    for (int q = 0; q < kTerms; ++q) {
+      *reinterpret_cast<uint2*>(dst + rec_code_offset(4 * p + q, b & 15)) = codes[q];
+      dst[rec_scale_offset(4 * p + q, b & 15)] = sf[q];
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ grouped GEMM
 struct PrefillParams {
   const uint8_t* arec;        // activation records [ntiles][KB][18432]
@@ -112,7 +182,10 @@ struct PrefillParams {
   const float* wts;           // PHASE 2: routing weights [P]
   uint8_t* orec;              // PHASE 1: FC2 activation records [ntiles][KB2][18432]
   __nv_bfloat16* y;           // PHASE 2: weighted rows [ntiles*128][H]
+  float* yf;                  // PHASE 4: weighted rows [ntiles*32][H] in fp32 (one rounding only, in the combine)
   int* status;
+  const float* rowscale;      // PHASE 3: 1 / g_t of every term row of the x operand [ntiles*128] (0 on padding rows)
+  float act_g1;               // PHASE 3/4: global scale of the first term of the SiLU*mul activations
   int NBLK, KB, KT, KB2, H;
   int dbg;                    // experiments only (B200MOE_PF_DEBUG): 1 epilogue without math, 2 no MMAs, 4 no scale moves
 };
@@ -445,15 +518,22 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     const int row = quad * 32 + lane;
     int ab = 0;
     uint32_t aph[2] = {0, 0};
-    const float gs_in = *P.gs_in;
+    const float gs_in = PHASE <= 2 ? *P.gs_in : 1.0f;
     const float gs_out = PHASE == 1 ? *P.gs_out : 0.f;
     for_each_segment([&](int t, int n0, int n1, int) {
       // per segment: the tile's expert and (FC2) this row's pair, fetched once
       float s = P.alpha[P.tile_expert[t]] / gs_in;   // FC1: alpha / gs_in; FC2: that times the row's routing weight (0 on padding rows)
       int pr = -1;
-      if (PHASE == 2) {
+      float rs = 0.f;   // W4A16 phases: 1 / g_t of this operand row's term
+      if (PHASE == 2 || PHASE == 4) {
         pr = P.row_pair[(long long)t * 128 + row];
         s = pr >= 0 ? s * P.wts[pr] : 0.f;
+      }
+      if (PHASE == 3) rs = P.rowscale[(long long)t * 128 + row];
+      if (PHASE == 4) {
+        float g = P.act_g1;
+        for (int q = 0; q < (lane & 3); ++q) g *= 6.0f;
+        rs = 1.0f / g;
       }
       for (int n = n0; n < n1; ++n) {
         if (!mbar_wait(&S.acc_full[ab], aph[ab], &S.abort_flag)) *P.status = 7;
@@ -483,6 +563,66 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             sfw |= (uint32_t)sb << (8 * bb);
           }
           *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+        } else if (PHASE == 3) {
+          // W4A16 FC1: rows 4p..4p+3 are the four terms of pair p; each scaled by its 1/g_t, the four lanes of a pair are
+          // added (they then all hold the pair's up / gate values), SiLU*mul, and the pair's activations are expanded into
+          // four terms again - lane t keeps term t, which is row 4p + t of FC2's operand record.
+          uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
+          uint32_t sfw = 0;
+          uint32_t upr[2][16], gtr[2][16];
+#pragma unroll
+          for (int bb = 0; bb < 2; ++bb) {
+            tmem_ld_32x32b_x16(taddr + 16 * (2 * half + bb), upr[bb]);
+            tmem_ld_32x32b_x16(taddr + 64 + 16 * (2 * half + bb), gtr[bb]);
+          }
+          tmem_ld_wait();
+          const int tq = lane & 3;
+#pragma unroll
+          for (int bb = 0; bb < 2; ++bb) {
+            const int blk = 2 * half + bb;
+            float a[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float u = __uint_as_float(upr[bb][i]) * rs, g = __uint_as_float(gtr[bb][i]) * rs;
+              u += __shfl_xor_sync(0xffffffffu, u, 1);
+              g += __shfl_xor_sync(0xffffffffu, g, 1);
+              u += __shfl_xor_sync(0xffffffffu, u, 2);
+              g += __shfl_xor_sync(0xffffffffu, g, 2);
+              g *= s, u *= s;
+              a[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+            }
+            uint2 codes[kTerms];
+            uint8_t sf[kTerms];
+            expand_block16(a, P.act_g1, codes, sf);
+            const uint2 mc = tq == 0 ? codes[0] : tq == 1 ? codes[1] : tq == 2 ? codes[2] : codes[3];
+            const uint32_t ms = tq == 0 ? sf[0] : tq == 1 ? sf[1] : tq == 2 ? sf[2] : sf[3];
+            *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = mc;
+            sfw |= ms << (8 * bb);
+          }
+          *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+        } else if (PHASE == 4) {
+          // W4A16 FC2: the four term rows of a pair are scaled and added; lane t of the pair stores columns 16t..16t+15 of
+          // this warp's 64-column half, so the four lanes write one contiguous 128-byte segment of the pair's row.
+          uint32_t r[4][16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
+          tmem_ld_wait();
+          float* yrow = P.yf + ((long long)t * 32 + (row >> 2)) * P.H + 128 * n + 64 * half + 16 * (lane & 3);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float v0 = __uint_as_float(r[c][i]) * rs;
+              v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+              v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+              o[i] = v0 * s;
+            }
+            if ((lane & 3) == c && pr >= 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(yrow + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+          }
         } else {
           // This thread holds 64 bf16 of its row (128 bytes); the warp transposes its 32 x 128-byte block through its own
           // patch of shared memory so that every store instruction writes whole 128-byte row segments (four rows per
@@ -559,6 +699,30 @@ __global__ void __launch_bounds__(256) k_prefill_combine(const __nv_bfloat16* __
   }
 }
 
+// the same from fp32 rows (W4A16 path: the only bf16 rounding of the layer is this one)
+__global__ void __launch_bounds__(256) k_combine_f32(const float* __restrict__ y, const int* __restrict__ dst_row, int M, int top_k, int H,
+                                                     __nv_bfloat16* __restrict__ out) {
+  const int chunks = H / 8;
+  const long long total = (long long)M * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int tok = (int)(i / chunks), c = (int)(i % chunks);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int r = dst_row[tok * top_k + j];
+      if (r < 0) continue;   // empty slot
+      const float4 a = *reinterpret_cast<const float4*>(y + (long long)r * H + c * 8), b = *reinterpret_cast<const float4*>(y + (long long)r * H + c * 8 + 4);
+      acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w, acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      o[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + (long long)tok * H + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -604,6 +768,45 @@ long long b200_prefill_workspace_bytes(int E, int H, int I, int top_k, int max_t
 
 __global__ void k_set2(float* p, float a, float b) { p[0] = a; p[1] = b; }
 
+// One GEMM launch. Phases 1/2 (W4A4): the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit
+// in shared memory and the scale columns fit in TMEM, otherwise the kernel that streams both operands. Phases 3/4 (W4A16)
+// exist for the resident-A kernel only.
+static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, cudaStream_t st) {
+  const int tail = 1024 + ((phase == 2) ? 8 * 32 * 144 : 0);   // barriers (+ the W4A4 FC2 epilogue's store patches)
+  int nsb = (227 * 1024 - 1024 - tail - 256 - KB * kRec) / kRec;
+  const int tmem_cap = (512 - 256 - 16 * KB) / 16;
+  if (nsb > tmem_cap) nsb = tmem_cap;
+  if (nsb > 12) nsb = 12;
+  const bool stream_a = getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1';
+  if (KB <= 12 && nsb >= 3 && !(stream_a && phase <= 2)) {
+    const int sm_r = 1024 + (KB + nsb) * kRec + tail;
+    const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : phase == 2 ? (const void*)k_prefill_gemm_r<2>
+                   : phase == 3 ? (const void*)k_prefill_gemm_r<3> : (const void*)k_prefill_gemm_r<4>;
+    static thread_local int configured_r[4] = {0, 0, 0, 0};
+    if (configured_r[phase - 1] < sm_r) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, sm_r));
+      configured_r[phase - 1] = sm_r;
+    }
+    if (phase == 1) k_prefill_gemm_r<1><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+    else if (phase == 2) k_prefill_gemm_r<2><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+    else if (phase == 3) k_prefill_gemm_r<3><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+    else k_prefill_gemm_r<4><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+  } else {
+    if (phase > 2) return B200MOE_ERR_SHAPE;
+    const int smem = 1024 + kPfStages * 2 * kRec + (int)sizeof(PfShared);
+    static thread_local bool configured = false;
+    if (!configured) {
+      B200_CUDA_TRY(cudaFuncSetAttribute(k_prefill_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      B200_CUDA_TRY(cudaFuncSetAttribute(k_prefill_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      configured = true;
+    }
+    if (phase == 1) k_prefill_gemm<1><<<sms, kPfThreads, smem, st>>>(p);
+    else k_prefill_gemm<2><<<sms, kPfThreads, smem, st>>>(p);
+  }
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
 // w1t / w2t: the weight tile records of b200moe_layer_prepack. gs_x / gs_a: global scales of the two activation quantisations.
 int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const uint8_t* w2t, const float* alpha1, const float* alpha2,
                          const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
@@ -631,49 +834,18 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   int* tile_first = src_tok;              // two tables of max_tiles entries
   int* tile_end = src_tok + max_tiles;
   if (Umax > 256) return B200MOE_ERR_LIMIT;
-  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, ntiles, tile_expert, tile_first, tile_end);
+  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 128, ntiles, tile_expert, tile_first, tile_end);
   B200_LAUNCH_CHECK();
   k_set2<<<1, 1, 0, st>>>(gs, gs_x, gs_a);
   B200_LAUNCH_CHECK();
   k_quantize_records<<<sms * 16, 256, 0, st>>>((const __nv_bfloat16*)x, pairs, tile_first, tile_end, ntiles, H, KB1, top_k, gs, w + L.xrec,
                                                row_pair, dst_row);
   B200_LAUNCH_CHECK();
-  const int smem = 1024 + kPfStages * 2 * kRec + (int)sizeof(PfShared);
-  static thread_local bool configured = false;
-  if (!configured) {
-    B200_CUDA_TRY(cudaFuncSetAttribute(k_prefill_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    B200_CUDA_TRY(cudaFuncSetAttribute(k_prefill_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = status, p.H = H;
   p.dbg = getenv("B200MOE_PF_DEBUG") ? atoi(getenv("B200MOE_PF_DEBUG")) : 0;
-  // per GEMM: the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit in shared memory and
-  // the scale columns fit in TMEM; otherwise the kernel that streams both operands
-  auto launch = [&](int phase, int KB) -> int {
-    const int tail = 1024 + (phase == 2 ? 8 * 32 * 144 : 0);   // barriers (+ the FC2 epilogue's store patches)
-    int nsb = (227 * 1024 - 1024 - tail - 256 - KB * kRec) / kRec;
-    const int tmem_cap = (512 - 256 - 16 * KB) / 16;
-    if (nsb > tmem_cap) nsb = tmem_cap;
-    if (nsb > 12) nsb = 12;
-    if (KB <= 12 && nsb >= 3 && !(getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1')) {
-      const int sm_r = 1024 + (KB + nsb) * kRec + tail;
-      const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : (const void*)k_prefill_gemm_r<2>;
-      static thread_local int configured_r[2] = {0, 0};
-      if (configured_r[phase - 1] < sm_r) {
-        B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, sm_r));
-        configured_r[phase - 1] = sm_r;
-      }
-      if (phase == 1) k_prefill_gemm_r<1><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
-      else k_prefill_gemm_r<2><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
-    } else {
-      if (phase == 1) k_prefill_gemm<1><<<sms, kPfThreads, smem, st>>>(p);
-      else k_prefill_gemm<2><<<sms, kPfThreads, smem, st>>>(p);
-    }
-    B200_LAUNCH_CHECK();
-    return B200MOE_OK;
-  };
+  auto launch = [&](int phase, int KB) -> int { return launch_gemm(p, phase, KB, sms, st); };
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.gs_in = gs, p.gs_out = gs + 1, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
@@ -697,4 +869,95 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
 int b200_prefill_status_offset(int E, int H, int I, int top_k, int max_tokens, long long* off) {
   *off = prefill_layout(E, H, I, top_k, max_tokens).status;
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// W4A16 layer call for mid-sized batches (the decode path's arithmetic, one pass over the touched experts' weights).
+struct MidLayout {
+  long long experts, offsets, pairs, route_ws, ntiles, tile_expert, tile_tab, row_pair, rowscale, dst_row, tok_amax, status, xrec, arec, y, total;
+  int max_tiles;
+};
+
+static MidLayout mid_layout(int E, int H, int I, int top_k, int max_tokens) {
+  MidLayout L;
+  const long long P = (long long)max_tokens * top_k;
+  const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
+  L.max_tiles = (int)(P / 32 + E);
+  long long o = 0;
+  L.experts = o, o = pf_align(o + 4LL * E);
+  L.offsets = o, o = pf_align(o + 4LL * (E + 1));
+  L.pairs = o, o = pf_align(o + 4 * P);
+  L.route_ws = o, o = pf_align(o + b200moe_route_workspace_bytes((int)P, E));
+  L.ntiles = o, o += 256;
+  L.tile_expert = o, o = pf_align(o + 4LL * L.max_tiles);
+  L.tile_tab = o, o = pf_align(o + 8LL * L.max_tiles);
+  L.row_pair = o, o = pf_align(o + 4LL * L.max_tiles * 128);
+  L.rowscale = o, o = pf_align(o + 4LL * L.max_tiles * 128);
+  L.dst_row = o, o = pf_align(o + 4 * P);
+  L.tok_amax = o, o = pf_align(o + 4LL * max_tokens);
+  L.status = o, o += 256;
+  L.xrec = o, o = pf_align(o + (long long)L.max_tiles * KB1 * kRec);
+  L.arec = o, o = pf_align(o + (long long)L.max_tiles * KB2 * kRec);
+  L.y = o, o = pf_align(o + (long long)L.max_tiles * 32 * H * 4);
+  L.total = o;
+  return L;
+}
+
+long long b200_mid_workspace_bytes(int E, int H, int I, int top_k, int max_tokens) { return mid_layout(E, H, I, top_k, max_tokens).total; }
+
+int b200_mid_status_offset(int E, int H, int I, int top_k, int max_tokens, long long* off) {
+  *off = mid_layout(E, H, I, top_k, max_tokens).status;
+  return 0;
+}
+
+int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const uint8_t* w2t, const float* alpha1, const float* alpha2,
+                     const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
+                     float act_g1, int sms, cudaStream_t st) {
+  const MidLayout L = mid_layout(E, H, I, top_k, ws_tokens);
+  if (ws_bytes < L.total || M > ws_tokens) return B200MOE_ERR_WORKSPACE;
+  uint8_t* w = (uint8_t*)ws;
+  const int P = M * top_k;
+  const int Umax = E < P ? E : P;
+  const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256, KT1 = (H / 16 + 3) / 4, KT2 = (I / 16 + 3) / 4;
+  if (Umax > 256 || KB1 > 12) return B200MOE_ERR_LIMIT;
+  int* experts = (int*)(w + L.experts);
+  int* offsets = (int*)(w + L.offsets);
+  int* pairs = (int*)(w + L.pairs);
+  int* ntiles = (int*)(w + L.ntiles);
+  int* tile_expert = (int*)(w + L.tile_expert);
+  int* tile_first = (int*)(w + L.tile_tab);
+  int* row_pair = (int*)(w + L.row_pair);
+  float* rowscale = (float*)(w + L.rowscale);
+  int* dst_row = (int*)(w + L.dst_row);
+  float* tok_amax = (float*)(w + L.tok_amax);
+  int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
+  if (rc != B200MOE_OK) return rc;
+  B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
+  const int max_tiles = P / 32 + Umax;
+  int* tile_end = tile_first + max_tiles;
+  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 32, ntiles, tile_expert, tile_first, tile_end);
+  B200_LAUNCH_CHECK();
+  k_token_amax<<<M, 128, 0, st>>>((const __nv_bfloat16*)x, H, tok_amax);
+  B200_LAUNCH_CHECK();
+  k_expand_records<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)x, tok_amax, pairs, tile_first, tile_end, ntiles, H, KB1, top_k, w + L.xrec,
+                                             row_pair, rowscale, dst_row);
+  B200_LAUNCH_CHECK();
+  PrefillParams p;
+  memset(&p, 0, sizeof(p));
+  p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = (int*)(w + L.status), p.H = H;
+  p.rowscale = rowscale, p.act_g1 = act_g1;
+  // FC1
+  p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.orec = w + L.arec;
+  p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
+  rc = launch_gemm(p, 3, KB1, sms, st);
+  if (rc != B200MOE_OK) return rc;
+  // FC2
+  p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.orec = nullptr;
+  p.wts = wts, p.yf = (float*)(w + L.y);
+  p.NBLK = H / 128, p.KB = KB2, p.KT = KT2;
+  rc = launch_gemm(p, 4, KB2, sms, st);
+  if (rc != B200MOE_OK) return rc;
+  k_combine_f32<<<sms * 4, 256, 0, st>>>((const float*)(w + L.y), dst_row, M, top_k, H, (__nv_bfloat16*)out);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
 }

@@ -100,6 +100,7 @@ class Weights:
         self.pairs = torch.empty(pmax, dtype=torch.int32, device=dev)
         self.act = torch.empty(pmax, self.I, dtype=torch.bfloat16, device=dev)
         self.prefill = None   # set by enable_prefill: the W4A4 path above MAXM tokens
+        self.mid = None       # set by enable_mid: one W4A16 call for 17..max_tokens tokens
         self._host_checked: set = set()   # (addresses, tokens) of host tensor sets forward_host has validated
         self._fwd_host = h.b200moe_decode_forward_host
         self._fwd = h.b200moe_decode_forward
@@ -140,6 +141,23 @@ class Weights:
 
     enable_cutlass_prefill = enable_prefill   # the reference's name for the same switch
 
+    def enable_mid(self, max_tokens: int = 256, workspace: torch.Tensor | None = None) -> None:
+        """Batches of 33..max_tokens tokens run as ONE W4A16 call (the decode arithmetic, a grouped GEMM over per-expert
+        gathered rows) instead of slices of 16 that each stream the touched experts again. `workspace`: a zeroed uint8
+        tensor to share between the layers of a stack (transient data of one call); allocated here when None."""
+        h = _lib.lib()
+        nbytes = int(h.b200moe_mid_workspace_bytes(self._h, int(max_tokens)))
+        if nbytes < 0:
+            _lib.check(nbytes, "enable_mid")
+        if workspace is None:
+            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device)
+        elif workspace.numel() < nbytes or workspace.dtype != torch.uint8:
+            raise ValueError(f"the shared mid-batch workspace needs {nbytes} bytes of uint8")
+        self.mid = SimpleNamespace(max_tokens=int(max_tokens), workspace=workspace)
+
+    def mid_status(self) -> None:
+        _lib.check(_lib.lib().b200moe_mid_status(self._h, _lib.ptr(self.mid.workspace), self.mid.max_tokens, _lib.stream_ptr()), "mid status")
+
     def _prefill_forward(self, x, ids, wts, out):
         pf = self.prefill
         for s in range(0, x.shape[0], pf.max_tokens):
@@ -176,6 +194,11 @@ class Weights:
                                torch.cuda.current_stream(x.device).cuda_stream)
                 if rc:
                     _lib.check(rc, "forward")
+            return out
+        if self.mid is not None and 2 * MAXM < m <= self.mid.max_tokens:   # up to two slices the decode kernel is ahead
+            _lib.check(_lib.lib().b200moe_mid_forward(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(),
+                                                      self.mid.workspace.data_ptr(), self.mid.workspace.numel(), self.mid.max_tokens,
+                                                      torch.cuda.current_stream(x.device).cuda_stream), "mid forward")
             return out
         if self.prefill is not None and prefill_mode() != "slices":
             return self.prefill.forward(x, ids, wts, out)

@@ -24,6 +24,7 @@ def layer(name, scale_layout="linear"):
         seed = {"tiny": 3, "qwen": 0}.get(name, 21)
         _cache[key] = (cfg, *make_layer(cfg["experts"], cfg["hidden"], cfg["inter"], cfg["top_k"], seed=seed, scale_layout=scale_layout))
     _cache[key][1].prefill = None        # the layers are shared between tests: each test starts without the W4A4 path
+    _cache[key][1].mid = None            # ... and without the one-call W4A16 path for mid-sized batches
     _cache[key][1].set_decode_impl("auto")
     return _cache[key]
 
