@@ -155,6 +155,19 @@ class Weights:
             raise ValueError(f"the shared mid-batch workspace needs {nbytes} bytes of uint8")
         self.mid = SimpleNamespace(max_tokens=int(max_tokens), workspace=workspace)
 
+    def mid_workspace_bytes(self, max_tokens: int) -> int:
+        """Bytes of the mid-batch workspace for `max_tokens`; raises for shapes the one-call path does not take."""
+        n = int(_lib.lib().b200moe_mid_workspace_bytes(self._h, int(max_tokens)))
+        if n < 0:
+            _lib.check(n, "mid workspace")
+        return n
+
+    def prefill_workspace_bytes(self, max_tokens: int) -> int:
+        n = int(_lib.lib().b200moe_prefill_workspace_bytes(self._h, int(max_tokens)))
+        if n < 0:
+            _lib.check(n, "prefill workspace")
+        return n
+
     def mid_status(self) -> None:
         _lib.check(_lib.lib().b200moe_mid_status(self._h, _lib.ptr(self.mid.workspace), self.mid.max_tokens, _lib.stream_ptr()), "mid status")
 
@@ -195,13 +208,13 @@ class Weights:
                 if rc:
                     _lib.check(rc, "forward")
             return out
-        if self.mid is not None and 2 * MAXM < m <= self.mid.max_tokens:   # up to two slices the decode kernel is ahead
+        if self.prefill is not None and prefill_mode() != "slices":   # W4A4, as the reference's batches above 16 tokens in that mode
+            return self.prefill.forward(x, ids, wts, out)
+        if self.mid is not None and 2 * MAXM < m <= self.mid.max_tokens:   # W4A16 in one call; up to two slices the decode kernel is ahead
             _lib.check(_lib.lib().b200moe_mid_forward(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(),
                                                       self.mid.workspace.data_ptr(), self.mid.workspace.numel(), self.mid.max_tokens,
                                                       torch.cuda.current_stream(x.device).cuda_stream), "mid forward")
             return out
-        if self.prefill is not None and prefill_mode() != "slices":
-            return self.prefill.forward(x, ids, wts, out)
         for s in range(0, m, MAXM):
             e = min(m, s + MAXM)
             self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e])
@@ -278,6 +291,20 @@ class Weights:
     def expert_bytes(self) -> int:
         """Packed FP4 + scale bytes of one expert (sm120fp4/kernels/bench_moe_baseline.py:190-191)."""
         return 3 * self.I * self.H // 2 + 3 * self.I * self.H // 16
+
+
+_SHARED_WS: dict = {}
+
+
+def shared_workspace(kind: str, device, nbytes: int) -> torch.Tensor:
+    """One zeroed workspace per (kind, device) for all layers of a model: the prefill and mid-batch workspaces only hold
+    transient data of one layer call, and the layers of a model run one after the other on one stream."""
+    key = (kind, str(device))
+    t = _SHARED_WS.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
+        _SHARED_WS[key] = t
+    return t
 
 
 def weights_from_vllm_layout(w13: torch.Tensor, w13_scale: torch.Tensor, w13_scale_2: torch.Tensor, w2: torch.Tensor,

@@ -19,7 +19,8 @@ from vllm.model_executor.layers.fused_moe.activation import MoEActivation
 from vllm.model_executor.layers.fused_moe.fused_moe_method_base import FusedMoEMethodBase
 from vllm.model_executor.layers.quantization.modelopt import ModelOptNvFp4Config, ModelOptNvFp4FusedMoE
 
-from .vllm_backend import Weights, _log, prefill_explicit, prefill_mode, weights_from_vllm_layout
+from ._lib import B200MoEError
+from .vllm_backend import Weights, _log, prefill_explicit, prefill_mode, shared_workspace, weights_from_vllm_layout
 
 
 class ModelOptNvFp4FusedMoESM120(ModelOptNvFp4FusedMoE):
@@ -70,8 +71,13 @@ class ModelOptNvFp4FusedMoESM120(ModelOptNvFp4FusedMoE):
                 if prefill_explicit():
                     raise ValueError("SM120FP4_PREFILL=cutlass needs the checkpoint's w13_input_scale and w2_input_scale")
                 _log("no activation input scales in this checkpoint: batches above 16 tokens run as slices")
-            else:
-                w.enable_prefill(layer.w13_input_scale.data, layer.w2_input_scale.data)
+            else:   # one workspace for all layers of the model: it only holds transient data of one layer call
+                w.enable_prefill(layer.w13_input_scale.data, layer.w2_input_scale.data,
+                                 workspace=shared_workspace("prefill", w.q1.device, w.prefill_workspace_bytes(8192)))
+        try:        # 33 .. 256 tokens in one W4A16 call instead of slices of 16; shapes it does not take keep the slices
+            w.enable_mid(256, workspace=shared_workspace("mid", w.q1.device, w.mid_workspace_bytes(256)))
+        except B200MoEError:
+            pass
         for name, t in (("w13_weight", w.q1), ("w13_weight_scale", w.s1_linear.view(torch.float8_e4m3fn)), ("w13_weight_scale_2", w.alpha1),
                         ("w2_weight", w.q2), ("w2_weight_scale", w.s2_linear.view(torch.float8_e4m3fn)), ("w2_weight_scale_2", w.alpha2)):
             layer.register_parameter(name, torch.nn.Parameter(t, requires_grad=False))
