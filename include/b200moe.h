@@ -132,7 +132,7 @@ int b200moe_stream_probe(const void* buf, long long bytes, int pattern, int pitc
 /* W4A16 layer call for mid-sized batches (17 tokens up to a few hundred): the arithmetic of b200moe_decode_forward as a
  * grouped GEMM over per-expert gathered rows (four NVFP4 terms per token-expert pair), one pass over the touched experts'
  * weights instead of one per 16-token slice (the reference runs slices of 16, sm120fp4/vllm_backend.py:147-172). Needs
- * b200moe_layer_prepack and H, I <= 2304 (b200moe_mid_workspace_bytes returns the shape error otherwise); the workspace
+ * b200moe_layer_prepack and H, I <= 3072 (b200moe_mid_workspace_bytes returns the shape error otherwise); the workspace
  * (zeroed once) holds transient data of one call and can be shared by the layers of a stack. */
 long long b200moe_mid_workspace_bytes(const b200moe_layer* layer, int max_tokens);
 int b200moe_mid_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights, int M,

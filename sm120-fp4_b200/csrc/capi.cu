@@ -453,7 +453,7 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
 
 extern "C" long long b200moe_mid_workspace_bytes(const b200moe_layer* L, int max_tokens) {
   if (!L || max_tokens <= 0) return B200MOE_ERR_ARG;
-  if (L->KB1 > 9 || L->KB2 > 9) return B200MOE_ERR_SHAPE;   // the operand tile (KB records) plus three weight stages must fit in shared memory
+  if (L->KB1 > 12 || L->KB2 > 12) return B200MOE_ERR_SHAPE;   // the operand tile's scale columns (16 per K box) must fit in TMEM
   return b200_mid_workspace_bytes(L->E, L->H, L->I, L->top_k, max_tokens);
 }
 

@@ -25,10 +25,15 @@ namespace b200 {
 constexpr int kRec = 18432;          // one tile record: 16 KB codes image + 4 x 512 B scale tiles
 constexpr int kPfStages = 5;         // ring stages of two records (A, B) each
 constexpr int kPfThreads = 256;      // warps 0-3 epilogue, 4 MMA issuer, 5 scale copier, 6-7 TMA producers
+// W4A16 phases (3, 4): the operand tile holds 64 rows (16 token-expert pairs x four terms) in 10 KB records (8 KB codes
+// image + four 512-byte scale tiles whose row groups 2 and 3 stay zero). The MMA still spans 128 rows: rows 64..127 read
+// whatever follows the record in shared memory, with zero scales, and their accumulator rows are ignored. Half the
+// resident bytes leave room for a weight ring twice as deep, which is what a batch that touches every expert once needs.
+constexpr int kMidRec = 8192 + 2048;
 
 // ------------------------------------------------------------------------------------------------ plan
 // experts/offsets: the router's tables. One thread per touched expert: its rows are cut into tiles of rows_per_tile rows
-// (128 for the W4A4 GEMM; 32 for the W4A16 GEMM, whose tile holds four term rows per token-expert pair), the tiles of
+// (128 for the W4A4 GEMM; 16 for the W4A16 GEMM, whose 64-row tile holds four term rows per token-expert pair), the tiles of
 // all experts are numbered in expert order by a block-wide scan. Output: ntiles[0], and per tile its expert and the range
 // [tile_first, tile_end) of the expert's rows in `pairs` that it holds (the last tile of an expert is partly empty).
 __global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ experts, const int* __restrict__ offsets, int Umax, int max_tiles,
@@ -102,8 +107,8 @@ __global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------------------------------------ x -> W4A16 records
-// Mid-sized batches (17 tokens up to a few hundred) keep the decode path's W4A16 arithmetic but run as a grouped GEMM over
-// per-expert gathered rows: a tile of 128 operand rows holds 32 token-expert pairs x four NVFP4 terms of the pair's token
+// Mid-sized batches (33 tokens up to a few hundred) keep the decode path's W4A16 arithmetic but run as a grouped GEMM over
+// per-expert gathered rows: a tile of 64 operand rows holds 16 token-expert pairs x four NVFP4 terms of the pair's token
 // row (row 4p + t = term t of pair p), so that an expert's weight records are streamed once for all of its pairs.
 __global__ void __launch_bounds__(128) k_token_amax(const __nv_bfloat16* __restrict__ x, int H, float* __restrict__ amax) {
   __shared__ float wm[4];
@@ -124,17 +129,17 @@ __global__ void __launch_bounds__(128) k_token_amax(const __nv_bfloat16* __restr
 
 // One thread per 16-value block of a pair row: the block's four terms go to rows 4p..4p+3 of the tile's record. The thread
 // of a pair's first block also records the pair of the four rows (row_pair), their 1 / g_t (rowscale) and the pair's row in
-// the output of FC2 (dst_row = tile * 32 + p).
+// the output of FC2 (dst_row = tile * 16 + p).
 __global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __restrict__ x, const float* __restrict__ tok_amax,
                                                         const int* __restrict__ pairs, const int* __restrict__ tile_first,
                                                         const int* __restrict__ tile_end, const int* __restrict__ ntiles, int H, int KB,
                                                         int top_k, uint8_t* __restrict__ rec, int* __restrict__ row_pair,
                                                         float* __restrict__ rowscale, int* __restrict__ dst_row) {
   const unsigned per_row = (unsigned)KB * 16u;
-  const unsigned total = (unsigned)ntiles[0] * 32u * per_row;
+  const unsigned total = (unsigned)ntiles[0] * 16u * per_row;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const unsigned prow = i / per_row, b = i - prow * per_row;
-    const int t = (int)(prow >> 5), p = (int)(prow & 31);
+    const int t = (int)(prow >> 4), p = (int)(prow & 15);
     const int j = tile_first[t] + p;
     int pr = -1;
     if (j < tile_end[t]) pr = pairs[j];
@@ -144,11 +149,11 @@ __global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __r
       float g = g1;
 #pragma unroll
       for (int q = 0; q < kTerms; ++q) {
-        row_pair[t * 128 + 4 * p + q] = pr;
-        rowscale[t * 128 + 4 * p + q] = pr >= 0 ? 1.0f / g : 0.f;
+        row_pair[t * 64 + 4 * p + q] = pr;
+        rowscale[t * 64 + 4 * p + q] = pr >= 0 ? 1.0f / g : 0.f;
         g *= 6.0f;
       }
-      if (pr >= 0) dst_row[pr] = t * 32 + p;
+      if (pr >= 0) dst_row[pr] = t * 16 + p;
     }
     uint2 codes[kTerms];
     uint8_t sf[kTerms];
@@ -160,11 +165,12 @@ __global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __r
 #pragma unroll
       for (int q = 0; q < kTerms; ++q) { codes[q] = make_uint2(0u, 0u); sf[q] = 0; }
     }
-    uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kRec;
+    uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kMidRec;
 #pragma unroll
     for (int q = 0; q < kTerms; ++q) {
-      *reinterpret_cast<uint2*>(dst + rec_code_offset(4 * p + q, b & 15)) = codes[q];
-      dst[rec_scale_offset(4 * p + q, b & 15)] = sf[q];
+      const int r = 4 * p + q;   // < 64: row groups 0 and 1 of the scale tiles
+      *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b & 15)) = codes[q];
+      dst[8192 + ((b & 15) >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b & 3)] = sf[q];
     }
   }
 }
@@ -382,8 +388,11 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int KB = P.KB, NBLK = P.NBLK;
+  constexpr int kARec = PHASE >= 3 ? kMidRec : kRec;            // bytes of one operand record
+  constexpr int kACodes = PHASE >= 3 ? 8192 : 16384;            // ... of which codes; the scale tiles follow
+  constexpr int kARows = PHASE >= 3 ? 64 : 128;                 // operand rows per tile
   uint8_t* abuf = smem;                      // KB records of the current row tile
-  uint8_t* ring = smem + KB * kRec;          // NSB weight records
+  uint8_t* ring = smem + ((KB * kARec + 1023) & ~1023);   // NSB weight records
   PrShared& S = *reinterpret_cast<PrShared*>(ring + NSB * kRec);
   uint8_t* stage = ring + NSB * kRec + 1024;   // PHASE 2: eight 32-row x 144-byte patches for the epilogue's transposed stores
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -425,8 +434,8 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
       for_each_segment([&](int t, int, int, int ord) {
         for (int kb = 0; kb < KB; ++kb) {
           if (ord >= 1 && !mbar_wait(&S.a_empty[kb], (uint32_t)((ord - 1) & 1), &S.abort_flag)) *P.status = 2;
-          mbar_expect_tx(&S.a_full[kb], kRec);
-          bulk_load(abuf + kb * kRec, P.arec + ((long long)t * KB + kb) * kRec, kRec, &S.a_full[kb]);
+          mbar_expect_tx(&S.a_full[kb], kARec);
+          bulk_load(abuf + kb * kARec, P.arec + ((long long)t * KB + kb) * kARec, kARec, &S.a_full[kb]);
         }
       });
     }
@@ -449,7 +458,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   } else if (warp >= 8 && warp < 12) {
     // ============================================================== scale warps
     const uint32_t lane_base = (uint32_t)((warp - 8) * 32) << 16;
-    const uint32_t a_u = smem_u32(abuf) + 16384 + lane * 16, b_u = smem_u32(ring) + 16384 + lane * 16;
+    const uint32_t a_u = smem_u32(abuf) + kACodes + lane * 16, b_u = smem_u32(ring) + 16384 + lane * 16;
     auto put = [&](uint32_t src, uint32_t dst_col) {   // four 512-byte scale tiles -> 16 TMEM columns of this quadrant
       uint32_t r[16];
 #pragma unroll
@@ -469,7 +478,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         for (int kb = 0; kb < KB; ++kb) {
           if (n == n0) {
             if (!mbar_wait(&S.a_full[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 1;
-            put(a_u + kb * kRec, tm_sfa + 16 * kb);
+            put(a_u + kb * kARec, tm_sfa + 16 * kb);
             if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
           }
           if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
@@ -495,7 +504,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
           if (first && !mbar_wait(&S.a_sfr[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 8;
           if (!mbar_wait(&S.b_sfr[slot], ph, &S.abort_flag)) *P.status = 8;
           tc_fence_after();
-          const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kRec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
+          const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kARec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
           const int nkt = kb == KB - 1 ? nkt_last : 4;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
@@ -525,11 +534,11 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
       float s = P.alpha[P.tile_expert[t]] / gs_in;   // FC1: alpha / gs_in; FC2: that times the row's routing weight (0 on padding rows)
       int pr = -1;
       float rs = 0.f;   // W4A16 phases: 1 / g_t of this operand row's term
-      if (PHASE == 2 || PHASE == 4) {
-        pr = P.row_pair[(long long)t * 128 + row];
+      if (PHASE == 2 || (PHASE == 4 && row < kARows)) {
+        pr = P.row_pair[(long long)t * kARows + row];
         s = pr >= 0 ? s * P.wts[pr] : 0.f;
       }
-      if (PHASE == 3) rs = P.rowscale[(long long)t * 128 + row];
+      if (PHASE == 3 && row < kARows) rs = P.rowscale[(long long)t * kARows + row];
       if (PHASE == 4) {
         float g = P.act_g1;
         for (int q = 0; q < (lane & 3); ++q) g *= 6.0f;
@@ -563,11 +572,13 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             sfw |= (uint32_t)sb << (8 * bb);
           }
           *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+        } else if (PHASE >= 3 && quad >= 2) {
+          // accumulator rows 64..127 of the W4A16 phases belong to no operand row
         } else if (PHASE == 3) {
           // W4A16 FC1: rows 4p..4p+3 are the four terms of pair p; each scaled by its 1/g_t, the four lanes of a pair are
           // added (they then all hold the pair's up / gate values), SiLU*mul, and the pair's activations are expanded into
           // four terms again - lane t keeps term t, which is row 4p + t of FC2's operand record.
-          uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
+          uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kMidRec;
           uint32_t sfw = 0;
           uint32_t upr[2][16], gtr[2][16];
 #pragma unroll
@@ -599,7 +610,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = mc;
             sfw |= ms << (8 * bb);
           }
-          *reinterpret_cast<uint16_t*>(dst + 16384 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
+          *reinterpret_cast<uint16_t*>(dst + 8192 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
         } else if (PHASE == 4) {
           // W4A16 FC2: the four term rows of a pair are scaled and added; lane t of the pair stores columns 16t..16t+15 of
           // this warp's 64-column half, so the four lanes write one contiguous 128-byte segment of the pair's row.
@@ -607,7 +618,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
 #pragma unroll
           for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
           tmem_ld_wait();
-          float* yrow = P.yf + ((long long)t * 32 + (row >> 2)) * P.H + 128 * n + 64 * half + 16 * (lane & 3);
+          float* yrow = P.yf + ((long long)t * 16 + (row >> 2)) * P.H + 128 * n + 64 * half + 16 * (lane & 3);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             float o[16];
@@ -773,13 +784,14 @@ __global__ void k_set2(float* p, float a, float b) { p[0] = a; p[1] = b; }
 // exist for the resident-A kernel only.
 static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, cudaStream_t st) {
   const int tail = 1024 + ((phase == 2) ? 8 * 32 * 144 : 0);   // barriers (+ the W4A4 FC2 epilogue's store patches)
-  int nsb = (227 * 1024 - 1024 - tail - 256 - KB * kRec) / kRec;
+  const int abytes = (KB * (phase >= 3 ? kMidRec : kRec) + 1023) & ~1023;   // the resident operand tile
+  int nsb = (227 * 1024 - 1024 - tail - 256 - abytes) / kRec;
   const int tmem_cap = (512 - 256 - 16 * KB) / 16;
   if (nsb > tmem_cap) nsb = tmem_cap;
   if (nsb > 12) nsb = 12;
   const bool stream_a = getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1';
   if (KB <= 12 && nsb >= 3 && !(stream_a && phase <= 2)) {
-    const int sm_r = 1024 + (KB + nsb) * kRec + tail;
+    const int sm_r = 1024 + abytes + nsb * kRec + tail;
     const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : phase == 2 ? (const void*)k_prefill_gemm_r<2>
                    : phase == 3 ? (const void*)k_prefill_gemm_r<3> : (const void*)k_prefill_gemm_r<4>;
     static thread_local int configured_r[4] = {0, 0, 0, 0};
@@ -882,7 +894,7 @@ static MidLayout mid_layout(int E, int H, int I, int top_k, int max_tokens) {
   MidLayout L;
   const long long P = (long long)max_tokens * top_k;
   const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
-  L.max_tiles = (int)(P / 32 + E);
+  L.max_tiles = (int)(P / 16 + E);
   long long o = 0;
   L.experts = o, o = pf_align(o + 4LL * E);
   L.offsets = o, o = pf_align(o + 4LL * (E + 1));
@@ -891,14 +903,14 @@ static MidLayout mid_layout(int E, int H, int I, int top_k, int max_tokens) {
   L.ntiles = o, o += 256;
   L.tile_expert = o, o = pf_align(o + 4LL * L.max_tiles);
   L.tile_tab = o, o = pf_align(o + 8LL * L.max_tiles);
-  L.row_pair = o, o = pf_align(o + 4LL * L.max_tiles * 128);
-  L.rowscale = o, o = pf_align(o + 4LL * L.max_tiles * 128);
+  L.row_pair = o, o = pf_align(o + 4LL * L.max_tiles * 64);
+  L.rowscale = o, o = pf_align(o + 4LL * L.max_tiles * 64);
   L.dst_row = o, o = pf_align(o + 4 * P);
   L.tok_amax = o, o = pf_align(o + 4LL * max_tokens);
   L.status = o, o += 256;
-  L.xrec = o, o = pf_align(o + (long long)L.max_tiles * KB1 * kRec);
-  L.arec = o, o = pf_align(o + (long long)L.max_tiles * KB2 * kRec);
-  L.y = o, o = pf_align(o + (long long)L.max_tiles * 32 * H * 4);
+  L.xrec = o, o = pf_align(o + (long long)L.max_tiles * KB1 * kMidRec);
+  L.arec = o, o = pf_align(o + (long long)L.max_tiles * KB2 * kMidRec);
+  L.y = o, o = pf_align(o + (long long)L.max_tiles * 16 * H * 4);
   L.total = o;
   return L;
 }
@@ -933,9 +945,9 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
   B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
-  const int max_tiles = P / 32 + Umax;
+  const int max_tiles = P / 16 + Umax;
   int* tile_end = tile_first + max_tiles;
-  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 32, ntiles, tile_expert, tile_first, tile_end);
+  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 16, ntiles, tile_expert, tile_first, tile_end);
   B200_LAUNCH_CHECK();
   k_token_amax<<<M, 128, 0, st>>>((const __nv_bfloat16*)x, H, tok_amax);
   B200_LAUNCH_CHECK();
@@ -946,6 +958,7 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   memset(&p, 0, sizeof(p));
   p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = (int*)(w + L.status), p.H = H;
   p.rowscale = rowscale, p.act_g1 = act_g1;
+  p.dbg = getenv("B200MOE_PF_DEBUG") ? atoi(getenv("B200MOE_PF_DEBUG")) : 0;
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
