@@ -575,11 +575,12 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         } else if (PHASE >= 3 && quad >= 2) {
           // accumulator rows 64..127 of the W4A16 phases belong to no operand row
         } else if (PHASE == 3) {
-          // W4A16 FC1: rows 4p..4p+3 are the four terms of pair p; each scaled by its 1/g_t, the four lanes of a pair are
-          // added (they then all hold the pair's up / gate values), SiLU*mul, and the pair's activations are expanded into
-          // four terms again - lane t keeps term t, which is row 4p + t of FC2's operand record.
+          // W4A16 FC1: rows 4p..4p+3 are the four terms of pair p, each scaled by its 1/g_t. This warp holds two 16-column
+          // blocks of the pair; lanes 0,1 of the pair's four end up with the sums of the first block and lanes 2,3 with
+          // those of the second (an exchange across the lane pairs, then one add inside them), so that SiLU*mul and the
+          // expansion of the activations into four terms run once per block: the even lane of each lane pair does it
+          // and writes all four term rows 4p..4p+3 of FC2's operand record.
           uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kMidRec;
-          uint32_t sfw = 0;
           uint32_t upr[2][16], gtr[2][16];
 #pragma unroll
           for (int bb = 0; bb < 2; ++bb) {
@@ -587,30 +588,31 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             tmem_ld_32x32b_x16(taddr + 64 + 16 * (2 * half + bb), gtr[bb]);
           }
           tmem_ld_wait();
-          const int tq = lane & 3;
+          const int tq = lane & 3, bsel = tq >> 1;
+          float a[16];
 #pragma unroll
-          for (int bb = 0; bb < 2; ++bb) {
-            const int blk = 2 * half + bb;
-            float a[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float u = __uint_as_float(upr[bb][i]) * rs, g = __uint_as_float(gtr[bb][i]) * rs;
-              u += __shfl_xor_sync(0xffffffffu, u, 1);
-              g += __shfl_xor_sync(0xffffffffu, g, 1);
-              u += __shfl_xor_sync(0xffffffffu, u, 2);
-              g += __shfl_xor_sync(0xffffffffu, g, 2);
-              g *= s, u *= s;
-              a[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
-            }
+          for (int i = 0; i < 16; ++i) {
+            const float u0 = __uint_as_float(upr[0][i]) * rs, u1 = __uint_as_float(upr[1][i]) * rs;
+            const float g0 = __uint_as_float(gtr[0][i]) * rs, g1v = __uint_as_float(gtr[1][i]) * rs;
+            float ku = bsel ? u1 : u0, kg = bsel ? g1v : g0;
+            ku += __shfl_xor_sync(0xffffffffu, bsel ? u0 : u1, 2);   // the lane two over keeps the other block and sends this one
+            kg += __shfl_xor_sync(0xffffffffu, bsel ? g0 : g1v, 2);
+            ku += __shfl_xor_sync(0xffffffffu, ku, 1);
+            kg += __shfl_xor_sync(0xffffffffu, kg, 1);
+            kg *= s, ku *= s;
+            a[i] = __fdividef(kg, 1.0f + __expf(-kg)) * ku;
+          }
+          if ((tq & 1) == 0) {
             uint2 codes[kTerms];
             uint8_t sf[kTerms];
             expand_block16(a, P.act_g1, codes, sf);
-            const uint2 mc = tq == 0 ? codes[0] : tq == 1 ? codes[1] : tq == 2 ? codes[2] : codes[3];
-            const uint32_t ms = tq == 0 ? sf[0] : tq == 1 ? sf[1] : tq == 2 ? sf[2] : sf[3];
-            *reinterpret_cast<uint2*>(dst + rec_code_offset(row, 4 * (n & 3) + blk)) = mc;
-            sfw |= ms << (8 * bb);
+            const int blk = 2 * half + bsel, r0 = row & ~3;
+#pragma unroll
+            for (int q = 0; q < kTerms; ++q) {
+              *reinterpret_cast<uint2*>(dst + rec_code_offset(r0 + q, 4 * (n & 3) + blk)) = codes[q];
+              dst[8192 + (n & 3) * 512 + ((r0 + q) & 31) * 16 + ((r0 + q) >> 5) * 4 + blk] = sf[q];
+            }
           }
-          *reinterpret_cast<uint16_t*>(dst + 8192 + (n & 3) * 512 + (row & 31) * 16 + (row >> 5) * 4 + 2 * half) = (uint16_t)sfw;
         } else if (PHASE == 4) {
           // W4A16 FC2: the four term rows of a pair are scaled and added; lane t of the pair stores columns 16t..16t+15 of
           // this warp's 64-column half, so the four lanes write one contiguous 128-byte segment of the pair's row.
