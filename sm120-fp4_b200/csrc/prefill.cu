@@ -620,21 +620,24 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
 #pragma unroll
           for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, r[c]);
           tmem_ld_wait();
-          float* yrow = P.yf + ((long long)t * 16 + (row >> 2)) * P.H + 128 * n + 64 * half + 16 * (lane & 3);
+          // reduce-scatter over the pair's four lanes: lane tq ends up with the sums of chunk tq only
+          const int tq = lane & 3, hi = tq >> 1, lo = tq & 1;
+          float o[16];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float o[16];
+          for (int i = 0; i < 16; ++i) {
+            float k2[2];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float v0 = __uint_as_float(r[c][i]) * rs;
-              v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
-              v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
-              o[i] = v0 * s;
+            for (int j = 0; j < 2; ++j) {
+              const float mine = __uint_as_float(hi ? r[2 + j][i] : r[j][i]) * rs, other = __uint_as_float(hi ? r[j][i] : r[2 + j][i]) * rs;
+              k2[j] = mine + __shfl_xor_sync(0xffffffffu, other, 2);   // the lane two over keeps the other two chunks and sends these
             }
-            if ((lane & 3) == c && pr >= 0) {
+            const float keep = lo ? k2[1] : k2[0], send = lo ? k2[0] : k2[1];
+            o[i] = (keep + __shfl_xor_sync(0xffffffffu, send, 1)) * s;
+          }
+          if (pr >= 0) {
+            float* yrow = P.yf + ((long long)t * 16 + (row >> 2)) * P.H + 128 * n + 64 * half + 16 * tq;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(yrow + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-            }
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(yrow + 4 * i) = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
           }
         } else {
           // This thread holds 64 bf16 of its row (128 bytes); the warp transposes its 32 x 128-byte block through its own
