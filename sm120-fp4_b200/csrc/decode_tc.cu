@@ -266,7 +266,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
   const int n1 = nu1 * KB1;
-  const int uA = (7 * U) / 8, qA = uA * CB1;
+  // With a single round of FC1 units (Q1 <= V) everything finishes together: gate A would open with gate B, so it is
+  // left out (no arrivals, nobody waits) and all of FC2 waits for gate B.
+  const bool use_gate_a = Q1 > V;
+  const int uA = use_gate_a ? (7 * U) / 8 : 0, qA = uA * CB1;
   const int nuA = v < qA ? (qA - v + V - 1) / V : 0;   // this worker's units of group A (its first ones)
   const int I2 = U * KB2;
   const int Wb = V / NB2, Wx = V % NB2;                // groups 0..Wx-1 have Wb + 1 workers
@@ -299,7 +302,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
         mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
         bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
       }
-      bool passed[2] = {false, false};
+      bool passed[2] = {!use_gate_a, false};
       int pend_slot[16], pend_idx[16], pend_g[16] = {0}, npend = 0, pend_head = 0;   // ring of 16: at most NS (<= 12) entries wait at a time
       int slot_g[12];                                                          // gate of the FC2 tile in each ring slot
       auto load_slab = [&](int slot, int idx) {   // activation slab (u, kb) of FC2: N x 128 B codes image + 4 scale tiles
@@ -610,7 +613,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
 
     // ---- FC1 pieces
     {
-      if (nuA == 0) arrive_gate(0);
+      if (use_gate_a && nuA == 0) arrive_gate(0);
       if (nu1 == 0) arrive_gate(1);
       for (int t = 0; t < nu1; ++t) {
         const int q = v + t * V, u = q / CB1, cb = q - u * CB1;   // a whole unit: K boxes 0..KB1-1 of (expert u, block cb)
@@ -674,7 +677,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           named_bar_sync(1, 128);
         }
         TC_ADD(tm_b, tfix);
-        if (t == nuA - 1) arrive_gate(0);
+        if (use_gate_a && t == nuA - 1) arrive_gate(0);
         if (t == nu1 - 1) arrive_gate(1);
       }
 #ifdef B200_TIMERS
