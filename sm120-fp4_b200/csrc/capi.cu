@@ -209,7 +209,7 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   p.scratch = (float*)(w + L->off_scratch);
   p.cnt1 = (unsigned*)(w + L->off_cnt1), p.cnt2 = (unsigned*)(w + L->off_cnt2);
   p.status = (int*)(w + L->off_status);
-  p.gridbar = (unsigned*)(w + L->off_status + 64);
+  p.gates = (unsigned long long*)(w + L->off_status + 128);
   p.experts_out = (int*)(w + L->off_tables);
   p.offsets_out = p.experts_out + L->umax_cap;
   p.pairs_out = p.offsets_out + L->umax_cap + 1;

@@ -56,7 +56,7 @@ struct DecodeTcParams {
   float* scratch;
   unsigned* cnt1;
   unsigned* cnt2;
-  unsigned* gridbar;
+  unsigned long long* gates; // workspace: arrival counters of the two FC1 gates; only ever incremented, V per launch and gate
   int* status;
   int* experts_out;
   int* offsets_out;

@@ -39,7 +39,7 @@ struct TcTables {
   float colscale[64];          // 1 / g_t of every B column of the FC1 operand (token-major, four terms per token)
   float a1[kTcMaxE], a2n[kTcMaxE];   // per touched expert (unit index): alpha1, alpha2 relative to the layer's largest alpha2
   int U;
-  unsigned gen0[2];           // generation words of the two FC1 gates as found at kernel entry
+  unsigned long long gate0[2];   // arrival counts of the two FC1 gates before this launch (a multiple of the worker count)
   volatile int abort_flag;
   int last_flag;
   uint32_t tmem_base;
@@ -195,9 +195,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   float my_w = 0.f, my_a1 = 0.f, my_a2 = 0.f;
   if (tid < npairs) { my_e = P.ids[tid]; my_w = P.wts[tid]; }
   const float a2inv = P.alpha2_ref[1];
-  unsigned my_gen = 0;
-  if (tid == 9 * 32) my_gen = ld_acquire_gpu(P.gridbar + 1);    // generation words of the two FC1 gates as this launch finds them
-  if (tid == 10 * 32) my_gen = ld_acquire_gpu(P.gridbar + 3);
+  // The gate counters are only ever incremented, by exactly V arrivals per launch and gate, and a launch starts after the
+  // gates of the launch before it on this workspace have opened: whatever this thread reads, rounding down to a multiple of
+  // V gives the count before this launch (other workers of this launch may have arrived already).
+  unsigned long long my_gate = 0;
+  if (tid == 9 * 32) my_gate = ld_acquire_gpu_u64(P.gates);
+  if (tid == 10 * 32) my_gate = ld_acquire_gpu_u64(P.gates + 1);
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) { mbar_init(&T.full[s], 1); mbar_init(&T.empty[s], 1); mbar_init(&T.sfr[s], 4); }
     for (int b = 0; b < 2; ++b) { mbar_init(&T.acc_full[b], 1); mbar_init(&T.acc_empty[b], 4); }
@@ -247,8 +250,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     T.a1[u] = my_a1;
     T.a2n[u] = my_a2 * a2inv;
   }
-  if (tid == 9 * 32) T.gen0[0] = my_gen;
-  if (tid == 10 * 32) T.gen0[1] = my_gen;
+  if (tid == 9 * 32) T.gate0[0] = my_gate - my_gate % (unsigned long long)V;
+  if (tid == 10 * 32) T.gate0[1] = my_gate - my_gate % (unsigned long long)V;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -324,7 +327,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
           if (passed[gg]) continue;
           bool ok = false;
           for (uint32_t it = 0; it < (1u << 24); ++it) {
-            if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) { ok = true; break; }
+            if (ld_acquire_gpu_u64(P.gates + gg) - T.gate0[gg] >= (unsigned long long)V) { ok = true; break; }
             if (T.abort_flag) break;
           }
           if (!ok) { T.abort_flag = 1; *P.status = 3; }
@@ -336,7 +339,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       auto peek_gate = [&](int g) {   // one look, no waiting: gates usually opened long before the tile that needs them is issued
         if (!local_ok && mbar_test_wait(&T.fc1_done, 0)) local_ok = true;
         for (int gg = 0; gg <= g && !passed[gg]; ++gg)
-          if (ld_acquire_gpu(P.gridbar + 2 * gg + 1) != T.gen0[gg]) { passed[gg] = true; fence_proxy_async(); }
+          if (ld_acquire_gpu_u64(P.gates + gg) - T.gate0[gg] >= (unsigned long long)V) { passed[gg] = true; fence_proxy_async(); }
           else break;
         flush();
       };
@@ -602,13 +605,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     auto arrive_gate = [&](int g) {
       fence_proxy_async();
       named_bar_sync(1, 128);
-      if (et == 0) {
-        const unsigned old = atom_add_acq_rel_gpu(P.gridbar + 2 * g, 1u);
-        if (old == (unsigned)(V - 1)) {
-          P.gridbar[2 * g] = 0;
-          atom_add_acq_rel_gpu(P.gridbar + 2 * g + 1, 1u);   // opens the gate; ordered after every arrival it acquired
-        }
-      }
+      if (et == 0) red_add_release_gpu_u64(P.gates + g, 1ull);   // nothing to wait for: the gate is open when V have arrived
     };
 
     // ---- FC1 pieces

@@ -169,4 +169,14 @@ __device__ __forceinline__ unsigned atom_add_acq_rel_gpu(unsigned* p, unsigned v
   return old;
 }
 
+// Arrival counters that are never reset: fire-and-forget add that releases the earlier writes, and the acquiring read.
+__device__ __forceinline__ void red_add_release_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
 }  // namespace b200
