@@ -541,17 +541,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       if (tm_d == 0) tm_d = clock64() - tm_begin;   // first accumulator ready
 #endif
       tc_fence_after();
+      uint32_t r[NB][16];   // all columns in flight before the one wait
 #pragma unroll
-      for (int c0 = 0; c0 < N; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld_32x32b_x16(tm_acc + 64 * ab + ((uint32_t)(quad * 32) << 16) + c0, r);
-        tmem_ld_wait();
+      for (int c = 0; c < NB; ++c) tmem_ld_32x32b_x16(tm_acc + 64 * ab + ((uint32_t)(quad * 32) << 16) + 16 * c, r[c]);
+      tmem_ld_wait();
 #pragma unroll
-        for (int tk = 0; tk < 4; ++tk)
-        {
-          const int o = per_column ? c0 + 4 * tk : 0;
-          val[c0 / 4 + tk] = __uint_as_float(r[4 * tk]) * cs[o] + __uint_as_float(r[4 * tk + 1]) * cs[o + 1] +
-                             __uint_as_float(r[4 * tk + 2]) * cs[o + 2] + __uint_as_float(r[4 * tk + 3]) * cs[o + 3];
+      for (int c = 0; c < NB; ++c) {
+#pragma unroll
+        for (int tk = 0; tk < 4; ++tk) {
+          const int o = per_column ? 16 * c + 4 * tk : 0;
+          val[4 * c + tk] = __uint_as_float(r[c][4 * tk]) * cs[o] + __uint_as_float(r[c][4 * tk + 1]) * cs[o + 1] +
+                            __uint_as_float(r[c][4 * tk + 2]) * cs[o + 2] + __uint_as_float(r[c][4 * tk + 3]) * cs[o + 3];
         }
       }
 #pragma unroll
