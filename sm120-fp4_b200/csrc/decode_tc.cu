@@ -269,9 +269,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const int Q1 = U * CB1;
   const int nu1 = v < Q1 ? (Q1 - v + V - 1) / V : 0;
   const int n1 = nu1 * KB1;
-  // With a single round of FC1 units (Q1 <= V) everything finishes together: gate A would open with gate B, so it is
-  // left out (no arrivals, nobody waits) and all of FC2 waits for gate B.
-  const bool use_gate_a = Q1 > V;
+  // With at most two rounds of FC1 units (Q1 <= 2V) gate A would open hardly before gate B, so it is left out (no
+  // arrivals, nobody waits) and all of FC2 waits for gate B.
+  const bool use_gate_a = Q1 > 2 * V;
   const int uA = use_gate_a ? (7 * U) / 8 : 0, qA = uA * CB1;
   const int nuA = v < qA ? (qA - v + V - 1) / V : 0;   // this worker's units of group A (its first ones)
   const int I2 = U * KB2;
