@@ -141,10 +141,11 @@ class Weights:
 
     enable_cutlass_prefill = enable_prefill   # the reference's name for the same switch
 
-    def enable_mid(self, max_tokens: int = 256, workspace: torch.Tensor | None = None) -> None:
+    def enable_mid(self, max_tokens: int = 256, workspace: torch.Tensor | None = None, min_tokens: int = 2 * MAXM + 1) -> None:
         """Batches of 33..max_tokens tokens run as ONE W4A16 call (the decode arithmetic, a grouped GEMM over per-expert
         gathered rows) instead of slices of 16 that each stream the touched experts again. `workspace`: a zeroed uint8
-        tensor to share between the layers of a stack (transient data of one call); allocated here when None."""
+        tensor to share between the layers of a stack (transient data of one call); allocated here when None. `min_tokens`:
+        first batch size that takes this path (an expert-parallel shard with few local experts gains from 17 on)."""
         h = _lib.lib()
         nbytes = int(h.b200moe_mid_workspace_bytes(self._h, int(max_tokens)))
         if nbytes < 0:
@@ -153,7 +154,7 @@ class Weights:
             workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device)
         elif workspace.numel() < nbytes or workspace.dtype != torch.uint8:
             raise ValueError(f"the shared mid-batch workspace needs {nbytes} bytes of uint8")
-        self.mid = SimpleNamespace(max_tokens=int(max_tokens), workspace=workspace)
+        self.mid = SimpleNamespace(max_tokens=int(max_tokens), min_tokens=max(int(min_tokens), MAXM + 1), workspace=workspace)
 
     def mid_workspace_bytes(self, max_tokens: int) -> int:
         """Bytes of the mid-batch workspace for `max_tokens`; raises for shapes the one-call path does not take."""
@@ -210,7 +211,7 @@ class Weights:
             return out
         if self.prefill is not None and prefill_mode() != "slices":   # W4A4, as the reference's batches above 16 tokens in that mode
             return self.prefill.forward(x, ids, wts, out)
-        if self.mid is not None and 2 * MAXM < m <= self.mid.max_tokens:   # W4A16 in one call; up to two slices the decode kernel is ahead
+        if self.mid is not None and self.mid.min_tokens <= m <= self.mid.max_tokens:   # W4A16 in one call (by default from 33 tokens: up to two slices of a full layer the decode kernel is ahead)
             _lib.check(_lib.lib().b200moe_mid_forward(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(),
                                                       self.mid.workspace.data_ptr(), self.mid.workspace.numel(), self.mid.max_tokens,
                                                       torch.cuda.current_stream(x.device).cuda_stream), "mid forward")
