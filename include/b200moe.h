@@ -21,6 +21,8 @@ extern "C" {
 #define B200MOE_ERR_TIMEOUT (-5)   /* a bounded device-side wait ran out */
 #define B200MOE_ERR_WORKSPACE (-6) /* workspace too small */
 #define B200MOE_ERR_LIMIT (-7)     /* size beyond a stated maximum */
+#define B200MOE_ERR_RANGE (-8)     /* an FC1 activation exceeded the range of the activation scale and was clipped */
+#define B200MOE_ERR_ORDER (-9)     /* topk_ids / topk_weights changed while the call was running */
 
 typedef struct b200moe_layer b200moe_layer; /* opaque decode-layer handle (host memory) */
 
@@ -51,6 +53,10 @@ int b200moe_quantize_nvfp4(const void* x, int dtype, const int* src_row, int row
 long long b200moe_route_workspace_bytes(int P, int E);
 int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* workspace,
                   long long workspace_bytes, void* stream);
+/* An id >= E is skipped (its pair appears in no table) and raises a flag in the workspace; this reads the flag of the last
+ * call that used `workspace` with the same P and E: 0 or B200MOE_ERR_ARG (the reference's router has no such check: its
+ * ids come straight from top-k, sm120fp4/kernels/moe_w4a16.py:48-83). Synchronises the stream. */
+int b200moe_route_status(const void* workspace, int P, int E, void* stream);
 
 /* Router for hosts that cannot provide scratch memory (no counterpart in the reference). Identical tables to b200moe_route,
  * but the intermediate histograms sit in a fixed array inside the library (about 129 KiB per GPU that loads it), so the call
@@ -59,6 +65,8 @@ int b200moe_route(const int* ids, int P, int E, int Umax, int* experts, int* off
  * (B200MOE_ERR_LIMIT beyond). The first call on each device looks up the array's device address - issue it before any
  * stream capture. Calls on one device share the array: do not let two of them overlap on the GPU. */
 int b200moe_route_static(const int* ids, int P, int E, int Umax, int* experts, int* offsets, int* pairs, void* stream);
+/* bad-id flag of the last b200moe_route_static call on the current device (same P, E); synchronises, allocates nothing */
+int b200moe_route_static_status(int P, int E, void* stream);
 
 /* ---- decode layer (M <= 16 tokens, W4A16): sm120fp4/vllm_backend.py:95-121 (Weights) and :147-190 (forward/_slice).
  * q1 u8 [E, 2I, H/2] rows [up ; gate]; s1 u8 [E, pad128(2I) * pad4(H/16)] 128x4-swizzled per expert; q2 u8 [E, H, I/2];
@@ -79,6 +87,10 @@ int b200moe_layer_sm_count(const b200moe_layer* layer);
 long long b200moe_layer_prepack_bytes(const b200moe_layer* layer);
 int b200moe_layer_prepack(b200moe_layer* layer, void* buffer, long long buffer_bytes, void* stream);
 int b200moe_layer_set_decode_impl(b200moe_layer* layer, int impl);
+/* Forget the checkpoint-layout codes and scales (the caller may free them): from then on only the tcgen05 paths run; the
+ * mma.sync kernel and b200moe_decode_fc1 / _fc2 return B200MOE_ERR_ARG. Needs b200moe_layer_prepack. The reference keeps a
+ * single copy of the weights too: its load-time re-layout is in place (sm120fp4/vllm_backend.py:193-206). */
+int b200moe_layer_release_checkpoint(b200moe_layer* layer);
 int b200moe_layer_set_act_scale(b200moe_layer* layer, float first_term_global_scale);
 
 /* ---- W4A4 prefill for any M <= max_tokens: the layer's own tcgen05 kind::mxf4nvf4 grouped GEMM in place of the reference's
@@ -90,11 +102,28 @@ int b200moe_prefill_forward(const b200moe_layer* layer, const void* x_bf16, cons
                             void* out_bf16, void* workspace, long long workspace_bytes, int max_tokens, float gs_x, float gs_a,
                             void* stream);
 int b200moe_prefill_status(const b200moe_layer* layer, const void* workspace, int max_tokens, void* stream);
+/* Byte offsets inside a prefill workspace sized for max_tokens, so that a tool or a test can read back what each stage of the
+ * last call wrote (the reference exposes its intermediates the same way, as tensors: sm120fp4/kernels/bench_moe_baseline.py:
+ * 53-74 returns them from `reference`). out14 = experts, offsets, pairs (router tables), ntiles, tile_expert, tile_first,
+ * tile_end (128-row tiles: expert, first and end index into pairs), row_pair [tiles*128], dst_row [pairs], x records,
+ * activation records, weighted bf16 rows, tile capacity, total bytes. A record is 18,432 bytes per (tile, 256-value K box):
+ * row r, 16-value block b at r*128 + (((b>>1) ^ (r&7)) << 4) + (b&1)*8 (8 code bytes), its scale byte at 16384 + (b>>2)*512 +
+ * (r&31)*16 + (r>>5)*4 + (b&3) - i.e. four 128x4 scale tiles. */
+int b200moe_prefill_workspace_map(const b200moe_layer* layer, int max_tokens, long long* out14);
 
 /* forward: x bf16 [M, H], topk_ids i32 [M, top_k], topk_weights f32 [M, top_k] -> out bf16 [M, H]; one launch
  * (routing + FC1 + SiLU*mul + FC2 + weighted combine). Replaces Weights._slice, sm120fp4/vllm_backend.py:174-190. */
 int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                            int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream);
+/* The same with flags. B200MOE_ORDERED: the two kernels of the call are ordinary stream-ordered launches. By default they are
+ * launched programmatically, so that the call's prologue and weight stream overlap the tail of whatever precedes it in
+ * the stream, and topk_ids / topk_weights are read at kernel entry: they must be complete when the kernel BEFORE this call
+ * starts (true for any producer that does not itself release its successors early). A violation is detected (the inputs are
+ * re-read after the stream dependency has resolved) and reported by b200moe_layer_status as B200MOE_ERR_ORDER. This is the
+ * per-call form of the reference's module-wide switches fc1_set_pdl / fc2_set_pdl (sm120fp4/vllm_backend.py:174-190). */
+#define B200MOE_ORDERED 1
+int b200moe_decode_forward_ex(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,
+                              int M, void* out_bf16, void* workspace, long long workspace_bytes, int flags, void* stream);
 /* b200moe_decode_forward for a caller whose tensors live in host memory: x bf16 [M, H], ids int32 [M, top_k], weights f32
  * [M, top_k] in, out bf16 [M, H] back. Page-locked buffers are read and written by the kernels directly across the host
  * link (no copy is enqueued); pageable buffers go through staging buffers inside the workspace. Everything is enqueued on
@@ -112,15 +141,17 @@ int b200moe_decode_fc2(const b200moe_layer* layer, const void* act_bf16, const i
 /* routing tables written by the last decode call, in the router's padded form (device-to-device copies on stream) */
 int b200moe_layer_route_tables(const b200moe_layer* layer, const void* workspace, int M, int* experts, int* offsets,
                                int* pairs, void* stream);
-/* status word of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT or B200MOE_ERR_ARG (bad expert id) */
+/* status words of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT, B200MOE_ERR_ARG (bad expert id),
+ * B200MOE_ERR_ORDER (routing inputs changed under the call) or B200MOE_ERR_RANGE (an FC1 activation above 2688 / act scale
+ * was clipped; the last two are cleared by the read) */
 int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void* stream);
 
 /* single-tile check of the tcgen05 building blocks (TMEM, descriptors, scale copies, kind::mxf4nvf4 MMA): d f32 [128, N]
  * = dequant(a)[128, K] x dequant(b)[N, K]^T with 128x4-swizzled block scales; N % 16 == 0 <= 128, K % 256 == 0 <= 1024.
- * knobs: null, or 8 host uint32 overriding the descriptor fields (unit-test use). The arithmetic it checks is the
- * reference GEMM of sm120fp4/reference.py:133-137. */
+ * scale_path: 0 = block scales into TMEM by tcgen05.cp, 1 = through registers (tcgen05.st); anything else is rejected. The
+ * arithmetic it checks is the reference GEMM of sm120fp4/reference.py:133-137. */
 int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
-                       const unsigned* knobs, int* status_dev, void* stream);
+                       int scale_path, int* status_dev, void* stream);
 
 /* HBM streaming floor of the kernels' access patterns, no math (the reference's k_stream probe,
  * sm120fp4/kernels/micro_floor.py:59-95): pattern 0 = 128-byte x box_rows TMA boxes from a row-major matrix of `pitch`
@@ -156,18 +187,6 @@ int b200moe_ep_plan(const int* ids, int m, int k, int world, int experts_per_ran
 int b200moe_ep_gather(const void* x, const int* ids, const float* wts, const int* send_tok, const int* offsets, int h, int k, int world,
                       int experts_per_rank, int max_rows, void* sx, int* meta, void* stream);
 int b200moe_ep_combine_rows(const void* back, const int* pos, int m, int h, int world, void* out, void* stream);
-
-/* issue-cost measurement of tcgen05 scale copies and MMAs (diagnostic; no counterpart in the reference): cycles_dev[0] =
- * cycles to issue `reps` rounds of {ncp copies, nmma MMAs 128 x N x 64, ncommit commits}, cycles_dev[1] = cycles until all completed
- * (device int64 x 4; [2], [3] = the same for the second issuing thread). flags: 1 two accumulators, 2 wait on a completed
- * mbarrier every round, 4 tcgen05 fence every round, 8 wait for the round's own commit, 16 copies from a second thread,
- * 32 converged warps with one elected lane instead of single diverged threads. */
-int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int flags, int ncommit, long long* cycles_dev, void* stream);
-
-/* per-worker cycle counters of the last decode launch (8 int64 per worker: consumer wait, math, fix-up, phase-1 end,
- * producer wait, producer grid wait, producer end, consumer end). Filled only by a library built with -DB200_TIMERS (a
- * diagnostic build; the reference has no counterpart); returns the number of workers copied. Synchronises the stream. */
-int b200moe_layer_debug_counters(const b200moe_layer* layer, const void* workspace, long long* out, int max_workers, void* stream);
 
 #ifdef __cplusplus
 }

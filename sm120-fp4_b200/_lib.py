@@ -9,7 +9,7 @@ _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libb200moe.so"
 _lib = None
 
-ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_WORKSPACE, ERR_LIMIT = -1, -2, -3, -4, -5, -6, -7
+ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_WORKSPACE, ERR_LIMIT, ERR_RANGE, ERR_ORDER = -1, -2, -3, -4, -5, -6, -7, -8, -9
 
 _P, _I, _LL = C.c_void_p, C.c_int, C.c_longlong
 SIGNATURES = {
@@ -23,7 +23,9 @@ SIGNATURES = {
     "b200moe_quantize_nvfp4": (_I, [_P, _I, _P, _I, _I, _P, _I, _P, _P, _I, _P]),
     "b200moe_route_workspace_bytes": (_LL, [_I, _I]),
     "b200moe_route": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _LL, _P]),
+    "b200moe_route_status": (_I, [_P, _I, _I, _P]),
     "b200moe_route_static": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "b200moe_route_static_status": (_I, [_I, _I, _P]),
     "b200moe_layer_create": (_I, [C.POINTER(_P), _I, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "b200moe_layer_destroy": (None, [_P]),
     "b200moe_layer_workspace_bytes": (_LL, [_P]),
@@ -32,19 +34,20 @@ SIGNATURES = {
     "b200moe_layer_prepack_bytes": (_LL, [_P]),
     "b200moe_layer_prepack": (_I, [_P, _P, _LL, _P]),
     "b200moe_layer_set_decode_impl": (_I, [_P, _I]),
+    "b200moe_layer_release_checkpoint": (_I, [_P]),
     "b200moe_layer_set_act_scale": (_I, [_P, C.c_float]),
     "b200moe_prefill_workspace_bytes": (_LL, [_P, _I]),
     "b200moe_prefill_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, C.c_float, C.c_float, _P]),
     "b200moe_prefill_status": (_I, [_P, _P, _I, _P]),
+    "b200moe_prefill_workspace_map": (_I, [_P, _I, _P]),
     "b200moe_decode_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
+    "b200moe_decode_forward_ex": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, _P]),
     "b200moe_decode_forward_host": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc1": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_decode_fc2": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _P]),
     "b200moe_layer_route_tables": (_I, [_P, _P, _I, _P, _P, _P, _P]),
     "b200moe_layer_status": (_I, [_P, _P, _P]),
-    "b200moe_layer_debug_counters": (_I, [_P, _P, _P, _I, _P]),
     "b200moe_stream_probe": (_I, [_P, _LL, _I, _I, _I, _I, _I, _I, _P, _P]),
-    "b200moe_umma_cost": (_I, [_I, _I, _I, _I, _I, _I, _P, _P]),
     "b200moe_mid_workspace_bytes": (_LL, [_P, _I]),
     "b200moe_mid_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, _P]),
     "b200moe_mid_status": (_I, [_P, _P, _I, _P]),
@@ -53,7 +56,12 @@ SIGNATURES = {
     "b200moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_ep_gather": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "b200moe_ep_combine_rows": (_I, [_P, _P, _I, _I, _I, _P, _P]),
-    "b200moe_umma_probe": (_I, [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P]),
+    "b200moe_umma_probe": (_I, [_P, _P, _P, _P, _I, _I, _P, _I, _P, _P]),
+}
+# exported only by a diagnostic build (include/b200moe_diag.h); bound when present
+DIAG_SIGNATURES = {
+    "b200moe_layer_debug_counters": (_I, [_P, _P, _P, _I, _P]),
+    "b200moe_umma_cost": (_I, [_I, _I, _I, _I, _I, _I, _P, _P]),
 }
 
 
@@ -73,6 +81,10 @@ def lib() -> C.CDLL:
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(h, name)     # AttributeError if the library does not export a declared symbol
             fn.restype, fn.argtypes = res, args
+        for name, (res, args) in DIAG_SIGNATURES.items():
+            if hasattr(h, name):
+                fn = getattr(h, name)
+                fn.restype, fn.argtypes = res, args
         _lib = h
     return _lib
 

@@ -20,8 +20,10 @@ FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-li
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 
-if os.environ.get("B200MOE_TIMERS") == "1":   # diagnostic build: per-worker cycle counters in the decode kernel
-    FLAGS.append("-DB200_TIMERS")
+if os.environ.get("B200MOE_DIAG") == "1" or os.environ.get("B200MOE_TIMERS") == "1":
+    # diagnostic build: per-worker cycle counters in the decode kernel, ablation switches of the prefill GEMM, and the entry
+    # points of include/b200moe_diag.h. Not the library that ships.
+    FLAGS += ["-DB200_TIMERS", "-DB200_PF_ABLATE", "-DB200_DIAGNOSTICS"]
 
 
 def nvcc() -> str:

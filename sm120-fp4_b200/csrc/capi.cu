@@ -83,6 +83,8 @@ extern "C" const char* b200moe_error_string(int code) {
     case B200MOE_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case B200MOE_ERR_WORKSPACE: return "workspace too small";
     case B200MOE_ERR_LIMIT: return "size beyond the stated maximum";
+    case B200MOE_ERR_RANGE: return "an intermediate activation exceeded the range of the activation scale (raise it with b200moe_layer_set_act_scale)";
+    case B200MOE_ERR_ORDER: return "topk_ids / topk_weights changed while the call was running: they were still being written when it started";
     default: return "unknown error";
   }
 }
@@ -177,10 +179,23 @@ extern "C" int b200moe_layer_prepack(b200moe_layer* L, void* buffer, long long b
   return B200MOE_OK;
 }
 
+// After prepack the tcgen05 paths (decode, mid-sized batches, W4A4 prefill) read only the tile records. A caller that does
+// not need the mma.sync kernel or the stand-alone FC1 / FC2 entry points may then free the checkpoint-layout codes and
+// scales (about half of the layer's memory); this makes the handle forget them, so that a later call that would need
+// them fails with B200MOE_ERR_ARG instead of reading freed memory.
+extern "C" int b200moe_layer_release_checkpoint(b200moe_layer* L) {
+  if (!L) return B200MOE_ERR_ARG;
+  if (!L->w1t) return B200MOE_ERR_ARG;   // nothing else to run from
+  L->q1 = L->s1 = L->q2 = L->s2 = nullptr;
+  if (L->decode_impl == 1) L->decode_impl = 0;
+  return B200MOE_OK;
+}
+
 // 0: tcgen05 kernel when the layer is prepacked, else the mma.sync kernel; 1: mma.sync kernel; 2: tcgen05 kernel.
 extern "C" int b200moe_layer_set_decode_impl(b200moe_layer* L, int impl) {
   if (!L || impl < 0 || impl > 2) return B200MOE_ERR_ARG;
   if (impl == 2 && !L->w1t) return B200MOE_ERR_ARG;
+  if (impl == 1 && !L->q1) return B200MOE_ERR_ARG;   // checkpoint-layout weights were released
   L->decode_impl = impl;
   return B200MOE_OK;
 }
@@ -193,12 +208,12 @@ extern "C" int b200moe_layer_set_act_scale(b200moe_layer* L, float g1) {
   return B200MOE_OK;
 }
 
-static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* ws, void* stream) {
+static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* ws, bool chained, void* stream) {
   uint8_t* w = (uint8_t*)ws;
   cudaStream_t st = (cudaStream_t)stream;
   const int nbv = M <= 4 ? 0 : M <= 8 ? 1 : 2;
   const int N = 16 << nbv;
-  int rc = b200_expand_x_launch(x, M, L->H, N, L->KB1, w + L->off_xb, (float*)(w + L->off_xscale), st);
+  int rc = b200_expand_x_launch(x, M, L->H, N, L->KB1, w + L->off_xb, (float*)(w + L->off_xscale), chained, st);
   if (rc != B200MOE_OK) return rc;
   DecodeTcParams p;
   memset(&p, 0, sizeof(p));
@@ -226,12 +241,13 @@ static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const floa
   }
   if (NS < 2) return B200MOE_ERR_SHAPE;
   p.NS = NS;
-  return b200_decode_tc_launch(p, L->sms, b200_decode_tc_smem_bytes(NS, p.region_bytes), st);
+  return b200_decode_tc_launch(p, L->sms, b200_decode_tc_smem_bytes(NS, p.region_bytes), chained, st);
 }
 
 static int decode_common(const b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* act_bf16,
                          int phases, int write_tables, void* ws, long long ws_bytes, void* stream) {
   if (!L || !ids || !wts || !ws) return B200MOE_ERR_ARG;
+  if (!L->q1) return B200MOE_ERR_ARG;   // the mma.sync kernel reads the checkpoint layout, which the caller released
   if ((phases & 1) && !x) return B200MOE_ERR_ARG;
   if ((phases & 2) && !out) return B200MOE_ERR_ARG;
   if (M < 0) return B200MOE_ERR_ARG;
@@ -282,8 +298,9 @@ static int decode_common(const b200moe_layer* L, const void* x, const int* ids, 
 
 // The whole decode layer: out[M, H] (bf16) = sum_j w[t,j] * FC2_e(silu(gate) * up), e = ids[t,j]. M <= 16.
 // Replaces sm120fp4.vllm_backend.Weights._slice (vllm_backend.py:174-190): route + FC1 + FC2 in one launch.
-extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
-                                      int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
+// flags bit 0 (B200MOE_ORDERED): both kernels of the call are ordinary stream-ordered launches.
+extern "C" int b200moe_decode_forward_ex(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
+                                         int M, void* out_bf16, void* workspace, long long workspace_bytes, int flags, void* stream) {
   // the tcgen05 kernel whenever the tile records exist and the shape fits it: x scale tiles of <= 12 K boxes in TMEM, one
   // worker group per 128-row output block
   if (L && L->w1t && L->decode_impl != 1 && L->sms <= 256 && L->KB1 <= 12 && L->NB2 <= L->sms) {
@@ -292,9 +309,14 @@ extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16
     if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
     if (((uintptr_t)workspace & 255) || ((uintptr_t)x_bf16 & 15)) return B200MOE_ERR_ARG;
     if (M == 0) return B200MOE_OK;
-    return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, stream);
+    return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, !(flags & 1), stream);
   }
   return decode_common(L, x_bf16, topk_ids, topk_weights, M, out_bf16, nullptr, 3, 1, workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200moe_decode_forward(const b200moe_layer* L, const void* x_bf16, const int* topk_ids, const float* topk_weights,
+                                      int M, void* out_bf16, void* workspace, long long workspace_bytes, void* stream) {
+  return b200moe_decode_forward_ex(L, x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, workspace_bytes, 0, stream);
 }
 
 // The same call for a host that keeps its tensors in host memory. Page-locked buffers (cudaHostAlloc, cudaHostRegister,
@@ -382,16 +404,27 @@ extern "C" int b200moe_layer_route_tables(const b200moe_layer* L, const void* wo
   return B200MOE_OK;
 }
 
-// Read the status word (synchronises the stream): 0, or B200MOE_ERR_TIMEOUT / B200MOE_ERR_ARG (expert id out of range).
-extern "C" int b200moe_layer_status(const b200moe_layer* L, const void* workspace, void* stream) {
-  if (!L || !workspace) return B200MOE_ERR_ARG;
-  int st = 0;
-  B200_CUDA_TRY(cudaMemcpyAsync(&st, (const uint8_t*)workspace + L->off_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
-  if (st == 0) return B200MOE_OK;
-  return st == 4 ? B200MOE_ERR_ARG : B200MOE_ERR_TIMEOUT;
+// Read the status words (synchronises the stream): 0, or B200MOE_ERR_TIMEOUT (a bounded wait ran out), B200MOE_ERR_ARG
+// (expert id out of range), B200MOE_ERR_ORDER (the routing inputs changed under the call), B200MOE_ERR_RANGE (an FC1
+// activation beyond the range of the activation scale was clipped). The range and order words are cleared by the read.
+static int read_status(const void* workspace, long long off, cudaStream_t st) {
+  int w[3] = {0, 0, 0};
+  uint8_t* p = (uint8_t*)const_cast<void*>(workspace) + off;
+  B200_CUDA_TRY(cudaMemcpyAsync(w, p, sizeof(w), cudaMemcpyDeviceToHost, st));
+  B200_CUDA_TRY(cudaStreamSynchronize(st));
+  if (w[1] || w[2]) B200_CUDA_TRY(cudaMemsetAsync(p + 4, 0, 8, st));
+  if (w[0]) return w[0] == 4 ? B200MOE_ERR_ARG : B200MOE_ERR_TIMEOUT;
+  if (w[2]) return B200MOE_ERR_ORDER;
+  if (w[1]) return B200MOE_ERR_RANGE;
+  return B200MOE_OK;
 }
 
+extern "C" int b200moe_layer_status(const b200moe_layer* L, const void* workspace, void* stream) {
+  if (!L || !workspace) return B200MOE_ERR_ARG;
+  return read_status(workspace, L->off_status, (cudaStream_t)stream);
+}
+
+#ifdef B200_DIAGNOSTICS
 // Copy the per-worker cycle counters of the last launch to the host (8 int64 per worker, 2 x SM-count workers). Only a
 // library built with -DB200_TIMERS fills them; otherwise they read zero. Synchronises the stream.
 extern "C" int b200moe_layer_debug_counters(const b200moe_layer* L, const void* workspace, long long* out, int max_workers, void* stream) {
@@ -401,6 +434,7 @@ extern "C" int b200moe_layer_debug_counters(const b200moe_layer* L, const void* 
   B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
   return n;
 }
+#endif  // B200_DIAGNOSTICS
 
 // ---- W4A4 prefill (any number of tokens up to the workspace's max_tokens): own tcgen05 grouped GEMM, replacing the
 // third-party CUTLASS hand-off of sm120fp4/vllm_backend.py:123-168. Needs b200moe_layer_prepack (weight tile records).
@@ -409,6 +443,7 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
                          const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
                          float gs_x, float gs_a, int sms, cudaStream_t st);
 int b200_prefill_status_offset(int E, int H, int I, int top_k, int max_tokens, long long* off);
+void b200_prefill_workspace_map(int E, int H, int I, int top_k, int max_tokens, long long* out);
 
 extern "C" long long b200moe_prefill_workspace_bytes(const b200moe_layer* L, int max_tokens) {
   if (!L || max_tokens <= 0) return B200MOE_ERR_ARG;
@@ -429,6 +464,15 @@ extern "C" int b200moe_prefill_forward(const b200moe_layer* L, const void* x_bf1
   if (M == 0) return B200MOE_OK;
   return b200_prefill_forward(L->E, L->H, L->I, L->top_k, L->w1t, L->w2t, L->alpha1, L->alpha2, x_bf16, topk_ids, topk_weights, M, out_bf16,
                               workspace, workspace_bytes, max_tokens, gs_x, gs_a, L->sms, (cudaStream_t)stream);
+}
+
+// Where the tables and tile records sit inside a prefill workspace sized for max_tokens (14 values, see the header): lets a
+// tool or a test read back what each stage of the last call wrote (router tables, NVFP4 records of x and of the SiLU*mul
+// activations, weighted rows). Host-side arithmetic only.
+extern "C" int b200moe_prefill_workspace_map(const b200moe_layer* L, int max_tokens, long long* out14) {
+  if (!L || !out14 || max_tokens <= 0) return B200MOE_ERR_ARG;
+  b200_prefill_workspace_map(L->E, L->H, L->I, L->top_k, max_tokens, out14);
+  return B200MOE_OK;
 }
 
 // status word of the prefill workspace; synchronises the stream
@@ -475,10 +519,7 @@ extern "C" int b200moe_mid_status(const b200moe_layer* L, const void* workspace,
   if (!L || !workspace) return B200MOE_ERR_ARG;
   long long off = 0;
   b200_mid_status_offset(L->E, L->H, L->I, L->top_k, max_tokens, &off);
-  int st = 0;
-  B200_CUDA_TRY(cudaMemcpyAsync(&st, (const uint8_t*)workspace + off, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-  B200_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
-  return st == 0 ? B200MOE_OK : B200MOE_ERR_TIMEOUT;
+  return read_status(workspace, off, (cudaStream_t)stream);
 }
 
 extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }

@@ -13,6 +13,8 @@ enum {
   B200MOE_ERR_TIMEOUT = -5,    // a bounded device-side wait ran out (status word set by the kernel)
   B200MOE_ERR_WORKSPACE = -6,  // workspace too small
   B200MOE_ERR_LIMIT = -7,      // size beyond a stated maximum
+  B200MOE_ERR_RANGE = -8,      // an intermediate activation exceeded the range of the fixed activation scale (results clipped)
+  B200MOE_ERR_ORDER = -9,      // the routing inputs changed while the call was running (they were not complete when it started)
 };
 
 namespace b200 {

@@ -57,7 +57,8 @@ struct DecodeTcParams {
   unsigned* cnt1;
   unsigned* cnt2;
   unsigned long long* gates; // workspace: arrival counters of the two FC1 gates; only ever incremented, V per launch and gate
-  int* status;
+  int* status;               // workspace: [0] code of the first bounded wait that ran out / bad expert id, [1] activation range
+                             // exceeded, [2] routing inputs changed under the call
   int* experts_out;
   int* offsets_out;
   int* pairs_out;
@@ -71,10 +72,10 @@ struct DecodeTcParams {
 }  // namespace b200
 
 int b200_decode_tc_smem_bytes(int NS, int region_bytes);
-int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, cudaStream_t st);
+int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, bool chained, cudaStream_t st);
 int b200_pack_tiles_launch(const void* q, const void* sf, void* out, int E, int rows_per_expert, int row_bytes, int blocks, int KB, int KT,
                            int fc1, int I, long long sf_stride, cudaStream_t st);
-int b200_decode_tc_launch(const b200::DecodeTcParams& p, int grid, int smem_bytes, cudaStream_t st);
+int b200_decode_tc_launch(const b200::DecodeTcParams& p, int grid, int smem_bytes, bool chained, cudaStream_t st);
 int b200_decode_smem_bytes(int NS, int region_bytes);
 int b200_decode_launch(const b200::DecodeParams& p, int grid, int smem_bytes, cudaStream_t st);
 int b200_act_to_frag_launch(const void* act, const int* ids, const int* experts, int Umax, int M, int top_k, int I, int KB2,

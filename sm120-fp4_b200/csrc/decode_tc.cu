@@ -299,12 +299,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     if (lane == 0) {
       const int pw = warp - 9;
       const uint64_t pol = policy_evict_first();
-      // the resident B operand of FC1 (x expanded into NVFP4 terms) and its scale tiles: one bulk copy
-      if (pw == 0 && n1 > 0) {
-        grid_dependency_wait();   // the x operand comes from the expansion kernel launched just before this one
-        mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
-        bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
-      }
+      // (The resident B operand of FC1 is fetched by an epilogue thread: it has to wait for the expansion kernel, and a
+      // producer that waited with it would leave half of the ring empty while the weights could already be streaming.)
       bool passed[2] = {!use_gate_a, false};
       int pend_slot[16], pend_idx[16], pend_g[16] = {0}, npend = 0, pend_head = 0;   // ring of 16: at most NS (<= 12) entries wait at a time
       int slot_g[12];                                                          // gate of the FC2 tile in each ring slot
@@ -451,6 +447,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     // The routing tables in the router's padded form, for callers that ask for them: written by these four warps of the
     // last worker (the one with the least FC1 work) once their tiles are through, off every critical path.
     if (blockIdx.x == V - 1 && P.experts_out) {
+      grid_dependency_wait();   // the tables of the previous call on this workspace may still be read by its tail
       const int t4 = tid - 128;
       for (int e = t4; e < P.E; e += 128)
         if (T.cnt[e] > 0) { P.experts_out[T.uidx[e] - 1] = e; P.offsets_out[T.uidx[e] - 1] = T.base[e] - T.cnt[e]; }
@@ -528,8 +525,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     const int row = quad * 32 + lane;              // accumulator row (MMA M index)
     __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
     __shared__ float s_w[16];
-    grid_dependency_wait();
+    grid_dependency_wait();   // everything before this kernel in the stream is complete and visible from here on
+    if (et == 0 && n1 > 0) {
+      // the resident B operand of FC1 (x expanded into NVFP4 terms by the kernel launched just before this one) and its
+      // scale tiles: one bulk copy
+      mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
+      bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
+    }
     if (et < N) T.colscale[et] = P.xscale[et];
+    // The routing inputs were read at entry, before the wait above, so that the weight stream could start early. If they
+    // were still being written then (a producer kernel that lets its successors start before it has written them), the
+    // copies used here are stale: say so instead of returning a wrong result silently.
+    for (int p = et; p < npairs; p += 128) {
+      int e2 = (int)ld_acquire_gpu(reinterpret_cast<const unsigned*>(P.ids) + p);
+      if (e2 < 0 || e2 >= P.E) e2 = -1;
+      const unsigned w2 = ld_acquire_gpu(reinterpret_cast<const unsigned*>(P.wts) + p);
+      if (e2 != T.ids[p] || w2 != __float_as_uint(T.wts[p])) P.status[2] = 1;
+    }
     named_bar_sync(1, 128);
     int ab = 0;
     uint32_t aph[2] = {0, 0};
@@ -656,7 +668,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
               for (int i = 0; i < 16; ++i) r[i] = s_ex[blk * 16 + i][tk];
               uint2 codes[kTerms];
               uint8_t sf[kTerms];
-              expand_block16(r, P.act_g1, codes, sf);
+              if (expand_block16(r, P.act_g1, codes, sf)) P.status[1] = 1;   // beyond the range of the fixed activation scale
 #pragma unroll
               for (int t = 0; t < kTerms; ++t) {
                 const int n = tk * kTerms + t;
@@ -726,7 +738,7 @@ static bool pdl_chain_enabled() {   // B200MOE_PDL_CHAIN=0: launch the expansion
   return on;
 }
 
-int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, cudaStream_t st) {
+int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, float* colscale, bool chained, cudaStream_t st) {
   // programmatic launch: the blocks may be scheduled while the previous kernel of the stream drains (if that kernel
   // allows it, as this library's layer kernel does); griddepcontrol.wait at their top keeps stream order for all data
   cudaLaunchConfig_t cfg;
@@ -735,7 +747,7 @@ int b200_expand_x_launch(const void* x, int M, int H, int N, int KB1, void* xb, 
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = pdl_chain_enabled() ? 1 : 0;
+  cfg.attrs = attr, cfg.numAttrs = chained && pdl_chain_enabled() ? 1 : 0;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   uint8_t* xbp = (uint8_t*)xb;
   void* args[] = {(void*)&xp, (void*)&M, (void*)&H, (void*)&N, (void*)&KB1, (void*)&xbp, (void*)&colscale};
@@ -755,7 +767,7 @@ int b200_pack_tiles_launch(const void* q, const void* sf, void* out, int E, int 
   return B200MOE_OK;
 }
 
-int b200_decode_tc_launch(const DecodeTcParams& p, int grid, int smem_bytes, cudaStream_t st) {
+int b200_decode_tc_launch(const DecodeTcParams& p, int grid, int smem_bytes, bool chained, cudaStream_t st) {
   void* args[] = {(void*)&p};
   const void* fn = p.M <= 4 ? (const void*)k_moe_decode_tc<1> : p.M <= 8 ? (const void*)k_moe_decode_tc<2> : (const void*)k_moe_decode_tc<4>;
   static thread_local int configured[3] = {0, 0, 0};
@@ -771,7 +783,7 @@ int b200_decode_tc_launch(const DecodeTcParams& p, int grid, int smem_bytes, cud
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
+  cfg.attrs = attr, cfg.numAttrs = chained ? 1 : 0;
   B200_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, args));
   return B200MOE_OK;
 }

@@ -184,11 +184,16 @@ __global__ void __launch_bounds__(256) k_ep_combine_rows(const __nv_bfloat16* __
 }  // namespace b200
 
 // ids int32 [m, k] (global ids, negative = empty slot) -> counts int32 [world], offsets int32 [world + 1], pos int32
-// [m, world], send_tok int32 [m * min(world, k)] (device buffers). m <= 8192 * 8, world <= 16.
+// [m, world], send_tok int32 [m * min(world, k)] (device buffers). 0 <= m <= 8192 * 8, world <= 16.
 extern "C" int b200moe_ep_plan(const int* ids, int m, int k, int world, int experts_per_rank, int* counts, int* offsets, int* pos,
                                int* send_tok, void* stream) {
-  if (!ids || !counts || !offsets || !pos || !send_tok) return B200MOE_ERR_ARG;
-  if (m < 1 || k < 1 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1) return B200MOE_ERR_SHAPE;
+  if (!counts || !offsets || (m > 0 && (!ids || !pos || !send_tok))) return B200MOE_ERR_ARG;
+  if (m < 0 || k < 1 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1) return B200MOE_ERR_SHAPE;
+  if (m == 0) {   // a rank with an empty batch still takes part in the exchange: it sends nothing to anybody
+    B200_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * world, (cudaStream_t)stream));
+    B200_CUDA_TRY(cudaMemsetAsync(offsets, 0, sizeof(int) * (world + 1), (cudaStream_t)stream));
+    return B200MOE_OK;
+  }
   k_ep_plan<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, m, k, world, experts_per_rank, counts, offsets, pos, send_tok);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
@@ -209,8 +214,9 @@ extern "C" int b200moe_ep_gather(const void* x, const int* ids, const float* wts
 
 // back bf16 [rows, h] (the partial rows in send-buffer order), pos int32 [m, world] -> out bf16 [m, h]
 extern "C" int b200moe_ep_combine_rows(const void* back, const int* pos, int m, int h, int world, void* out, void* stream) {
-  if (!back || !pos || !out) return B200MOE_ERR_ARG;
-  if (m < 1 || h <= 0 || h % 8 || world < 1 || world > kEpMaxWorld) return B200MOE_ERR_SHAPE;
+  if (m > 0 && (!back || !pos || !out)) return B200MOE_ERR_ARG;
+  if (m < 0 || h <= 0 || h % 8 || world < 1 || world > kEpMaxWorld) return B200MOE_ERR_SHAPE;
+  if (m == 0) return B200MOE_OK;
   const int total = m * (h / 8);
   int grid = (total + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;

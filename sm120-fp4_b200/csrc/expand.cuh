@@ -33,8 +33,11 @@ __device__ __forceinline__ uint32_t cvt_f32x8_e2m1(const float* v) {
 // codes[t] = 8 packed bytes (element 2j in the low nibble), sf[t] = E4M3 scale byte. The residual is taken against the
 // codes and the scale actually emitted, so any rounding on the way (approximate reciprocal included) is absorbed by the
 // next term.
-__device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (&codes)[kTerms], uint8_t (&sf)[kTerms]) {
+// Returns true when the block's maximum lies beyond what the first term can hold (its scale clamps at 448, i.e. values
+// above 2688 / g1): the later terms, with their larger global scales, cannot absorb the clipped part.
+__device__ __forceinline__ bool expand_block16(float (&r)[16], float g1, uint2 (&codes)[kTerms], uint8_t (&sf)[kTerms]) {
   float g = g1, ginv = __frcp_rn(g1);
+  bool clipped = false;
 #pragma unroll
   for (int t = 0; t < kTerms; ++t) {
     float m[8];
@@ -43,7 +46,9 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
 #pragma unroll
     for (int i = 0; i < 4; ++i) m[i] = fmaxf(m[i], m[i + 4]);
     const float amax = fmaxf(fmaxf(m[0], m[2]), fmaxf(m[1], m[3]));
-    const uint8_t sb = tc_e4m3(fminf(amax * (1.0f / 6.0f) * g, 448.0f));
+    const float want = amax * (1.0f / 6.0f) * g;
+    if (t == 0) clipped = want > 464.0f;   // 464 is the first value that no longer rounds down to 448
+    const uint8_t sb = tc_e4m3(fminf(want, 448.0f));
     const float sv = tc_e4m3_value(sb);
     const float scale = sv > 0.f ? g * __frcp_rn(sv) : 0.f, back = sv * ginv;
     float sc[16];
@@ -67,6 +72,7 @@ __device__ __forceinline__ void expand_block16(float (&r)[16], float g1, uint2 (
     g *= 6.0f;
     ginv *= (1.0f / 6.0f);
   }
+  return clipped;
 }
 
 }  // namespace b200

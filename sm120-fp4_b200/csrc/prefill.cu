@@ -31,6 +31,14 @@ constexpr int kPfThreads = 256;      // warps 0-3 epilogue, 4 MMA issuer, 5 scal
 // resident bytes leave room for a weight ring twice as deep, which is what a batch that touches every expert once needs.
 constexpr int kMidRec = 8192 + 2048;
 
+// Ablation switches of the resident-operand GEMM (what a phase costs when a part of it is left out) exist only in a
+// diagnostic build (-DB200_PF_ABLATE, read from B200MOE_PF_ABLATE at launch); the product build compiles them away.
+#ifdef B200_PF_ABLATE
+#define PF_ABLATE(bit) (P.dbg & (bit))
+#else
+#define PF_ABLATE(bit) false
+#endif
+
 // ------------------------------------------------------------------------------------------------ plan
 // experts/offsets: the router's tables. One thread per touched expert: its rows are cut into tiles of rows_per_tile rows
 // (128 for the W4A4 GEMM; 16 for the W4A16 GEMM, whose 64-row tile holds four term rows per token-expert pair), the tiles of
@@ -69,40 +77,111 @@ __global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ ex
 __device__ __forceinline__ int rec_code_offset(int r, int b16) { return r * 128 + ((((b16 >> 1) ^ (r & 7))) << 4) + (b16 & 1) * 8; }
 __device__ __forceinline__ int rec_scale_offset(int r, int b16) { return 16384 + (b16 >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b16 & 3); }
 
-// ------------------------------------------------------------------------------------------------ x -> records
-// One thread per 16-value block of a padded row. rec [ntiles][KB][18432]; K padded to KB*256 with zero codes/scales. The
-// thread of a row's first block also records the row's pair (row_pair, -1 for padding) and the pair's row (dst_row).
-__global__ void __launch_bounds__(256) k_quantize_records(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pairs,
-                                                          const int* __restrict__ tile_first, const int* __restrict__ tile_end,
-                                                          const int* __restrict__ ntiles, int H, int KB, int top_k,
-                                                          const float* __restrict__ gs_ptr, uint8_t* __restrict__ rec,
-                                                          int* __restrict__ row_pair, int* __restrict__ dst_row) {
-  const float gs = *gs_ptr;
-  __shared__ float s_scale[128];   // gs / (E4M3 value) for every scale byte: one division per table entry instead of one per block
-  fill_scale_table(s_scale, gs, threadIdx.x, blockDim.x);
+// ------------------------------------------------------------------------------------------------ row map
+// The tile plan of the W4A4 path and the map between token-expert pairs and operand rows, in one launch. Every block
+// repeats the (tiny) scan over the touched experts in shared memory: expert u owns tiles [tbase[u], tbase[u+1]) of 128
+// rows; block 0 also writes the tile tables the GEMM kernels read. Then, grid-wide, one thread per padded operand row:
+// row_pair[row] = the pair the row holds (-1 on the padding rows of an expert's last tile), dst_row[pair] = row; the
+// scale bytes of padding rows are zeroed in the x records (a zero scale silences whatever codes the row holds, so their
+// codes are never written). Pairs whose slot is empty (negative id) are not in `pairs`: they get dst_row = -1 here.
+__global__ void __launch_bounds__(256) k_prefill_rowmap(const int* __restrict__ ids, int P, const int* __restrict__ experts,
+                                                        const int* __restrict__ offsets, const int* __restrict__ pairs, int Umax, int max_tiles,
+                                                        int KB, int* __restrict__ ntiles, int* __restrict__ tile_expert,
+                                                        int* __restrict__ tile_first, int* __restrict__ tile_end, uint8_t* __restrict__ rec,
+                                                        int* __restrict__ row_pair, int* __restrict__ dst_row) {
+  __shared__ int wsum[8];
+  __shared__ int tbase[257];   // first tile of touched expert u; tbase[U..] = total
+  __shared__ int s_lo[256], s_hi[256];
+  const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
+  int e = -1, lo = 0, hi = 0;
+  if (u < Umax) {
+    e = experts[u];
+    if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
+  }
+  const int mine = (hi - lo + 127) >> 7;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += a;
+  }
+  if (lane == 31) wsum[warp] = inc;
   __syncthreads();
-  const unsigned per_row = (unsigned)KB * 16u;
-  const unsigned total = (unsigned)ntiles[0] * 128u * per_row;
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const unsigned row = i / per_row, b = i - row * per_row;
-    const int t = (int)(row >> 7), r = (int)(row & 127);
-    const int j = tile_first[t] + r;
-    int pr = -1;
-    if (j < tile_end[t]) pr = pairs[j];
-    if (b == 0) {
-      row_pair[row] = pr;
-      if (pr >= 0) dst_row[pr] = (int)row;
+  int base = inc - mine;
+  for (int w2 = 0; w2 < warp; ++w2) base += wsum[w2];
+  tbase[u] = base;
+  s_lo[u] = lo, s_hi[u] = hi;
+  if (u == 255) tbase[256] = base + mine;
+  __syncthreads();
+  const int NT = min(tbase[256], max_tiles);
+  if (blockIdx.x == 0) {
+    if (u == 0) ntiles[0] = NT;
+    for (int j = 0; j < mine && base + j < max_tiles; ++j) {
+      tile_expert[base + j] = e;
+      tile_first[base + j] = lo + j * 128;
+      tile_end[base + j] = hi;
     }
+  }
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gsz = gridDim.x * blockDim.x;
+  for (int p = gtid; p < P; p += gsz)
+    if (ids[p] < 0) dst_row[p] = -1;
+  for (int row = gtid; row < NT * 128; row += gsz) {
+    const int t = row >> 7, r = row & 127;
+    int a = 0, b = 255;   // the touched expert whose tile range holds t: last u with tbase[u] <= t
+    while (a < b) {
+      const int mid = (a + b + 1) >> 1;
+      if (tbase[mid] <= t) a = mid; else b = mid - 1;
+    }
+    const int j = s_lo[a] + (t - tbase[a]) * 128 + r;
+    const int pr = j < s_hi[a] ? pairs[j] : -1;
+    row_pair[row] = pr;
+    if (pr >= 0) {
+      dst_row[pr] = row;
+    } else {
+      for (int kb = 0; kb < KB; ++kb) {
+        uint8_t* sfp = rec + ((long long)t * KB + kb) * kRec + 16384 + (r & 31) * 16 + (r >> 5) * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint32_t*>(sfp + q * 512) = 0u;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ x -> records
+// One block of 128 threads per token, one thread per 16-value block (a second round for rows of more than 2048 values):
+// the token's row is read and quantised ONCE (the reference's block arithmetic, bit-exact) and its codes and scale bytes are
+// then stored into the record rows of each of its top_k pairs (dst_row, -1 = empty slot). rec [ntiles][KB][18432]; blocks
+// beyond H inside the last K box are written as zero codes and zero scales.
+__global__ void __launch_bounds__(128) k_quantize_scatter(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dst_row, int M, int H,
+                                                          int KB, int top_k, float gs, uint8_t* __restrict__ rec) {
+  __shared__ float s_scale[128];   // gs / (E4M3 value) for every scale byte: one division per table entry instead of one per block
+  __shared__ int s_row[16];
+  fill_scale_table(s_scale, gs, threadIdx.x, blockDim.x);
+  const int tok = blockIdx.x;
+  if (threadIdx.x < top_k) s_row[threadIdx.x] = dst_row[tok * top_k + threadIdx.x];
+  __syncthreads();
+  const int nblk = KB * 16;
+  for (int b = threadIdx.x; b < ((nblk + 127) & ~127); b += 128) {   // whole warps stay in the loop: the shuffles below need them
     uint2 pk = make_uint2(0u, 0u);
-    uint8_t sb = 0;
-    if (pr >= 0 && (int)b * 16 < H) {
+    uint32_t sb = 0;
+    if (b < nblk && b * 16 < H) {
       float v[16];
-      load16(x + (long long)(pr / top_k) * H + b * 16, v);
+      load16(x + (long long)tok * H + b * 16, v);
       sb = quantize_block16_t(v, gs, s_scale, pk);
     }
-    uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kRec;
-    *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b & 15)) = pk;
-    dst[rec_scale_offset(r, b & 15)] = sb;
+    // the four scale bytes of one 64-value K step are adjacent in a record: lane 4i gathers them into one 32-bit store
+    uint32_t sf4 = sb | (__shfl_down_sync(0xffffffffu, sb, 1) << 8);
+    sf4 |= __shfl_down_sync(0xffffffffu, sf4, 2) << 16;
+    const int kb = b >> 4, b16 = b & 15;
+    if (b >= nblk) continue;
+    for (int j = 0; j < top_k; ++j) {
+      const int row = s_row[j];
+      if (row < 0) continue;
+      uint8_t* dst = rec + ((long long)(row >> 7) * KB + kb) * kRec;
+      const int r = row & 127;
+      *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b16)) = pk;
+      if ((b & 3) == 0) *reinterpret_cast<uint32_t*>(dst + rec_scale_offset(r, b16)) = sf4;
+    }
   }
 }
 
@@ -183,8 +262,8 @@ struct PrefillParams {
   const int* tile_expert;
   const int* row_pair;        // [ntiles*128] pair index or -1
   const float* alpha;         // per-expert weight scale
-  const float* gs_in;         // global scale the A operand was quantised with
-  const float* gs_out;        // PHASE 1: global scale for the activation re-quantisation
+  float gs_in;                // global scale the A operand was quantised with
+  float gs_out;               // PHASE 1: global scale for the activation re-quantisation
   const float* wts;           // PHASE 2: routing weights [P]
   uint8_t* orec;              // PHASE 1: FC2 activation records [ntiles][KB2][18432]
   __nv_bfloat16* y;           // PHASE 2: weighted rows [ntiles*128][H]
@@ -193,7 +272,7 @@ struct PrefillParams {
   const float* rowscale;      // PHASE 3: 1 / g_t of every term row of the x operand [ntiles*128] (0 on padding rows)
   float act_g1;               // PHASE 3/4: global scale of the first term of the SiLU*mul activations
   int NBLK, KB, KT, KB2, H;
-  int dbg;                    // experiments only (B200MOE_PF_DEBUG): 1 epilogue without math, 2 no MMAs, 4 no scale moves
+  int dbg;                    // ablation build only (-DB200_PF_ABLATE): 1 epilogue without math, 2 no MMAs, 4 no scale moves
 };
 
 struct PfShared {
@@ -296,7 +375,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(const __grid_con
     const int row = warp * 32 + lane;
     int ab = 0;
     uint32_t aph[2] = {0, 0};
-    const float gs_in = *P.gs_in;
+    const float gs_in = P.gs_in;
     for (long long w = blockIdx.x; w < nwork; w += gridDim.x) {
       const int t = (int)(w / NBLK), nblk = (int)(w % NBLK);
       const int e = P.tile_expert[t];
@@ -306,7 +385,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(const __grid_con
       if (PHASE == 1) {
         // columns 0..63 = up, 64..127 = gate of intermediate columns 64*nblk..; SiLU*mul, re-quantise 4 blocks of 16
         const float s = P.alpha[e] / gs_in;
-        const float gs_out = *P.gs_out;
+        const float gs_out = P.gs_out;
         uint8_t* dst = P.orec + ((long long)t * P.KB2 + (nblk >> 2)) * kRec;
         uint32_t sfw = 0;
 #pragma unroll
@@ -482,7 +561,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
           }
           if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
-          if (!(P.dbg & 4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
+          if (!PF_ABLATE(4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
           if (lane == 0) mbar_arrive(&S.b_sfr[slot]);
           if (++slot == NSB) { slot = 0; ph ^= 1u; }
         }
@@ -508,7 +587,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
           const int nkt = kb == KB - 1 ? nkt_last : 4;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
-            if (jj < nkt && !(P.dbg & 2))
+            if (jj < nkt && !PF_ABLATE(2))
               umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
                               (kb > 0 || jj > 0) ? 1u : 0u, el);
           umma_commit_p(&S.b_empty[slot], el);
@@ -527,8 +606,8 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     const int row = quad * 32 + lane;
     int ab = 0;
     uint32_t aph[2] = {0, 0};
-    const float gs_in = PHASE <= 2 ? *P.gs_in : 1.0f;
-    const float gs_out = PHASE == 1 ? *P.gs_out : 0.f;
+    const float gs_in = PHASE <= 2 ? P.gs_in : 1.0f;
+    const float gs_out = PHASE == 1 ? P.gs_out : 0.f;
     for_each_segment([&](int t, int n0, int n1, int) {
       // per segment: the tile's expert and (FC2) this row's pair, fetched once
       float s = P.alpha[P.tile_expert[t]] / gs_in;   // FC1: alpha / gs_in; FC2: that times the row's routing weight (0 on padding rows)
@@ -548,7 +627,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         if (!mbar_wait(&S.acc_full[ab], aph[ab], &S.abort_flag)) *P.status = 7;
         tc_fence_after();
         const uint32_t taddr = tm_acc + 128 * ab + ((uint32_t)(quad * 32) << 16);
-        if (P.dbg & 1) {
+        if (PF_ABLATE(1)) {
         } else if (PHASE == 1) {
           // columns 0..63 = up, 64..127 = gate of intermediate columns 64*n..; SiLU*mul, re-quantise blocks of 16
           uint8_t* dst = P.orec + ((long long)t * P.KB2 + (n >> 2)) * kRec;
@@ -605,7 +684,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
           if ((tq & 1) == 0) {
             uint2 codes[kTerms];
             uint8_t sf[kTerms];
-            expand_block16(a, P.act_g1, codes, sf);
+            if (expand_block16(a, P.act_g1, codes, sf)) P.status[1] = 1;   // beyond the range of the fixed activation scale
             const int blk = 2 * half + bsel, r0 = row & ~3;
 #pragma unroll
             for (int q = 0; q < kTerms; ++q) {
@@ -748,7 +827,7 @@ extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* expert
 extern "C" long long b200moe_route_workspace_bytes(int P, int E);
 
 struct PrefillLayout {
-  long long experts, offsets, pairs, route_ws, ntiles, tile_expert, src_tok, row_pair, dst_row, gs, status, xrec, arec, y, total;
+  long long experts, offsets, pairs, route_ws, ntiles, tile_expert, tile_tab, row_pair, dst_row, status, xrec, arec, y, total;
   int max_tiles;
 };
 
@@ -766,10 +845,9 @@ static PrefillLayout prefill_layout(int E, int H, int I, int top_k, int max_toke
   L.route_ws = o, o = pf_align(o + b200moe_route_workspace_bytes((int)P, E));
   L.ntiles = o, o += 256;
   L.tile_expert = o, o = pf_align(o + 4LL * L.max_tiles);
-  L.src_tok = o, o = pf_align(o + 4LL * L.max_tiles * 128);
+  L.tile_tab = o, o = pf_align(o + 8LL * L.max_tiles);   // tile_first [max_tiles], then tile_end [max_tiles]
   L.row_pair = o, o = pf_align(o + 4LL * L.max_tiles * 128);
   L.dst_row = o, o = pf_align(o + 4 * P);
-  L.gs = o, o += 256;
   L.status = o, o += 256;
   L.xrec = o, o = pf_align(o + (long long)L.max_tiles * KB1 * kRec);
   L.arec = o, o = pf_align(o + (long long)L.max_tiles * KB2 * kRec);
@@ -782,7 +860,15 @@ long long b200_prefill_workspace_bytes(int E, int H, int I, int top_k, int max_t
   return prefill_layout(E, H, I, top_k, max_tokens).total;
 }
 
-__global__ void k_set2(float* p, float a, float b) { p[0] = a; p[1] = b; }
+// Byte offsets of the tables and records inside a prefill workspace, for tools and tests that read them back:
+// out[0..11] = experts, offsets, pairs, ntiles, tile_expert, tile_first, tile_end, row_pair, dst_row, x records, activation
+// records, weighted rows; out[12] = tile capacity, out[13] = total bytes.
+void b200_prefill_workspace_map(int E, int H, int I, int top_k, int max_tokens, long long* out) {
+  const PrefillLayout L = prefill_layout(E, H, I, top_k, max_tokens);
+  const long long v[14] = {L.experts, L.offsets, L.pairs, L.ntiles, L.tile_expert, L.tile_tab, L.tile_tab + 4LL * L.max_tiles, L.row_pair,
+                           L.dst_row, L.xrec, L.arec, L.y, L.max_tiles, L.total};
+  for (int i = 0; i < 14; ++i) out[i] = v[i];
+}
 
 // One GEMM launch. Phases 1/2 (W4A4): the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit
 // in shared memory and the scale columns fit in TMEM, otherwise the kernel that streams both operands. Phases 3/4 (W4A16)
@@ -794,8 +880,7 @@ static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, cudaS
   const int tmem_cap = (512 - 256 - 16 * KB) / 16;
   if (nsb > tmem_cap) nsb = tmem_cap;
   if (nsb > 12) nsb = 12;
-  const bool stream_a = getenv("B200MOE_PREFILL_STREAM_A") && getenv("B200MOE_PREFILL_STREAM_A")[0] == '1';
-  if (KB <= 12 && nsb >= 3 && !(stream_a && phase <= 2)) {
+  if (KB <= 12 && nsb >= 3) {
     const int sm_r = 1024 + abytes + nsb * kRec + tail;
     const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : phase == 2 ? (const void*)k_prefill_gemm_r<2>
                    : phase == 3 ? (const void*)k_prefill_gemm_r<3> : (const void*)k_prefill_gemm_r<4>;
@@ -825,6 +910,7 @@ static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, cudaS
 }
 
 // w1t / w2t: the weight tile records of b200moe_layer_prepack. gs_x / gs_a: global scales of the two activation quantisations.
+// Launches: router (3) -> row map (tile plan fused) -> token-major quantiser -> FC1 GEMM -> FC2 GEMM -> combine.
 int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const uint8_t* w2t, const float* alpha1, const float* alpha2,
                          const void* x, const int* ids, const float* wts, int M, void* out, void* ws, long long ws_bytes, int ws_tokens,
                          float gs_x, float gs_a, int sms, cudaStream_t st) {
@@ -839,45 +925,42 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   int* pairs = (int*)(w + L.pairs);
   int* ntiles = (int*)(w + L.ntiles);
   int* tile_expert = (int*)(w + L.tile_expert);
-  int* src_tok = (int*)(w + L.src_tok);
+  int* tile_first = (int*)(w + L.tile_tab);
+  int* tile_end = tile_first + L.max_tiles;
   int* row_pair = (int*)(w + L.row_pair);
   int* dst_row = (int*)(w + L.dst_row);
-  float* gs = (float*)(w + L.gs);
   int* status = (int*)(w + L.status);
+  if (Umax > 256) return B200MOE_ERR_LIMIT;
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
-  B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
-  const int max_tiles = P / 128 + Umax;
-  int* tile_first = src_tok;              // two tables of max_tiles entries
-  int* tile_end = src_tok + max_tiles;
-  if (Umax > 256) return B200MOE_ERR_LIMIT;
-  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 128, ntiles, tile_expert, tile_first, tile_end);
-  B200_LAUNCH_CHECK();
-  k_set2<<<1, 1, 0, st>>>(gs, gs_x, gs_a);
-  B200_LAUNCH_CHECK();
-  k_quantize_records<<<sms * 16, 256, 0, st>>>((const __nv_bfloat16*)x, pairs, tile_first, tile_end, ntiles, H, KB1, top_k, gs, w + L.xrec,
-                                               row_pair, dst_row);
+  const int max_tiles = P / 128 + Umax;   // tiles this batch can need (<= the workspace's capacity)
+  {
+    const int rows = max_tiles * 128;
+    int grid = (rows + 255) / 256;
+    if (grid > sms * 8) grid = sms * 8;
+    k_prefill_rowmap<<<grid, 256, 0, st>>>(ids, P, experts, offsets, pairs, Umax, max_tiles, KB1, ntiles, tile_expert, tile_first, tile_end,
+                                           w + L.xrec, row_pair, dst_row);
+    B200_LAUNCH_CHECK();
+  }
+  k_quantize_scatter<<<M, 128, 0, st>>>((const __nv_bfloat16*)x, dst_row, M, H, KB1, top_k, gs_x, w + L.xrec);
   B200_LAUNCH_CHECK();
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = status, p.H = H;
-  p.dbg = getenv("B200MOE_PF_DEBUG") ? atoi(getenv("B200MOE_PF_DEBUG")) : 0;
-  auto launch = [&](int phase, int KB) -> int { return launch_gemm(p, phase, KB, sms, st); };
+#ifdef B200_PF_ABLATE
+  p.dbg = getenv("B200MOE_PF_ABLATE") ? atoi(getenv("B200MOE_PF_ABLATE")) : 0;
+#endif
   // FC1
-  p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.gs_in = gs, p.gs_out = gs + 1, p.orec = w + L.arec;
+  p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.gs_in = gs_x, p.gs_out = gs_a, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
-  {
-    const int rc1 = launch(1, KB1);
-    if (rc1 != B200MOE_OK) return rc1;
-  }
+  rc = launch_gemm(p, 1, KB1, sms, st);
+  if (rc != B200MOE_OK) return rc;
   // FC2
-  p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.gs_in = gs + 1, p.gs_out = nullptr, p.orec = nullptr;
+  p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.gs_in = gs_a, p.gs_out = 0.f, p.orec = nullptr;
   p.wts = wts, p.y = (__nv_bfloat16*)(w + L.y);
   p.NBLK = H / 128, p.KB = KB2, p.KT = KT2;
-  {
-    const int rc2 = launch(2, KB2);
-    if (rc2 != B200MOE_OK) return rc2;
-  }
+  rc = launch_gemm(p, 2, KB2, sms, st);
+  if (rc != B200MOE_OK) return rc;
   k_prefill_combine<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)(w + L.y), dst_row, M, top_k, H, (__nv_bfloat16*)out);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
@@ -963,7 +1046,9 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   memset(&p, 0, sizeof(p));
   p.ntiles = ntiles, p.tile_expert = tile_expert, p.row_pair = row_pair, p.status = (int*)(w + L.status), p.H = H;
   p.rowscale = rowscale, p.act_g1 = act_g1;
-  p.dbg = getenv("B200MOE_PF_DEBUG") ? atoi(getenv("B200MOE_PF_DEBUG")) : 0;
+#ifdef B200_PF_ABLATE
+  p.dbg = getenv("B200MOE_PF_ABLATE") ? atoi(getenv("B200MOE_PF_ABLATE")) : 0;
+#endif
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;

@@ -4,6 +4,7 @@
 // The reference ranks each pair with an O(P^2) loop in one block; here a stable counting sort over chunks of pairs
 // scales to prefill sizes (P = 65,536 and beyond): no atomic decides any position.
 #include "common.cuh"
+#include <atomic>
 
 namespace b200 {
 
@@ -148,6 +149,22 @@ extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* expert
   return B200MOE_OK;
 }
 
+// An expert id >= E is skipped by the kernels (its pair appears in no table, the tables of the other pairs are as if its
+// slot were empty) and raises a flag inside the scratch memory. This reads the flag of the last call that used `workspace`
+// with the same P and E: 0, or B200MOE_ERR_ARG. Synchronises the stream.
+static int route_read_bad(const int* scratch, int P, int E, cudaStream_t st) {
+  const long long nchunks = (P + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  int bad = 0;
+  B200_CUDA_TRY(cudaMemcpyAsync(&bad, scratch + nchunks * E + E, sizeof(int), cudaMemcpyDeviceToHost, st));
+  B200_CUDA_TRY(cudaStreamSynchronize(st));
+  return bad ? B200MOE_ERR_ARG : B200MOE_OK;
+}
+
+extern "C" int b200moe_route_status(const void* workspace, int P, int E, void* stream) {
+  if (!workspace || P < 0 || E <= 0 || E > ROUTE_MAXE) return B200MOE_ERR_ARG;
+  return route_read_bad((const int*)workspace, P, E, (cudaStream_t)stream);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Router for callers that cannot hand over scratch memory.
 //
@@ -165,16 +182,16 @@ static __device__ __align__(256) int g_route_static[kRouteStaticInts];
 // looked up per device with cudaGetSymbolAddress, with that device current, the first time the entry point runs there.
 static int route_static_address(int** out) {
   constexpr int kMaxDevices = 64;
-  static int* addr[kMaxDevices] = {};
+  static std::atomic<int*> addr[kMaxDevices];   // zero-initialised; threads that race on a first call store the same value
   int dev = 0;
   B200_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return B200MOE_ERR_DEVICE;
-  if (!addr[dev]) {
-    int* p = nullptr;
+  int* p = addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     B200_CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_route_static));
-    addr[dev] = p;
+    addr[dev].store(p, std::memory_order_release);
   }
-  *out = addr[dev];
+  *out = p;
   return B200MOE_OK;
 }
 
@@ -211,4 +228,15 @@ extern "C" int b200moe_route_static(const int* ids, int P, int E, int Umax, int*
     B200_LAUNCH_CHECK();
   }
   return B200MOE_OK;
+}
+
+// The bad-id flag of the last b200moe_route_static call on the current device (same P and E): 0 or B200MOE_ERR_ARG.
+// Synchronises the stream; allocates nothing.
+extern "C" int b200moe_route_static_status(int P, int E, void* stream) {
+  if (P < 0 || E <= 0) return B200MOE_ERR_ARG;
+  if (P > kRouteStaticMaxPairs || E > kRouteStaticMaxExperts) return B200MOE_ERR_LIMIT;
+  int* scratch = nullptr;
+  const int rc = route_static_address(&scratch);
+  if (rc != B200MOE_OK) return rc;
+  return route_read_bad(scratch, P, E, (cudaStream_t)stream);
 }

@@ -1,7 +1,7 @@
 // Single-tile check of the tcgen05 block-scaled FP4 MMA building blocks (TMEM allocation, shared-memory descriptors,
 // scale-factor copies, kind::mxf4nvf4 MMA, accumulator loads): D[128, N] = dequant(A)[128, K] * dequant(B)[N, K]^T.
 // One CTA, operands staged by ordinary stores in the layout a 128B-swizzled TMA box produces. It is the unit test of
-// tcgen05.cuh; the descriptor fields can be overridden from the host so a test can state which encoding is the live one.
+// tcgen05.cuh; the two ways the kernels move block scales into TMEM (tcgen05.cp, or registers + tcgen05.st) can be selected.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -112,6 +112,7 @@ __global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict
 }
 
 
+#ifdef B200_DIAGNOSTICS
 // Issue-cost measurement of the tcgen05 operations the kernels use: `reps` rounds of {ncp scale copies, nmma MMAs of
 // shape 128 x N x 64, ncommit commits}, timed with clock64 around issue and around issue + completion.
 // flags: 1 = alternate between two accumulators; 2 = every round also waits on an mbarrier whose phase completed long
@@ -199,10 +200,13 @@ __global__ void __launch_bounds__(128, 1) k_umma_cost(int N, int reps, int ncp, 
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
+#endif  // B200_DIAGNOSTICS
+
 }  // namespace b200
 
 using namespace b200;
 
+#ifdef B200_DIAGNOSTICS
 // cycles_dev: device int64 x 4 = {issue, completion} cycles of the first and (flags & 16) of the second issuing thread
 extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int flags, int ncommit, long long* cycles_dev, void* stream) {
   if (!cycles_dev || N < 16 || N > 128 || N % 16 || reps < 1 || reps > 4096 || ncp < 0 || ncp > 64 || nmma < 0 || nmma > 64 || ncommit < 0 || ncommit > 8 || flags < 0 || flags > 63) return B200MOE_ERR_ARG;
@@ -212,20 +216,18 @@ extern "C" int b200moe_umma_cost(int N, int reps, int ncp, int nmma, int flags, 
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
+#endif  // B200_DIAGNOSTICS
 
 // a u8 [128, K/2], sfa u8 128x4-swizzled over [128, K/16], b u8 [N, K/2], sfb u8 128x4-swizzled over [N -> 128, K/16],
-// d f32 [128, N]; N a multiple of 16 up to 128, K a multiple of 256 up to 1024. knobs: 8 uint32 on the host, or null
-// for the defaults the library itself uses.
+// d f32 [128, N]; N a multiple of 16 up to 128, K a multiple of 256 up to 1024. scale_path: 0 = block scales copied into
+// TMEM by tcgen05.cp, 1 = through registers by tcgen05.st (the path the layer kernels use). Nothing else is accepted: the
+// descriptor fields themselves are fixed to the two encodings the library uses.
 extern "C" int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
-                                  const unsigned* knobs, int* status_dev, void* stream) {
+                                  int scale_path, int* status_dev, void* stream) {
   if (!a || !sfa || !b || !sfb || !d || !status_dev) return B200MOE_ERR_ARG;
   if (N < 16 || N > 128 || N % 16 || K < 256 || K > 1024 || K % 256) return B200MOE_ERR_SHAPE;
-  ProbeKnobs kn = {16, 1024, 2, 0, 128, 0, 2, 4};
-  if (knobs) kn = {knobs[0], knobs[1], knobs[2], knobs[3], knobs[4], knobs[5], knobs[6], knobs[7]};
-  // a scale copy writes 4 TMEM columns and must start on a multiple of 4 (anything else is a misaligned-address fault);
-  // descriptor offsets are multiples of 16 bytes by construction
-  if ((kn.sf_sbo == 0 && kn.sf_col_step != 4) || kn.sf_col_step % 4 || kn.sf_col_step > 8 || (kn.op_lbo & 15) || (kn.op_sbo & 15) || (kn.sf_lbo & 15) || (kn.sf_sbo & 15) || kn.op_layout > 6)
-    return B200MOE_ERR_ARG;
+  if (scale_path != 0 && scale_path != 1) return B200MOE_ERR_ARG;
+  const ProbeKnobs kn = scale_path == 0 ? ProbeKnobs{16, 1024, 2, 0, 128, 0, 2, 4} : ProbeKnobs{16, 1024, 2, 0, 0, 0, 2, 4};
   const int nkb = K / 256;
   const int smem = 1024 + nkb * (16384 * 2 + 4096);
   B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -86,7 +86,7 @@ class Weights:
                                           _lib.ptr(self.alpha1), _lib.ptr(self.q2), _lib.ptr(self.s2), _lib.ptr(self.alpha2)),
                    "Weights")
         self._h = handle
-        dev = q1.device
+        dev = self.device = q1.device
         self.ws_bytes = int(h.b200moe_layer_workspace_bytes(self._h))
         self.workspace = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=dev)
         # kernel-native copies for the tcgen05 decode kernel (FC1 scale tiles per 64-column block, alpha2 normaliser)
@@ -104,7 +104,14 @@ class Weights:
         self._host_checked: set = set()   # (addresses, tokens) of host tensor sets forward_host has validated
         self._fwd_host = h.b200moe_decode_forward_host
         self._fwd = h.b200moe_decode_forward
+        self._fwd_ex = h.b200moe_decode_forward_ex
         self._ws_ptr = self.workspace.data_ptr()
+
+    def release_checkpoint_layout(self) -> None:
+        """Drop the checkpoint-layout codes and scales (about half of the layer's device memory): every tcgen05 path reads
+        the tile records of the prepack only. Afterwards `set_decode_impl("mma")`, `fc1` and `fc2` raise."""
+        _lib.check(_lib.lib().b200moe_layer_release_checkpoint(self._h), "release_checkpoint_layout")
+        self.q1 = self.q2 = self.s1 = self.s2 = self.s1_linear = self.s2_linear = None
 
     def __del__(self):
         try:
@@ -133,7 +140,7 @@ class Weights:
         if nbytes < 0:
             _lib.check(nbytes, "enable_prefill")
         if workspace is None:
-            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device)
+            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         elif workspace.numel() < nbytes or workspace.dtype != torch.uint8:
             raise ValueError(f"the shared prefill workspace needs {nbytes} bytes of uint8")
         self.prefill = SimpleNamespace(max_tokens=int(max_tokens), gs_x=1.0 / one(a1_scale), gs_a=1.0 / one(a2_scale),
@@ -151,7 +158,7 @@ class Weights:
         if nbytes < 0:
             _lib.check(nbytes, "enable_mid")
         if workspace is None:
-            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.q1.device)
+            workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         elif workspace.numel() < nbytes or workspace.dtype != torch.uint8:
             raise ValueError(f"the shared mid-batch workspace needs {nbytes} bytes of uint8")
         self.mid = SimpleNamespace(max_tokens=int(max_tokens), min_tokens=max(int(min_tokens), MAXM + 1), workspace=workspace)
@@ -188,9 +195,11 @@ class Weights:
     # ------------------------------------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
                 pdl: bool | None = None) -> torch.Tensor:
-        """The MoE forward for a batch of any size (sm120fp4/vllm_backend.py:147-172). `pdl` is accepted for signature
-        compatibility: the two launches of a decode call are always programmatic (B200MOE_PDL_CHAIN=0 in the environment
-        makes the first of them an ordinary stream-ordered launch)."""
+        """The MoE forward for a batch of any size (sm120fp4/vllm_backend.py:147-172). `pdl` (the reference's per-call
+        switch for programmatic dependent launch): None or True - the two launches of a decode call are programmatic, so the
+        call overlaps the tail of its predecessor in the stream and reads topk_ids / topk_weights at kernel entry (they must
+        be complete when the kernel before this call starts; a violation is reported by `status()`); False - ordinary
+        stream-ordered launches, no such requirement."""
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.H:
             raise TypeError(f"x must be bf16 [tokens, {self.H}]")
         m = x.shape[0]
@@ -204,8 +213,11 @@ class Weights:
             out = torch.empty_like(x)
         if m <= MAXM:   # the decode call: one foreign-function call, no slicing
             if m:
-                rc = self._fwd(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(), self._ws_ptr, self.ws_bytes,
-                               torch.cuda.current_stream(x.device).cuda_stream)
+                st = torch.cuda.current_stream(x.device).cuda_stream
+                if pdl is False:
+                    rc = self._fwd_ex(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(), self._ws_ptr, self.ws_bytes, 1, st)
+                else:
+                    rc = self._fwd(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(), self._ws_ptr, self.ws_bytes, st)
                 if rc:
                     _lib.check(rc, "forward")
             return out
@@ -218,7 +230,7 @@ class Weights:
             return out
         for s in range(0, m, MAXM):
             e = min(m, s + MAXM)
-            self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e])
+            self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e], 1 if pdl is False else 0)
         return out
 
     def forward_host(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -242,7 +254,7 @@ class Weights:
             if len(self._host_checked) > 4096:
                 self._host_checked.clear()
             self._host_checked.add(key)
-        st = torch.cuda.current_stream(self.q1.device).cuda_stream
+        st = torch.cuda.current_stream(self.device).cuda_stream
         fn = self._fwd_host
         px, pi, pw, po = key[0], key[1], key[2], key[3]
         for s in range(0, m, MAXM):
@@ -252,9 +264,9 @@ class Weights:
                 _lib.check(rc, "forward_host")
         return out
 
-    def _slice(self, x, ids, wts, out) -> None:
-        _lib.check(_lib.lib().b200moe_decode_forward(self._h, _lib.ptr(x), _lib.ptr(ids), _lib.ptr(wts), x.shape[0], _lib.ptr(out),
-                                                     _lib.ptr(self.workspace), self.ws_bytes, _lib.stream_ptr()), "forward")
+    def _slice(self, x, ids, wts, out, flags: int = 0) -> None:
+        _lib.check(_lib.lib().b200moe_decode_forward_ex(self._h, _lib.ptr(x), _lib.ptr(ids), _lib.ptr(wts), x.shape[0], _lib.ptr(out),
+                                                        _lib.ptr(self.workspace), self.ws_bytes, flags, _lib.stream_ptr()), "forward")
 
     def fc1(self, x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, act: torch.Tensor) -> None:
         """FC1 + SiLU*mul alone: act bf16 [tokens*top_k, I], row = pair index."""

@@ -39,17 +39,150 @@ def check_layer_output(got: torch.Tensor, want: np.ndarray, what=""):
 
 
 def check_w4a4_output(got: torch.Tensor, want: np.ndarray, what=""):
-    """W4A4 bar. The SiLU*mul activations are re-quantised to FP4 between the two GEMMs; an activation that sits on a
-    rounding boundary can take the neighbouring code when the fp32 sum feeding it was accumulated in another order, which
-    moves single outputs by more than fp32 round-off. So: normwise error < 1 %, at most 0.1 % of the elements beyond the
-    layer bar of 2e-2 x output RMS, and none beyond 8e-2 x RMS."""
+    """W4A4 output against the plain fp32 oracle: reported, and held to the normwise bar only. The SiLU*mul activations are
+    re-quantised to FP4 between the two GEMMs, so an activation whose fp32 value sits on a rounding boundary may take the
+    neighbouring code; whether every such difference IS a boundary case, and the 2e-2 x RMS bar on the outputs given the
+    kernel's own codes, is what check_prefill_call establishes."""
     g = got.float().cpu().numpy()
     assert np.isfinite(g).all(), f"{what}: non-finite output"
     rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
     err = np.abs(g - want)
     rel = float(np.linalg.norm(g - want) / max(np.linalg.norm(want), 1e-30))
-    frac = float((err > 2e-2 * rms).mean())
     assert rel < 1e-2, f"{what}: normwise error {rel:.3e}"
-    assert frac <= 1e-3, f"{what}: {frac:.2e} of the elements beyond 2e-2 * rms"
-    assert err.max() <= 8e-2 * rms, f"{what}: max-abs error {err.max():.3e} > 8e-2 * rms ({rms:.3e})"
     return float(err.max()) / rms, rel
+
+
+# ---------------------------------------------------------------------------------------------------- prefill read-back
+REC = 18432
+
+
+def prefill_map(w, max_tokens: int) -> dict:
+    import ctypes as C
+    import sm120fp4_b200._lib as L
+    buf = (C.c_longlong * 14)()
+    L.check(L.lib().b200moe_prefill_workspace_map(w._h, int(max_tokens), buf), "prefill map")
+    names = ("experts", "offsets", "pairs", "ntiles", "tile_expert", "tile_first", "tile_end", "row_pair", "dst_row", "xrec", "arec", "y",
+             "max_tiles", "total")
+    return dict(zip(names, [int(v) for v in buf]))
+
+
+def _i32(ws: torch.Tensor, off: int, n: int) -> np.ndarray:
+    return ws[off:off + 4 * n].view(torch.int32).cpu().numpy()
+
+
+_r = np.arange(128)[:, None]
+_CODE_IDX = (_r * 128 + (((np.arange(128)[None, :] >> 4) ^ (_r & 7)) << 4) + (np.arange(128)[None, :] & 15))          # [row, byte of the 128-byte row]
+_b = np.arange(16)[None, :]
+_SF_IDX = 16384 + (_b >> 2) * 512 + (_r & 31) * 16 + (_r >> 5) * 4 + (_b & 3)                                           # [row, 16-value block]
+
+
+def read_records(ws: torch.Tensor, off: int, ntiles: int, kb: int):
+    """Tile records [ntiles][kb][18432] -> (packed codes u8 [ntiles*128, kb*128], scale bytes u8 [ntiles*128, kb*16], raw)."""
+    raw = ws[off:off + ntiles * kb * REC].cpu().numpy().reshape(ntiles, kb, REC)
+    codes = raw[:, :, _CODE_IDX]            # [t, kb, row, 128]
+    sf = raw[:, :, _SF_IDX]                 # [t, kb, row, 16]
+    return (codes.transpose(0, 2, 1, 3).reshape(ntiles * 128, kb * 128), sf.transpose(0, 2, 1, 3).reshape(ntiles * 128, kb * 16), raw)
+
+
+def check_prefill_call(w, ow, x, ids, wts, out, max_tokens, sample_tokens=None, what=""):
+    """Stage-by-stage parity of one W4A4 prefill call that has just run on `w` (Weights with enable_prefill) against the
+    oracle, from the workspace the call left behind:
+      1. router tables bit-exact;
+      2. the x records (codes and 128x4 scale tiles) byte-equal to oracle.quantize_nvfp4 + to_128x4 of the gathered rows;
+      3. the re-quantised SiLU*mul activations: every scale byte and code a value the reference quantiser can produce from
+         an input inside the fp32-accumulation interval of the exact activation (differences from the nominal quantisation
+         are counted as flips and each must sit within that interval of a rounding boundary);
+      4. the oracle's FC2 + combine computed from the KERNEL'S OWN activation codes against the kernel's output: bf16 max-abs
+         error <= 2e-2 x output RMS with zero exceptions, and inside the exact accumulation bound.
+    Returns a dict of the measured maxima."""
+    from oracle import conformance as C
+    m, k = ids.shape
+    h, inter, e_n = ow.H, ow.I, ow.E
+    kb1, kb2 = (h + 255) // 256, (inter + 255) // 256
+    mp = prefill_map(w, max_tokens)
+    ws = w.prefill.workspace
+    idn, wn, xf = ids.numpy(), wts.numpy(), x.float().numpy()
+    p = m * k
+    umax = min(e_n, p)
+    # ---- 1. router
+    wex, woff, wpairs = O.route_padded(idn, e_n)
+    assert np.array_equal(_i32(ws, mp["experts"], umax), wex), f"{what}: experts"
+    assert np.array_equal(_i32(ws, mp["offsets"], umax + 1), woff), f"{what}: offsets"
+    assert np.array_equal(_i32(ws, mp["pairs"], p), wpairs), f"{what}: pairs"
+    nt = int(_i32(ws, mp["ntiles"], 1)[0])
+    counts = np.diff(woff[: (wex >= 0).sum() + 1])
+    assert nt == int(((counts + 127) // 128).sum()), f"{what}: tile count"
+    row_pair = _i32(ws, mp["row_pair"], nt * 128)
+    tile_expert = _i32(ws, mp["tile_expert"], nt)
+    valid = row_pair >= 0
+    routed = np.nonzero(idn.reshape(-1) >= 0)[0]          # empty slots (negative ids) own no row
+    assert np.array_equal(np.sort(row_pair[valid]), routed), f"{what}: every routed pair owns exactly one row"
+    assert np.array_equal(idn.reshape(-1)[row_pair[valid]], np.repeat(tile_expert, 128)[valid]), f"{what}: rows sit in their expert's tiles"
+    dst_row = _i32(ws, mp["dst_row"], p)
+    assert np.array_equal(np.nonzero(valid)[0], np.sort(dst_row[routed])) and np.array_equal(row_pair[dst_row[routed]], routed)
+    assert (dst_row[idn.reshape(-1) < 0] == -1).all(), f"{what}: empty slots must map to no row"
+    # ---- 2. x records, byte for byte
+    one = np.ones(1, dtype=np.float32) * np.float32(w.prefill.gs_x)
+    qx, sx, _ = O.quantize_nvfp4(xf, one)
+    codes, sfs, raw = read_records(ws, mp["xrec"], nt, kb1)
+    tok_of_row = np.where(valid, row_pair // k, 0)
+    assert np.array_equal(codes[valid][:, : h // 2], qx[tok_of_row[valid]]), f"{what}: x codes differ from the reference quantiser"
+    assert np.array_equal(sfs[valid][:, : h // 16], sx[tok_of_row[valid]]), f"{what}: x block scales differ from the reference quantiser"
+    assert not sfs[~valid].any(), f"{what}: padding rows must carry zero scales"
+    assert not sfs[:, h // 16:].any(), f"{what}: K padding must carry zero scales"
+    for t in sorted({0, nt - 1, int(np.argmin(valid.reshape(nt, 128).sum(axis=1)))}):   # whole scale tiles against to_128x4
+        rows = slice(t * 128, t * 128 + 128)
+        lin = np.where(valid[rows, None], sx[tok_of_row[rows]], 0).astype(np.uint8)
+        lin = np.pad(lin, ((0, 0), (0, kb1 * 16 - lin.shape[1])))
+        sw = O.to_128x4(lin).reshape(-1)
+        assert np.array_equal(sw, raw[t, :, 16384:].reshape(-1)), f"{what}: scale tiles of row tile {t} differ from to_128x4"
+    # ---- 3. / 4. sampled tokens, all of their pairs
+    if sample_tokens is None:
+        sample_tokens = np.arange(m)
+    sample_tokens = np.asarray(sample_tokens)
+    acodes, asfs, _ = read_records(ws, mp["arec"], nt, kb2)
+    gs_a = float(w.prefill.gs_a)
+    xq = C.dequant_exact(qx, sx, float(one[0]))
+    got = out.float().cpu().numpy()
+    res = dict(flips=0, scale_flips=0, ambiguous=0, blocks=0, max_flip=0.0, pairs=0)
+    expect = np.zeros((len(sample_tokens), k, h))
+    ebound = np.zeros((len(sample_tokens), k, h))
+    pos = {int(t): i for i, t in enumerate(sample_tokens)}
+    sel = np.isin(np.arange(m), sample_tokens)
+    for e in np.unique(idn[sel]):
+        if e < 0:
+            continue
+        tok, slot = np.nonzero((idn == e) & sel[:, None])
+        rows = dst_row[tok * k + slot]
+        w1d = C.dequant_exact(ow.q1[e], ow.s1[e].reshape(2 * inter, h // 16), 1.0) * float(ow.alpha1[e])
+        lo, hi, nom = C.fc1_activation_interval(xq[tok], w1d, inter)
+        v = C.requantised_membership(lo, hi, acodes[rows][:, : inter // 2], asfs[rows][:, : inter // 16], gs_a, nominal=nom)
+        assert v["conformant"], f"{what}: expert {e}: re-quantised activations outside what the reference quantiser can produce: {v}"
+        res["flips"] += v["code_flips"]; res["scale_flips"] += v["scale_flips"]; res["ambiguous"] += v["ambiguous_blocks"]
+        res["blocks"] += v["blocks"]; res["pairs"] += len(rows)
+        res["max_flip"] = max(res["max_flip"], v.get("max_flip_distance_over_halfwidth", 0.0))
+        a_gpu = C.dequant_exact(acodes[rows][:, : inter // 2], asfs[rows][:, : inter // 16], gs_a)
+        w2d = C.dequant_exact(ow.q2[e], ow.s2[e].reshape(h, inter // 16), 1.0) * float(ow.alpha2[e])
+        c, cb, _ = C.interval_gemm(a_gpu, a_gpu, w2d)
+        wf = wn[tok, slot].astype(np.float64)[:, None]
+        r_lo, r_hi = C._round_bf16_interval((c - cb) * wf, (c + cb) * wf, 4 * C.U32)
+        for i, (t, sl) in enumerate(zip(tok, slot)):
+            expect[pos[int(t)], sl] = (r_lo[i] + r_hi[i]) / 2
+            ebound[pos[int(t)], sl] = (r_hi[i] - r_lo[i]) / 2
+    nominal = np.zeros((len(sample_tokens), h))
+    for sl in range(k):                       # the kernel's combine: fp32 sum in slot order
+        nominal = nominal + expect[:, sl]
+    bound = ebound.sum(axis=1) + k * C.U32 * np.abs(expect).sum(axis=1)
+    bound = bound + 0.5 * C.ulp(np.abs(nominal) + bound, "bf16")
+    g = got[sample_tokens]
+    plain = O.moe_reference(xf[sample_tokens], ow, idn[sample_tokens], wn[sample_tokens], act_quant=True) if w.prefill.gs_x == 1.0 and gs_a == 1.0 else nominal
+    rms = float(np.sqrt((plain.astype(np.float64) ** 2).mean()))
+    err = np.abs(g - nominal)
+    res["max_abs_over_rms_own_codes"] = float(err.max() / rms)
+    res["max_err_over_bound"] = float((err / bound).max())
+    res["max_abs_over_rms_plain_oracle"] = float(np.abs(g - plain).max() / rms)
+    res["normwise_plain_oracle"] = float(np.linalg.norm(g - plain) / max(np.linalg.norm(plain), 1e-30))
+    assert err.max() <= 2e-2 * rms, f"{what}: FC2 + combine from the kernel's own codes: max-abs {err.max():.3e} > 2e-2 x rms {rms:.3e}"
+    assert (err <= bound).all(), f"{what}: FC2 + combine outside the exact accumulation bound ({res['max_err_over_bound']:.2f} x)"
+    assert res["normwise_plain_oracle"] < 1e-2, f"{what}: normwise error against the plain oracle {res['normwise_plain_oracle']:.3e}"
+    return res

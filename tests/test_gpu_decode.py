@@ -220,3 +220,91 @@ def test_host_buffer_entry_point_equals_the_device_call(m):
     w.status()
     with pytest.raises(TypeError):
         w.forward_host(hx.cuda(), hid, hw, hout)
+
+
+def test_routing_inputs_written_by_the_kernel_just_before_the_call():
+    """topk_ids / topk_weights are read at kernel entry, before the stream dependency of the programmatic launch has resolved.
+    Here they are written by a copy kernel enqueued immediately before every call, alternating between two routings without
+    any synchronisation in between: every output must be the one of its own routing, and no call may report stale inputs."""
+    cfg, w, ow = layer("mid")
+    sets = []
+    for seed in (41, 42):
+        x, ids, wts = inputs(cfg, 9, seed)
+        want = run(w, x, ids, wts).clone()
+        check_layer_output(want, O.moe_reference(x.float().numpy(), ow, ids.numpy(), wts.numpy()), f"seed {seed}")
+        sets.append((x.cuda(), ids.cuda(), wts.cuda(), want))
+    ids_live, wts_live = torch.empty_like(sets[0][1]), torch.empty_like(sets[0][2])
+    outs = []
+    for i in range(24):
+        xd, idd, wd, _ = sets[i & 1]
+        ids_live.copy_(idd)
+        wts_live.copy_(wd)
+        outs.append(w.forward(xd, ids_live, wts_live))
+    w.status()                      # raises on B200MOE_ERR_ORDER
+    for i, o in enumerate(outs):
+        assert torch.equal(o, sets[i & 1][3]), f"call {i} used stale routing inputs"
+
+
+def test_ordered_launch_flag_gives_the_same_bits():
+    """pdl=False: both kernels of the call are ordinary stream-ordered launches (the reference's per-call PDL switch)."""
+    cfg, w, ow = layer("mid")
+    for m in (3, 16, 40):
+        x, ids, wts = inputs(cfg, m, 7000 + m)
+        a = run(w, x, ids, wts).clone()
+        b = w.forward(x.cuda(), ids.cuda(), wts.cuda(), pdl=False)
+        w.status()
+        assert torch.equal(a, b)
+
+
+def test_activation_range_is_reported_not_clipped_silently():
+    """The FC1 -> FC2 activations are expanded with a fixed first-term scale: block maxima above 2688 / scale are clipped, and
+    the status call says so; with a scale that covers the range the same input meets the bar again."""
+    import sm120fp4_b200._lib as L
+    cfg, w, ow = layer("tiny")
+    x, ids, wts = inputs(cfg, 6, 77)
+    x = (x.float() * 250.0).to(torch.bfloat16)
+    try:
+        w.forward(x.cuda(), ids.cuda(), wts.cuda())
+        with pytest.raises(L.B200MoEError) as ei:
+            w.status()
+        assert ei.value.code == L.ERR_RANGE
+        w.status()                                   # the flag is cleared by the read
+        w.set_act_scale(8.0 / 4096.0)
+        out = run(w, x, ids, wts)
+        check_layer_output(out, O.moe_reference(x.float().numpy(), ow, ids.numpy(), wts.numpy()), "large activations, wider scale")
+    finally:
+        w.set_act_scale(8.0)
+
+
+def test_fifty_calls_are_bit_identical():
+    """The reference's determinism check (sm120fp4/kernels/moe_layer.py:177-181): 50 calls, one result."""
+    for name, m, routing in (("qwen", 16, "random"), ("qwen", 1, "fixed8"), ("mid", 7, "random")):
+        cfg, w, _ = layer(name)
+        x, ids, wts = inputs(cfg, m, 123, routing)
+        xd, idd, wd = x.cuda(), ids.cuda(), wts.cuda()
+        first = w.forward(xd, idd, wd).clone()
+        for _ in range(50):
+            assert torch.equal(w.forward(xd, idd, wd), first), f"{name} m={m}"
+        w.status()
+
+
+def test_released_checkpoint_layout_keeps_the_tensor_core_paths():
+    import sm120fp4_b200._lib as L
+    from helpers import make_layer
+    cfg = SHAPES["mid"]
+    w, ow = make_layer(cfg["experts"], cfg["hidden"], cfg["inter"], cfg["top_k"], seed=21)
+    x, ids, wts = inputs(cfg, 12, 5)
+    a = run(w, x, ids, wts).clone()
+    w.release_checkpoint_layout()
+    assert w.q1 is None
+    assert torch.equal(run(w, x, ids, wts), a)
+    with pytest.raises(L.B200MoEError):
+        w.set_decode_impl("mma")
+    with pytest.raises(L.B200MoEError):
+        w.fc1(x.cuda(), ids.cuda(), wts.cuda(), torch.empty(12 * cfg["top_k"], cfg["inter"], dtype=torch.bfloat16, device="cuda"))
+    x2, ids2, wts2 = inputs(cfg, 100, 6)
+    w.enable_prefill(max_tokens=128)
+    out = w.forward(x2.cuda(), ids2.cuda(), wts2.cuda())
+    w.prefill_status()
+    from helpers import check_w4a4_output
+    check_w4a4_output(out, O.moe_reference(x2.float().numpy(), ow, ids2.numpy(), wts2.numpy(), act_quant=True), "prefill after release")

@@ -9,9 +9,8 @@ from oracle import nvfp4_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def probe(a, b, knobs=None):
+def probe(a, b, scale_path=0):
     """a [128, K], b [N, K] fp32 -> (D from the tensor cores, D expected) with NVFP4 operands, global scale 1."""
-    import ctypes as C
     import sm120fp4_b200._lib as L
     one = np.ones(1, dtype=np.float32)
     qa, sa, _ = O.quantize_nvfp4(a, one)
@@ -22,8 +21,7 @@ def probe(a, b, knobs=None):
     d = torch.full((128, n), float("nan"), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ta, tsa, tb, tsb = dev(qa), dev(O.to_128x4(sa)), dev(qb), dev(O.to_128x4(sb))
-    kn = None if knobs is None else (C.c_uint * 8)(*knobs)
-    L.check(L.lib().b200moe_umma_probe(L.ptr(ta), L.ptr(tsa), L.ptr(tb), L.ptr(tsb), n, k, L.ptr(d), kn, L.ptr(status), L.stream_ptr()), "probe")
+    L.check(L.lib().b200moe_umma_probe(L.ptr(ta), L.ptr(tsa), L.ptr(tb), L.ptr(tsb), n, k, L.ptr(d), scale_path, L.ptr(status), L.stream_ptr()), "probe")
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a bounded wait ran out in the probe kernel"
     return d.cpu().numpy(), want.astype(np.float32)
@@ -43,11 +41,11 @@ def test_block_scaled_fp4_tile_matches_oracle(n, k):
 @pytest.mark.parametrize("n,k", [(64, 256), (16, 1024), (128, 512)])
 def test_scales_through_registers_match_the_copy_path(n, k):
     """The decode kernel moves scale tiles shared memory -> registers -> TMEM (tcgen05.st by four warps, one per lane
-    quadrant) instead of tcgen05.cp; descriptor knob sf_sbo = 0 selects that path in the probe."""
+    quadrant) instead of tcgen05.cp; scale_path = 1 selects that path in the probe, and nothing but 0 and 1 is accepted."""
     rng = np.random.default_rng(n * 77 + k)
     a = rng.standard_normal((128, k)).astype(np.float32) * 2
     b = rng.standard_normal((n, k)).astype(np.float32)
     got_cp, want = probe(a, b)
-    got_st, _ = probe(a, b, knobs=(16, 1024, 2, 0, 0, 0, 2, 4))
+    got_st, _ = probe(a, b, scale_path=1)
     assert np.array_equal(got_cp, got_st)
     assert np.abs(got_st - want).max() <= 1e-3 * np.abs(want).max() + 1e-4

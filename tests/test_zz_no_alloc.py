@@ -29,7 +29,8 @@ def test_static_router_matches_the_workspace_router_twice_in_a_row():
     """Two back-to-back calls with different inputs: the second must not see anything the first left in the shared array.
     Integer tables: the comparison is exact."""
     rng = np.random.default_rng(11)
-    calls = [(4096, 128, 8), (37, 256, 6)]          # a large batch first, then a small ragged one over more experts
+    calls = [(4096, 128, 8), (37, 256, 6), (8192, 256, 8)]   # a large batch, a small ragged one over more experts, then the
+                                                             # stated limits: 65,536 pairs over 256 experts
     for tokens, experts_n, top_k in calls:
         ids_np = np.argsort(rng.random((tokens, experts_n)), axis=1)[:, :top_k].astype(np.int32)
         ids = torch.from_numpy(ids_np).cuda()
@@ -45,3 +46,19 @@ def test_static_router_rejects_sizes_beyond_its_built_in_scratch():
     t = torch.zeros(8, dtype=torch.int32, device="cuda")
     assert h.b200moe_route_static(L.ptr(t), 65537, 128, 8, L.ptr(t), L.ptr(t), L.ptr(t), L.stream_ptr()) == L.ERR_LIMIT
     assert h.b200moe_route_static(L.ptr(t), 8, 257, 8, L.ptr(t), L.ptr(t), L.ptr(t), L.stream_ptr()) == L.ERR_LIMIT
+
+
+def test_static_router_reports_an_expert_id_out_of_range():
+    """An id >= E is skipped and flagged; the status call (which allocates nothing either) returns the argument error."""
+    import sm120fp4_b200._lib as L
+    h = L.lib()
+    ids = torch.tensor([[0, 3], [9, 1], [2, 2]], dtype=torch.int32, device="cuda")     # 9 is out of range for 8 experts
+    ex = torch.empty(6, dtype=torch.int32, device="cuda")
+    off = torch.empty(7, dtype=torch.int32, device="cuda")
+    pairs = torch.full((6,), -7, dtype=torch.int32, device="cuda")
+    L.check(h.b200moe_route_static(L.ptr(ids), 6, 8, 6, L.ptr(ex), L.ptr(off), L.ptr(pairs), L.stream_ptr()), "route_static")
+    assert h.b200moe_route_static_status(6, 8, L.stream_ptr()) == L.ERR_ARG
+    assert off.cpu().tolist()[:5] == [0, 1, 2, 4, 5] and ex.cpu().tolist() == [0, 1, 2, 3, -1, -1]
+    good = torch.tensor([[0, 3], [7, 1], [2, 2]], dtype=torch.int32, device="cuda")
+    L.check(h.b200moe_route_static(L.ptr(good), 6, 8, 6, L.ptr(ex), L.ptr(off), L.ptr(pairs), L.stream_ptr()), "route_static")
+    assert h.b200moe_route_static_status(6, 8, L.stream_ptr()) == 0
