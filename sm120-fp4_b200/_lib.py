@@ -5,8 +5,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libb200moe.so"
+# B200MOE_LIB: load another build of the same library (the diagnostic build of `build.py --diag`); default: the product build
+LIB_PATH = Path(os.environ["B200MOE_LIB"]) if os.environ.get("B200MOE_LIB") else _PKG / "libb200moe.so"
 _lib = None
 
 ERR_ARG, ERR_SHAPE, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT, ERR_WORKSPACE, ERR_LIMIT, ERR_RANGE, ERR_ORDER = -1, -2, -3, -4, -5, -6, -7, -8, -9

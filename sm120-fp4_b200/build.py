@@ -20,10 +20,12 @@ FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-li
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 
-if os.environ.get("B200MOE_DIAG") == "1" or os.environ.get("B200MOE_TIMERS") == "1":
-    # diagnostic build: per-worker cycle counters in the decode kernel, ablation switches of the prefill GEMM, and the entry
-    # points of include/b200moe_diag.h. Not the library that ships.
+DIAG = "--diag" in sys.argv or os.environ.get("B200MOE_DIAG") == "1"
+if DIAG:
+    # diagnostic build (libb200moe_diag.so, loaded with B200MOE_LIB=<path>): per-worker cycle counters in the decode kernel,
+    # ablation switches of the prefill GEMM, and the entry points of include/b200moe_diag.h. Not the library that ships.
     FLAGS += ["-DB200_TIMERS", "-DB200_PF_ABLATE", "-DB200_DIAGNOSTICS"]
+    LIB = PKG / "libb200moe_diag.so"
 
 
 def nvcc() -> str:
@@ -48,7 +50,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     if not force and not stale():
         return LIB
     objs = []
-    out_dir = PKG / "build"
+    out_dir = PKG / ("build_diag" if DIAG else "build")
     out_dir.mkdir(exist_ok=True)
     procs = []
     for src in sources():

@@ -7,7 +7,22 @@ import torch
 from . import _lib
 
 
+_WS: dict = {}   # (device index, stream) -> scratch tensor, grown on demand: steady-state calls allocate nothing
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream)
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        _WS[key] = ws
+    return ws
+
+
 def route(ids: torch.Tensor, num_experts: int, experts: torch.Tensor, offsets: torch.Tensor, pairs: torch.Tensor) -> None:
+    """Fills the caller's tables on the current stream. The scratch memory of the counting sort is kept per (device, stream)
+    and only grows, so a call of a size seen before allocates nothing (it can be captured into a CUDA graph) and calls on
+    different streams do not share scratch."""
     if ids.dtype != torch.int32 or experts.dtype != torch.int32 or offsets.dtype != torch.int32 or pairs.dtype != torch.int32:
         raise TypeError("route takes int32 tensors")
     p, umax = ids.numel(), experts.numel()
@@ -18,9 +33,10 @@ def route(ids: torch.Tensor, num_experts: int, experts: torch.Tensor, offsets: t
     nbytes = h.b200moe_route_workspace_bytes(p, num_experts)
     if nbytes < 0:
         _lib.check(int(nbytes), "route")
-    ws = torch.empty(max(int(nbytes), 4), dtype=torch.uint8, device=ids.device)
+    st = _lib.stream_ptr()
+    ws = _workspace(ids.device, st, int(nbytes))
     _lib.check(h.b200moe_route(_lib.ptr(ids), p, num_experts, umax, _lib.ptr(experts), _lib.ptr(offsets), _lib.ptr(pairs), _lib.ptr(ws),
-                               ws.numel(), _lib.stream_ptr()), "route")
+                               ws.numel(), st), "route")
 
 
 def route_tables(ids: torch.Tensor, num_experts: int):

@@ -15,7 +15,7 @@ from types import SimpleNamespace
 
 import torch
 
-from . import _lib
+from . import _lib, moe_layer
 from .layouts import padded_sf_shape, to_128x4
 
 ENV = "SM120FP4_MOE"
@@ -37,6 +37,28 @@ def prefill_mode() -> str:
 
 def prefill_explicit() -> bool:
     return os.environ.get(PREFILL_ENV, "") in ("cutlass", "w4a4")
+
+
+_KERNELS = None
+
+
+def kernels() -> SimpleNamespace:
+    """The kernel groups under the names the reference's loader returns (sm120fp4/vllm_backend.py:64-80): `layer` (the
+    selection rule), `route`, `fc1_cc`, `fc2_cc`, `fc1_tc`, `fc2_pf`. Binding only: the library is prebuilt."""
+    global _KERNELS
+    if _KERNELS is None:
+        from . import kernels as K, moe_layer
+        _KERNELS = SimpleNamespace(layer=moe_layer, route=K.moe.build(), fc1_cc=K.fc1.build(), fc2_cc=K.fc2.build(),
+                                   fc1_tc=K.fc1m.build(), fc2_pf=K.fc2p.build())
+    return _KERNELS
+
+
+def set_pdl(k: SimpleNamespace, on: bool) -> None:
+    """The reference's module-wide switch (sm120fp4/vllm_backend.py:83-87); here `forward(..., pdl=...)` carries it per call."""
+    k.fc1_cc.fc1_set_pdl(on)
+    k.fc2_cc.fc2_set_pdl(on)
+    k.fc1_tc.fc1_mma_set_pdl(on)
+    k.fc2_pf.fc2_pf_set_pdl(on)
 
 
 def rotate_halves(t: torch.Tensor, inter: int) -> torch.Tensor:
@@ -102,6 +124,8 @@ class Weights:
         self.prefill = None   # set by enable_prefill: the W4A4 path above MAXM tokens
         self.mid = None       # set by enable_mid: one W4A16 call for 17..max_tokens tokens
         self._host_checked: set = set()   # (addresses, tokens) of host tensor sets forward_host has validated
+        from . import kernels as _k
+        _k.register(self)
         self._fwd_host = h.b200moe_decode_forward_host
         self._fwd = h.b200moe_decode_forward
         self._fwd_ex = h.b200moe_decode_forward_ex
@@ -221,14 +245,17 @@ class Weights:
                 if rc:
                     _lib.check(rc, "forward")
             return out
-        if self.prefill is not None and prefill_mode() != "slices":   # W4A4, as the reference's batches above 16 tokens in that mode
+        path = moe_layer.regime(m, self.H, self.I, prefill=self.prefill is not None and prefill_mode() != "slices",
+                                mid_max_tokens=self.mid.max_tokens if self.mid is not None else 0,
+                                mid_min_tokens=self.mid.min_tokens if self.mid is not None else 0)
+        if path == "prefill_w4a4":   # W4A4, as the reference's batches above 16 tokens in that mode
             return self.prefill.forward(x, ids, wts, out)
-        if self.mid is not None and self.mid.min_tokens <= m <= self.mid.max_tokens:   # W4A16 in one call (by default from 33 tokens: up to two slices of a full layer the decode kernel is ahead)
+        if path == "mid_w4a16":      # W4A16 in one call
             _lib.check(_lib.lib().b200moe_mid_forward(self._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, out.data_ptr(),
                                                       self.mid.workspace.data_ptr(), self.mid.workspace.numel(), self.mid.max_tokens,
                                                       torch.cuda.current_stream(x.device).cuda_stream), "mid forward")
             return out
-        for s in range(0, m, MAXM):
+        for s in range(0, m, MAXM):  # "decode_slices"
             e = min(m, s + MAXM)
             self._slice(x[s:e], ids[s:e], wts[s:e], out[s:e], 1 if pdl is False else 0)
         return out

@@ -105,10 +105,15 @@ def check_prefill_call(w, ow, x, ids, wts, out, max_tokens, sample_tokens=None, 
     p = m * k
     umax = min(e_n, p)
     # ---- 1. router
-    wex, woff, wpairs = O.route_padded(idn, e_n)
+    flat = idn.reshape(-1)
+    live = np.nonzero(flat >= 0)[0]                        # empty slots (negative ids) appear in no table
+    ex_l, off_l, order = O.route(flat[live])
+    wex = np.full(umax, -1, dtype=np.int32)
+    woff = np.full(umax + 1, live.size, dtype=np.int32)
+    wex[: ex_l.size], woff[: off_l.size] = ex_l, off_l
     assert np.array_equal(_i32(ws, mp["experts"], umax), wex), f"{what}: experts"
     assert np.array_equal(_i32(ws, mp["offsets"], umax + 1), woff), f"{what}: offsets"
-    assert np.array_equal(_i32(ws, mp["pairs"], p), wpairs), f"{what}: pairs"
+    assert np.array_equal(_i32(ws, mp["pairs"], p)[: live.size], live[order]), f"{what}: pairs"
     nt = int(_i32(ws, mp["ntiles"], 1)[0])
     counts = np.diff(woff[: (wex >= 0).sum() + 1])
     assert nt == int(((counts + 127) // 128).sum()), f"{what}: tile count"

@@ -38,10 +38,24 @@ def test_host_side_mirrors():
     import torch
     from sm120fp4_b200 import moe_layer, padded_sf_shape, vllm_backend as vb
     assert padded_sf_shape(100, 5) == (128, 8) and padded_sf_shape(1536, 128) == (1536, 128)
-    assert moe_layer.choice(1) == moe_layer.choice(16) and moe_layer.use_pdl(1) is False
-    assert moe_layer.regime(16) == "decode_w4a16" and moe_layer.regime(17) == "prefill_w4a4"
+    # the selection rule states what runs (sm120fp4/kernels/moe_layer.py:60-93 is the reference's rule for its kernels)
+    assert moe_layer.choice(1) == moe_layer.choice(16) == ("tcgen05_fused", "tcgen05_fused") and moe_layer.use_pdl(1) and moe_layer.use_pdl(16)
+    assert moe_layer.choice(4, 2816, 704) == ("tcgen05_fused", "tcgen05_fused")            # the Gemma shape: no crossover below 16 tokens
+    assert moe_layer.choice(4, 4096, 1024) == ("mma_sync_fused", "mma_sync_fused")          # x scale tiles no longer fit in TMEM
+    assert moe_layer.regime(16) == "decode" and moe_layer.regime(17) == "decode_slices"
+    assert moe_layer.regime(17, prefill=True) == "prefill_w4a4" and moe_layer.regime(4096, prefill=True, mid_max_tokens=256) == "prefill_w4a4"
+    assert moe_layer.regime(32, mid_max_tokens=256, mid_min_tokens=33) == "decode_slices" and moe_layer.regime(33, mid_max_tokens=256) == "mid_w4a16"
+    assert moe_layer.regime(257, mid_max_tokens=256) == "decode_slices" and moe_layer.regime(64, 4096, 1024, mid_max_tokens=256) == "decode_slices"
+    assert moe_layer.regime(20, mid_max_tokens=128, mid_min_tokens=17) == "mid_w4a16"
     with pytest.raises(ValueError):
         moe_layer.choice(17)
+    with pytest.raises(ValueError):
+        moe_layer.choice(1, 2000, 768)
+    k = vb.kernels()                                                                         # the reference's loader surface
+    assert k.layer is moe_layer and callable(k.route.route) and callable(k.fc1_cc.fc1_w4a16) and callable(k.fc1_tc.fc1_mma)
+    assert callable(k.fc2_cc.fc2_w4a16) and callable(k.fc2_pf.fc2_pf) and moe_layer.fc1.build() is k.fc1_cc
+    vb.set_pdl(k, False)
+    vb.set_pdl(k, True)
     t = torch.arange(24).reshape(2, 4, 3)
     assert torch.equal(vb.rotate_halves(vb.rotate_halves(t, 2), 2), t)
     assert torch.equal(vb.rotate_halves(t, 2)[:, :2], t[:, 2:])
