@@ -26,6 +26,7 @@ sys.path.insert(0, str(ROOT))
 
 MS = (1, 2, 4, 8, 16)
 ROUTINGS = ("random", "fixed8")
+EP_TRANSPORT = os.environ.get("B200MOE_EP_TRANSPORT", "nccl")   # "peer": rows stored straight into the peers' receive arrays
 
 
 def peaks():
@@ -34,18 +35,6 @@ def peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
-
-
-def cases(cfg, only=None):
-    from sm120fp4_b200 import synth
-    out = []
-    for routing in ROUTINGS:
-        for m in MS:
-            if only and f"{m}:{routing}" not in only:
-                continue
-            x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 1000 + m if routing == "random" else 7, routing)
-            out.append(dict(m=m, routing=routing, x=x, ids=ids, wts=wts, touched=int(torch.unique(ids).numel())))
-    return out
 
 
 class ClockSampler:
@@ -114,27 +103,41 @@ def time_region(fn, sync):
     return s.elapsed_time(e)
 
 
-def run_ours(a):
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+def flush_l2(buf):
+    buf.add_(1)   # a read-modify-write over a buffer larger than L2
+
+
+def decode_sweep(cfg, layers, dev, steps, warmup, use_graph, rank, world, dist, eps=None, only=None, e2e=True, cold=True):
+    """The ten-case decode sweep over a chain of layer calls. world == 1: `Weights.forward` per call. world > 1: every call
+    goes through `ExpertParallelMoE` over sharded experts (dispatch and combine exchanges inside the timed region); every
+    rank brings its own batch of M tokens per case. Returns per-case microseconds, the step time (max over ranks), the
+    end-to-end step time and the bytes of a step."""
     from sm120fp4_b200 import synth
-    cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
-    from sm120fp4_b200.ep import shard_range
-    layers = build_layers(cfg, a.layers, dev)
-    cs = cases(cfg, set(a.cases.split(",")) if a.cases else None)
-    for c in cs:
-        c["xd"], c["idd"], c["wd"] = c["x"].to(dev), c["ids"].to(dev), c["wts"].to(dev)
-        c["out"] = torch.empty_like(c["xd"])
-        c["hx"], c["hid"], c["hw"] = c["x"].pin_memory(), c["ids"].pin_memory(), c["wts"].pin_memory()
-        c["hout"] = torch.empty_like(c["x"]).pin_memory()
-    ebytes = layers[0].expert_bytes()
+    e, h, k = cfg["experts"], cfg["hidden"], cfg["top_k"]
+    cs = []
+    for routing in ROUTINGS:
+        for m in MS:
+            if only and f"{m}:{routing}" not in only:
+                continue
+            seed = (1000 + m if routing == "random" else 7) + 7919 * rank
+            x, ids, wts = synth.decode_inputs(m, e, h, k, seed, routing)
+            c = dict(m=m, routing=routing, x=x, ids=ids, wts=wts, touched=int(torch.unique(ids).numel()))
+            c["xd"], c["idd"], c["wd"] = x.to(dev), ids.to(dev), wts.to(dev)
+            c["out"] = torch.empty_like(c["xd"])
+            c["hx"], c["hid"], c["hw"] = x.pin_memory(), ids.pin_memory(), wts.pin_memory()
+            c["hout"] = torch.empty_like(x).pin_memory()
+            cs.append(c)
+    n_layers = len(layers)
+
+    def call(li, c, xd, idd, wd, out):
+        if eps is None:
+            layers[li].forward(xd, idd, wd, out=out)
+        else:
+            eps[li].forward(xd, idd, wd, out=out)
+
+    def chain(c):
+        for li in range(n_layers):
+            call(li, c, c["xd"], c["idd"], c["wd"], c["out"])
 
     def sync():
         torch.cuda.synchronize()
@@ -142,30 +145,22 @@ def run_ours(a):
             dist.barrier()
             torch.cuda.synchronize()
 
-    # ---- one CUDA graph per case: the chain of L layer calls (device-resident inputs)
-    def chain(c):
-        for w in layers:
-            w.forward(c["xd"], c["idd"], c["wd"], out=c["out"])
-
-    graphs, use_graph = {}, not a.no_graph
-    stream = torch.cuda.Stream()
-    with torch.cuda.stream(stream):
-        for c in cs:
-            chain(c)   # first call outside capture (function attributes, lazy init)
-        torch.cuda.synchronize()
-        if use_graph:
-            try:
-                for idx, c in enumerate(cs):
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=stream):
-                        chain(c)
-                    graphs[idx] = g
-            except Exception as ex:  # noqa: BLE001
-                print(f"graph capture unavailable ({type(ex).__name__}: {ex}); timing direct launches", file=sys.stderr)
-                graphs, use_graph = {}, False
-                torch.cuda.synchronize()
-    for w in layers:
-        w.status()
+    graphs = {}
+    stream = torch.cuda.current_stream()
+    for c in cs:
+        chain(c)   # first call outside capture (function attributes, lazy init, buffer allocation)
+    sync()
+    if use_graph:
+        try:
+            for idx, c in enumerate(cs):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    chain(c)
+                graphs[idx] = g
+        except Exception as ex:  # noqa: BLE001
+            print(f"graph capture unavailable ({type(ex).__name__}: {ex}); timing direct launches", file=sys.stderr)
+            graphs, use_graph = {}, False
+            sync()
 
     def run_case(idx):
         if use_graph:
@@ -177,86 +172,155 @@ def run_ours(a):
         for idx in range(len(cs)):
             run_case(idx)
 
-    def e2e_step():   # the C-ABI call with host buffers: copies in, layer, copy out, all inside the timed region
+    def e2e_step():   # host buffers in, host buffers out, every call, inside the timed region
         for c in cs:
-            for w in layers:
-                w.forward_host(c["hx"], c["hid"], c["hw"], c["hout"])
+            if eps is None:
+                for w in layers:
+                    w.forward_host(c["hx"], c["hid"], c["hw"], c["hout"])
+            else:
+                for li in range(n_layers):
+                    xd = c["hx"].to(dev, non_blocking=True)
+                    idd, wd = c["hid"].to(dev, non_blocking=True), c["hw"].to(dev, non_blocking=True)
+                    call(li, c, xd, idd, wd, c["out"])
+                    c["hout"].copy_(c["out"], non_blocking=True)
 
-    with torch.cuda.stream(stream):
-        for _ in range(a.warmup):
-            step()
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        per_case_ms = np.zeros(len(cs))
-        sync()
-        t_total = 0.0
-        for _ in range(a.steps):
-            for idx in range(len(cs)):
-                ms = time_region(lambda: run_case(idx), torch.cuda.synchronize)
-                per_case_ms[idx] += ms
-                t_total += ms
-        sync()
-        # the whole-step time, all cases back to back in one timed region (this is the reported step time)
-        step_ms = time_region(lambda: [step() for _ in range(a.steps)], sync) / a.steps
-        for _ in range(max(1, a.warmup // 2)):
+    for _ in range(warmup):
+        step()
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    per_case_ms = np.zeros(len(cs))
+    sync()
+    for _ in range(steps):
+        for idx in range(len(cs)):
+            per_case_ms[idx] += time_region(lambda: run_case(idx), sync if dist is not None else torch.cuda.synchronize)
+    sync()
+    step_ms = time_region(lambda: [step() for _ in range(steps)], sync) / steps   # all cases back to back: the reported step time
+    e2e_ms = None
+    if e2e:
+        for _ in range(max(1, warmup // 2)):
             e2e_step()
-        e2e_ms = time_region(lambda: [e2e_step() for _ in range(a.steps)], sync) / a.steps
-        clocks = sampler.stop() if rank == 0 else None
+        e2e_ms = time_region(lambda: [e2e_step() for _ in range(steps)], sync) / steps
+    clocks = sampler.stop() if rank == 0 else None
+    cold_us = None
+    if cold and eps is None:
+        # one layer call alone with L2 flushed before it (the reference's method, sm120fp4/kernels/micro_floor.py:189-222):
+        # nothing of the call overlaps a predecessor, and its weights come from HBM
+        flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+        cold_us = []
+        for c in cs:
+            ts = []
+            for r in range(7):
+                w = layers[r % n_layers]
+                flush_l2(flush)
+                ts.append(time_region(lambda: w.forward(c["xd"], c["idd"], c["wd"], out=c["out"]), torch.cuda.synchronize) * 1e3)
+            cold_us.append(sorted(ts)[len(ts) // 2])
+        del flush
     for w in layers:
         w.status()
     if dist is not None:
-        t = torch.tensor([step_ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([step_ms, e2e_ms or 0.0] + list(per_case_ms), device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms, e2e_ms = float(t[0]), float(t[1])
+        step_ms, e2e_ms, per_case_ms = float(t[0]), (float(t[1]) if e2e else None), t[2:].cpu().numpy()
+        tt = torch.tensor([c["touched"] for c in cs], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt)                       # sum over ranks of the experts each rank's own batch touches
+        touched = tt.cpu().numpy()
+    else:
+        touched = np.array([c["touched"] for c in cs], dtype=np.float64)
+    ebytes = 3 * cfg["inter"] * cfg["hidden"] // 2 + 3 * cfg["inter"] * cfg["hidden"] // 16
+    detail = []
+    for idx, c in enumerate(cs):
+        us = per_case_ms[idx] / steps / n_layers * 1e3
+        gbs = touched[idx] * ebytes / (us * 1e-6) / 1e9
+        d = {"m": c["m"], "routing": c["routing"], "touched_experts": int(touched[idx]), "us_per_layer": round(us, 2), "hbm_gbs": round(gbs, 1)}
+        if cold_us is not None:
+            d["us_single_layer_cold"] = round(cold_us[idx], 2)
+        detail.append(d)
+    io = dict(h2d=int(sum(c["x"].numel() * 2 + c["ids"].numel() * 4 + c["wts"].numel() * 4 for c in cs) * n_layers),
+              d2h=int(sum(c["x"].numel() * 2 for c in cs) * n_layers))
+    return dict(detail=detail, step_ms=step_ms, e2e_ms=e2e_ms, step_bytes=float(touched.sum()) * ebytes * n_layers, per_case_ms=per_case_ms,
+                clocks=clocks, graph=use_graph, cases=len(cs), io=io, ebytes=ebytes)
+
+
+def run_ours(a):
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    from sm120fp4_b200 import synth
+    from sm120fp4_b200.ep import ExpertParallelMoE, shard_range
+    cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
+    only = set(a.cases.split(",")) if a.cases else None
+    stream = torch.cuda.Stream()
     extras = {}
-    if not a.no_extras:
-        with torch.cuda.stream(stream):
+    with torch.cuda.stream(stream):
+        if world == 1:
+            layers = build_layers(cfg, a.layers, dev)
+            eps = None
+        else:   # experts sharded over the ranks: every layer call is dispatch -> local layer -> combine
+            layers = build_layers(cfg, a.layers, dev, shard=shard_range(cfg["experts"], rank, world))
+            ws = None
+            for w in layers:   # a rank receives up to 16 rows from every peer: one W4A16 call for all of them
+                w.enable_mid(max_tokens=world * MS[-1], workspace=ws, min_tokens=17)
+                ws = w.mid.workspace
+            eps = [ExpertParallelMoE(w.forward, cfg["experts"], cfg["top_k"], capacity=MS[-1], transport=EP_TRANSPORT) for w in layers]
+        r = decode_sweep(cfg, layers, dev, a.steps, a.warmup, not a.no_graph, rank, world, dist, eps=eps, only=only)
+        if world > 1:
+            extras["ep_parity"] = ep_parity(cfg, eps[0], dist, world, rank, dev)
+        if not a.no_extras:
             if world == 1:
+                other = dict(synth.GEMMA if a.shape == "qwen" else synth.QWEN)
                 extras["prefill"] = prefill_numbers(cfg, layers[:2], dev)
                 extras["ep"] = ep_stack(cfg, layers, None, 1, 0, dev, stack=a.ep_layers)
-            else:
-                del graphs
-                layers.clear()
+                del layers[4:]
                 torch.cuda.empty_cache()
-                sharded = build_layers(cfg, a.layers, dev, shard=shard_range(cfg["experts"], rank, world))
-                extras["ep"] = ep_stack(cfg, sharded, dist, world, rank, dev, stack=a.ep_layers)
+                ol = build_layers(other, 8, dev)   # the second BASELINE shape: 8 distinct weight sets (larger than L2)
+                ro = decode_sweep(other, ol, dev, max(2, a.steps // 4), a.warmup, not a.no_graph, 0, 1, None, e2e=False, cold=False)
+                extras["cases_" + ("gemma" if a.shape == "qwen" else "qwen")] = {
+                    "shape": other, "layers_in_chain": 8, "hbm_gbs": round(ro["step_bytes"] / (ro["step_ms"] * 1e-3) / 1e9, 1), "cases": ro["detail"]}
+                del ol
+            else:
+                for w in layers:
+                    w.mid = None
+                extras["ep"] = ep_stack(cfg, layers, dist, world, rank, dev, stack=a.ep_layers)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
     peak, peak_src = peaks()
-    step_bytes = sum(c["touched"] for c in cs) * ebytes * a.layers
-    value = world * step_bytes / (step_ms * 1e-3) / 1e9
-    detail = []
-    for idx, c in enumerate(cs):
-        us = per_case_ms[idx] / a.steps / a.layers * 1e3
-        gbs = c["touched"] * ebytes / (us * 1e-6) / 1e9
-        detail.append({"m": c["m"], "routing": c["routing"], "touched_experts": c["touched"], "us_per_layer": round(us, 2),
-                       "hbm_gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)})
-    launches = a.steps * len(cs) * a.layers
-    kernel_ms = float(per_case_ms.sum()) / a.steps
-    achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+    value = r["step_bytes"] / (r["step_ms"] * 1e-3) / 1e9
+    for d in r["detail"]:
+        d["frac_of_peak"] = round(d["hbm_gbs"] / world / peak, 3)
+    launches = a.steps * r["cases"] * a.layers
+    kernel_ms = float(r["per_case_ms"].sum()) / a.steps
+    achieved = r["step_bytes"] / world / (kernel_ms * 1e-3) / 1e9
     traffic = None
     tp = ROOT / "profiles" / "decode_traffic.json"
     if tp.exists():
         traffic = json.loads(tp.read_text()).get("dram_bytes_per_launch")
-    cpu = cpu_baseline(cfg, a) if not a.no_cpu else None
+    cpu = cpu_baseline(cfg, a) if (not a.no_cpu and world == 1) else None
+    par = "single" if world == 1 else "expert"
     line = {
         "metric": "moe_decode_layer_hbm_gbs_on_touched_expert_bytes", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
-        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(r["step_ms"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "nvfp4 weights x f16 activations, fp32 accumulate (W4A16)", "data": "synthetic",
-        "config": {"workload": f"{a.shape}-shaped MoE layer decode sweep M in {list(MS)} x routing {list(ROUTINGS)}; E={cfg['experts']} H={cfg['hidden']} I={cfg['inter']} top-{cfg['top_k']}",
-                   "layers_in_chain": a.layers, "l2": f"inputs larger than L2: each call reads one of {a.layers} distinct {ebytes * cfg['experts'] / 1e6:.0f} MB weight sets",
-                   "graph_replay": use_graph, "parallelism": "replicas" if world > 1 else "single"},
-        "cases": detail,
+        "config": {"workload": workload_name(a.shape, cfg),
+                   "layers_in_chain": a.layers, "l2": f"inputs larger than L2: each call reads one of {a.layers} distinct {r['ebytes'] * cfg['experts'] / 1e6:.0f} MB weight sets",
+                   "graph_replay": r["graph"], "parallelism": par,
+                   "bytes": "per case, the experts each GPU's own batch of M tokens touches x packed FP4 + scale bytes of an expert, summed over the GPUs"
+                            + ("" if world == 1 else " (experts are sharded: one touched by several GPUs' batches is streamed once, by its owner; the exchanges are inside the timed region)")},
+        "cases": r["detail"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": traffic, "peak_source": peak_src, "kernel": "k_moe_decode_tc",
-                     "bytes_per_launch": round(step_bytes / (len(cs) * a.layers))},
-        "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(e2e_ms, 3),
-                "h2d_bytes_per_step": int(sum(c["x"].numel() * 2 + c["ids"].numel() * 4 + c["wts"].numel() * 4 for c in cs) * a.layers),
-                "d2h_bytes_per_step": int(sum(c["x"].numel() * 2 for c in cs) * a.layers)},
-        "gpu_launches": launches, "clocks": clocks, "cpu_baseline": cpu,
+                     "traffic": traffic if world == 1 else None, "peak_source": peak_src, "kernel": "k_moe_decode_tc" if world == 1 else "k_prefill_gemm_r<3>",
+                     "bytes_per_launch": round(r["step_bytes"] / world / (r["cases"] * a.layers)), "per_gpu": world > 1},
+        "e2e": {"value": round(r["step_bytes"] / (r["e2e_ms"] * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(r["e2e_ms"], 3),
+                "h2d_bytes_per_step": r["io"]["h2d"] * world, "d2h_bytes_per_step": r["io"]["d2h"] * world},
+        "gpu_launches": launches * (2 if world == 1 else 12), "clocks": r["clocks"], "cpu_baseline": cpu,
     }
     line.update(extras)
     print(json.dumps(line))
@@ -264,29 +328,69 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
+def ep_parity(cfg, ep, dist, world, rank, dev):
+    """Expert-parallel output against the un-sharded layer: rank 0 also holds the full layer 0 (the same seeded weights the
+    shards were cut from) and runs its own batch through it; reported as max-abs / RMS and as bit-identity from call to call."""
+    from sm120fp4_b200 import synth
+    res = {}
+    full = build_layers(cfg, 1, dev)[0] if rank == 0 else None
+    for m in (16, 1):
+        x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 1000 + m + 7919 * rank)
+        xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
+        out = ep.forward(xd, idd, wd).clone()
+        again = ep.forward(xd, idd, wd)
+        if rank == 0:
+            want = full.forward(xd, idd, wd).float()
+            rms = float(want.pow(2).mean().sqrt())
+            res[f"m{m}"] = {"max_abs_over_rms": round(float((out.float() - want).abs().max()) / rms, 5),
+                            "bit_identical_call_to_call": bool(torch.equal(out, again))}
+    if rank == 0:
+        full.status()
+        res["against"] = "the un-sharded layer on rank 0 (the shards' seeded weights), rank 0's batch; partial rows cross the exchange in bf16"
+    return res
+
+
 def prefill_numbers(cfg, layers, dev, reps=5):
-    """W4A4 prefill (own tcgen05 grouped GEMM): us per layer call and TFLOP/s on 6*M*k*I*H flop at M = 256 .. 8192."""
+    """W4A4 prefill (own tcgen05 grouped GEMM): us per layer call and TFLOP/s on 6*M*k*I*H flop at M = 256 .. 8192, CUDA-graph
+    replay of the two-layer chain; with the fraction of the nominal dense FP4 peak and of the layer's HBM floor (all experts'
+    packed weights once + x in + out: the bound at these sizes, see the roofline note)."""
     from sm120fp4_b200 import synth
     ws = None
     for w in layers:
         w.enable_prefill(max_tokens=8192, workspace=ws)
         ws = w.prefill.workspace
+    peak_hbm, _ = peaks()
     rows = []
+    ebytes = layers[0].expert_bytes()
     for m in (256, 1024, 4096, 8192):
         x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 9000 + m)
         xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
         out = torch.empty_like(xd)
-        for _ in range(2):
+
+        def chain():
             for w in layers:
                 w.forward(xd, idd, wd, out=out)
-        ts = []
-        for _ in range(reps):
-            ts.append(time_region(lambda: [w.forward(xd, idd, wd, out=out) for w in layers], torch.cuda.synchronize) / len(layers))
-        ts.sort()
+        for _ in range(2):
+            chain()
+        torch.cuda.synchronize()
+        run, graphed = chain, False
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
+                chain()
+            run, graphed = g.replay, True
+            run()
+        except Exception as ex:  # noqa: BLE001
+            print(f"prefill: graph capture unavailable ({type(ex).__name__}: {ex})", file=sys.stderr)
+        ts = sorted(time_region(run, torch.cuda.synchronize) / len(layers) for _ in range(reps))
         t = ts[len(ts) // 2]
         flop = 6.0 * m * cfg["top_k"] * cfg["inter"] * cfg["hidden"]
-        rows.append({"m": m, "us_per_layer": round(t * 1e3, 1), "tflops": round(flop / t / 1e9, 1),
-                     "frac_of_dense_fp4_nominal": round(flop / t / 1e9 / 9000.0, 4)})
+        touched = int(torch.unique(ids).numel())
+        floor_bytes = touched * ebytes + 2 * m * cfg["hidden"] * 2
+        rows.append({"m": m, "us_per_layer": round(t * 1e3, 1), "tflops": round(flop / t / 1e9, 1), "graph_replay": graphed,
+                     "roofline": {"bound": "tensor", "flop": flop, "achieved": round(flop / t / 1e9, 1), "peak": 9000.0, "unit": "TFLOP/s",
+                                  "frac": round(flop / t / 1e9 / 9000.0, 4), "peak_source": "nominal dense FP4 (no measured FP4 peak on this pool)",
+                                  "hbm_floor_us": round(floor_bytes / peak_hbm / 1e3, 1), "frac_of_hbm_floor": round(floor_bytes / peak_hbm / 1e3 / (t * 1e3), 4)}})
     layers[0].prefill_status()
     for w in layers:
         w.prefill = None
@@ -294,9 +398,10 @@ def prefill_numbers(cfg, layers, dev, reps=5):
 
 
 def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, prefill_tokens=4096, reps=3):
-    """The expert-parallel stack of BASELINE configs[4]: `stack` layer calls (cycling over the resident layer objects, each
-    holding E / world experts), decode with 16 tokens per GPU (fixed-capacity dispatch, no host sync) and prefill with 4096
-    tokens per GPU (variable-size dispatch, W4A4 path). Device-timed, max over ranks. Returns tokens/s and per-layer us."""
+    """The expert-parallel stack of 48 Qwen3-30B-A3B-shaped layers: `stack` layer calls (cycling over the resident layer
+    objects, each holding E / world experts), decode with 16 tokens per GPU (fixed-capacity dispatch, no host sync) and
+    prefill with 4096 tokens per GPU (variable-size dispatch, W4A4 path). Device-timed, max over ranks. Returns tokens/s and
+    per-layer us."""
     from sm120fp4_b200 import synth
     from sm120fp4_b200.ep import ExpertParallelMoE
     e, k = cfg["experts"], cfg["top_k"]
@@ -309,10 +414,10 @@ def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, pr
                 ws = w.prefill.workspace
         if name == "decode" and world > 1:   # a rank receives 16 rows from every peer: one W4A16 call instead of `world` slices
             for w in layers:
-                w.enable_mid(max_tokens=world * decode_tokens, workspace=ws)
+                w.enable_mid(max_tokens=world * decode_tokens, workspace=ws, min_tokens=17)
                 ws = w.mid.workspace
             ws = None
-        eps = [ExpertParallelMoE(w.forward, e, k, capacity=cap) for w in layers]
+        eps = [ExpertParallelMoE(w.forward, e, k, capacity=cap, transport=EP_TRANSPORT) for w in layers]
         x, ids, wts = synth.decode_inputs(m, e, cfg["hidden"], k, 7000 + 13 * rank + m)
         xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
 
@@ -409,28 +514,36 @@ def cpu_baseline(cfg, a):
             "sample": f"oracle (numpy restatement of the reference's CPU path) on one layer call, M=4 random routing, median of 3 ({sec:.2f} s per call)"}
 
 
+def workload_name(shape, cfg):
+    return (f"{shape}-shaped MoE layer decode sweep M in {list(MS)} x routing {list(ROUTINGS)}; E={cfg['experts']} H={cfg['hidden']} "
+            f"I={cfg['inter']} top-{cfg['top_k']}")
+
+
 def run_reference(a):
     """The reference arm: the reference's CPU algorithm for this path (the oracle port; the reference itself is a PyTorch
-    package that cannot travel to the GPU box) on the host cores, on a bounded sample of the same workload."""
+    package that cannot travel to the GPU box) on the host cores, with all the threads numpy's BLAS takes. One step = one
+    layer call for each of the ten cases of the sweep (same seeds as the GPU arm); dequantisation of the touched experts is
+    inside the timed region, as in the reference's CPU path (sm120fp4/kernels/bench_moe_baseline.py:53-74)."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
     from sm120fp4_b200 import synth
     cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
+    sweep = [(m, routing) for routing in ROUTINGS for m in MS]
     for _ in range(min(a.warmup, 1)):
         cpu_forward_timed(cfg, 1, "random", 1)
     tot_s, tot_b = 0.0, 0
     for _ in range(a.steps):
-        for m, routing in ((1, "random"), (4, "random"), (4, "fixed8")):
+        for m, routing in sweep:
             s, b = cpu_forward_timed(cfg, m, routing, 1)
             tot_s += s
             tot_b += b
     val = tot_b / tot_s / 1e9
-    sample = "per step: one layer call each at (M=1 random), (M=4 random), (M=4 fixed8) of the decode sweep; numpy/BLAS threads"
+    sample = "per step: one layer call for each of the ten cases of the sweep; numpy/BLAS threads; dequantisation inside the timed region"
     line = {"impl": "reference", "metric": "moe_decode_layer_hbm_gbs_on_touched_expert_bytes", "value": round(val, 4), "unit": "GB/s",
             "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(tot_s / a.steps * 1e3, 1),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 on dequantised NVFP4", "data": "synthetic",
-            "config": {"workload": f"{a.shape}-shaped MoE layer decode sweep (bounded sample)"},
+            "config": {"workload": workload_name(a.shape, cfg)},
             "cpu_baseline": {"value": round(val, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
             "e2e": {"value": round(val, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))

@@ -141,6 +141,12 @@ int b200moe_decode_fc2(const b200moe_layer* layer, const void* act_bf16, const i
 /* routing tables written by the last decode call, in the router's padded form (device-to-device copies on stream) */
 int b200moe_layer_route_tables(const b200moe_layer* layer, const void* workspace, int M, int* experts, int* offsets,
                                int* pairs, void* stream);
+/* Byte offsets inside a decode workspace of what the tcgen05 decode kernel computed with in the last call, for tools and tests
+ * (as b200moe_prefill_workspace_map): out8 = the x operand (per 256-value K box N rows of 128 code bytes in the 128-byte
+ * swizzle - row 4*token + term, 16-byte chunk c at c ^ (row & 7) - then ceil(H/64) scale tiles of 512 bytes), its 1/g_t per
+ * row (float [N]), the activation slabs ([touched expert][K box of I]: N rows of 128 code bytes + four 512-byte scale tiles),
+ * slab bytes for N = 16, 32, 64 (tokens <= 4, 8, 16), the activation scale (float bits), slab capacity in experts. */
+int b200moe_layer_workspace_map(const b200moe_layer* layer, long long* out8);
 /* status words of the workspace; synchronises the stream. 0, B200MOE_ERR_TIMEOUT, B200MOE_ERR_ARG (bad expert id),
  * B200MOE_ERR_ORDER (routing inputs changed under the call) or B200MOE_ERR_RANGE (an FC1 activation above 2688 / act scale
  * was clipped; the last two are cleared by the read) */
@@ -152,6 +158,11 @@ int b200moe_layer_status(const b200moe_layer* layer, const void* workspace, void
  * arithmetic it checks is the reference GEMM of sm120fp4/reference.py:133-137. */
 int b200moe_umma_probe(const void* a, const void* sfa, const void* b, const void* sfb, int N, int K, float* d,
                        int scale_path, int* status_dev, void* stream);
+
+/* the same check for a CTA pair (tcgen05 cta_group::2: two SMs, one 256 x 128 x 64 MMA): a u8 [256, K/2], sfa 128x4-swizzled
+ * over [256, K/16], b u8 [128, K/2], sfb 128x4-swizzled over [128, K/16], d f32 [256, 128], status_dev int32 [2]. */
+int b200moe_umma_pair_probe(const void* a, const void* sfa, const void* b, const void* sfb, int K, float* d, int* status_dev,
+                            void* stream);
 
 /* HBM streaming floor of the kernels' access patterns, no math (the reference's k_stream probe,
  * sm120fp4/kernels/micro_floor.py:59-95): pattern 0 = 128-byte x box_rows TMA boxes from a row-major matrix of `pitch`
@@ -172,10 +183,20 @@ int b200moe_mid_status(const b200moe_layer* layer, const void* workspace, int ma
 
 /* expert-parallel fixed-capacity dispatch and combine (no counterpart in the reference: it declines expert parallelism,
  * sm120fp4/vllm_classes.py:46-47). dispatch: x bf16 [m, h], ids int32 [m, k] (global ids, negative = empty slot), wts f32
- * [m, k] -> sx bf16 [world, cap, h] and meta int32 [world, cap, 2k] (local ids, then the weights' float bits); block d is
- * what rank d receives. combine: y bf16 [world, cap, h] -> out bf16 [m, h], summed in rank order in fp32. */
+ * [m, k] -> per destination rank d a block of cap rows: token rows at dst_x[d] (bf16 [cap, h]; a row is stored only where d
+ * owns one of its experts), the destination's local expert ids at dst_ids[d] (int32 [cap, k], -1 = not d's) and the routing
+ * weights at dst_wts[d] (f32 [cap, k]). dst_x / dst_ids / dst_wts / dst_flag are HOST arrays of `world` device pointers: into
+ * one packed send buffer (rows | ids | weights per destination - a single all-to-all then carries all three, and
+ * b200moe_ep_unpack splits what arrived), or straight into the destination GPUs' receive arrays (plain peer stores over
+ * NVLink); in that case dst_flag[d] is a counter in d's memory that is bumped once per row after the row is visible there,
+ * and the destination waits with b200moe_ep_wait (bounded: a wait that runs out sets *status to 1 + the late peer's rank
+ * and returns). b200moe_ep_return sends the partial rows back the same way. combine: y bf16 [world, cap, h] -> out bf16
+ * [m, h], summed in rank order in fp32. */
 int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
-                        void* sx, int* meta, void* stream);
+                        void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag, void* stream);
+int b200moe_ep_unpack(const void* rbuf, long long block_bytes, int world, int cap, int h, int k, void* rx, int* rid, float* rw, void* stream);
+int b200moe_ep_wait(const unsigned* flags, int world, int per_call, unsigned* calls, int* status, void* stream);
+int b200moe_ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag, void* stream);
 int b200moe_ep_combine(const void* y, int m, int h, int world, int cap, void* out, void* stream);
 /* variable-size exchange (prefill batches; no counterpart in the reference either). plan: counts int32 [world], offsets int32
  * [world + 1], pos int32 [m, world] (row of token t in the send buffer for destination d, or -1), send_tok int32 [rows]

@@ -271,12 +271,15 @@ def interval_gemm(alo, ahi, w):
     return c, hw @ np.abs(w).T + gamma(k) * cabs + (2.0 + k) * U64 * cabs, cabs
 
 
-def fc1_activation_interval(xq: np.ndarray, w1d: np.ndarray, inter: int, extra_rel: float = 0.0):
+def fc1_activation_interval(xq: np.ndarray, w1d: np.ndarray, inter: int, extra_rel: float = 0.0, xabs: np.ndarray | None = None):
     """The interval [lo, hi] of a = silu(gate) * up for rows xq (float64, exact operand values) against one expert's
     dequantised FC1 weights w1d [2I, H] (rows [up ; gate], alpha folded in), when FC1 is accumulated in fp32 in any order
     and SiLU*mul is evaluated in fp32 with fast math and no intermediate rounding (this library's FC1 epilogues).
     Returns (lo, hi, nominal)."""
-    f, fb, _ = interval_gemm(xq, xq, w1d)
+    f, fb, cabs = interval_gemm(xq, xq, w1d)
+    if xabs is not None:   # the operand is a sum of terms accumulated separately: the bound runs over the terms' magnitudes
+        cabs = np.asarray(xabs, dtype=np.float64) @ np.abs(w1d).T
+        fb = gamma(w1d.shape[1]) * cabs + (2.0 + w1d.shape[1]) * U64 * cabs + 8 * U32 * cabs
     fb = fb + 4 * U32 * np.abs(f) + extra_rel * np.abs(f)       # the alpha / gs multiplies in fp32
     up, bu, gate, bg = f[:, :inter], fb[:, :inter], f[:, inter:], fb[:, inter:]
     slo, shi = hull_silu(gate - bg, gate + bg)
@@ -354,3 +357,24 @@ def block_quantize_interval(lo: np.ndarray, hi: np.ndarray, gs: float = 1.0, blo
             vlo = np.where(use, np.minimum(vlo, c), vlo)
             vhi = np.where(use, np.maximum(vhi, c), vhi)
     return vlo.reshape(rows, k), vhi.reshape(rows, k), int((s_a != s_b).sum())
+
+
+# ------------------------------------------------------------------------------------------------ W4A16 term expansion
+EXPANSION_TERMS = 4
+# Residual of the expansion of a 16-value block into four NVFP4 terms, relative to the block maximum: every term leaves at
+# most one E2M1 step at the top of its range times its (rounded-up) block scale, (1 + 1/16) / 6 of what it was given.
+EXPANSION_RESIDUAL = ((1.0 + 1.0 / 16.0) / 6.0) ** EXPANSION_TERMS
+
+
+def expansion_value(codes: np.ndarray, sf_bits: np.ndarray, g1: np.ndarray, block: int = BLOCK):
+    """The value a four-term operand stands for, and the sum of its terms' magnitudes. codes u8 [terms, rows, K/2] packed
+    E2M1, sf_bits u8 [terms, rows, K/16], g1 [rows] (or scalar): first-term global scale; term t carries g1 * 6^t."""
+    terms = codes.shape[0]
+    g = np.asarray(g1, dtype=np.float64).reshape(-1, 1)
+    val = 0.0
+    mag = 0.0
+    for t in range(terms):
+        v = scaled_operand(codes[t], sf_bits[t], block) / (2.0 * g * 6.0 ** t)
+        val = val + v
+        mag = mag + np.abs(v)
+    return val, mag

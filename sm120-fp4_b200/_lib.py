@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200moe_layer_workspace_bytes": (_LL, [_P]),
     "b200moe_layer_workspace_init": (_I, [_P, _P, _LL, _P]),
     "b200moe_layer_sm_count": (_I, [_P]),
+    "b200moe_layer_workspace_map": (_I, [_P, _P]),
     "b200moe_layer_prepack_bytes": (_LL, [_P]),
     "b200moe_layer_prepack": (_I, [_P, _P, _LL, _P]),
     "b200moe_layer_set_decode_impl": (_I, [_P, _I]),
@@ -54,12 +55,16 @@ SIGNATURES = {
     "b200moe_mid_workspace_bytes": (_LL, [_P, _I]),
     "b200moe_mid_forward": (_I, [_P, _P, _P, _P, _I, _P, _P, _LL, _I, _P]),
     "b200moe_mid_status": (_I, [_P, _P, _I, _P]),
-    "b200moe_ep_dispatch": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "b200moe_ep_dispatch": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "b200moe_ep_unpack": (_I, [_P, _LL, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "b200moe_ep_wait": (_I, [_P, _I, _I, _P, _P, _P]),
+    "b200moe_ep_return": (_I, [_P, _I, _I, _I, _I, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _I, _I, _I, _I, _P, _P]),
     "b200moe_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_ep_gather": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "b200moe_ep_combine_rows": (_I, [_P, _P, _I, _I, _I, _P, _P]),
     "b200moe_umma_probe": (_I, [_P, _P, _P, _P, _I, _I, _P, _I, _P, _P]),
+    "b200moe_umma_pair_probe": (_I, [_P, _P, _P, _P, _I, _P, _P, _P]),
 }
 # exported only by a diagnostic build (include/b200moe_diag.h); bound when present
 DIAG_SIGNATURES = {

@@ -534,3 +534,17 @@ extern "C" int b200moe_mid_status(const b200moe_layer* L, const void* workspace,
 }
 
 extern "C" int b200moe_layer_sm_count(const b200moe_layer* L) { return L ? L->sms : B200MOE_ERR_ARG; }
+
+// Where the tcgen05 decode kernel's operands sit inside a decode workspace, for tools and tests that read back what the last
+// call computed with: out8 = offset of the expanded x operand, of its 1/g_t column scales, of the expanded FC1->FC2
+// activation slabs, bytes of one slab for N = 16 / 32 / 64 operand columns, the first-term activation scale as float bits,
+// and the capacity (touched experts) of the slab array.
+extern "C" int b200moe_layer_workspace_map(const b200moe_layer* L, long long* out8) {
+  if (!L || !out8) return B200MOE_ERR_ARG;
+  out8[0] = L->off_xb, out8[1] = L->off_xscale, out8[2] = L->off_aslab;
+  out8[3] = 16 * 128 + 2048, out8[4] = 32 * 128 + 2048, out8[5] = 64 * 128 + 2048;
+  unsigned bits;
+  memcpy(&bits, &L->act_g1, 4);
+  out8[6] = bits, out8[7] = L->umax_cap;
+  return B200MOE_OK;
+}

@@ -9,15 +9,30 @@ namespace b200 {
 
 // Block (row, dest): row `row` of the block sent to rank `dest` is token `row` (zeros beyond the batch), its top-k slots
 // re-indexed to the destination's local experts; slots the destination does not own become id -1 / weight 0.
-// meta[dest][row][0..k) = local ids (int32), meta[dest][row][k..2k) = routing weights (float bits).
+// Where a block lands is given per destination: D.x[dest] / D.ids[dest] / D.wts[dest] point at the block's rows, local ids
+// and weights (cap rows each). For the NCCL exchange they point into one packed send buffer (rows | ids | weights per
+// destination, so that ONE all-to-all carries all three); for the peer-store exchange they point straight into the
+// destination GPU's receive arrays across NVLink (plain stores; no multicast), and D.flag[dest] is a counter in the
+// destination's memory that every block bumps (system-scope, after a system-scope fence) once its row has been stored.
+constexpr int kEpMaxWorld = 16;
+
+struct EpDest {
+  __nv_bfloat16* x[kEpMaxWorld];
+  int* ids[kEpMaxWorld];
+  float* wts[kEpMaxWorld];
+  unsigned* flag[kEpMaxWorld];   // null: no signalling (stream-ordered exchange follows)
+};
+
 __global__ void __launch_bounds__(128) k_ep_dispatch(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
-                                                     const float* __restrict__ wts, int m, int h, int k, int per, int cap,
-                                                     __nv_bfloat16* __restrict__ sx, int* __restrict__ meta) {
+                                                     const float* __restrict__ wts, int m, int h, int k, int per, const __grid_constant__ EpDest D) {
   const int row = blockIdx.x, dest = blockIdx.y;
-  const long long o = (long long)dest * cap + row;
-  uint4* dst = reinterpret_cast<uint4*>(sx + o * h);
+  uint4* dst = reinterpret_cast<uint4*>(D.x[dest] + (long long)row * h);
   const uint4* src = reinterpret_cast<const uint4*>(x + (long long)row * h);
-  for (int i = threadIdx.x; i < h / 8; i += blockDim.x) dst[i] = row < m ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+  bool any = false;
+  if (row < m)
+    for (int j = 0; j < k; ++j) { const int e = ids[row * k + j]; any |= e >= 0 && e / per == dest; }
+  // a row none of whose experts live on the destination travels as its (all empty) slots only: the kernels skip such rows
+  if (any) for (int i = threadIdx.x; i < h / 8; i += blockDim.x) dst[i] = src[i];
   for (int j = threadIdx.x; j < k; j += blockDim.x) {
     int id = -1;
     float w = 0.f;
@@ -25,8 +40,73 @@ __global__ void __launch_bounds__(128) k_ep_dispatch(const __nv_bfloat16* __rest
       const int e = ids[row * k + j];
       if (e >= 0 && e / per == dest) { id = e - dest * per; w = wts[row * k + j]; }
     }
-    meta[o * 2 * k + j] = id;
-    meta[o * 2 * k + k + j] = __float_as_int(w);
+    D.ids[dest][row * k + j] = id;
+    D.wts[dest][row * k + j] = w;
+  }
+  if (D.flag[dest]) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      atomicAdd_system(D.flag[dest], 1u);
+    }
+  }
+}
+
+// Bounded wait of the consumer side of the peer-store exchange: thread s waits until peer s has bumped flags[s] `per_call`
+// more times than this rank has consumed so far (calls[0] counts this rank's calls; the counters only ever grow, so nothing is
+// reset between calls). A wait that runs out sets *status and returns - the data of that peer is then stale, which the
+// caller learns from the status word, not from a hang.
+__global__ void k_ep_wait(const unsigned* __restrict__ flags, int world, unsigned per_call, unsigned* __restrict__ calls, int* __restrict__ status) {
+  const int s = threadIdx.x;
+  const unsigned want = (calls[0] + 1u) * per_call;
+  if (s < world) {
+    bool ok = false;
+    for (unsigned it = 0; it < (1u << 22); ++it) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
+      if ((int)(v - want) >= 0) { ok = true; break; }
+      if (it > 1024u) __nanosleep(200);
+    }
+    if (!ok) *status = 1 + s;
+  }
+  __syncthreads();
+  if (s == 0) calls[0] += 1u;
+}
+
+// Received blocks of the NCCL exchange (per source: rows | ids | weights) -> the contiguous arrays the layer call takes.
+__global__ void __launch_bounds__(128) k_ep_unpack(const uint8_t* __restrict__ rbuf, long long block_bytes, int cap, int h, int k,
+                                                   __nv_bfloat16* __restrict__ rx, int* __restrict__ rid, float* __restrict__ rw) {
+  const int row = blockIdx.x, srcr = blockIdx.y;
+  const uint8_t* blk = rbuf + srcr * block_bytes;
+  const int* bid = reinterpret_cast<const int*>(blk + (long long)cap * h * 2) + row * k;
+  const float* bw = reinterpret_cast<const float*>(blk + (long long)cap * h * 2 + (long long)cap * k * 4) + row * k;
+  const long long o = (long long)srcr * cap + row;
+  bool any = false;
+  for (int j = 0; j < k; ++j) any |= bid[j] >= 0;
+  if (any) {
+    const uint4* src = reinterpret_cast<const uint4*>(blk + (long long)row * h * 2);
+    uint4* dst = reinterpret_cast<uint4*>(rx + o * h);
+    for (int i = threadIdx.x; i < h / 8; i += blockDim.x) dst[i] = src[i];
+  }
+  for (int j = threadIdx.x; j < k; j += blockDim.x) { rid[o * k + j] = bid[j]; rw[o * k + j] = bw[j]; }
+}
+
+// The partial rows a rank computed for source s (rows s*cap .. s*cap + cap of yl) go back into s's `back` array at block
+// `rank` by plain peer stores, then one bump of s's return flag per row.
+struct EpBack {
+  __nv_bfloat16* y[kEpMaxWorld];
+  unsigned* flag[kEpMaxWorld];
+};
+
+__global__ void __launch_bounds__(128) k_ep_return(const __nv_bfloat16* __restrict__ yl, int cap, int h, int rank, const __grid_constant__ EpBack B) {
+  const int row = blockIdx.x, srcr = blockIdx.y;
+  const uint4* src = reinterpret_cast<const uint4*>(yl + ((long long)srcr * cap + row) * h);
+  uint4* dst = reinterpret_cast<uint4*>(B.y[srcr] + ((long long)rank * cap + row) * h);
+  for (int i = threadIdx.x; i < h / 8; i += blockDim.x) dst[i] = src[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    atomicAdd_system(B.flag[srcr], 1u);
   }
 }
 
@@ -60,14 +140,65 @@ __global__ void __launch_bounds__(256) k_ep_combine(const __nv_bfloat16* __restr
 
 using namespace b200;
 
-// x bf16 [m, h], ids int32 [m, k] (global expert ids, negative = empty slot), wts f32 [m, k] -> sx bf16 [world, cap, h],
-// meta int32 [world, cap, 2k]. experts_per_rank = E / world; m <= cap; h a multiple of 8.
+// x bf16 [m, h], ids int32 [m, k] (global expert ids, negative = empty slot), wts f32 [m, k] -> per destination d a block of
+// cap rows: rows at dst_x[d] (bf16 [cap, h]), local ids at dst_ids[d] (int32 [cap, k]), weights at dst_wts[d] (f32 [cap, k]);
+// the three pointer tables are HOST arrays of `world` device pointers. dst_flag: null, or a host array of `world` device
+// pointers to counters that every block bumps after its row is stored (peer-store exchange). experts_per_rank = E / world;
+// m <= cap; h a multiple of 8. A row is copied only where the destination owns one of its experts.
 extern "C" int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank,
-                                   int cap, void* sx, int* meta, void* stream) {
-  if (!x || !ids || !wts || !sx || !meta) return B200MOE_ERR_ARG;
-  if (m < 0 || m > cap || h <= 0 || h % 8 || k < 1 || world < 1 || experts_per_rank < 1 || cap < 1) return B200MOE_ERR_SHAPE;
-  k_ep_dispatch<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, m, h, k, experts_per_rank, cap,
-                                                                     (__nv_bfloat16*)sx, meta);
+                                   int cap, void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag,
+                                   void* stream) {
+  if (!x || !ids || !wts || !dst_x || !dst_ids || !dst_wts) return B200MOE_ERR_ARG;
+  if (m < 0 || m > cap || h <= 0 || h % 8 || k < 1 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1 || cap < 1) return B200MOE_ERR_SHAPE;
+  EpDest D;
+  for (int d = 0; d < kEpMaxWorld; ++d) {
+    const bool live = d < world;
+    D.x[d] = live ? (__nv_bfloat16*)dst_x[d] : nullptr;
+    D.ids[d] = live ? dst_ids[d] : nullptr;
+    D.wts[d] = live ? dst_wts[d] : nullptr;
+    D.flag[d] = live && dst_flag ? dst_flag[d] : nullptr;
+    if (live && (!D.x[d] || !D.ids[d] || !D.wts[d])) return B200MOE_ERR_ARG;
+  }
+  k_ep_dispatch<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, m, h, k, experts_per_rank, D);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// rbuf: `world` received blocks of block_bytes each (rows bf16 [cap, h] | ids int32 [cap, k] | weights f32 [cap, k]) ->
+// rx bf16 [world * cap, h], rid int32 [world * cap, k], rw f32 [world * cap, k]
+extern "C" int b200moe_ep_unpack(const void* rbuf, long long block_bytes, int world, int cap, int h, int k, void* rx, int* rid, float* rw,
+                                 void* stream) {
+  if (!rbuf || !rx || !rid || !rw) return B200MOE_ERR_ARG;
+  if (world < 1 || cap < 1 || h <= 0 || h % 8 || k < 1 || block_bytes < (long long)cap * (h * 2 + k * 8) || block_bytes % 16) return B200MOE_ERR_SHAPE;
+  k_ep_unpack<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const uint8_t*)rbuf, block_bytes, cap, h, k, (__nv_bfloat16*)rx, rid, rw);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// Consumer side of the peer-store exchange: wait (bounded) until every one of `world` peers has bumped its counter in `flags`
+// per_call more times; `calls` is this rank's own call counter (device, starts at 0), `status` a device word that a wait that
+// ran out sets to 1 + the peer's rank.
+extern "C" int b200moe_ep_wait(const unsigned* flags, int world, int per_call, unsigned* calls, int* status, void* stream) {
+  if (!flags || !calls || !status) return B200MOE_ERR_ARG;
+  if (world < 1 || world > kEpMaxWorld || per_call < 1) return B200MOE_ERR_SHAPE;
+  k_ep_wait<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, (unsigned)per_call, calls, status);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// yl bf16 [world * cap, h] (this rank's partial rows, block s for source s) -> peer s's back array at block `rank`
+// (back_y[s]: bf16 [world, cap, h] in s's memory), then cap bumps of back_flag[s]. Host arrays of `world` device pointers.
+extern "C" int b200moe_ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
+                                 void* stream) {
+  if (!yl || !back_y || !back_flag) return B200MOE_ERR_ARG;
+  if (world < 1 || world > kEpMaxWorld || cap < 1 || h <= 0 || h % 8 || rank < 0 || rank >= world) return B200MOE_ERR_SHAPE;
+  EpBack B;
+  for (int d = 0; d < kEpMaxWorld; ++d) {
+    B.y[d] = d < world ? (__nv_bfloat16*)back_y[d] : nullptr;
+    B.flag[d] = d < world ? back_flag[d] : nullptr;
+    if (d < world && (!B.y[d] || !B.flag[d])) return B200MOE_ERR_ARG;
+  }
+  k_ep_return<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)yl, cap, h, rank, B);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }
@@ -86,8 +217,6 @@ extern "C" int b200moe_ep_combine(const void* y, int m, int h, int world, int ca
 // ---------------------------------------------------------------------------------------------------------------------
 // Variable-size exchange (prefill batches): a token row travels once to every rank that owns at least one of its experts.
 namespace b200 {
-
-constexpr int kEpMaxWorld = 16;
 
 // One block. Thread i owns the contiguous tokens [i*c, (i+1)*c): per destination, an exclusive scan over the threads gives
 // every sent (token, destination) its row in the send buffer - destination-major, token order within a destination.

@@ -112,6 +112,100 @@ __global__ void __launch_bounds__(128, 1) k_umma_probe(const uint8_t* __restrict
 }
 
 
+// The same check for a CTA pair (cta_group::2): D[256, 128] = dequant(A)[256, K] * dequant(B)[128, K]^T. A cluster of two CTAs:
+// CTA r stages A rows 128r.., the scale tiles of those rows, B rows 64r.. and the scale tiles of ALL 128 B rows (every CTA of
+// the pair keeps the B scales of the whole N in its own TMEM); scales go through registers; the leader issues the MMAs and one
+// commit that arrives on both CTAs' barriers; each CTA reads its own 128 accumulator rows.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+    k_umma2_probe(const uint8_t* __restrict__ a, const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ b, const uint8_t* __restrict__ sfb,
+                  int K, float* __restrict__ d, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int nkb = K / 256;
+  uint8_t* sA = smem;                          // [nkb][128 rows][128 B]
+  uint8_t* sB = sA + nkb * 16384;              // [nkb][64 rows][128 B]
+  uint8_t* sSFA = sB + nkb * 8192;             // [nkb*4][512 B]
+  uint8_t* sSFB = sSFA + nkb * 2048;
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc2(&tmem_base, 256);
+    tmem_relinquish2();
+  }
+  const int row_bytes = K / 2;
+  for (int i = tid; i < nkb * 128 * 8; i += 128) {
+    const int kb = i / 1024, r = (i / 8) % 128, ch = i % 8;
+    const uint4 va = *reinterpret_cast<const uint4*>(a + (long long)(128 * rank + r) * row_bytes + kb * 128 + ch * 16);
+    *reinterpret_cast<uint4*>(sA + kb * 16384 + r * 128 + ((ch ^ (r & 7)) << 4)) = va;
+    if (r < 64) {
+      const uint4 vb = *reinterpret_cast<const uint4*>(b + (long long)(64 * rank + r) * row_bytes + kb * 128 + ch * 16);
+      *reinterpret_cast<uint4*>(sB + kb * 8192 + r * 128 + ((ch ^ (r & 7)) << 4)) = vb;
+    }
+  }
+  for (int i = tid; i < nkb * 2048 / 16; i += 128) {
+    reinterpret_cast<uint4*>(sSFA)[i] = reinterpret_cast<const uint4*>(sfa + (long long)rank * nkb * 2048)[i];   // row block `rank` of the 128x4 layout
+    reinterpret_cast<uint4*>(sSFB)[i] = reinterpret_cast<const uint4*>(sfb)[i];
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = tmem_base;
+  const uint32_t d_tmem = tb, sfa_tmem = tb + 128, sfb_tmem = tb + 192;
+  {
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    for (int kb = 0; kb < nkb; ++kb) {
+      uint32_t ra[16], rb[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 va = lds128(smem_u32(sSFA + (kb * 4 + j) * 512 + (tid & 31) * 16));
+        const uint4 vb = lds128(smem_u32(sSFB + (kb * 4 + j) * 512 + (tid & 31) * 16));
+        ra[4 * j] = va.x, ra[4 * j + 1] = va.y, ra[4 * j + 2] = va.z, ra[4 * j + 3] = va.w;
+        rb[4 * j] = vb.x, rb[4 * j + 1] = vb.y, rb[4 * j + 2] = vb.z, rb[4 * j + 3] = vb.w;
+      }
+      tmem_st_32x32b_x16(sfa_tmem + 16 * kb + lane_base, ra);
+      tmem_st_32x32b_x16(sfb_tmem + 16 * kb + lane_base, rb);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  cluster_sync_all();          // both CTAs' operands and scales are in place
+  tc_fence_after();
+  if (rank == 0 && warp == 1) {
+    const uint32_t el = elect_one();
+    const uint32_t idesc = idesc_mxf4nvf4_pair(128);
+    for (int kb = 0; kb < nkb; ++kb)
+      for (int j = 0; j < 4; ++j) {
+        const uint64_t ad = smem_desc_sw128_kmajor(smem_u32(sA + kb * 16384)) + (uint64_t)(2 * j);
+        const uint64_t bd = smem_desc_sw128_kmajor(smem_u32(sB + kb * 8192)) + (uint64_t)(2 * j);
+        umma2_mxf4nvf4_p(d_tmem, ad, bd, idesc, sfa_tmem + 16 * kb + 4 * j, sfb_tmem + 16 * kb + 4 * j, (kb | j) != 0, el);
+      }
+    umma2_commit_p(&bar, (uint16_t)3, el);
+  }
+  if (!mbar_wait(&bar, 0, &abort_flag, 1u << 18)) status[rank] = 1;
+  tc_fence_after();
+  if (!abort_flag) {
+    for (int c0 = 0; c0 < 128; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(d_tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) d[(long long)(128 * rank + tid) * 128 + c0 + i] = __uint_as_float(r[i]);
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();          // nobody frees TMEM while the peer may still be read by the pair's MMAs
+  if (warp == 0) tmem_dealloc2(tb, 256);
+}
+
 #ifdef B200_DIAGNOSTICS
 // Issue-cost measurement of the tcgen05 operations the kernels use: `reps` rounds of {ncp scale copies, nmma MMAs of
 // shape 128 x N x 64, ncommit commits}, timed with clock64 around issue and around issue + completion.
@@ -233,6 +327,21 @@ extern "C" int b200moe_umma_probe(const void* a, const void* sfa, const void* b,
   B200_CUDA_TRY(cudaFuncSetAttribute(k_umma_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   k_umma_probe<<<1, 128, smem, (cudaStream_t)stream>>>((const uint8_t*)a, (const uint8_t*)sfa, (const uint8_t*)b, (const uint8_t*)sfb, N, K,
                                                         d, kn, status_dev);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// The CTA-pair form: a u8 [256, K/2], sfa u8 128x4-swizzled over [256, K/16], b u8 [128, K/2], sfb u8 128x4-swizzled over
+// [128, K/16], d f32 [256, 128], status int32 [2] (one word per CTA of the pair); K a multiple of 256 up to 1024.
+extern "C" int b200moe_umma_pair_probe(const void* a, const void* sfa, const void* b, const void* sfb, int K, float* d, int* status_dev,
+                                       void* stream) {
+  if (!a || !sfa || !b || !sfb || !d || !status_dev) return B200MOE_ERR_ARG;
+  if (K < 256 || K > 1024 || K % 256) return B200MOE_ERR_SHAPE;
+  const int nkb = K / 256;
+  const int smem = 1024 + nkb * (16384 + 8192 + 4096);
+  B200_CUDA_TRY(cudaFuncSetAttribute(k_umma2_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  k_umma2_probe<<<2, 128, smem, (cudaStream_t)stream>>>((const uint8_t*)a, (const uint8_t*)sfa, (const uint8_t*)b, (const uint8_t*)sfb, K, d,
+                                                         status_dev);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }

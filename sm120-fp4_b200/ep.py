@@ -13,7 +13,11 @@ Per layer call, on every rank:
                  fp32 (a fixed order: results are bit-identical call to call) and rounds once to bf16.
 Rows are exchanged with `all_to_all_single`; the split sizes travel first as a tiny all-to-all of counts (one host
 synchronisation per layer call), or - for decode batches - `capacity` fixes every (source, destination) block at a
-constant number of rows so that nothing has to come back to the host and the call is CUDA-graph capturable.
+constant number of rows so that nothing has to come back to the host and the call is CUDA-graph capturable. The
+fixed-capacity exchange has two transports: one packed NCCL all-to-all each way (rows, ids and weights in one buffer), or -
+`transport="peer"`, when the ranks can map one another's memory - kernels that store the rows straight into the destination
+GPU's receive arrays over NVLink and bump a counter there, with a bounded wait on the receiving side (no NCCL call, no
+multicast; a peer that never arrives shows up as an error status, not as a hang).
 """
 from __future__ import annotations
 
@@ -54,22 +58,35 @@ class ExpertParallelMoE:
     rank's own layer over its shard (e.g. `Weights.forward` built from experts [lo, hi))."""
 
     def __init__(self, local_forward: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor], num_experts: int, top_k: int,
-                 group=None, capacity: int | None = None):
+                 group=None, capacity: int | None = None, transport: str = "nccl"):
         self.local_forward, self.E, self.k = local_forward, num_experts, top_k
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.lo, self.hi = shard_range(num_experts, self.rank, self.world)
         self.capacity = capacity
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport is 'nccl' or 'peer'")
+        self.transport = transport if (capacity is not None and self.world > 1) else "nccl"
         self.last_sent_rows = 0   # rows this rank dispatched in the last call (for traffic accounting)
+        try:
+            import inspect
+            self._lf_out = "out" in inspect.signature(local_forward).parameters
+        except (TypeError, ValueError):
+            self._lf_out = False
 
     # -------------------------------------------------------------------------------------------- variable-size exchange
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if self.capacity is not None:
-            return self.forward_fixed(x, topk_ids, topk_weights)
+            return self.forward_fixed(x, topk_ids, topk_weights, out)
         if self.world == 1:   # one rank owns every expert: nothing to dispatch
             self.last_sent_rows = 0
-            return self.local_forward(x, topk_ids, topk_weights)
+            y = self.local_forward(x, topk_ids, topk_weights)
+            return y if out is None else out.copy_(y)
+        y = self._forward_variable(x, topk_ids, topk_weights)
+        return y if out is None else out.copy_(y)
+
+    def _forward_variable(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         m, h = x.shape
         if x.is_cuda:
             return self._forward_variable_cuda(x, topk_ids, topk_weights)
@@ -106,7 +123,7 @@ class ExpertParallelMoE:
         ids = topk_ids.to(torch.int32).contiguous()
         wts = topk_weights.to(torch.float32).contiguous()
         x = x.contiguous()
-        max_rows = m * min(world, k)
+        max_rows = m * min(world, k)   # a rank with an empty batch (m == 0) sends nothing but takes part in every collective
         plan = torch.empty(2 * world + 1 + m * world + max_rows, dtype=torch.int32, device=dev)
         counts, offsets = plan[:world], plan[world:2 * world + 1]
         pos, send_tok = plan[2 * world + 1:2 * world + 1 + m * world], plan[2 * world + 1 + m * world:]
@@ -149,11 +166,12 @@ class ExpertParallelMoE:
         return out.to(dtype)
 
     # -------------------------------------------------------------------------------------------- fixed-capacity exchange
-    def forward_fixed(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+    def forward_fixed(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Every (source, destination) block holds exactly `capacity` rows (>= the tokens of a rank's batch): row t of the
         block is token t, its slots masked to -1 when the destination owns none of its experts. No host synchronisation and
         no allocation after the first call of a shape: the call can be captured into a CUDA graph. On a CUDA device the
-        dispatch and the combine are one library kernel each; on the CPU (gloo tests) the same arithmetic runs in torch."""
+        dispatch, the unpacking and the combine are one library kernel each; on the CPU (gloo tests) the same arithmetic runs
+        in torch."""
         m, h = x.shape
         c = self.capacity
         if m > c:
@@ -161,42 +179,123 @@ class ExpertParallelMoE:
         per = self.E // self.world
         self.last_sent_rows = self.world * c
         if not x.is_cuda:
-            return self._forward_fixed_torch(x, topk_ids, topk_weights)
+            y = self._forward_fixed_torch(x, topk_ids, topk_weights)
+            return y if out is None else out.copy_(y)
         from . import _lib
         lib = _lib.lib()
         b = self._buffers(h, x.device, x.dtype)
-        ids = topk_ids.to(torch.int32).contiguous()
-        wts = topk_weights.to(torch.float32).contiguous()
-        _lib.check(lib.b200moe_ep_dispatch(_lib.ptr(x.contiguous()), _lib.ptr(ids), _lib.ptr(wts), m, h, self.k, self.world, per, c,
-                                           _lib.ptr(b.sx), _lib.ptr(b.smeta), _lib.stream_ptr()), "ep dispatch")
-        if self.world == 1:
-            rx, rmeta = b.sx, b.smeta
+        ids = topk_ids if topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() else topk_ids.to(torch.int32).contiguous()
+        wts = topk_weights if topk_weights.dtype == torch.float32 and topk_weights.is_contiguous() else topk_weights.to(torch.float32).contiguous()
+        if not x.is_contiguous():
+            x = x.contiguous()
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        w, k = self.world, self.k
+        _lib.check(lib.b200moe_ep_dispatch(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.dst_x, b.dst_ids, b.dst_wts,
+                                           b.dst_flag, st), "ep dispatch")
+        if b.peer:
+            _lib.check(lib.b200moe_ep_wait(b.flags_in.data_ptr(), w, c, b.calls.data_ptr(), b.status.data_ptr(), st), "ep wait")
+        elif w > 1:
+            dist.all_to_all_single(b.rbuf, b.sbuf, group=self.group)
+        if not b.peer:   # split the received blocks (world == 1: the send buffer itself) into the arrays the layer call takes
+            src = b.rbuf if w > 1 else b.sbuf
+            _lib.check(lib.b200moe_ep_unpack(src.data_ptr(), b.block_bytes, w, c, h, k, b.rx.data_ptr(), b.rid.data_ptr(), b.rw.data_ptr(), st),
+                       "ep unpack")
+        if self._lf_out:
+            yl = self.local_forward(b.rx, b.rid, b.rw, out=b.yl)
         else:
-            dist.all_to_all_single(b.rx.view(-1, h), b.sx.view(-1, h), group=self.group)
-            dist.all_to_all_single(b.rmeta.view(-1, 2 * self.k), b.smeta.view(-1, 2 * self.k), group=self.group)
-            rx, rmeta = b.rx, b.rmeta
-        rid = rmeta[:, :, :self.k].reshape(-1, self.k)
-        rw = rmeta[:, :, self.k:].reshape(-1, self.k).view(torch.float32)
-        yl = self.local_forward(rx.view(-1, h), rid, rw)
-        if self.world == 1:
+            yl = self.local_forward(b.rx, b.rid, b.rw)
+        if w == 1:
             y = yl
-        else:
-            dist.all_to_all_single(b.y.view(-1, h), yl.contiguous().view(-1, h), group=self.group)
+        elif b.peer:
+            _lib.check(lib.b200moe_ep_return(yl.data_ptr(), w, c, h, self.rank, b.back_y, b.back_flag, st), "ep return")
+            _lib.check(lib.b200moe_ep_wait(b.flags_back.data_ptr(), w, c, b.calls.data_ptr() + 4, b.status.data_ptr(), st), "ep wait")
             y = b.y
-        out = torch.empty(m, h, dtype=x.dtype, device=x.device)
-        _lib.check(lib.b200moe_ep_combine(_lib.ptr(y), m, h, self.world, c, _lib.ptr(out), _lib.stream_ptr()), "ep combine")
+        else:
+            dist.all_to_all_single(b.y.view(-1, h), yl.view(-1, h), group=self.group)
+            y = b.y
+        if out is None:
+            out = torch.empty(m, h, dtype=x.dtype, device=x.device)
+        _lib.check(lib.b200moe_ep_combine(y.data_ptr(), m, h, w, c, out.data_ptr(), st), "ep combine")
         return out
+
+    def status(self) -> None:
+        """Synchronise and raise if a bounded wait of the peer-store exchange ran out (a peer's rows never arrived)."""
+        b = getattr(self, "_buf", None)
+        if b is not None and b.peer:
+            v = int(b.status.item())
+            if v:
+                b.status.zero_()
+                raise RuntimeError(f"expert-parallel exchange: rank {v - 1} did not deliver its rows within the wait limit")
 
     def _buffers(self, h: int, device, dtype):
         key = (h, str(device), dtype)
-        if getattr(self, "_buf_key", None) != key:
-            from types import SimpleNamespace
-            w, c, k = self.world, self.capacity, self.k
-            mk = lambda *shape, dt: torch.zeros(*shape, dtype=dt, device=device)  # noqa: E731
-            self._buf = SimpleNamespace(sx=mk(w, c, h, dt=dtype), rx=mk(w, c, h, dt=dtype), y=mk(w, c, h, dt=dtype),
-                                        smeta=mk(w, c, 2 * k, dt=torch.int32), rmeta=mk(w, c, 2 * k, dt=torch.int32))
-            self._buf_key = key
-        return self._buf
+        if getattr(self, "_buf_key", None) == key:
+            return self._buf
+        import ctypes as C
+        from types import SimpleNamespace
+        w, c, k = self.world, self.capacity, self.k
+        block = c * (h * 2 + k * 8)
+        block = (block + 255) // 256 * 256
+        z = lambda *shape, dt: torch.zeros(*shape, dtype=dt, device=device)  # noqa: E731
+        b = SimpleNamespace(block_bytes=block, peer=False, rx=None, rid=None, rw=None, y=None,
+                            yl=z(w * c, h, dt=dtype), dst_flag=None)
+        parr = lambda vals: (C.c_void_p * len(vals))(*vals)  # noqa: E731
+        if self.transport == "peer":
+            try:
+                self._peer_buffers(b, h, device, dtype, parr)
+            except Exception as ex:  # noqa: BLE001 - no peer mapping on this system: fall back to the NCCL transport, loudly
+                import sys
+                print(f"expert-parallel peer transport unavailable ({type(ex).__name__}: {ex}); using the NCCL exchange", file=sys.stderr)
+                b.peer = False
+        if self.transport == "peer" and self.world > 1:
+            ok = torch.tensor([1 if b.peer else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            b.peer = bool(int(ok.item()))
+        if not b.peer:
+            b.sbuf, b.rbuf = z(w, block, dt=torch.uint8), z(w, block, dt=torch.uint8)
+            b.rx, b.rid, b.rw = z(w * c, h, dt=dtype), z(w * c, k, dt=torch.int32), z(w * c, k, dt=torch.float32)
+            b.y = z(w, c, h, dt=dtype)
+            base = b.sbuf.data_ptr()
+            b.dst_x = parr([base + d * block for d in range(w)])
+            b.dst_ids = parr([base + d * block + c * h * 2 for d in range(w)])
+            b.dst_wts = parr([base + d * block + c * h * 2 + c * k * 4 for d in range(w)])
+            b.dst_flag = None
+        self._buf, self._buf_key = b, key
+        return b
+
+    def _peer_buffers(self, b, h, device, dtype, parr) -> None:
+        """One symmetric allocation per rank: [rx | rid | rw | back | flags_in | flags_back], mapped into every peer."""
+        import torch.distributed._symmetric_memory as symm
+        w, c, k = self.world, self.capacity, self.k
+        n_rx, n_id = w * c * h * 2, w * c * k * 4
+        off_rid, off_rw, off_back = n_rx, n_rx + n_id, n_rx + 2 * n_id
+        off_fin = off_back + w * c * h * 2
+        off_fback = off_fin + 256
+        total = off_fback + 256
+        buf = symm.empty(total, dtype=torch.uint8, device=device)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+        torch.cuda.synchronize(device)
+        hdl.barrier()
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        b.symm, b.handle = buf, hdl
+        b.rx = buf[:n_rx].view(dtype).view(w * c, h)
+        b.rid = buf[off_rid:off_rid + n_id].view(torch.int32).view(w * c, k)
+        b.rw = buf[off_rw:off_rw + n_id].view(torch.float32).view(w * c, k)
+        b.y = buf[off_back:off_back + w * c * h * 2].view(dtype).view(w, c, h)
+        b.flags_in = buf[off_fin:off_fin + 4 * w].view(torch.int32)
+        b.flags_back = buf[off_fback:off_fback + 4 * w].view(torch.int32)
+        b.calls = torch.zeros(2, dtype=torch.int32, device=device)
+        b.status = torch.zeros(1, dtype=torch.int32, device=device)
+        r = self.rank
+        # my block inside destination d's arrays starts at row r * c
+        b.dst_x = parr([ptrs[d] + r * c * h * 2 for d in range(w)])
+        b.dst_ids = parr([ptrs[d] + off_rid + r * c * k * 4 for d in range(w)])
+        b.dst_wts = parr([ptrs[d] + off_rw + r * c * k * 4 for d in range(w)])
+        b.dst_flag = parr([ptrs[d] + off_fin + 4 * r for d in range(w)])
+        b.back_y = parr([ptrs[s] + off_back for s in range(w)])
+        b.back_flag = parr([ptrs[s] + off_fback + 4 * r for s in range(w)])
+        b.peer = True
 
     def _forward_fixed_torch(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         m, h = x.shape

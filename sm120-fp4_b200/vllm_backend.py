@@ -333,6 +333,16 @@ class Weights:
         return 3 * self.I * self.H // 2 + 3 * self.I * self.H // 16
 
 
+def map_expert_ids(topk_ids: torch.Tensor, topk_weights: torch.Tensor, expert_map: torch.Tensor):
+    """Global expert ids -> the ids of this rank's shard under an engine's expert map (int tensor [global experts]: local id,
+    or -1 for an expert another rank owns). Slots of other ranks' experts become id -1 with weight 0, which every kernel of
+    this package skips; the row such a call returns is the partial sum over this rank's experts."""
+    emap = expert_map.to(device=topk_ids.device)
+    local = emap[topk_ids.long()].to(torch.int32)
+    own = local >= 0
+    return torch.where(own, local, torch.full_like(local, -1)), torch.where(own, topk_weights.to(torch.float32), torch.zeros((), device=topk_ids.device))
+
+
 _SHARED_WS: dict = {}
 
 

@@ -191,3 +191,115 @@ def check_prefill_call(w, ow, x, ids, wts, out, max_tokens, sample_tokens=None, 
     assert (err <= bound).all(), f"{what}: FC2 + combine outside the exact accumulation bound ({res['max_err_over_bound']:.2f} x)"
     assert res["normwise_plain_oracle"] < 1e-2, f"{what}: normwise error against the plain oracle {res['normwise_plain_oracle']:.3e}"
     return res
+
+
+# ---------------------------------------------------------------------------------------------------- decode read-back
+def decode_map(w) -> dict:
+    import ctypes as C
+    import sm120fp4_b200._lib as L
+    buf = (C.c_longlong * 8)()
+    L.check(L.lib().b200moe_layer_workspace_map(w._h, buf), "decode map")
+    v = [int(t) for t in buf]
+    return dict(xb=v[0], xscale=v[1], aslab=v[2], slab={16: v[3], 32: v[4], 64: v[5]}, act_g1=float(np.array([v[6]], dtype=np.uint32).view(np.float32)[0]),
+                umax=v[7])
+
+
+def _operand_rows(raw: np.ndarray, n: int, kb: int, sf_off: int, nkt: int | None = None):
+    """raw u8: kb boxes of [n rows][128 B] (128-byte swizzle) then nkt scale tiles (default 4 per box) from sf_off -> (codes
+    [n, kb*128], scales [n, kb*16], zero beyond the last tile)."""
+    r = np.arange(n)[:, None]
+    by = np.arange(128)[None, :]
+    idx = r * 128 + (((by >> 4) ^ (r & 7)) << 4) + (by & 15)
+    codes = np.stack([raw[k * n * 128:(k + 1) * n * 128][idx] for k in range(kb)], axis=1).reshape(n, kb * 128)
+    nkt = 4 * kb if nkt is None else nkt
+    b = np.arange(nkt * 4)[None, :]
+    sidx = sf_off + (b >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b & 3)
+    sf = np.zeros((n, kb * 16), dtype=np.uint8)
+    sf[:, : nkt * 4] = raw[sidx]
+    return codes, sf
+
+
+def check_decode_call(w, ow, x, ids, wts, out, what=""):
+    """The tolerance-free gate of one tcgen05 decode call (M <= 16) that has just run on `w`, from the operands the kernel left
+    in its workspace (the method of the reference's interval oracle, sm120fp4/moe_oracle.py:82-150, with this kernel's
+    rounding points):
+      1. the four-term NVFP4 expansion of x stands for x up to the expansion's residual bound, element by element;
+      2. the expanded FC1 -> FC2 activations lie inside the interval of silu(gate) * up * weight that exact FC1 products of
+         the kernel's own x operand, accumulated in fp32 in any order, can give - widened by the expansion residual;
+      3. the output lies inside the fp32-accumulation bound of the exact FC2 + combine of the kernel's own activation
+         operand, plus one bf16 rounding.
+    Returns the measured maxima (each as a fraction of its bound)."""
+    from oracle import conformance as C
+    m, k = ids.shape
+    h, inter = ow.H, ow.I
+    kb1, kb2 = (h + 255) // 256, (inter + 255) // 256
+    n = 16 if m <= 4 else 32 if m <= 8 else 64
+    mp = decode_map(w)
+    ws = w.workspace
+    idn, wn, xf = ids.numpy(), wts.numpy().astype(np.float32), x.float().numpy().astype(np.float64)
+    # ---- 1. x operand
+    kt1 = (h // 16 + 3) // 4
+    raw = ws[mp["xb"]:mp["xb"] + kb1 * n * 128 + kt1 * 512].cpu().numpy()
+    codes, sfs = _operand_rows(raw, n, kb1, kb1 * n * 128, kt1)
+    colscale = ws[mp["xscale"]:mp["xscale"] + 4 * n].view(torch.float32).cpu().numpy().astype(np.float64)
+    tk_codes = codes.reshape(n // 4, 4, -1).transpose(1, 0, 2)[:, :m, : h // 2]          # [term, token, H/2]
+    tk_sf = sfs.reshape(n // 4, 4, -1).transpose(1, 0, 2)[:, :m, : h // 16]
+    cs = colscale.reshape(n // 4, 4)[:m]                                                  # 1 / g_t per token and term
+    xt = 0.0
+    xmag = 0.0
+    for t in range(4):
+        v = C.scaled_operand(tk_codes[t], tk_sf[t]) * 0.5 * cs[:, t:t + 1]
+        xt, xmag = xt + v, xmag + np.abs(v)
+    bmax = np.repeat(np.abs(xf).reshape(m, -1, 16).max(axis=-1), 16, axis=1)
+    res_x = np.abs(xf - xt)
+    bound_x = C.EXPANSION_RESIDUAL * bmax + 1e-6 * np.abs(xf).max(axis=1, keepdims=True)
+    r = {"x_residual_over_bound": float((res_x / bound_x).max())}
+    assert (res_x <= bound_x).all(), f"{what}: the x operand is further from x than four NVFP4 terms leave ({r['x_residual_over_bound']:.2f} x the bound)"
+    # ---- 2. activation operand, expert by expert (slab order = ascending touched experts)
+    touched = sorted(set(int(e) for e in idn.reshape(-1) if e >= 0))
+    a2max = float(np.abs(ow.alpha2).max())
+    slab_b = mp["slab"][n]
+    g1a = mp["act_g1"]
+    act = {}
+    worst_a = 0.0
+    for u, e in enumerate(touched):
+        tok = np.nonzero((idn == e).any(axis=1))[0]
+        wsum = np.array([wn[t][idn[t] == e].astype(np.float32).sum(dtype=np.float32) for t in tok], dtype=np.float32)
+        wf = (wsum * np.float32(np.float32(ow.alpha2[e]) * np.float32(1.0 / a2max))).astype(np.float64)[:, None]
+        w1d = C.dequant_exact(ow.q1[e], ow.s1[e].reshape(2 * inter, h // 16), 1.0) * float(ow.alpha1[e])
+        lo, hi, nom = C.fc1_activation_interval(xt[tok], w1d, inter, xabs=xmag[tok])
+        lo, hi = np.minimum(lo * wf, hi * wf), np.maximum(lo * wf, hi * wf)
+        wid = 4 * C.U32 * np.maximum(np.abs(lo), np.abs(hi))
+        lo, hi = lo - wid, hi + wid
+        sraw = ws[mp["aslab"] + u * kb2 * slab_b:mp["aslab"] + (u + 1) * kb2 * slab_b].cpu().numpy().reshape(kb2, slab_b)
+        ac = np.concatenate([_operand_rows(sraw[kb], n, 1, n * 128)[0] for kb in range(kb2)], axis=1)
+        asf = np.concatenate([_operand_rows(sraw[kb], n, 1, n * 128)[1] for kb in range(kb2)], axis=1)
+        rows = (tok[:, None] * 4 + np.arange(4)[None, :])                                # operand rows of the routed tokens
+        a_t, _ = C.expansion_value(ac[rows.T][:, :, : inter // 2], asf[rows.T][:, :, : inter // 16], g1a)
+        bm = np.repeat(np.maximum(np.abs(lo), np.abs(hi)).reshape(len(tok), -1, 16).max(axis=-1), 16, axis=1)
+        slack = C.EXPANSION_RESIDUAL * bm + 2.0 ** -9 / (g1a * 216.0)
+        ok = (a_t >= lo - slack) & (a_t <= hi + slack)
+        dist = np.maximum(lo - a_t, a_t - hi) / slack
+        worst_a = max(worst_a, float(dist.max()))
+        assert ok.all(), f"{what}: expert {e}: expanded activations outside the interval exact FC1 products allow ({float(dist.max()):.2f} x the slack)"
+        for i, t in enumerate(tok):
+            act[(int(t), e)] = a_t[i]
+    r["activation_excess_over_slack"] = max(worst_a, 0.0)
+    # ---- 3. output from the kernel's own activation operand
+    exact = np.zeros((m, h))
+    sabs = np.zeros((m, h))
+    for e in touched:
+        w2 = C.dequant_exact(ow.q2[e], ow.s2[e].reshape(h, inter // 16), 1.0) * a2max
+        for t in range(m):
+            if (t, e) in act:
+                exact[t] += act[(t, e)] @ w2.T
+                sabs[t] += np.abs(act[(t, e)]) @ np.abs(w2).T
+    kk = max(1, len(touched)) * inter
+    bound = (C.gamma(kk) + 16 * C.U32) * sabs * 1.25 + 0.5 * C.ulp(np.abs(exact) + C.gamma(kk) * sabs, "bf16")   # 1.25: the terms' magnitudes
+    got = out.float().cpu().numpy().astype(np.float64)
+    err = np.abs(got - exact)
+    r["out_err_over_bound"] = float((err / bound).max())
+    rms = float(np.sqrt((exact ** 2).mean()))
+    r["out_max_abs_over_rms_own_operands"] = float(err.max() / max(rms, 1e-30))
+    assert (err <= bound).all(), f"{what}: output outside the accumulation bound of its own operands ({r['out_err_over_bound']:.2f} x)"
+    return r

@@ -308,3 +308,21 @@ def test_released_checkpoint_layout_keeps_the_tensor_core_paths():
     w.prefill_status()
     from helpers import check_w4a4_output
     check_w4a4_output(out, O.moe_reference(x2.float().numpy(), ow, ids2.numpy(), wts2.numpy(), act_quant=True), "prefill after release")
+
+
+@pytest.mark.parametrize("name,m,routing", [("tiny", 3, "random"), ("mid", 8, "random"), ("mid", 16, "fixed8"), ("odd", 5, "random"),
+                                            ("qwen", 1, "random"), ("qwen", 16, "random"), ("qwen", 4, "fixed8"), ("gemma", 8, "random")])
+def test_decode_conformance_gate_without_a_tolerance(name, m, routing):
+    """The interval gate (the reference's distinctive quality bar: sm120fp4/oracle.py:96-183, sm120fp4/moe_oracle.py:82-150)
+    with this kernel's rounding points, on the operands the call left in its workspace."""
+    from helpers import check_decode_call
+    cfg, w, ow = layer(name)
+    w.set_decode_impl("tcgen05")
+    try:
+        x, ids, wts = inputs(cfg, m, 8100 + m, routing)
+        out = run(w, x, ids, wts)
+        r = check_decode_call(w, ow, x, ids, wts, out, f"{name} m={m} {routing}")
+        print(f"{name} m={m} {routing}: x residual {r['x_residual_over_bound']:.2f} of its bound, activations {r['activation_excess_over_slack']:.2f} "
+              f"of the slack beyond the interval, output {r['out_err_over_bound']:.2f} of its bound ({r['out_max_abs_over_rms_own_operands']:.2e} x rms)")
+    finally:
+        w.set_decode_impl("auto")

@@ -49,3 +49,28 @@ def test_scales_through_registers_match_the_copy_path(n, k):
     got_st, _ = probe(a, b, scale_path=1)
     assert np.array_equal(got_cp, got_st)
     assert np.abs(got_st - want).max() <= 1e-3 * np.abs(want).max() + 1e-4
+
+
+@pytest.mark.parametrize("k", [256, 512, 1024])
+def test_cta_pair_mma_matches_oracle(k):
+    """tcgen05 cta_group::2: two CTAs of a cluster as one 256 x 128 x 64 MMA unit (A and accumulator rows split over the two
+    CTAs, B rows split over their shared memories, one commit arriving on both)."""
+    import sm120fp4_b200._lib as L
+    rng = np.random.default_rng(4000 + k)
+    a = rng.standard_normal((256, k)).astype(np.float32) * 3
+    b = rng.standard_normal((128, k)).astype(np.float32) * 0.5
+    one = np.ones(1, dtype=np.float32)
+    qa, sa, _ = O.quantize_nvfp4(a, one)
+    qb, sb, _ = O.quantize_nvfp4(b, one)
+    want = (O.dequantize_nvfp4(qa, sa, one) @ O.dequantize_nvfp4(qb, sb, one).T).astype(np.float32)
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()  # noqa: E731
+    d = torch.full((256, 128), float("nan"), device="cuda")
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ta, tsa, tb, tsb = dev(qa), dev(O.to_128x4(sa)), dev(qb), dev(O.to_128x4(sb))
+    L.check(L.lib().b200moe_umma_pair_probe(L.ptr(ta), L.ptr(tsa), L.ptr(tb), L.ptr(tsb), k, L.ptr(d), L.ptr(status), L.stream_ptr()), "pair probe")
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0], "a bounded wait ran out in the pair probe"
+    got = d.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = np.abs(got - want).max()
+    assert err <= 1e-3 * np.abs(want).max() + 1e-4, f"max err {err} vs max |D| {np.abs(want).max()}"

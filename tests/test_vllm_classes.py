@@ -23,12 +23,13 @@ def test_fits_accepts_the_reference_shapes_and_more():
     assert fits(moe_config()) == (True, "")
     assert fits(moe_config(intermediate_size_per_partition=1024))[0]
     assert fits(moe_config(hidden_dim=2816, intermediate_size_per_partition=704))[0]      # the Gemma-4 shape
+    assert fits(moe_config(moe_parallel_config=NS(use_ep=True), num_local_experts=16))[0]  # expert parallelism is taken
 
 
 @pytest.mark.parametrize("kw,word", [
     (dict(activation=MoEActivation.GELU), "SiLU"), (dict(is_act_and_mul=False), "SiLU"),
     (dict(hidden_dim=2000), "hidden size"), (dict(intermediate_size_per_partition=700), "intermediate size"),
-    (dict(moe_parallel_config=NS(use_ep=True)), "expert parallelism"), (dict(in_dtype=torch.float16), "bf16")])
+    (dict(in_dtype=torch.float16), "bf16"), (dict(num_local_experts=512), "at most 256"), (dict(experts_per_token=32), "at most 16")])
 def test_fits_declines_with_a_reason(kw, word):
     ok, why = vc.SM120Fp4MoEMethod.fits(moe_config(**kw))
     assert not ok and word in why
@@ -50,8 +51,22 @@ def test_apply_refuses_what_the_kernels_do_not_do():
         m.apply(NS(), x, None, None, object(), None)
     with pytest.raises(NotImplementedError, match="apply_router_weight_on_input"):
         m.apply(NS(apply_router_weight_on_input=True), x, None, None, None, None)
-    with pytest.raises(NotImplementedError, match="expert map"):
-        m.apply(NS(expert_map=torch.zeros(4)), x, None, None, None, None)
+
+
+def test_expert_map_masks_other_ranks_experts():
+    """With an expert map the local shard runs with the other ranks' slots masked (id -1, weight 0): partial rows."""
+    from sm120fp4_b200.vllm_backend import map_expert_ids
+    emap = torch.tensor([-1, -1, -1, -1, 0, 1, 2, 3])                    # this rank owns global experts 4..7
+    ids = torch.tensor([[0, 5], [7, 4], [2, 3]], dtype=torch.int32)
+    wts = torch.tensor([[0.25, 0.75], [0.5, 0.5], [0.9, 0.1]])
+    lid, lw = map_expert_ids(ids, wts, emap)
+    assert lid.tolist() == [[-1, 1], [3, 0], [-1, -1]] and lid.dtype == torch.int32
+    assert lw.tolist() == [[0.0, 0.75], [0.5, 0.5], [0.0, 0.0]]
+    seen = {}
+    m = object.__new__(vc.SM120Fp4MoEMethod)
+    m.weights = NS(forward=lambda x, i, w: seen.update(ids=i, wts=w) or x)
+    m.apply(NS(expert_map=emap), torch.zeros(3, 128, dtype=torch.bfloat16), wts, ids, None, None)
+    assert seen["ids"].tolist() == lid.tolist() and seen["wts"].tolist() == lw.tolist()
 
 
 def test_register_is_a_no_op_without_the_switch(monkeypatch):
