@@ -132,8 +132,8 @@ def decode_sweep(cfg, layers, dev, steps, warmup, use_graph, rank, world, dist, 
     def call(li, c, xd, idd, wd, out):
         if eps is None:
             layers[li].forward(xd, idd, wd, out=out)
-        else:
-            eps[li].forward(xd, idd, wd, out=out)
+        else:   # every rank brings c["m"] tokens: the exchange blocks hold exactly that many rows
+            eps[li].forward(xd, idd, wd, out=out, rows=c["m"])
 
     def chain(c):
         for li in range(n_layers):
@@ -289,8 +289,7 @@ def run_ours(a):
                     w.mid = None
                 extras["ep"] = ep_stack(cfg, layers, dist, world, rank, dev, stack=a.ep_layers)
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        finish(dist)
         return
     peak, peak_src = peaks()
     value = r["step_bytes"] / (r["step_ms"] * 1e-3) / 1e9
@@ -323,9 +322,23 @@ def run_ours(a):
         "gpu_launches": launches * (2 if world == 1 else 12), "clocks": r["clocks"], "cpu_baseline": cpu,
     }
     line.update(extras)
-    print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    finish(dist)
+
+
+def finish(dist):
+    """Leave the process group. With the peer-store transport the ranks hold mappings of one another's memory; they are
+    dropped first, and all ranks leave together."""
+    if dist is None:
+        return
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if EP_TRANSPORT == "peer":
+        sys.stdout.flush()
+        os._exit(0)        # the mappings are released with the process; a collective teardown after that has been seen to wait forever
+    dist.destroy_process_group()
 
 
 def ep_parity(cfg, ep, dist, world, rank, dev):

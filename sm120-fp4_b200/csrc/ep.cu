@@ -331,9 +331,9 @@ extern "C" int b200moe_ep_plan(const int* ids, int m, int k, int world, int expe
 // rows [0, offsets[world]) of sx bf16 [rows, h] and meta int32 [rows, 2k] (local ids, then the weights' float bits)
 extern "C" int b200moe_ep_gather(const void* x, const int* ids, const float* wts, const int* send_tok, const int* offsets, int h, int k, int world,
                                  int experts_per_rank, int max_rows, void* sx, int* meta, void* stream) {
-  if (!x || !ids || !wts || !send_tok || !offsets || !sx || !meta) return B200MOE_ERR_ARG;
   if (h <= 0 || h % 8 || k < 1 || world < 1 || world > kEpMaxWorld || max_rows < 0) return B200MOE_ERR_SHAPE;
-  if (max_rows == 0) return B200MOE_OK;
+  if (max_rows == 0) return B200MOE_OK;   // nothing to send (an empty batch): the buffers may be null
+  if (!x || !ids || !wts || !send_tok || !offsets || !sx || !meta) return B200MOE_ERR_ARG;
   const int grid = max_rows < 148 * 16 ? max_rows : 148 * 16;
   k_ep_gather<<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, send_tok, offsets, h, k, world, experts_per_rank,
                                                       (__nv_bfloat16*)sx, meta);

@@ -86,7 +86,7 @@ __device__ __forceinline__ int rec_scale_offset(int r, int b16) { return 16384 +
 // codes are never written). Pairs whose slot is empty (negative id) are not in `pairs`: they get dst_row = -1 here.
 __global__ void __launch_bounds__(256) k_prefill_rowmap(const int* __restrict__ ids, int P, const int* __restrict__ experts,
                                                         const int* __restrict__ offsets, const int* __restrict__ pairs, int Umax, int max_tiles,
-                                                        int KB, int* __restrict__ ntiles, int* __restrict__ tile_expert,
+                                                        int KB, int even, int* __restrict__ ntiles, int* __restrict__ tile_expert,
                                                         int* __restrict__ tile_first, int* __restrict__ tile_end, uint8_t* __restrict__ rec,
                                                         int* __restrict__ row_pair, int* __restrict__ dst_row) {
   __shared__ int wsum[8];
@@ -98,7 +98,9 @@ __global__ void __launch_bounds__(256) k_prefill_rowmap(const int* __restrict__ 
     e = experts[u];
     if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
   }
-  const int mine = (hi - lo + 127) >> 7;
+  // `even`: an expert's tile count is rounded up to an even number (CTA pairs take two tiles of one expert at a time); the
+  // extra tile holds padding rows only
+  const int mine = even ? 2 * ((hi - lo + 255) >> 8) : (hi - lo + 127) >> 7;
   int inc = mine;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -449,12 +451,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(const __grid_con
 // last column block of the tile releases them, so there is no drain between row tiles.
 // Warps 0-7: epilogue (two per TMEM lane quadrant, each half of the columns); 8-11: scale warps (scale tiles shared
 // memory -> registers -> TMEM, one warp per lane quadrant); 12: MMA issuer (converged warp, one elected lane);
-// 13: producer of activation records; 14: producer of weight records.
-constexpr int kPrThreads = 15 * 32;
+// 13: producer of activation records; 14, 15: producers of weight records (alternate records: one thread issues at most
+// ~3 M bulk copies per second, less than the record rate the MMAs can take).
+constexpr int kPrThreads = 16 * 32;
 
 struct PrShared {
   uint64_t a_full[12], a_empty[12], a_sfr[12];   // per K box of the resident activation tile
   uint64_t b_full[12], b_empty[12], b_sfr[12];   // per ring stage of weight records
+  uint64_t b_peer[12];                           // CTA pairs, even CTA: the odd CTA's copy of the stage (which holds the scale tiles) has landed
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -462,7 +466,16 @@ struct PrShared {
 
 static_assert(sizeof(PrShared) <= 1024, "the epilogue's store patches start 1024 bytes after the barriers");
 
-template <int PHASE>
+// PAIR: two CTAs of a cluster (an SM pair) take two row tiles of one expert and run them as ONE 256-row MMA per weight
+// record (tcgen05 cta_group::2): CTA r keeps its own tile's records resident and streams only its half of every weight
+// record with ONE bulk copy - the even CTA code rows 0..63 (8 KB), the odd CTA code rows 64..127 and the scale tiles that
+// follow them in the record (10 KB) - so a weight byte fetched from L2 feeds twice the math. Both CTAs need the B scales of
+// all 128 rows in their own TMEM: the even CTA's scale warps read them from the odd CTA's shared memory (distributed shared
+// memory; 2 KB per record) instead of fetching them a second time - an SM only accepts a few million bulk copies per second.
+// Every load is an ordinary per-CTA bulk copy (nothing is multicast). The even CTA issues the MMAs and
+// its commits arrive on both CTAs' barriers; the scale warps and epilogue warps of the odd CTA arrive on the even CTA's
+// barriers across the cluster. The tile plan gives every expert an even number of tiles in this mode.
+template <int PHASE, bool PAIR>
 __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_constant__ PrefillParams P, int NSB) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -470,37 +483,53 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   constexpr int kARec = PHASE >= 3 ? kMidRec : kRec;            // bytes of one operand record
   constexpr int kACodes = PHASE >= 3 ? 8192 : 16384;            // ... of which codes; the scale tiles follow
   constexpr int kARows = PHASE >= 3 ? 64 : 128;                 // operand rows per tile
+  constexpr int kBSlot = PAIR ? 8192 + 2048 : kRec;             // bytes of a ring stage: half the code rows + all scale tiles, or a whole record
+  constexpr int kBCodes = PAIR ? 8192 : 16384;
+  static_assert(!PAIR || PHASE <= 2, "the CTA-pair form exists for the W4A4 phases");
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;          // CTA of the pair; 0 issues the MMAs
   uint8_t* abuf = smem;                      // KB records of the current row tile
-  uint8_t* ring = smem + ((KB * kARec + 1023) & ~1023);   // NSB weight records
-  PrShared& S = *reinterpret_cast<PrShared*>(ring + NSB * kRec);
-  uint8_t* stage = ring + NSB * kRec + 1024;   // PHASE 2: eight 32-row x 144-byte patches for the epilogue's transposed stores
+  uint8_t* ring = smem + ((KB * kARec + 1023) & ~1023);   // NSB weight stages
+  PrShared& S = *reinterpret_cast<PrShared*>(ring + ((NSB * kBSlot + 1023) & ~1023));
+  uint8_t* stage = reinterpret_cast<uint8_t*>(&S) + 1024;   // PHASE 2: eight 32-row x 144-byte patches for the epilogue's transposed stores
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int k = 0; k < KB; ++k) { mbar_init(&S.a_full[k], 1); mbar_init(&S.a_empty[k], 1); mbar_init(&S.a_sfr[k], 4); }
-    for (int s = 0; s < NSB; ++s) { mbar_init(&S.b_full[s], 1); mbar_init(&S.b_empty[s], 1); mbar_init(&S.b_sfr[s], 4); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 8); }
+    const int nsf = PAIR ? 8 : 4, nep = PAIR ? 16 : 8;   // arrivals of the scale warps / epilogue warps of one or both CTAs
+    for (int k = 0; k < KB; ++k) { mbar_init(&S.a_full[k], 1); mbar_init(&S.a_empty[k], 1); mbar_init(&S.a_sfr[k], nsf); }
+    for (int s = 0; s < NSB; ++s) { mbar_init(&S.b_full[s], 1); mbar_init(&S.b_empty[s], 1); mbar_init(&S.b_sfr[s], nsf); mbar_init(&S.b_peer[s], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], nep); }
     S.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 12) { tmem_alloc(&S.tmem_base, 512); tmem_relinquish(); }
+  if (warp == 12) {
+    if (PAIR) { tmem_alloc2(&S.tmem_base, 512); tmem_relinquish2(); }
+    else { tmem_alloc(&S.tmem_base, 512); tmem_relinquish(); }
+  }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
+  // arrive on barrier `bar` of the CTA that issues the MMAs: this CTA, or the even CTA of the pair across the cluster
+  auto arrive_at_issuer = [&](uint64_t* bar) {
+    if (!PAIR || rank == 0) mbar_arrive(bar);
+    else mbar_arrive_cluster(mapa_shared(smem_u32(bar), 0));
+  };
   const uint32_t tmem = S.tmem_base;
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 256, tm_sfb = tmem + 256 + 16 * KB;   // 2 x 128 | KB x 16 | NSB x 16
   // This CTA's work: segments (row tile t, column blocks [n0, n1)). Whole tiles are dealt round-robin for as many full
   // rounds as there are (tiles t and t + 1 of one expert then run on neighbouring CTAs at the same time and in the same
   // block order, so the second reader of a weight record finds it in L2); the tiles left over are cut into equal ranges
   // of column blocks so that every CTA gets a share of them.
-  const int NT = P.ntiles[0], G = (int)gridDim.x, cta = (int)blockIdx.x;
+  // (PAIR: the unit is a pair of tiles (2u, 2u + 1) and the worker a cluster; this CTA's tile of unit u is 2u + rank.)
+  constexpr int kPer = PAIR ? 2 : 1;
+  const int NT = P.ntiles[0] / kPer, G = (int)gridDim.x / kPer, cta = (int)blockIdx.x / kPer;
   const int rounds = NT / G, T0 = rounds * G;
   const int rem = (NT - T0) * NBLK, per = (rem + G - 1) / G;
   const int ra = min(rem, cta * per), rb = min(rem, ra + per);
   auto for_each_segment = [&](auto&& body) {   // body(t, n0, n1, ordinal)
     int ord = 0;
-    for (int r = 0; r < rounds; ++r) body(r * G + cta, 0, NBLK, ord++);
+    for (int r = 0; r < rounds; ++r) body((r * G + cta) * kPer + (int)rank, 0, NBLK, ord++);
     for (int a2 = ra; a2 < rb;) {
-      const int t = T0 + a2 / NBLK, n0 = a2 % NBLK, n1 = min(NBLK, n0 + (rb - a2));
+      const int t = (T0 + a2 / NBLK) * kPer + (int)rank, n0 = a2 % NBLK, n1 = min(NBLK, n0 + (rb - a2));
       body(t, n0, n1, ord++);
       a2 += n1 - n0;
     }
@@ -519,16 +548,28 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
       });
     }
     __syncwarp();
-  } else if (warp == 14) {
-    // ============================================================== weight records: one per (item, K box)
+  } else if (warp == 14 || warp == 15) {
+    // ============================================================== weight records: one per (item, K box); the two producers
+    // walk the same sequence and issue alternate positions
     if (lane == 0) {
       int slot = 0, use = 0;
+      bool mine = warp == 14;
       for_each_segment([&](int t, int n0, int n1, int) {
         const uint8_t* src = P.wrec + ((long long)P.tile_expert[t] * NBLK + n0) * KB * kRec;
         for (int i = 0; i < (n1 - n0) * KB; ++i) {   // the records of consecutive column blocks of an expert are contiguous
-          if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
-          mbar_expect_tx(&S.b_full[slot], kRec);
-          bulk_load(ring + slot * kRec, src + (long long)i * kRec, kRec, &S.b_full[slot]);
+          if (mine) {
+            if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
+            if (PAIR) {   // this CTA's 64 code rows of the record (rows are 128 bytes, 8-row groups contiguous); the odd CTA's copy
+                          // runs on through the scale tiles, which follow row 127
+              const uint32_t nbytes = rank == 0 ? 8192u : 8192u + 2048u;
+              mbar_expect_tx(&S.b_full[slot], nbytes);
+              bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + 8192 * rank, nbytes, &S.b_full[slot]);
+            } else {
+              mbar_expect_tx(&S.b_full[slot], kBSlot);
+              bulk_load(ring + slot * kRec, src + (long long)i * kRec, kRec, &S.b_full[slot]);
+            }
+          }
+          mine = !mine;
           if (++slot == NSB) { slot = 0; ++use; }
         }
       });
@@ -537,7 +578,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   } else if (warp >= 8 && warp < 12) {
     // ============================================================== scale warps
     const uint32_t lane_base = (uint32_t)((warp - 8) * 32) << 16;
-    const uint32_t a_u = smem_u32(abuf) + kACodes + lane * 16, b_u = smem_u32(ring) + 16384 + lane * 16;
+    const uint32_t a_u = smem_u32(abuf) + kACodes + lane * 16, b_u = smem_u32(ring) + kBCodes + lane * 16;
     auto put = [&](uint32_t src, uint32_t dst_col) {   // four 512-byte scale tiles -> 16 TMEM columns of this quadrant
       uint32_t r[16];
 #pragma unroll
@@ -558,43 +599,74 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
           if (n == n0) {
             if (!mbar_wait(&S.a_full[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 1;
             put(a_u + kb * kARec, tm_sfa + 16 * kb);
-            if (lane == 0) mbar_arrive(&S.a_sfr[kb]);
+            if (lane == 0) arrive_at_issuer(&S.a_sfr[kb]);
           }
           if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
-          if (!PF_ABLATE(4)) put(b_u + slot * kRec, tm_sfb + 16 * slot);
-          if (lane == 0) mbar_arrive(&S.b_sfr[slot]);
+          if (PAIR && rank == 1 && lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&S.b_peer[slot]), 0));   // the even CTA may read the scale tiles
+          if (PAIR && rank == 0) {   // the scale tiles of the stage sit in the odd CTA's shared memory
+            if (!mbar_wait_cluster(&S.b_peer[slot], ph, &S.abort_flag)) *P.status = 1;
+            const uint32_t src = mapa_shared(b_u + slot * kBSlot, 1);
+            uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 t4 = lds128_cluster(src + j * 512);
+              r[4 * j] = t4.x, r[4 * j + 1] = t4.y, r[4 * j + 2] = t4.z, r[4 * j + 3] = t4.w;
+            }
+            tmem_st_32x32b_x16(tm_sfb + 16 * slot + lane_base, r);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+          } else if (!PF_ABLATE(4)) {
+            put(b_u + slot * kBSlot, tm_sfb + 16 * slot);
+          }
+          if (lane == 0) arrive_at_issuer(&S.b_sfr[slot]);
           if (++slot == NSB) { slot = 0; ph ^= 1u; }
         }
     });
   } else if (warp == 12) {
-    // ============================================================== MMA issuer
+    // ============================================================== MMA issuer (PAIR: of the even CTA only)
     const uint32_t el = elect_one();
-    const uint32_t idesc = idesc_mxf4nvf4(128, 128);
+    const uint32_t idesc = PAIR ? idesc_mxf4nvf4_pair(128) : idesc_mxf4nvf4(128, 128);
     const uint64_t desc0 = smem_desc_sw128_kmajor(0);
     const uint32_t a16 = smem_u32(abuf) >> 4, b16 = smem_u32(ring) >> 4;
     int slot = 0, ab = 0, works = 0;
     uint32_t ph = 0;
     uint32_t aph[2] = {0, 0};
+    auto wait_ready = [&](uint64_t* bar, uint32_t parity) {   // arrivals may come from the peer CTA: acquire at cluster scope
+      return PAIR ? mbar_wait_cluster(bar, parity, &S.abort_flag) : mbar_wait(bar, parity, &S.abort_flag);
+    };
+    if (!PAIR || rank == 0)
     for_each_segment([&](int, int n0, int n1, int ord) {
       for (int n = n0; n < n1; ++n) {
         const bool first = n == n0, last = n == n1 - 1;
-        if (works >= 2 && !mbar_wait(&S.acc_empty[ab], aph[ab] ^ 1u, &S.abort_flag)) *P.status = 5;
+        if (works >= 2 && !wait_ready(&S.acc_empty[ab], aph[ab] ^ 1u)) *P.status = 5;
         for (int kb = 0; kb < KB; ++kb) {
-          if (first && !mbar_wait(&S.a_sfr[kb], (uint32_t)(ord & 1), &S.abort_flag)) *P.status = 8;
-          if (!mbar_wait(&S.b_sfr[slot], ph, &S.abort_flag)) *P.status = 8;
+          if (first && !wait_ready(&S.a_sfr[kb], (uint32_t)(ord & 1))) *P.status = 8;
+          if (!wait_ready(&S.b_sfr[slot], ph)) *P.status = 8;
           tc_fence_after();
-          const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kARec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kRec >> 4));
+          const uint64_t ad = desc0 | (uint64_t)(a16 + kb * (kARec >> 4)), bd = desc0 | (uint64_t)(b16 + slot * (kBSlot >> 4));
           const int nkt = kb == KB - 1 ? nkt_last : 4;
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj)
-            if (jj < nkt && !PF_ABLATE(2))
-              umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
-                              (kb > 0 || jj > 0) ? 1u : 0u, el);
-          umma_commit_p(&S.b_empty[slot], el);
-          if (last) umma_commit_p(&S.a_empty[kb], el);   // the next segment's record of this box may land
+            if (jj < nkt && !PF_ABLATE(2)) {
+              if (PAIR)
+                umma2_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
+                                 (kb > 0 || jj > 0) ? 1u : 0u, el);
+              else
+                umma_mxf4nvf4_p(tm_acc + 128 * ab, ad + 2 * jj, bd + 2 * jj, idesc, tm_sfa + 16 * kb + 4 * jj, tm_sfb + 16 * slot + 4 * jj,
+                                (kb > 0 || jj > 0) ? 1u : 0u, el);
+            }
+          if (PAIR) {   // one commit frees the stage (and, after a tile's last block, the operand box) in both CTAs
+            umma2_commit_p(&S.b_empty[slot], (uint16_t)3, el);
+            if (last) umma2_commit_p(&S.a_empty[kb], (uint16_t)3, el);
+          } else {
+            umma_commit_p(&S.b_empty[slot], el);
+            if (last) umma_commit_p(&S.a_empty[kb], el);   // the next segment's record of this box may land
+          }
           if (++slot == NSB) { slot = 0; ph ^= 1u; }
         }
-        umma_commit_p(&S.acc_full[ab], el);
+        if (PAIR) umma2_commit_p(&S.acc_full[ab], (uint16_t)3, el);
+        else umma_commit_p(&S.acc_full[ab], el);
         aph[ab] ^= 1u;
         ab ^= 1;
         ++works;
@@ -751,7 +823,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&S.acc_empty[ab]);
+        if (lane == 0) arrive_at_issuer(&S.acc_empty[ab]);
         aph[ab] ^= 1u;
         ab ^= 1;
       }
@@ -759,7 +831,11 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) tmem_dealloc(tmem, 512);
+  if (PAIR) cluster_sync_all();   // the pair's last MMAs read both CTAs' shared memory and write both CTAs' TMEM
+  if (warp == 12) {
+    if (PAIR) tmem_dealloc2(tmem, 512);
+    else tmem_dealloc(tmem, 512);
+  }
   if (S.abort_flag)
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
 }
@@ -837,7 +913,7 @@ static PrefillLayout prefill_layout(int E, int H, int I, int top_k, int max_toke
   PrefillLayout L;
   const long long P = (long long)max_tokens * top_k;
   const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
-  L.max_tiles = (int)(P / 128 + E);
+  L.max_tiles = (int)(P / 128 + 2 * E);   // every expert may end in a partly filled tile, plus one empty tile to make its count even
   long long o = 0;
   L.experts = o, o = pf_align(o + 4LL * E);
   L.offsets = o, o = pf_align(o + 4LL * (E + 1));
@@ -873,28 +949,56 @@ void b200_prefill_workspace_map(int E, int H, int I, int top_k, int max_tokens, 
 // One GEMM launch. Phases 1/2 (W4A4): the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit
 // in shared memory and the scale columns fit in TMEM, otherwise the kernel that streams both operands. Phases 3/4 (W4A16)
 // exist for the resident-A kernel only.
-static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, cudaStream_t st) {
+// B200MOE_PREFILL_PAIR: "1" / "0" force the W4A4 GEMMs to run as CTA pairs (256 rows per weight record, cta_group::2) or as
+// single CTAs; unset: pairs from kPairMinTokens tokens on (below, most experts hold less than one full tile and the second
+// tile of a pair would be padding).
+static int pair_mode_setting() {
+  static const int v = [] { const char* c = getenv("B200MOE_PREFILL_PAIR"); return !c ? -1 : c[0] == '1' ? 1 : 0; }();
+  return v;
+}
+constexpr int kPairMinTokens = 2048;
+
+// Whether the W4A4 GEMMs of this shape run as CTA pairs: both phases' resident tiles and at least 3 ring stages must fit.
+static bool prefill_pairs(int H, int I, int M) {
+  const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
+  const int setting = pair_mode_setting();
+  if (setting == 0 || (setting < 0 && M < kPairMinTokens) || KB1 > 12 || KB2 > 12) return false;
+  const int a1 = KB1 * kRec, n1 = (227 * 1024 - 3072 - a1) / 10240;
+  return n1 >= 3 && (512 - 256 - 16 * KB1) / 16 >= 3;
+}
+
+static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, bool pair, cudaStream_t st) {
   const int tail = 1024 + ((phase == 2) ? 8 * 32 * 144 : 0);   // barriers (+ the W4A4 FC2 epilogue's store patches)
   const int abytes = (KB * (phase >= 3 ? kMidRec : kRec) + 1023) & ~1023;   // the resident operand tile
-  int nsb = (227 * 1024 - 1024 - tail - 256 - abytes) / kRec;
+  const int slot_bytes = pair ? 10240 : kRec;
+  int nsb = (227 * 1024 - 2048 - tail - 256 - abytes) / slot_bytes;
   const int tmem_cap = (512 - 256 - 16 * KB) / 16;
   if (nsb > tmem_cap) nsb = tmem_cap;
   if (nsb > 12) nsb = 12;
   if (KB <= 12 && nsb >= 3) {
-    const int sm_r = 1024 + abytes + nsb * kRec + tail;
-    const void* fn = phase == 1 ? (const void*)k_prefill_gemm_r<1> : phase == 2 ? (const void*)k_prefill_gemm_r<2>
-                   : phase == 3 ? (const void*)k_prefill_gemm_r<3> : (const void*)k_prefill_gemm_r<4>;
-    static thread_local int configured_r[4] = {0, 0, 0, 0};
-    if (configured_r[phase - 1] < sm_r) {
+    const int sm_r = 1024 + abytes + ((nsb * slot_bytes + 1023) & ~1023) + tail;
+    const void* fn = pair ? (phase == 1 ? (const void*)k_prefill_gemm_r<1, true> : (const void*)k_prefill_gemm_r<2, true>)
+                   : phase == 1 ? (const void*)k_prefill_gemm_r<1, false> : phase == 2 ? (const void*)k_prefill_gemm_r<2, false>
+                   : phase == 3 ? (const void*)k_prefill_gemm_r<3, false> : (const void*)k_prefill_gemm_r<4, false>;
+    if (pair && phase > 2) return B200MOE_ERR_SHAPE;
+    static thread_local int configured_r[6] = {0, 0, 0, 0, 0, 0};
+    const int ci = pair ? 3 + phase : phase - 1;
+    if (configured_r[ci] < sm_r) {
       B200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, sm_r));
-      configured_r[phase - 1] = sm_r;
+      configured_r[ci] = sm_r;
     }
-    if (phase == 1) k_prefill_gemm_r<1><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
-    else if (phase == 2) k_prefill_gemm_r<2><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
-    else if (phase == 3) k_prefill_gemm_r<3><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
-    else k_prefill_gemm_r<4><<<sms, kPrThreads, sm_r, st>>>(p, nsb);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(pair ? (sms & ~1) : sms), cfg.blockDim = dim3(kPrThreads), cfg.dynamicSmemBytes = (size_t)sm_r, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = pair ? 1 : 0;
+    PrefillParams pp = p;
+    void* args[] = {(void*)&pp, (void*)&nsb};
+    B200_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, args));
   } else {
-    if (phase > 2) return B200MOE_ERR_SHAPE;
+    if (phase > 2 || pair) return B200MOE_ERR_SHAPE;
     const int smem = 1024 + kPfStages * 2 * kRec + (int)sizeof(PfShared);
     static thread_local bool configured = false;
     if (!configured) {
@@ -933,12 +1037,13 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   if (Umax > 256) return B200MOE_ERR_LIMIT;
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
-  const int max_tiles = P / 128 + Umax;   // tiles this batch can need (<= the workspace's capacity)
+  const bool pair = prefill_pairs(H, I, M) && sms >= 2;
+  const int max_tiles = P / 128 + 2 * Umax;   // tiles this batch can need (<= the workspace's capacity)
   {
     const int rows = max_tiles * 128;
     int grid = (rows + 255) / 256;
     if (grid > sms * 8) grid = sms * 8;
-    k_prefill_rowmap<<<grid, 256, 0, st>>>(ids, P, experts, offsets, pairs, Umax, max_tiles, KB1, ntiles, tile_expert, tile_first, tile_end,
+    k_prefill_rowmap<<<grid, 256, 0, st>>>(ids, P, experts, offsets, pairs, Umax, max_tiles, KB1, pair ? 1 : 0, ntiles, tile_expert, tile_first, tile_end,
                                            w + L.xrec, row_pair, dst_row);
     B200_LAUNCH_CHECK();
   }
@@ -953,13 +1058,13 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.gs_in = gs_x, p.gs_out = gs_a, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
-  rc = launch_gemm(p, 1, KB1, sms, st);
+  rc = launch_gemm(p, 1, KB1, sms, pair, st);
   if (rc != B200MOE_OK) return rc;
   // FC2
   p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.gs_in = gs_a, p.gs_out = 0.f, p.orec = nullptr;
   p.wts = wts, p.y = (__nv_bfloat16*)(w + L.y);
   p.NBLK = H / 128, p.KB = KB2, p.KT = KT2;
-  rc = launch_gemm(p, 2, KB2, sms, st);
+  rc = launch_gemm(p, 2, KB2, sms, pair, st);
   if (rc != B200MOE_OK) return rc;
   k_prefill_combine<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)(w + L.y), dst_row, M, top_k, H, (__nv_bfloat16*)out);
   B200_LAUNCH_CHECK();
@@ -1052,13 +1157,13 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   // FC1
   p.arec = w + L.xrec, p.wrec = w1t, p.alpha = alpha1, p.orec = w + L.arec;
   p.NBLK = I / 64, p.KB = KB1, p.KT = KT1, p.KB2 = KB2;
-  rc = launch_gemm(p, 3, KB1, sms, st);
+  rc = launch_gemm(p, 3, KB1, sms, false, st);
   if (rc != B200MOE_OK) return rc;
   // FC2
   p.arec = w + L.arec, p.wrec = w2t, p.alpha = alpha2, p.orec = nullptr;
   p.wts = wts, p.yf = (float*)(w + L.y);
   p.NBLK = H / 128, p.KB = KB2, p.KT = KT2;
-  rc = launch_gemm(p, 4, KB2, sms, st);
+  rc = launch_gemm(p, 4, KB2, sms, false, st);
   if (rc != B200MOE_OK) return rc;
   k_combine_f32<<<sms * 4, 256, 0, st>>>((const float*)(w + L.y), dst_row, M, top_k, H, (__nv_bfloat16*)out);
   B200_LAUNCH_CHECK();

@@ -76,9 +76,10 @@ class ExpertParallelMoE:
             self._lf_out = False
 
     # -------------------------------------------------------------------------------------------- variable-size exchange
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
+                rows: int | None = None) -> torch.Tensor:
         if self.capacity is not None:
-            return self.forward_fixed(x, topk_ids, topk_weights, out)
+            return self.forward_fixed(x, topk_ids, topk_weights, out, rows)
         if self.world == 1:   # one rank owns every expert: nothing to dispatch
             self.last_sent_rows = 0
             y = self.local_forward(x, topk_ids, topk_weights)
@@ -166,24 +167,26 @@ class ExpertParallelMoE:
         return out.to(dtype)
 
     # -------------------------------------------------------------------------------------------- fixed-capacity exchange
-    def forward_fixed(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """Every (source, destination) block holds exactly `capacity` rows (>= the tokens of a rank's batch): row t of the
-        block is token t, its slots masked to -1 when the destination owns none of its experts. No host synchronisation and
-        no allocation after the first call of a shape: the call can be captured into a CUDA graph. On a CUDA device the
-        dispatch, the unpacking and the combine are one library kernel each; on the CPU (gloo tests) the same arithmetic runs
-        in torch."""
+    def forward_fixed(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor | None = None,
+                      rows: int | None = None) -> torch.Tensor:
+        """Every (source, destination) block holds exactly `rows` rows (default: `capacity`; at least the tokens of any rank's
+        batch, and THE SAME NUMBER ON EVERY RANK - engines that pad decode batches to a common size pass that size, so that a
+        destination runs world x rows rows and not world x capacity): row t of the block is token t, its slots masked to -1
+        when the destination owns none of its experts. No host synchronisation and no allocation after the first call of a
+        shape: the call can be captured into a CUDA graph. On a CUDA device the dispatch, the unpacking and the combine are one
+        library kernel each; on the CPU (gloo tests) the same arithmetic runs in torch."""
         m, h = x.shape
-        c = self.capacity
-        if m > c:
-            raise ValueError(f"batch of {m} tokens exceeds the dispatch capacity {c}")
+        c = self.capacity if rows is None else int(rows)
+        if m > c or c > self.capacity:
+            raise ValueError(f"batch of {m} tokens / block of {c} rows exceeds the dispatch capacity {self.capacity}")
         per = self.E // self.world
         self.last_sent_rows = self.world * c
         if not x.is_cuda:
-            y = self._forward_fixed_torch(x, topk_ids, topk_weights)
+            y = self._forward_fixed_torch(x, topk_ids, topk_weights, c)
             return y if out is None else out.copy_(y)
         from . import _lib
         lib = _lib.lib()
-        b = self._buffers(h, x.device, x.dtype)
+        b = self._buffers(c, h, x.device, x.dtype)
         ids = topk_ids if topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() else topk_ids.to(torch.int32).contiguous()
         wts = topk_weights if topk_weights.dtype == torch.float32 and topk_weights.is_contiguous() else topk_weights.to(torch.float32).contiguous()
         if not x.is_contiguous():
@@ -220,20 +223,21 @@ class ExpertParallelMoE:
 
     def status(self) -> None:
         """Synchronise and raise if a bounded wait of the peer-store exchange ran out (a peer's rows never arrived)."""
-        b = getattr(self, "_buf", None)
-        if b is not None and b.peer:
-            v = int(b.status.item())
-            if v:
-                b.status.zero_()
-                raise RuntimeError(f"expert-parallel exchange: rank {v - 1} did not deliver its rows within the wait limit")
+        for b in getattr(self, "_bufs", {}).values():
+            if b.peer:
+                v = int(b.status.item())
+                if v:
+                    b.status.zero_()
+                    raise RuntimeError(f"expert-parallel exchange: rank {v - 1} did not deliver its rows within the wait limit")
 
-    def _buffers(self, h: int, device, dtype):
-        key = (h, str(device), dtype)
-        if getattr(self, "_buf_key", None) == key:
-            return self._buf
+    def _buffers(self, c: int, h: int, device, dtype):
+        key = (c, h, str(device), dtype)
+        bufs = self.__dict__.setdefault("_bufs", {})
+        if key in bufs:
+            return bufs[key]
         import ctypes as C
         from types import SimpleNamespace
-        w, c, k = self.world, self.capacity, self.k
+        w, k = self.world, self.k
         block = c * (h * 2 + k * 8)
         block = (block + 255) // 256 * 256
         z = lambda *shape, dt: torch.zeros(*shape, dtype=dt, device=device)  # noqa: E731
@@ -242,7 +246,7 @@ class ExpertParallelMoE:
         parr = lambda vals: (C.c_void_p * len(vals))(*vals)  # noqa: E731
         if self.transport == "peer":
             try:
-                self._peer_buffers(b, h, device, dtype, parr)
+                self._peer_buffers(b, c, h, device, dtype, parr)
             except Exception as ex:  # noqa: BLE001 - no peer mapping on this system: fall back to the NCCL transport, loudly
                 import sys
                 print(f"expert-parallel peer transport unavailable ({type(ex).__name__}: {ex}); using the NCCL exchange", file=sys.stderr)
@@ -260,13 +264,14 @@ class ExpertParallelMoE:
             b.dst_ids = parr([base + d * block + c * h * 2 for d in range(w)])
             b.dst_wts = parr([base + d * block + c * h * 2 + c * k * 4 for d in range(w)])
             b.dst_flag = None
-        self._buf, self._buf_key = b, key
+        bufs[key] = b
+        self._buf = b   # the most recent set (what tests and tools look at)
         return b
 
-    def _peer_buffers(self, b, h, device, dtype, parr) -> None:
+    def _peer_buffers(self, b, c, h, device, dtype, parr) -> None:
         """One symmetric allocation per rank: [rx | rid | rw | back | flags_in | flags_back], mapped into every peer."""
         import torch.distributed._symmetric_memory as symm
-        w, c, k = self.world, self.capacity, self.k
+        w, k = self.world, self.k
         n_rx, n_id = w * c * h * 2, w * c * k * 4
         off_rid, off_rw, off_back = n_rx, n_rx + n_id, n_rx + 2 * n_id
         off_fin = off_back + w * c * h * 2
@@ -297,9 +302,8 @@ class ExpertParallelMoE:
         b.back_flag = parr([ptrs[s] + off_fback + 4 * r for s in range(w)])
         b.peer = True
 
-    def _forward_fixed_torch(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+    def _forward_fixed_torch(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, c: int) -> torch.Tensor:
         m, h = x.shape
-        c = self.capacity
         per = self.E // self.world
         ids = topk_ids.to(torch.int64)
         wts = topk_weights.to(torch.float32)

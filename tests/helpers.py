@@ -116,7 +116,12 @@ def check_prefill_call(w, ow, x, ids, wts, out, max_tokens, sample_tokens=None, 
     assert np.array_equal(_i32(ws, mp["pairs"], p)[: live.size], live[order]), f"{what}: pairs"
     nt = int(_i32(ws, mp["ntiles"], 1)[0])
     counts = np.diff(woff[: (wex >= 0).sum() + 1])
-    assert nt == int(((counts + 127) // 128).sum()), f"{what}: tile count"
+    import os
+    setting = os.environ.get("B200MOE_PREFILL_PAIR", "")
+    if (setting == "1" or (setting == "" and m >= 2048)) and kb1 <= 10:   # CTA pairs: an even number of tiles per expert
+        assert nt == int((2 * ((counts + 255) // 256)).sum()), f"{what}: tile count (pairs)"
+    else:
+        assert nt == int(((counts + 127) // 128).sum()), f"{what}: tile count"
     row_pair = _i32(ws, mp["row_pair"], nt * 128)
     tile_expert = _i32(ws, mp["tile_expert"], nt)
     valid = row_pair >= 0

@@ -114,7 +114,11 @@ def _worker(rank, world, port, q):
         import traceback
         q.put((rank, "error", traceback.format_exc()))
     finally:
-        dist.destroy_process_group()
+        # leave without tearing the process group down: the parent has the results, and a teardown that waits for a peer which
+        # is already gone would only delay the test
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -131,6 +135,8 @@ def test_two_rank_expert_parallel_matches_the_full_layer():
     res = [q.get(timeout=300) for _ in range(2)]
     for p in procs:
         p.join(timeout=60)
+        if p.is_alive():
+            p.kill()
     for r in res:
         assert r[1] != "error", r[2]
         for err, rms, same, what in r[1]:
