@@ -458,7 +458,6 @@ constexpr int kPrThreads = 16 * 32;
 struct PrShared {
   uint64_t a_full[12], a_empty[12], a_sfr[12];   // per K box of the resident activation tile
   uint64_t b_full[12], b_empty[12], b_sfr[12];   // per ring stage of weight records
-  uint64_t b_peer[12];                           // CTA pairs, even CTA: the odd CTA's copy of the stage (which holds the scale tiles) has landed
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -468,10 +467,8 @@ static_assert(sizeof(PrShared) <= 1024, "the epilogue's store patches start 1024
 
 // PAIR: two CTAs of a cluster (an SM pair) take two row tiles of one expert and run them as ONE 256-row MMA per weight
 // record (tcgen05 cta_group::2): CTA r keeps its own tile's records resident and streams only its half of every weight
-// record with ONE bulk copy - the even CTA code rows 0..63 (8 KB), the odd CTA code rows 64..127 and the scale tiles that
-// follow them in the record (10 KB) - so a weight byte fetched from L2 feeds twice the math. Both CTAs need the B scales of
-// all 128 rows in their own TMEM: the even CTA's scale warps read them from the odd CTA's shared memory (distributed shared
-// memory; 2 KB per record) instead of fetching them a second time - an SM only accepts a few million bulk copies per second.
+// record - code rows 64r..64r+63 plus the record's scale tiles (both CTAs need the B scales of all 128 rows in their own
+// TMEM), 10 KB instead of 18 KB - so a weight byte fetched from L2 feeds twice the math.
 // Every load is an ordinary per-CTA bulk copy (nothing is multicast). The even CTA issues the MMAs and
 // its commits arrive on both CTAs' barriers; the scale warps and epilogue warps of the odd CTA arrive on the even CTA's
 // barriers across the cluster. The tile plan gives every expert an even number of tiles in this mode.
@@ -495,7 +492,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   if (tid == 0) {
     const int nsf = PAIR ? 8 : 4, nep = PAIR ? 16 : 8;   // arrivals of the scale warps / epilogue warps of one or both CTAs
     for (int k = 0; k < KB; ++k) { mbar_init(&S.a_full[k], 1); mbar_init(&S.a_empty[k], 1); mbar_init(&S.a_sfr[k], nsf); }
-    for (int s = 0; s < NSB; ++s) { mbar_init(&S.b_full[s], 1); mbar_init(&S.b_empty[s], 1); mbar_init(&S.b_sfr[s], nsf); mbar_init(&S.b_peer[s], 4); }
+    for (int s = 0; s < NSB; ++s) { mbar_init(&S.b_full[s], 1); mbar_init(&S.b_empty[s], 1); mbar_init(&S.b_sfr[s], nsf); }
     for (int b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], nep); }
     S.abort_flag = 0;
     fence_mbar_init();
@@ -559,13 +556,11 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         for (int i = 0; i < (n1 - n0) * KB; ++i) {   // the records of consecutive column blocks of an expert are contiguous
           if (mine) {
             if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
-            if (PAIR) {   // this CTA's 64 code rows of the record (rows are 128 bytes, 8-row groups contiguous); the odd CTA's copy
-                          // runs on through the scale tiles, which follow row 127
-              const uint32_t nbytes = rank == 0 ? 8192u : 8192u + 2048u;
-              mbar_expect_tx(&S.b_full[slot], nbytes);
-              bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + 8192 * rank, nbytes, &S.b_full[slot]);
+            mbar_expect_tx(&S.b_full[slot], kBSlot);
+            if (PAIR) {   // this CTA's 64 code rows of the record (rows are 128 bytes, 8-row groups contiguous) and all of its scale tiles
+              bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + 8192 * rank, 8192, &S.b_full[slot]);
+              bulk_load(ring + slot * kBSlot + 8192, src + (long long)i * kRec + 16384, 2048, &S.b_full[slot]);
             } else {
-              mbar_expect_tx(&S.b_full[slot], kBSlot);
               bulk_load(ring + slot * kRec, src + (long long)i * kRec, kRec, &S.b_full[slot]);
             }
           }
@@ -602,23 +597,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             if (lane == 0) arrive_at_issuer(&S.a_sfr[kb]);
           }
           if (!mbar_wait(&S.b_full[slot], ph, &S.abort_flag)) *P.status = 1;
-          if (PAIR && rank == 1 && lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&S.b_peer[slot]), 0));   // the even CTA may read the scale tiles
-          if (PAIR && rank == 0) {   // the scale tiles of the stage sit in the odd CTA's shared memory
-            if (!mbar_wait_cluster(&S.b_peer[slot], ph, &S.abort_flag)) *P.status = 1;
-            const uint32_t src = mapa_shared(b_u + slot * kBSlot, 1);
-            uint32_t r[16];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 t4 = lds128_cluster(src + j * 512);
-              r[4 * j] = t4.x, r[4 * j + 1] = t4.y, r[4 * j + 2] = t4.z, r[4 * j + 3] = t4.w;
-            }
-            tmem_st_32x32b_x16(tm_sfb + 16 * slot + lane_base, r);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-          } else if (!PF_ABLATE(4)) {
-            put(b_u + slot * kBSlot, tm_sfb + 16 * slot);
-          }
+          if (!PF_ABLATE(4)) put(b_u + slot * kBSlot, tm_sfb + 16 * slot);
           if (lane == 0) arrive_at_issuer(&S.b_sfr[slot]);
           if (++slot == NSB) { slot = 0; ph ^= 1u; }
         }
@@ -949,20 +928,22 @@ void b200_prefill_workspace_map(int E, int H, int I, int top_k, int max_tokens, 
 // One GEMM launch. Phases 1/2 (W4A4): the resident-A kernel when the row tile's KB records plus at least 3 weight stages fit
 // in shared memory and the scale columns fit in TMEM, otherwise the kernel that streams both operands. Phases 3/4 (W4A16)
 // exist for the resident-A kernel only.
-// B200MOE_PREFILL_PAIR: "1" / "0" force the W4A4 GEMMs to run as CTA pairs (256 rows per weight record, cta_group::2) or as
-// single CTAs; unset: pairs from kPairMinTokens tokens on (below, most experts hold less than one full tile and the second
-// tile of a pair would be padding).
-static int pair_mode_setting() {
-  static const int v = [] { const char* c = getenv("B200MOE_PREFILL_PAIR"); return !c ? -1 : c[0] == '1' ? 1 : 0; }();
-  return v;
+// B200MOE_PREFILL_PAIR=1: the W4A4 GEMMs run as CTA pairs (256 rows per weight record, cta_group::2). Correct (the parity
+// tests run in both modes) but off by default, because it is slower on this part as built: the hand-over of a ring stage
+// crosses the cluster three times (the odd CTA's scale warps arrive on the even CTA's barrier, the even CTA's commit arrives
+// on both CTAs' barriers), and with that round trip a seven-stage ring delivers a record about every 0.9 us where the
+// single-CTA form takes 0.35 us - measured at 4096 tokens: FC1 231 us as pairs against 98 us, FC2 144 us against 60 us,
+// and still 238 us with MMAs, scale moves and epilogue arithmetic all switched off. Fetching the B scales once per pair and
+// reading them across the cluster (one bulk copy per CTA and record instead of two) made it slower still (312 us).
+static bool pair_mode_enabled() {
+  static const bool on = [] { const char* c = getenv("B200MOE_PREFILL_PAIR"); return c && c[0] == '1'; }();
+  return on;
 }
-constexpr int kPairMinTokens = 2048;
 
 // Whether the W4A4 GEMMs of this shape run as CTA pairs: both phases' resident tiles and at least 3 ring stages must fit.
-static bool prefill_pairs(int H, int I, int M) {
+static bool prefill_pairs(int H, int I) {
   const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
-  const int setting = pair_mode_setting();
-  if (setting == 0 || (setting < 0 && M < kPairMinTokens) || KB1 > 12 || KB2 > 12) return false;
+  if (!pair_mode_enabled() || KB1 > 12 || KB2 > 12) return false;
   const int a1 = KB1 * kRec, n1 = (227 * 1024 - 3072 - a1) / 10240;
   return n1 >= 3 && (512 - 256 - 16 * KB1) / 16 >= 3;
 }
@@ -1037,7 +1018,7 @@ int b200_prefill_forward(int E, int H, int I, int top_k, const uint8_t* w1t, con
   if (Umax > 256) return B200MOE_ERR_LIMIT;
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
-  const bool pair = prefill_pairs(H, I, M) && sms >= 2;
+  const bool pair = prefill_pairs(H, I) && sms >= 2;
   const int max_tiles = P / 128 + 2 * Umax;   // tiles this batch can need (<= the workspace's capacity)
   {
     const int rows = max_tiles * 128;

@@ -134,11 +134,6 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ uint4 lds128_cluster(uint32_t cluster_addr) {   // 16 bytes from a (peer) CTA's shared memory
-  uint4 v;
-  asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(cluster_addr) : "memory");
-  return v;
-}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {   // release at cluster scope: the peer's waiter sees this CTA's writes
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
 }
