@@ -198,6 +198,16 @@ int b200moe_ep_unpack(const void* rbuf, long long block_bytes, int world, int ca
 int b200moe_ep_wait(const unsigned* flags, int world, int per_call, unsigned* calls, int* status, void* stream);
 int b200moe_ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag, void* stream);
 int b200moe_ep_combine(const void* y, int m, int h, int world, int cap, void* out, void* stream);
+/* The peer-store exchange in two launches per layer call instead of five: dispatch_wait = b200moe_ep_dispatch with counters +
+ * the bounded wait for every peer's rows (flags_in: this rank's counters, one per peer; calls: device word, zeroed once, that
+ * counts this rank's calls); return_combine = b200moe_ep_return + the bounded wait for the partial rows coming back
+ * (flags_back) + b200moe_ep_combine over this rank's `back` array (bf16 [world, cap, h]). */
+int b200moe_ep_dispatch_wait(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
+                             void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag,
+                             const unsigned* flags_in, unsigned* calls, int* status, void* stream);
+int b200moe_ep_return_combine(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
+                              const unsigned* flags_back, const unsigned* calls, int* status, const void* back, int m, void* out,
+                              void* stream);
 /* variable-size exchange (prefill batches; no counterpart in the reference either). plan: counts int32 [world], offsets int32
  * [world + 1], pos int32 [m, world] (row of token t in the send buffer for destination d, or -1), send_tok int32 [rows]
  * (destination-major, token order within a destination). gather: the rows of the send buffer (sx bf16 [rows, h], meta int32

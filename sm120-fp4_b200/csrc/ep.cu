@@ -23,8 +23,34 @@ struct EpDest {
   unsigned* flag[kEpMaxWorld];   // null: no signalling (stream-ordered exchange follows)
 };
 
+// Bounded wait on `world` arrival counters (lane s polls counter s) until each has reached `want`; a wait that runs out sets
+// *status to 1 + the late peer's rank and returns. Called by one whole warp.
+__device__ __forceinline__ void ep_wait_counters(const unsigned* flags, int world, unsigned want, int* status) {
+  const int s = threadIdx.x & 31;
+  if (s < world) {
+    bool ok = false;
+    for (unsigned it = 0; it < (1u << 22); ++it) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
+      if ((int)(v - want) >= 0) { ok = true; break; }
+      if (it > 1024u) __nanosleep(200);
+    }
+    if (!ok) *status = 1 + s;
+  }
+  __syncwarp();
+}
+
+struct EpWait {
+  const unsigned* flags;   // null: the kernel does not wait
+  unsigned* calls;         // this rank's call counter (only ever incremented, once per layer call, by the dispatch kernel)
+  int* status;
+  int world;
+  unsigned per_call;
+};
+
 __global__ void __launch_bounds__(128) k_ep_dispatch(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
-                                                     const float* __restrict__ wts, int m, int h, int k, int per, const __grid_constant__ EpDest D) {
+                                                     const float* __restrict__ wts, int m, int h, int k, int per, const __grid_constant__ EpDest D,
+                                                     const EpWait W) {
   const int row = blockIdx.x, dest = blockIdx.y;
   uint4* dst = reinterpret_cast<uint4*>(D.x[dest] + (long long)row * h);
   const uint4* src = reinterpret_cast<const uint4*>(x + (long long)row * h);
@@ -50,6 +76,13 @@ __global__ void __launch_bounds__(128) k_ep_dispatch(const __nv_bfloat16* __rest
       atomicAdd_system(D.flag[dest], 1u);
     }
   }
+  // Peer-store exchange: the kernel only completes when every peer's rows of this call have arrived (one block waits; the
+  // peers' sends do not depend on this wait), so whatever follows in the stream finds its input in place.
+  if (W.flags && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 32) {
+    const unsigned n = W.calls[0] + 1u;
+    ep_wait_counters(W.flags, W.world, n * W.per_call, W.status);
+    if (threadIdx.x == 0) W.calls[0] = n;
+  }
 }
 
 // Bounded wait of the consumer side of the peer-store exchange: thread s waits until peer s has bumped flags[s] `per_call`
@@ -57,20 +90,9 @@ __global__ void __launch_bounds__(128) k_ep_dispatch(const __nv_bfloat16* __rest
 // reset between calls). A wait that runs out sets *status and returns - the data of that peer is then stale, which the
 // caller learns from the status word, not from a hang.
 __global__ void k_ep_wait(const unsigned* __restrict__ flags, int world, unsigned per_call, unsigned* __restrict__ calls, int* __restrict__ status) {
-  const int s = threadIdx.x;
   const unsigned want = (calls[0] + 1u) * per_call;
-  if (s < world) {
-    bool ok = false;
-    for (unsigned it = 0; it < (1u << 22); ++it) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + s) : "memory");
-      if ((int)(v - want) >= 0) { ok = true; break; }
-      if (it > 1024u) __nanosleep(200);
-    }
-    if (!ok) *status = 1 + s;
-  }
-  __syncthreads();
-  if (s == 0) calls[0] += 1u;
+  ep_wait_counters(flags, world, want, status);
+  if (threadIdx.x == 0) calls[0] += 1u;
 }
 
 // Received blocks of the NCCL exchange (per source: rows | ids | weights) -> the contiguous arrays the layer call takes.
@@ -98,7 +120,11 @@ struct EpBack {
   unsigned* flag[kEpMaxWorld];
 };
 
-__global__ void __launch_bounds__(128) k_ep_return(const __nv_bfloat16* __restrict__ yl, int cap, int h, int rank, const __grid_constant__ EpBack B) {
+// With `out` the same kernel also finishes the layer call: block (row, 0) then waits (bounded) until every peer's partial
+// rows of this call are in this rank's `back` array and writes out[row] = bf16(sum over ranks, in rank order, in fp32).
+__global__ void __launch_bounds__(128) k_ep_return(const __nv_bfloat16* __restrict__ yl, int cap, int h, int rank, const __grid_constant__ EpBack B,
+                                                   const EpWait W, const __nv_bfloat16* __restrict__ back, int m, int world,
+                                                   __nv_bfloat16* __restrict__ out) {
   const int row = blockIdx.x, srcr = blockIdx.y;
   const uint4* src = reinterpret_cast<const uint4*>(yl + ((long long)srcr * cap + row) * h);
   uint4* dst = reinterpret_cast<uint4*>(B.y[srcr] + ((long long)rank * cap + row) * h);
@@ -107,6 +133,28 @@ __global__ void __launch_bounds__(128) k_ep_return(const __nv_bfloat16* __restri
   if (threadIdx.x == 0) {
     __threadfence_system();
     atomicAdd_system(B.flag[srcr], 1u);
+  }
+  if (!out || srcr != 0 || row >= m) return;
+  if (threadIdx.x < 32) ep_wait_counters(W.flags, W.world, W.calls[0] * W.per_call, W.status);   // the dispatch kernel of this call counted it
+  __syncthreads();
+  for (int c = threadIdx.x; c < h / 8; c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(back + ((long long)r * cap + row) * h + c * 8));
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += __uint_as_float(w4[q] << 16);
+        acc[2 * q + 1] += __uint_as_float(w4[q] & 0xffff0000u);
+      }
+    }
+    uint32_t o4[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat162 hh = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      o4[q] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+    *reinterpret_cast<uint4*>(out + (long long)row * h + c * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
   }
 }
 
@@ -145,9 +193,8 @@ using namespace b200;
 // the three pointer tables are HOST arrays of `world` device pointers. dst_flag: null, or a host array of `world` device
 // pointers to counters that every block bumps after its row is stored (peer-store exchange). experts_per_rank = E / world;
 // m <= cap; h a multiple of 8. A row is copied only where the destination owns one of its experts.
-extern "C" int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank,
-                                   int cap, void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag,
-                                   void* stream) {
+static int ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
+                       void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag, const EpWait& W, void* stream) {
   if (!x || !ids || !wts || !dst_x || !dst_ids || !dst_wts) return B200MOE_ERR_ARG;
   if (m < 0 || m > cap || h <= 0 || h % 8 || k < 1 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1 || cap < 1) return B200MOE_ERR_SHAPE;
   EpDest D;
@@ -159,9 +206,27 @@ extern "C" int b200moe_ep_dispatch(const void* x, const int* ids, const float* w
     D.flag[d] = live && dst_flag ? dst_flag[d] : nullptr;
     if (live && (!D.x[d] || !D.ids[d] || !D.wts[d])) return B200MOE_ERR_ARG;
   }
-  k_ep_dispatch<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, m, h, k, experts_per_rank, D);
+  k_ep_dispatch<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, m, h, k, experts_per_rank, D, W);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_dispatch(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank,
+                                   int cap, void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag,
+                                   void* stream) {
+  const EpWait none = {nullptr, nullptr, nullptr, 0, 0u};
+  return ep_dispatch(x, ids, wts, m, h, k, world, experts_per_rank, cap, dst_x, dst_ids, dst_wts, dst_flag, none, stream);
+}
+
+// The peer-store dispatch and the wait for the peers' rows in ONE launch: as b200moe_ep_dispatch with dst_flag, and the kernel
+// only completes once the counters in `flags_in` (this rank's, one per peer) have all grown by `cap` since the previous
+// call; `calls` (device, zeroed once) counts this rank's calls.
+extern "C" int b200moe_ep_dispatch_wait(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank,
+                                        int cap, void* const* dst_x, int* const* dst_ids, float* const* dst_wts, unsigned* const* dst_flag,
+                                        const unsigned* flags_in, unsigned* calls, int* status, void* stream) {
+  if (!dst_flag || !flags_in || !calls || !status) return B200MOE_ERR_ARG;
+  const EpWait W = {flags_in, calls, status, world, (unsigned)cap};
+  return ep_dispatch(x, ids, wts, m, h, k, world, experts_per_rank, cap, dst_x, dst_ids, dst_wts, dst_flag, W, stream);
 }
 
 // rbuf: `world` received blocks of block_bytes each (rows bf16 [cap, h] | ids int32 [cap, k] | weights f32 [cap, k]) ->
@@ -188,19 +253,37 @@ extern "C" int b200moe_ep_wait(const unsigned* flags, int world, int per_call, u
 
 // yl bf16 [world * cap, h] (this rank's partial rows, block s for source s) -> peer s's back array at block `rank`
 // (back_y[s]: bf16 [world, cap, h] in s's memory), then cap bumps of back_flag[s]. Host arrays of `world` device pointers.
-extern "C" int b200moe_ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
-                                 void* stream) {
+static int ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag, const EpWait& W,
+                     const void* back, int m, void* out, void* stream) {
   if (!yl || !back_y || !back_flag) return B200MOE_ERR_ARG;
-  if (world < 1 || world > kEpMaxWorld || cap < 1 || h <= 0 || h % 8 || rank < 0 || rank >= world) return B200MOE_ERR_SHAPE;
+  if (world < 1 || world > kEpMaxWorld || cap < 1 || h <= 0 || h % 8 || rank < 0 || rank >= world || m < 0 || m > cap) return B200MOE_ERR_SHAPE;
   EpBack B;
   for (int d = 0; d < kEpMaxWorld; ++d) {
     B.y[d] = d < world ? (__nv_bfloat16*)back_y[d] : nullptr;
     B.flag[d] = d < world ? back_flag[d] : nullptr;
     if (d < world && (!B.y[d] || !B.flag[d])) return B200MOE_ERR_ARG;
   }
-  k_ep_return<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)yl, cap, h, rank, B);
+  k_ep_return<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)yl, cap, h, rank, B, W, (const __nv_bfloat16*)back, m, world,
+                                                                  (__nv_bfloat16*)out);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_return(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
+                                 void* stream) {
+  const EpWait none = {nullptr, nullptr, nullptr, 0, 0u};
+  return ep_return(yl, world, cap, h, rank, back_y, back_flag, none, nullptr, 0, nullptr, stream);
+}
+
+// Return, wait and combine in ONE launch (after b200moe_ep_dispatch_wait of the same call, which counted it in `calls`): the
+// partial rows go to their sources; then, per token row, the kernel waits until `flags_back` shows every peer's rows of this
+// call in `back` (this rank's bf16 [world, cap, h]) and writes out bf16 [m, h], summed in rank order in fp32.
+extern "C" int b200moe_ep_return_combine(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
+                                         const unsigned* flags_back, const unsigned* calls, int* status, const void* back, int m, void* out,
+                                         void* stream) {
+  if (!flags_back || !calls || !status || !back || !out) return B200MOE_ERR_ARG;
+  const EpWait W = {flags_back, const_cast<unsigned*>(calls), status, world, (unsigned)cap};
+  return ep_return(yl, world, cap, h, rank, back_y, back_flag, W, back, m, out, stream);
 }
 
 // y bf16 [world, cap, h] (the partial rows that came back, block r from rank r) -> out bf16 [m, h]

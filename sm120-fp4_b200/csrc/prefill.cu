@@ -4,9 +4,10 @@
 // SiLU*mul activations quantised to NVFP4 by the bit-exact quantiser, fp32 accumulation, weighted sum over the top-k.
 //
 // Pipeline (all on the caller's stream, no host synchronisation):
-//   route (route.cu) -> k_prefill_plan: per-expert row segments padded to 128-row tiles, gather map
-//   k_quantize_records: bf16 x -> NVFP4 "tile records" (128 rows x 256 codes in the 128-byte-swizzle shared-memory image
-//                       + four 512 B scale tiles, 18 KB contiguous), rows gathered per expert
+//   route (route.cu) -> k_prefill_rowmap: per-expert row segments padded to 128-row tiles (the tile plan) and the map between
+//                       token-expert pairs and operand rows
+//   k_quantize_scatter: bf16 x -> NVFP4 "tile records" (128 rows x 256 codes in the 128-byte-swizzle shared-memory image
+//                       + four 512 B scale tiles, 18 KB contiguous): every token row quantised once, stored to its pairs' rows
 //   k_prefill_gemm<1>:  FC1 tiles (128 rows x [64 up | 64 gate] columns), epilogue SiLU*mul + NVFP4 re-quantisation
 //                       straight into FC2's tile records (scales written in the 128x4 order)
 //   k_prefill_gemm<2>:  FC2 tiles (128 rows x 128 columns), epilogue alpha * routing weight -> bf16 rows per (token, expert)
@@ -38,40 +39,6 @@ constexpr int kMidRec = 8192 + 2048;
 #else
 #define PF_ABLATE(bit) false
 #endif
-
-// ------------------------------------------------------------------------------------------------ plan
-// experts/offsets: the router's tables. One thread per touched expert: its rows are cut into tiles of rows_per_tile rows
-// (128 for the W4A4 GEMM; 16 for the W4A16 GEMM, whose 64-row tile holds four term rows per token-expert pair), the tiles of
-// all experts are numbered in expert order by a block-wide scan. Output: ntiles[0], and per tile its expert and the range
-// [tile_first, tile_end) of the expert's rows in `pairs` that it holds (the last tile of an expert is partly empty).
-__global__ void __launch_bounds__(256) k_prefill_plan(const int* __restrict__ experts, const int* __restrict__ offsets, int Umax, int max_tiles,
-                                                      int rows_per_tile, int* __restrict__ ntiles, int* __restrict__ tile_expert,
-                                                      int* __restrict__ tile_first, int* __restrict__ tile_end) {
-  __shared__ int wsum[8];
-  const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
-  int e = -1, lo = 0, hi = 0;
-  if (u < Umax) {
-    e = experts[u];
-    if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
-  }
-  const int mine = (hi - lo + rows_per_tile - 1) / rows_per_tile;
-  int inc = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int a = __shfl_up_sync(0xffffffffu, inc, o);
-    if (lane >= o) inc += a;
-  }
-  if (lane == 31) wsum[warp] = inc;
-  __syncthreads();
-  int base = inc - mine;
-  for (int w2 = 0; w2 < warp; ++w2) base += wsum[w2];
-  if (u == 255) ntiles[0] = min(base + mine, max_tiles);
-  for (int j = 0; j < mine && base + j < max_tiles; ++j) {
-    tile_expert[base + j] = e;
-    tile_first[base + j] = lo + j * rows_per_tile;
-    tile_end[base + j] = hi;
-  }
-}
 
 // byte offset inside a tile record of 8 consecutive codes bytes (one 16-value block) of row r, K block b16 (0..15)
 __device__ __forceinline__ int rec_code_offset(int r, int b16) { return r * 128 + ((((b16 >> 1) ^ (r & 7))) << 4) + (b16 & 1) * 8; }
@@ -188,12 +155,91 @@ __global__ void __launch_bounds__(128) k_quantize_scatter(const __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------------------------------------ x -> W4A16 records
-// Mid-sized batches (33 tokens up to a few hundred) keep the decode path's W4A16 arithmetic but run as a grouped GEMM over
+// Mid-sized batches (17 tokens up to a few hundred) keep the decode path's W4A16 arithmetic but run as a grouped GEMM over
 // per-expert gathered rows: a tile of 64 operand rows holds 16 token-expert pairs x four NVFP4 terms of the pair's token
-// row (row 4p + t = term t of pair p), so that an expert's weight records are streamed once for all of its pairs.
-__global__ void __launch_bounds__(128) k_token_amax(const __nv_bfloat16* __restrict__ x, int H, float* __restrict__ amax) {
+// row (row 4p + t = term t of pair p), so that an expert's weight records are streamed once for all of its pairs. Two
+// launches build the records (tile plan, pair-row map and the reset of the row table in one kernel; token amax and
+// expansion in one token-major kernel that expands a token's row ONCE and stores it into the rows of each of its pairs) -
+// a mid-sized batch is bound by launches, not by bytes.
+//
+// Row map: every block repeats the scan over the touched experts (tiles of 16 pairs); block 0 writes the tile tables. One
+// thread per pair row of every tile: row_pair of its four term rows, dst_row of the pair; the scale bytes of pair rows
+// that hold no pair are zeroed in the x records (so their codes never need writing).
+__global__ void __launch_bounds__(256) k_mid_rowmap(const int* __restrict__ ids, int P, const int* __restrict__ experts, const int* __restrict__ offsets,
+                                                    const int* __restrict__ pairs, int Umax, int max_tiles, int KB, int* __restrict__ ntiles,
+                                                    int* __restrict__ tile_expert, int* __restrict__ tile_first, int* __restrict__ tile_end,
+                                                    uint8_t* __restrict__ rec, int* __restrict__ row_pair, int* __restrict__ dst_row) {
+  __shared__ int wsum[8];
+  __shared__ int tbase[257];
+  __shared__ int s_lo[256], s_hi[256];
+  const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
+  int e = -1, lo = 0, hi = 0;
+  if (u < Umax) {
+    e = experts[u];
+    if (e >= 0) { lo = offsets[u]; hi = offsets[u + 1]; }
+  }
+  const int mine = (hi - lo + 15) >> 4;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += a;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  int base = inc - mine;
+  for (int w2 = 0; w2 < warp; ++w2) base += wsum[w2];
+  tbase[u] = base;
+  s_lo[u] = lo, s_hi[u] = hi;
+  if (u == 255) tbase[256] = base + mine;
+  __syncthreads();
+  const int NT = min(tbase[256], max_tiles);
+  if (blockIdx.x == 0) {
+    if (u == 0) ntiles[0] = NT;
+    for (int j = 0; j < mine && base + j < max_tiles; ++j) {
+      tile_expert[base + j] = e;
+      tile_first[base + j] = lo + j * 16;
+      tile_end[base + j] = hi;
+    }
+  }
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gsz = gridDim.x * blockDim.x;
+  for (int p = gtid; p < P; p += gsz)
+    if (ids[p] < 0) dst_row[p] = -1;
+  for (int prow = gtid; prow < NT * 16; prow += gsz) {
+    const int t = prow >> 4, p = prow & 15;
+    int a = 0, b = 255;
+    while (a < b) {
+      const int mid = (a + b + 1) >> 1;
+      if (tbase[mid] <= t) a = mid; else b = mid - 1;
+    }
+    const int j = s_lo[a] + (t - tbase[a]) * 16 + p;
+    const int pr = j < s_hi[a] ? pairs[j] : -1;
+#pragma unroll
+    for (int q = 0; q < kTerms; ++q) row_pair[t * 64 + 4 * p + q] = pr;
+    if (pr >= 0) {
+      dst_row[pr] = prow;
+    } else {
+      for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+        for (int q = 0; q < kTerms; ++q) {
+          const int r = 4 * p + q;
+          uint8_t* sfp = rec + ((long long)t * KB + kb) * kMidRec + 8192 + (r & 31) * 16 + (r >> 5) * 4;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<uint32_t*>(sfp + jj * 512) = 0u;
+        }
+    }
+  }
+}
+
+// One block of 128 threads per token: token amax, then every 16-value block expanded into four NVFP4 terms ONCE and stored
+// into the four term rows of each of the token's pairs (dst_row[pair] = tile * 16 + pair row); the first four threads also
+// write the rows' 1 / g_t.
+__global__ void __launch_bounds__(128) k_expand_scatter(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dst_row, int M, int H, int KB,
+                                                        int top_k, uint8_t* __restrict__ rec, float* __restrict__ rowscale) {
   __shared__ float wm[4];
+  __shared__ int s_row[16];
   const int tok = blockIdx.x, tid = threadIdx.x;
+  if (tid < top_k) s_row[tid] = dst_row[tok * top_k + tid];
   float m = 0.f;
   for (int i = tid * 8; i < H; i += 128 * 8) {
     const uint4 v = *reinterpret_cast<const uint4*>(x + (long long)tok * H + i);
@@ -205,40 +251,21 @@ __global__ void __launch_bounds__(128) k_token_amax(const __nv_bfloat16* __restr
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((tid & 31) == 0) wm[tid >> 5] = m;
   __syncthreads();
-  if (tid == 0) amax[tok] = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
-}
-
-// One thread per 16-value block of a pair row: the block's four terms go to rows 4p..4p+3 of the tile's record. The thread
-// of a pair's first block also records the pair of the four rows (row_pair), their 1 / g_t (rowscale) and the pair's row in
-// the output of FC2 (dst_row = tile * 16 + p).
-__global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __restrict__ x, const float* __restrict__ tok_amax,
-                                                        const int* __restrict__ pairs, const int* __restrict__ tile_first,
-                                                        const int* __restrict__ tile_end, const int* __restrict__ ntiles, int H, int KB,
-                                                        int top_k, uint8_t* __restrict__ rec, int* __restrict__ row_pair,
-                                                        float* __restrict__ rowscale, int* __restrict__ dst_row) {
-  const unsigned per_row = (unsigned)KB * 16u;
-  const unsigned total = (unsigned)ntiles[0] * 16u * per_row;
-  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const unsigned prow = i / per_row, b = i - prow * per_row;
-    const int t = (int)(prow >> 4), p = (int)(prow & 15);
-    const int j = tile_first[t] + p;
-    int pr = -1;
-    if (j < tile_end[t]) pr = pairs[j];
-    const int tok = pr >= 0 ? pr / top_k : 0;
-    const float g1 = pr >= 0 ? 2688.0f / fmaxf(tok_amax[tok], 1e-30f) : 0.f;
-    if (b == 0) {
-      float g = g1;
-#pragma unroll
-      for (int q = 0; q < kTerms; ++q) {
-        row_pair[t * 64 + 4 * p + q] = pr;
-        rowscale[t * 64 + 4 * p + q] = pr >= 0 ? 1.0f / g : 0.f;
-        g *= 6.0f;
-      }
-      if (pr >= 0) dst_row[pr] = t * 16 + p;
+  m = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+  const float g1 = 2688.0f / fmaxf(m, 1e-30f);
+  if (tid < kTerms) {
+    float g = g1;
+    for (int q = 0; q < tid; ++q) g *= 6.0f;
+    for (int j = 0; j < top_k; ++j) {
+      const int prow = s_row[j];
+      if (prow >= 0) rowscale[(prow >> 4) * 64 + 4 * (prow & 15) + tid] = 1.0f / g;
     }
+  }
+  const int nblk = KB * 16;
+  for (int b = tid; b < nblk; b += 128) {
     uint2 codes[kTerms];
     uint8_t sf[kTerms];
-    if (pr >= 0 && (int)b * 16 < H) {
+    if (b * 16 < H) {
       float v[16];
       load16(x + (long long)tok * H + b * 16, v);
       expand_block16(v, g1, codes, sf);
@@ -246,12 +273,17 @@ __global__ void __launch_bounds__(256) k_expand_records(const __nv_bfloat16* __r
 #pragma unroll
       for (int q = 0; q < kTerms; ++q) { codes[q] = make_uint2(0u, 0u); sf[q] = 0; }
     }
-    uint8_t* dst = rec + ((long long)t * KB + (b >> 4)) * kMidRec;
+    for (int j = 0; j < top_k; ++j) {
+      const int prow = s_row[j];
+      if (prow < 0) continue;
+      uint8_t* dst = rec + ((long long)(prow >> 4) * KB + (b >> 4)) * kMidRec;
+      const int p = prow & 15;
 #pragma unroll
-    for (int q = 0; q < kTerms; ++q) {
-      const int r = 4 * p + q;   // < 64: row groups 0 and 1 of the scale tiles
-      *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b & 15)) = codes[q];
-      dst[8192 + ((b & 15) >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b & 3)] = sf[q];
+      for (int q = 0; q < kTerms; ++q) {
+        const int r = 4 * p + q;
+        *reinterpret_cast<uint2*>(dst + rec_code_offset(r, b & 15)) = codes[q];
+        dst[8192 + ((b & 15) >> 2) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b & 3)] = sf[q];
+      }
     }
   }
 }
@@ -1115,18 +1147,18 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   int* row_pair = (int*)(w + L.row_pair);
   float* rowscale = (float*)(w + L.rowscale);
   int* dst_row = (int*)(w + L.dst_row);
-  float* tok_amax = (float*)(w + L.tok_amax);
   int rc = b200moe_route(ids, P, E, Umax, experts, offsets, pairs, w + L.route_ws, L.total - L.route_ws, st);
   if (rc != B200MOE_OK) return rc;
-  B200_CUDA_TRY(cudaMemsetAsync(dst_row, 0xff, sizeof(int) * (size_t)P, st));
   const int max_tiles = P / 16 + Umax;
   int* tile_end = tile_first + max_tiles;
-  k_prefill_plan<<<1, 256, 0, st>>>(experts, offsets, Umax, max_tiles, 16, ntiles, tile_expert, tile_first, tile_end);
-  B200_LAUNCH_CHECK();
-  k_token_amax<<<M, 128, 0, st>>>((const __nv_bfloat16*)x, H, tok_amax);
-  B200_LAUNCH_CHECK();
-  k_expand_records<<<sms * 8, 256, 0, st>>>((const __nv_bfloat16*)x, tok_amax, pairs, tile_first, tile_end, ntiles, H, KB1, top_k, w + L.xrec,
-                                             row_pair, rowscale, dst_row);
+  {
+    int grid = (max_tiles * 16 + 255) / 256;
+    if (grid > sms * 4) grid = sms * 4;
+    k_mid_rowmap<<<grid, 256, 0, st>>>(ids, P, experts, offsets, pairs, Umax, max_tiles, KB1, ntiles, tile_expert, tile_first, tile_end, w + L.xrec,
+                                       row_pair, dst_row);
+    B200_LAUNCH_CHECK();
+  }
+  k_expand_scatter<<<M, 128, 0, st>>>((const __nv_bfloat16*)x, dst_row, M, H, KB1, top_k, w + L.xrec, rowscale);
   B200_LAUNCH_CHECK();
   PrefillParams p;
   memset(&p, 0, sizeof(p));

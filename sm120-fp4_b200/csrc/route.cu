@@ -111,6 +111,86 @@ __global__ void __launch_bounds__(32) k_route_place(const int* __restrict__ ids,
   }
 }
 
+// The whole router in one launch for small batches (P <= kRouteSmallMaxP pairs, E <= 256 experts: decode-sized and mid-sized
+// batches, where three launches cost more than the work). One block of 32 warps; warp w owns the contiguous pairs
+// [w * L, (w + 1) * L). Counts per (warp, expert) in shared memory, a scan over the warps per expert and over the experts,
+// then every warp walks its pairs in index order exactly as k_route_place does. Same tables, bit for bit.
+constexpr int kRouteSmallMaxP = 4096, kRouteSmallMaxE = 256;
+
+__global__ void __launch_bounds__(1024) k_route_small(const int* __restrict__ ids, int P, int E, int Umax, int* __restrict__ experts,
+                                                      int* __restrict__ offsets, int* __restrict__ pairs, int* __restrict__ bad,
+                                                      int* __restrict__ num_touched) {
+  __shared__ int wc[32][kRouteSmallMaxE];     // pairs of expert e in warp w's range, then the start of that range's run in `pairs`
+  __shared__ int tot[kRouteSmallMaxE], uidx[kRouteSmallMaxE];
+  __shared__ int s_bad;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 32 * kRouteSmallMaxE; i += 1024) (&wc[0][0])[i] = 0;
+  if (tid == 0) s_bad = 0;
+  __syncthreads();
+  const int L = ((P + 31) / 32 + 31) & ~31;   // pairs per warp, a multiple of 32
+  const int p0 = warp * L, p1 = min(P, p0 + L);
+  for (int p = p0 + lane; p < p1; p += 32) {
+    const int e = ids[p];
+    if (e < 0) continue;
+    if (e >= E) { s_bad = 1; continue; }
+    atomicAdd(&wc[warp][e], 1);
+  }
+  __syncthreads();
+  if (tid < kRouteSmallMaxE) {   // thread e: exclusive scan of expert e's counts over the warps
+    int c = 0;
+    for (int w = 0; w < 32; ++w) { const int v = wc[w][tid]; wc[w][tid] = c; c += v; }
+    tot[tid] = c;
+  }
+  __syncthreads();
+  if (warp == 0) {               // scan over the experts: bases and touched-expert indices (8 experts per lane)
+    int c[8], sc = 0, sf = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { c[i] = tot[lane * 8 + i]; sc += c[i]; sf += c[i] > 0; }
+    int ic = sc, iff = sf;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, ic, o), b = __shfl_up_sync(0xffffffffu, iff, o);
+      if (lane >= o) { ic += a; iff += b; }
+    }
+    int rc = ic - sc, rf = iff - sf;
+    const int routed = __shfl_sync(0xffffffffu, ic, 31), U = __shfl_sync(0xffffffffu, iff, 31);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = lane * 8 + i;
+      tot[e] = rc;                          // start of expert e in `pairs`
+      if (c[i] > 0) {
+        if (rf < Umax) { experts[rf] = e; offsets[rf] = rc; }
+        ++rf;
+      }
+      uidx[e] = rf;
+      rc += c[i];
+    }
+    for (int u = U + lane; u < Umax; u += 32) { experts[u] = -1; offsets[u + 1] = routed; }
+    if (lane == 0) {
+      if (U <= Umax) offsets[U] = routed;
+      if (num_touched) *num_touched = U;
+      if (bad) *bad = s_bad;
+    }
+  }
+  __syncthreads();
+  for (int e = lane; e < kRouteSmallMaxE; e += 32) wc[warp][e] += tot[e];   // this warp's running position per expert
+  __syncwarp();
+  for (int s = p0; s < p1; s += 32) {
+    const int p = s + lane;
+    int e = p < p1 ? ids[p] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned active = __ballot_sync(0xffffffffu, e >= 0);
+    if (e >= 0) {
+      const unsigned peers = __match_any_sync(active, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      pairs[wc[warp][e] + rank] = p;
+      __syncwarp(active);
+      if (rank == __popc(peers) - 1) wc[warp][e] += __popc(peers);
+    }
+    __syncwarp();
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -135,6 +215,11 @@ extern "C" int b200moe_route(const int* ids, int P, int E, int Umax, int* expert
   int* expert_base = hist + (long long)nchunks * E;
   int* bad = expert_base + E;
   int* num_touched = bad + 1;
+  if (P > 0 && P <= kRouteSmallMaxP && E <= kRouteSmallMaxE) {   // small batch: one launch
+    k_route_small<<<1, 1024, 0, st>>>(ids, P, E, Umax, experts, offsets, pairs, bad, num_touched);
+    B200_LAUNCH_CHECK();
+    return B200MOE_OK;
+  }
   B200_CUDA_TRY(cudaMemsetAsync(bad, 0, 2 * sizeof(int), st));
   if (nchunks > 0) {
     k_route_hist<<<nchunks, 128, E * sizeof(int), st>>>(ids, P, E, hist, bad);

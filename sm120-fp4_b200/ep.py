@@ -193,12 +193,14 @@ class ExpertParallelMoE:
             x = x.contiguous()
         st = torch.cuda.current_stream(x.device).cuda_stream
         w, k = self.world, self.k
-        _lib.check(lib.b200moe_ep_dispatch(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.dst_x, b.dst_ids, b.dst_wts,
-                                           b.dst_flag, st), "ep dispatch")
-        if b.peer:
-            _lib.check(lib.b200moe_ep_wait(b.flags_in.data_ptr(), w, c, b.calls.data_ptr(), b.status.data_ptr(), st), "ep wait")
-        elif w > 1:
-            dist.all_to_all_single(b.rbuf, b.sbuf, group=self.group)
+        if b.peer:   # rows stored straight into the peers' receive arrays; the kernel completes when the peers' rows are here
+            _lib.check(lib.b200moe_ep_dispatch_wait(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.dst_x, b.dst_ids, b.dst_wts,
+                                                    b.dst_flag, b.flags_in.data_ptr(), b.calls.data_ptr(), b.status.data_ptr(), st), "ep dispatch")
+        else:
+            _lib.check(lib.b200moe_ep_dispatch(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.dst_x, b.dst_ids, b.dst_wts,
+                                               b.dst_flag, st), "ep dispatch")
+            if w > 1:
+                dist.all_to_all_single(b.rbuf, b.sbuf, group=self.group)
         if not b.peer:   # split the received blocks (world == 1: the send buffer itself) into the arrays the layer call takes
             src = b.rbuf if w > 1 else b.sbuf
             _lib.check(lib.b200moe_ep_unpack(src.data_ptr(), b.block_bytes, w, c, h, k, b.rx.data_ptr(), b.rid.data_ptr(), b.rw.data_ptr(), st),
@@ -207,17 +209,17 @@ class ExpertParallelMoE:
             yl = self.local_forward(b.rx, b.rid, b.rw, out=b.yl)
         else:
             yl = self.local_forward(b.rx, b.rid, b.rw)
+        if out is None:
+            out = torch.empty(m, h, dtype=x.dtype, device=x.device)
+        if b.peer:   # partial rows back to their sources, wait for this rank's own, sum in rank order: one launch
+            _lib.check(lib.b200moe_ep_return_combine(yl.data_ptr(), w, c, h, self.rank, b.back_y, b.back_flag, b.flags_back.data_ptr(),
+                                                     b.calls.data_ptr(), b.status.data_ptr(), b.y.data_ptr(), m, out.data_ptr(), st), "ep return")
+            return out
         if w == 1:
             y = yl
-        elif b.peer:
-            _lib.check(lib.b200moe_ep_return(yl.data_ptr(), w, c, h, self.rank, b.back_y, b.back_flag, st), "ep return")
-            _lib.check(lib.b200moe_ep_wait(b.flags_back.data_ptr(), w, c, b.calls.data_ptr() + 4, b.status.data_ptr(), st), "ep wait")
-            y = b.y
         else:
             dist.all_to_all_single(b.y.view(-1, h), yl.view(-1, h), group=self.group)
             y = b.y
-        if out is None:
-            out = torch.empty(m, h, dtype=x.dtype, device=x.device)
         _lib.check(lib.b200moe_ep_combine(y.data_ptr(), m, h, w, c, out.data_ptr(), st), "ep combine")
         return out
 

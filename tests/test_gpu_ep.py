@@ -244,3 +244,37 @@ def test_peer_store_primitives_on_one_gpu():
     torch.cuda.synchronize()
     for s_ in range(world):
         assert torch.equal(back[s_, me], yl[s_ * cap:(s_ + 1) * cap]) and int(bflags[s_, me]) == cap
+
+
+def test_fused_peer_exchange_kernels_single_rank():
+    """dispatch + wait and return + wait + combine as one launch each, with this GPU as its own only peer: the rows a call
+    sends to itself come back summed (world 1: the sum is the row), call after call, with the counters never reset."""
+    import ctypes as C
+    import sm120fp4_b200._lib as L
+    lib = L.lib()
+    cap, h, k, experts = 8, 256, 4, 8
+    g = torch.Generator().manual_seed(9)
+    rx = torch.zeros(cap, h, dtype=torch.bfloat16, device="cuda")
+    rid = torch.zeros(cap, k, dtype=torch.int32, device="cuda")
+    rw = torch.zeros(cap, k, device="cuda")
+    back = torch.zeros(1, cap, h, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    calls = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    arr = lambda v: (C.c_void_p * len(v))(*v)  # noqa: E731
+    for call in range(3):
+        m = 5 + call
+        x = torch.randn(m, h, generator=g).to(torch.bfloat16).cuda()
+        ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(m)]).to(torch.int32).cuda()
+        wts = torch.rand(m, k, generator=g).cuda()
+        out = torch.full((m, h), float("nan"), dtype=torch.bfloat16, device="cuda")
+        L.check(lib.b200moe_ep_dispatch_wait(L.ptr(x), L.ptr(ids), L.ptr(wts), m, h, k, 1, experts, cap, arr([rx.data_ptr()]), arr([rid.data_ptr()]),
+                                             arr([rw.data_ptr()]), arr([flags[0:].data_ptr()]), L.ptr(flags), L.ptr(calls), L.ptr(status),
+                                             L.stream_ptr()), "dispatch_wait")
+        yl = (rx.float() * 2).to(torch.bfloat16)                       # stands for the local layer
+        L.check(lib.b200moe_ep_return_combine(L.ptr(yl), 1, cap, h, 0, arr([back.data_ptr()]), arr([flags[1:].data_ptr()]), L.ptr(flags[1:]),
+                                              L.ptr(calls), L.ptr(status), L.ptr(back), m, L.ptr(out), L.stream_ptr()), "return_combine")
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0 and int(calls.item()) == call + 1 and flags.tolist() == [cap * (call + 1)] * 2
+        assert torch.equal(rid[:m], ids) and torch.equal(rw[:m], wts) and torch.equal(rx[:m], x)
+        assert torch.equal(out, (x.float() * 2).to(torch.bfloat16))
