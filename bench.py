@@ -258,6 +258,12 @@ def run_ours(a):
     only = set(a.cases.split(",")) if a.cases else None
     stream = torch.cuda.Stream()
     extras = {}
+    if a.prefill_only:   # profiling helper: only the W4A4 prefill chain of two layers at the given sizes, one JSON line of its rows
+        with torch.cuda.stream(stream):
+            rows = prefill_numbers(cfg, build_layers(cfg, 2, dev), dev, reps=max(1, a.steps), sizes=[int(v) for v in a.prefill_only.split(",")],
+                                   graph=not a.no_graph)
+        print(json.dumps({"prefill": rows}))
+        return
     with torch.cuda.stream(stream):
         if world == 1:
             layers = build_layers(cfg, a.layers, dev)
@@ -363,7 +369,7 @@ def ep_parity(cfg, ep, dist, world, rank, dev):
     return res
 
 
-def prefill_numbers(cfg, layers, dev, reps=5):
+def prefill_numbers(cfg, layers, dev, reps=5, sizes=(256, 1024, 4096, 8192), graph=True):
     """W4A4 prefill (own tcgen05 grouped GEMM): us per layer call and TFLOP/s on 6*M*k*I*H flop at M = 256 .. 8192, CUDA-graph
     replay of the two-layer chain; with the fraction of the nominal dense FP4 peak and of the layer's HBM floor (all experts'
     packed weights once + x in + out: the bound at these sizes, see the roofline note)."""
@@ -375,7 +381,7 @@ def prefill_numbers(cfg, layers, dev, reps=5):
     peak_hbm, _ = peaks()
     rows = []
     ebytes = layers[0].expert_bytes()
-    for m in (256, 1024, 4096, 8192):
+    for m in sizes:
         x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 9000 + m)
         xd, idd, wd = x.to(dev), ids.to(dev), wts.to(dev)
         out = torch.empty_like(xd)
@@ -388,11 +394,12 @@ def prefill_numbers(cfg, layers, dev, reps=5):
         torch.cuda.synchronize()
         run, graphed = chain, False
         try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
-                chain()
-            run, graphed = g.replay, True
-            run()
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
+                    chain()
+                run, graphed = g.replay, True
+                run()
         except Exception as ex:  # noqa: BLE001
             print(f"prefill: graph capture unavailable ({type(ex).__name__}: {ex})", file=sys.stderr)
         ts = sorted(time_region(run, torch.cuda.synchronize) / len(layers) for _ in range(reps))
@@ -575,6 +582,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill and expert-parallel stack measurements")
     ap.add_argument("--ep-layers", type=int, default=48, help="layer calls in the expert-parallel stack")
+    ap.add_argument("--prefill-only", default="", help="profiling helper: only the W4A4 prefill chain at these token counts, e.g. 4096")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)

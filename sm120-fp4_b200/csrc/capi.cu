@@ -208,26 +208,15 @@ extern "C" int b200moe_layer_set_act_scale(b200moe_layer* L, float g1) {
   return B200MOE_OK;
 }
 
-// x_remote: x lives in host memory (read across the host link): it is then expanded once by k_expand_x instead of by every
-// worker of the layer kernel.
-static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* ws, bool chained, bool x_remote,
-                     void* stream) {
+static int decode_tc(b200moe_layer* L, const void* x, const int* ids, const float* wts, int M, void* out, void* ws, bool chained, void* stream) {
   uint8_t* w = (uint8_t*)ws;
   cudaStream_t st = (cudaStream_t)stream;
   const int nbv = M <= 4 ? 0 : M <= 8 ? 1 : 2;
   const int N = 16 << nbv;
-  // B200MOE_EXPAND_IN_KERNEL=1: every worker of the layer kernel expands x itself instead of reading the operand that
-  // k_expand_x built. Measured slower from 2 tokens on (a few hundred dependent-arithmetic blocks per worker cost more
-  // than the two kernel boundaries they save); kept as a switch for experiments.
-  static const bool expand_in_kernel = [] { const char* c = getenv("B200MOE_EXPAND_IN_KERNEL"); return c && c[0] == '1'; }();
-  const bool separate = x_remote || !expand_in_kernel;
-  if (separate) {
-    const int rc = b200_expand_x_launch(x, M, L->H, N, L->KB1, w + L->off_xb, (float*)(w + L->off_xscale), chained, st);
-    if (rc != B200MOE_OK) return rc;
-  }
+  int rc = b200_expand_x_launch(x, M, L->H, N, L->KB1, w + L->off_xb, (float*)(w + L->off_xscale), chained, st);
+  if (rc != B200MOE_OK) return rc;
   DecodeTcParams p;
   memset(&p, 0, sizeof(p));
-  p.x = separate ? nullptr : (const __nv_bfloat16*)x;
   p.w1t = L->w1t, p.w2t = L->w2t, p.alpha1 = L->alpha1, p.alpha2 = L->alpha2, p.alpha2_ref = L->alpha2_ref;
   p.xb = w + L->off_xb, p.xscale = (const float*)(w + L->off_xscale);
   p.aslab = w + L->off_aslab;
@@ -320,7 +309,7 @@ extern "C" int b200moe_decode_forward_ex(const b200moe_layer* L, const void* x_b
     if (workspace_bytes < L->ws_bytes) return B200MOE_ERR_WORKSPACE;
     if (((uintptr_t)workspace & 255) || ((uintptr_t)x_bf16 & 15)) return B200MOE_ERR_ARG;
     if (M == 0) return B200MOE_OK;
-    return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, !(flags & 1), (flags & 2) != 0, stream);
+    return decode_tc(const_cast<b200moe_layer*>(L), x_bf16, topk_ids, topk_weights, M, out_bf16, workspace, !(flags & 1), stream);
   }
   return decode_common(L, x_bf16, topk_ids, topk_weights, M, out_bf16, nullptr, 3, 1, workspace, workspace_bytes, stream);
 }
@@ -357,8 +346,8 @@ extern "C" int b200moe_decode_forward_host(const b200moe_layer* L, const void* x
   void* vi = in_place ? device_view(ids_host) : nullptr;
   void* vw = in_place ? device_view(wts_host) : nullptr;
   void* vo = in_place ? device_view(out_host) : nullptr;
-  if (vx && vi && vw && vo && !((uintptr_t)vx & 15))   // flag 2: x is read across the host link
-    return b200moe_decode_forward_ex(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, 2, stream);
+  if (vx && vi && vw && vo && !((uintptr_t)vx & 15))
+    return b200moe_decode_forward(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, stream);
   uint8_t* w = (uint8_t*)workspace;
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* dx = w + L->off_hstage;

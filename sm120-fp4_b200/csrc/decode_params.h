@@ -47,7 +47,6 @@ struct DecodeTcParams {
   const float* alpha1;
   const float* alpha2;
   const float* alpha2_ref;   // [0] = max over experts of alpha2, [1] = its reciprocal
-  const __nv_bfloat16* x;    // [M, H] in device memory: the kernel expands it itself; null: xb / xscale below were built by k_expand_x
   const uint8_t* xb;         // expanded x operand: [KB1][N][128 B] images then [KT1][512] scale tiles
   const float* xscale;       // 1 / g_t per column of the x operand [N]
   uint8_t* aslab;            // expanded activations (FC2 operand): [Umax][KB2] slabs of N*128 + 2048 bytes

@@ -22,7 +22,6 @@
 #include "tcgen05.cuh"
 #include "decode_params.h"
 #include "expand.cuh"
-#include "nvfp4_math.cuh"
 #include <string.h>
 #include <stdlib.h>
 
@@ -38,7 +37,6 @@ struct TcTables {
   float wts[kTcMaxP];
   int cnt[kTcMaxE], base[kTcMaxE], uidx[kTcMaxE], experts[kTcMaxE];
   float colscale[64];          // 1 / g_t of every B column of the FC1 operand (token-major, four terms per token)
-  float g1[16];                // first-term global scale of every token (in-kernel expansion of x)
   float a1[kTcMaxE], a2n[kTcMaxE];   // per touched expert (unit index): alpha1, alpha2 relative to the layer's largest alpha2
   int U;
   unsigned long long gate0[2];   // arrival counts of the two FC1 gates before this launch (a multiple of the worker count)
@@ -296,60 +294,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
   const uint32_t tm_acc = tmem, tm_sfa = tmem + 128, tm_sfb = tmem + 320;   // accumulators 2 x 64 | weight scales NS x 16 (<= 192) | operand scales (<= 192)
   uint8_t* xb_sf = region + KB1 * (N * 128);   // scale tiles of the resident x operand (same bulk copy)
 
-  // ---------------------------------------------------------------- x -> B operand of FC1, inside this kernel
-  // With x in device memory every worker expands x itself (288 threads: all warps but the producers, which keep the weight
-  // stream going meanwhile) straight into the shared-memory image the MMAs read: token amax, then each 16-value block into
-  // four NVFP4 terms. That is redundant work - a few hundred blocks per worker - but it takes two kernel boundaries
-  // (previous kernel -> expansion kernel -> this kernel, several microseconds of completion and launch latency) off the
-  // path between the arrival of x and the first MMA. P.x == nullptr: the operand was built by k_expand_x (host-memory x).
-  const bool expand_here = P.x != nullptr;
-  if (expand_here && warp < 9 && n1 > 0) {
-    grid_dependency_wait();   // x belongs to whatever ran before this kernel in the stream
-    const int H = P.H, M = P.M;
-    for (int tok = warp; tok < M; tok += 9) {
-      float m = 0.f;
-      for (int i = lane * 8; i < H; i += 256) {
-        const uint4 v4 = *reinterpret_cast<const uint4*>(P.x + (long long)tok * H + i);
-        const uint32_t w4[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w4[q] << 16)), fabsf(__uint_as_float(w4[q] & 0xffff0000u))));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      if (lane == 0) T.g1[tok] = 2688.0f / fmaxf(m, 1e-30f);
-    }
-    named_bar_sync(2, 288);
-    if (tid < N) {
-      const int tok = tid >> 2;
-      float g = tok < M ? T.g1[tok] : 1.f;
-      for (int t = 0; t < (tid & 3); ++t) g *= 6.0f;
-      T.colscale[tid] = tok < M ? 1.0f / g : 0.f;
-    }
-    const int nblk = KB1 * 16, total = (N / kTerms) * nblk;
-    for (int i = tid; i < total; i += 288) {
-      const int tok = i / nblk, b = i - tok * nblk;
-      uint2 codes[kTerms];
-      uint8_t sf[kTerms];
-      if (tok < M && b * 16 < H) {
-        float r[16];
-        load16(P.x + (long long)tok * H + b * 16, r);
-        expand_block16(r, T.g1[tok], codes, sf);
-      } else {
-#pragma unroll
-        for (int t = 0; t < kTerms; ++t) { codes[t] = make_uint2(0u, 0u); sf[t] = 0; }
-      }
-      const int kb = b >> 4, chunk = (b & 15) >> 1, half = b & 1;
-#pragma unroll
-      for (int t = 0; t < kTerms; ++t) {
-        const int n = tok * kTerms + t;
-        *reinterpret_cast<uint2*>(region + (kb * N + n) * 128 + ((chunk ^ (n & 7)) << 4) + half * 8) = codes[t];
-        if ((b >> 2) < P.KT1) xb_sf[(b >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (b & 3)] = sf[t];
-      }
-    }
-    fence_proxy_async();      // generic-proxy stores -> visible to the tensor-core (async) proxy
-    named_bar_sync(2, 288);
-  }
-
   if (warp >= 9) {
     // ============================================================== TMA producers (one thread each)
     // Both producers walk the worker's whole tile sequence with incremental indices (no divisions in the loop) and
@@ -484,7 +428,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       if (lane == 0) mbar_arrive(&T.sfr[si]);
       if (++si == NS) { si = 0; ph ^= 1u; }
     };
-    if (n1 > 0 && !expand_here && !mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
+    if (n1 > 0 && !mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
     for (int j = 0, kb = 0; j < n1; ++j) {
       if (!mbar_wait(&T.full[si], ph, &T.abort_flag)) *P.status = 1;
       TC_TRACE(j, 1);
@@ -550,7 +494,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
       ab ^= 1;
       ++pieces;
     };
-    if (n1 > 0 && !expand_here) {
+    if (n1 > 0) {
       if (!mbar_wait(&T.xb_full, 0, &T.abort_flag)) *P.status = 6;
       tc_fence_after();
     }
@@ -584,15 +528,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_moe_decode_tc(const __grid_co
     __shared__ float s_ex[64][17];                 // gate values / activations of one unit: [column][token]
     __shared__ float s_w[16];
     grid_dependency_wait();   // everything before this kernel in the stream is complete and visible from here on
-    if (!expand_here) {
-      if (et == 0 && n1 > 0) {
-        // the resident B operand of FC1 (x expanded into NVFP4 terms by the kernel launched just before this one) and its
-        // scale tiles: one bulk copy
-        mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
-        bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
-      }
-      if (et < N) T.colscale[et] = P.xscale[et];
+    if (et == 0 && n1 > 0) {
+      // the resident B operand of FC1 (x expanded into NVFP4 terms by the kernel launched just before this one) and its
+      // scale tiles: one bulk copy
+      mbar_expect_tx(&T.xb_full, KB1 * (N * 128) + P.KT1 * 512);
+      bulk_load(region, P.xb, KB1 * (N * 128) + P.KT1 * 512, &T.xb_full);
     }
+    if (et < N) T.colscale[et] = P.xscale[et];
     // The routing inputs were read at entry, before the wait above, so that the weight stream could start early. If they
     // were still being written then (a producer kernel that lets its successors start before it has written them), the
     // copies used here are stale: say so instead of returning a wrong result silently.

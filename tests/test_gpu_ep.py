@@ -64,6 +64,8 @@ def _worker(rank, world, port, q):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import faulthandler
+    faulthandler.dump_traceback_later(120, exit=True)   # a rank stuck in a collective shows where, and ends, instead of hanging the test
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -93,6 +95,7 @@ def _worker(rank, world, port, q):
             return O._bf16_round(acc)
 
         for cap, m, transport in ((None, 7 + rank, "nccl"), (16, 16, "nccl"), (None, 40, "nccl"), (16, 9 + rank, "peer"), (None, 5 * rank, "nccl")):
+            print(f"rank {rank}: capacity={cap} m={m} {transport}", file=sys.stderr, flush=True)
             x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 300 + rank + m)
             ep = ExpertParallelMoE(local.forward, cfg["experts"], cfg["top_k"], capacity=cap, transport=transport)
             out = ep.forward(x.cuda(), ids.cuda(), wts.cuda())
@@ -132,7 +135,7 @@ def test_two_rank_expert_parallel_matches_the_full_layer():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(2)]
+    res = [q.get(timeout=150) for _ in range(2)]
     for p in procs:
         p.join(timeout=60)
         if p.is_alive():
