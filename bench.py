@@ -26,7 +26,8 @@ sys.path.insert(0, str(ROOT))
 
 MS = (1, 2, 4, 8, 16)
 ROUTINGS = ("random", "fixed8")
-EP_TRANSPORT = os.environ.get("B200MOE_EP_TRANSPORT", "nccl")   # "peer": rows stored straight into the peers' receive arrays
+# "peer" (default): rows stored straight into the peers' receive arrays over NVLink; "nccl": one packed all-to-all each way
+EP_TRANSPORT = os.environ.get("B200MOE_EP_TRANSPORT", "peer")
 
 
 def peaks():

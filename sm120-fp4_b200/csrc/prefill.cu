@@ -643,8 +643,8 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     int slot = 0, ab = 0, works = 0;
     uint32_t ph = 0;
     uint32_t aph[2] = {0, 0};
-    auto wait_ready = [&](uint64_t* bar, uint32_t parity) {   // arrivals may come from the peer CTA: acquire at cluster scope
-      return PAIR ? mbar_wait_cluster(bar, parity, &S.abort_flag) : mbar_wait(bar, parity, &S.abort_flag);
+    auto wait_ready = [&](uint64_t* bar, uint32_t parity) {   // arrivals may come from the peer CTA (see mbar_arrive_cluster)
+      return mbar_wait(bar, parity, &S.abort_flag);
     };
     if (!PAIR || rank == 0)
     for_each_segment([&](int, int n0, int n1, int ord) {

@@ -134,8 +134,12 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {   // release at cluster scope: the peer's waiter sees this CTA's writes
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+// Arrival on a barrier of another CTA of the cluster. Default semantics (release at CTA scope): what the waiter consumes
+// after these arrivals is tensor memory written by tcgen05.st / read by tcgen05.ld, ordered by tcgen05.wait and the
+// tcgen05 fences on either side, never ordinary memory of the arriving CTA - and a release at cluster scope costs the
+// arriving warp about a microsecond per arrival.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {   // acquire at cluster scope
   uint32_t ok;

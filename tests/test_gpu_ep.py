@@ -84,15 +84,17 @@ def _worker(rank, world, port, q):
         full = O.ExpertWeights(q1.cpu().numpy(), s1.cpu().numpy(), (1 / g1).cpu().numpy(), q2.cpu().numpy(), s2.cpu().numpy(), (1 / g2).cpu().numpy())
         res = []
 
-        def expected(x, ids, wts):
-            """The exchange's rounding points: every owner rank returns ONE bf16 row per token (its experts already summed
-            in fp32), the source adds the rows in rank order in fp32 and rounds once."""
-            acc = np.zeros((x.shape[0], cfg["hidden"]), dtype=np.float32)
+        def exchange_bound(x, ids, wts):
+            """The exchange's rounding points: every owner rank returns ONE bf16 row per token (its experts already summed in
+            fp32); the source adds the rows in rank order in fp32 and rounds once. Against the plain oracle (no rounding
+            between the experts) each returned row therefore adds at most half a bf16 ulp of its own value, 2^-9 |partial|,
+            to the error an un-sharded layer call may have: that sum is the elementwise allowance returned here."""
+            extra = np.zeros((x.shape[0], cfg["hidden"]), dtype=np.float32)
             per = cfg["experts"] // world
             for r in range(world):
                 wr = np.where((ids.numpy() // per) == r, wts.numpy(), 0.0).astype(np.float32)
-                acc += O._bf16_round(O.moe_reference(x.float().numpy(), full, ids.numpy(), wr))
-            return O._bf16_round(acc)
+                extra += np.abs(O.moe_reference(x.float().numpy(), full, ids.numpy(), wr)) * 2.0 ** -9
+            return extra
 
         for cap, m, transport in ((None, 7 + rank, "nccl"), (16, 16, "nccl"), (None, 40, "nccl"), (16, 9 + rank, "peer"), (None, 5 * rank, "nccl")):
             print(f"rank {rank}: capacity={cap} m={m} {transport}", file=sys.stderr, flush=True)
@@ -105,13 +107,14 @@ def _worker(rank, world, port, q):
             if m == 0:   # an empty batch on one rank: it still takes part in every exchange
                 res.append((0.0, 1.0, out.shape == (0, cfg["hidden"]), "empty"))
                 continue
-            want = expected(x, ids, wts)
             plain = O.moe_reference(x.float().numpy(), full, ids.numpy(), wts.numpy())
             rms = float(np.sqrt((plain ** 2).mean()))
-            err = float(np.abs(out.float().cpu().numpy() - want).max())
+            diff = np.abs(out.float().cpu().numpy() - plain)
+            # the un-sharded layer's own bar (2e-2 x RMS) plus the half-ulps of the bf16 rows that crossed the exchange
+            over = float((diff - exchange_bound(x, ids, wts)).max())
             used = getattr(getattr(ep, "_buf", None), "peer", False)
-            res.append((err, rms, all(torch.equal(out, o) for o in outs), f"cap={cap} m={m} {transport} peer_used={used} "
-                        f"plain-oracle {float(np.abs(out.float().cpu().numpy() - plain).max()) / rms:.2e}"))
+            res.append((over, rms, all(torch.equal(out, o) for o in outs), f"cap={cap} m={m} {transport} peer_used={used} "
+                        f"max |out - oracle| {float(diff.max()) / rms:.2e} x rms, beyond the exchange's rounding allowance"))
         q.put((rank, res))
     except Exception as ex:  # noqa: BLE001
         import traceback
@@ -121,6 +124,8 @@ def _worker(rank, world, port, q):
         # is already gone would only delay the test
         torch.cuda.synchronize()
         sys.stdout.flush()
+        q.close()
+        q.join_thread()   # the queue hands its items to a feeder thread: let it finish before the process goes
         os._exit(0)
 
 
