@@ -512,8 +512,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   constexpr int kARec = PHASE >= 3 ? kMidRec : kRec;            // bytes of one operand record
   constexpr int kACodes = PHASE >= 3 ? 8192 : 16384;            // ... of which codes; the scale tiles follow
   constexpr int kARows = PHASE >= 3 ? 64 : 128;                 // operand rows per tile
-  constexpr int kBSlot = PAIR ? 8192 + 2048 : kRec;             // bytes of a ring stage: half the code rows + all scale tiles, or a whole record
-  constexpr int kBCodes = PAIR ? 8192 : 16384;
+  constexpr int kBSlot = kRec;                                  // bytes of a ring stage
   static_assert(!PAIR || PHASE <= 2, "the CTA-pair form exists for the W4A4 phases");
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;          // CTA of the pair; 0 issues the MMAs
   uint8_t* abuf = smem;                      // KB records of the current row tile
@@ -588,13 +587,13 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
         for (int i = 0; i < (n1 - n0) * KB; ++i) {   // the records of consecutive column blocks of an expert are contiguous
           if (mine) {
             if (use >= 1 && !mbar_wait(&S.b_empty[slot], (uint32_t)((use - 1) & 1), &S.abort_flag)) *P.status = 2;
-            mbar_expect_tx(&S.b_full[slot], kBSlot);
-            if (PAIR) {   // this CTA's 64 code rows of the record (rows are 128 bytes, 8-row groups contiguous) and all of its scale tiles
-              bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + 8192 * rank, 8192, &S.b_full[slot]);
-              bulk_load(ring + slot * kBSlot + 8192, src + (long long)i * kRec + 16384, 2048, &S.b_full[slot]);
-            } else {
-              bulk_load(ring + slot * kRec, src + (long long)i * kRec, kRec, &S.b_full[slot]);
-            }
+            // PAIR: this CTA's 64 code rows of the record (rows are 128 bytes, 8-row groups contiguous) and all of its scale
+            // tiles, in ONE copy (a CTA cannot issue copies faster than records arrive otherwise): the odd CTA's rows and the
+            // scale tiles are the record's last 10 KB; the even CTA's rows are its first 8 KB, so it takes the whole record
+            // and leaves the middle unused.
+            const int skip = PAIR && rank == 1 ? 8192 : 0;
+            mbar_expect_tx(&S.b_full[slot], kRec - skip);
+            bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + skip, kRec - skip, &S.b_full[slot]);
           }
           mine = !mine;
           if (++slot == NSB) { slot = 0; ++use; }
@@ -605,7 +604,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
   } else if (warp >= 8 && warp < 12) {
     // ============================================================== scale warps
     const uint32_t lane_base = (uint32_t)((warp - 8) * 32) << 16;
-    const uint32_t a_u = smem_u32(abuf) + kACodes + lane * 16, b_u = smem_u32(ring) + kBCodes + lane * 16;
+    const uint32_t a_u = smem_u32(abuf) + kACodes + lane * 16, b_u = smem_u32(ring) + (PAIR && rank == 1 ? 8192 : 16384) + lane * 16;
     auto put = [&](uint32_t src, uint32_t dst_col) {   // four 512-byte scale tiles -> 16 TMEM columns of this quadrant
       uint32_t r[16];
 #pragma unroll
@@ -961,12 +960,16 @@ void b200_prefill_workspace_map(int E, int H, int I, int top_k, int max_tokens, 
 // in shared memory and the scale columns fit in TMEM, otherwise the kernel that streams both operands. Phases 3/4 (W4A16)
 // exist for the resident-A kernel only.
 // B200MOE_PREFILL_PAIR=1: the W4A4 GEMMs run as CTA pairs (256 rows per weight record, cta_group::2). Correct (the parity
-// tests run in both modes) but off by default, because it is slower on this part as built: the hand-over of a ring stage
-// crosses the cluster three times (the odd CTA's scale warps arrive on the even CTA's barrier, the even CTA's commit arrives
-// on both CTAs' barriers), and with that round trip a seven-stage ring delivers a record about every 0.9 us where the
-// single-CTA form takes 0.35 us - measured at 4096 tokens: FC1 231 us as pairs against 98 us, FC2 144 us against 60 us,
-// and still 238 us with MMAs, scale moves and epilogue arithmetic all switched off. Fetching the B scales once per pair and
-// reading them across the cluster (one bulk copy per CTA and record instead of two) made it slower still (312 us).
+// tests run in both modes) but off by default: per row tile it is as fast as the single-CTA form, not faster, and the tile
+// plan must give every expert an even number of tiles (+20 % tiles at 4096 tokens over 128 experts, +11 % at 8192).
+// Measured at 4096 tokens: FC1 116 us as pairs against 98 us, FC2 73 us against 60 us. Why pairing does not pay as built:
+// both CTAs' ring stages must sit at the same shared-memory offsets (one B descriptor serves both), the even CTA's code rows
+// and the scale tiles are the two ends of a record, so a stage is 18 KB in both CTAs and FC1 (144 KB of resident
+// activations) keeps four stages - and a stage's round trip (copy, scale move, MMA, commit back across the cluster) is longer
+// for a pair; FC2 is bound by its epilogue and its bf16 rows, which pairing does not change. Two copies of 8 + 2 KB per CTA
+// and record allow seven 10 KB stages but run into the rate at which an SM accepts bulk copies (same total time).
+// Barrier arrivals across the cluster use default (CTA-scope) semantics; with release/acquire at cluster scope every
+// arrival and every poll took about a microsecond and the pair form was 2.3 times slower than the single-CTA form.
 static bool pair_mode_enabled() {
   static const bool on = [] { const char* c = getenv("B200MOE_PREFILL_PAIR"); return c && c[0] == '1'; }();
   return on;
@@ -976,14 +979,14 @@ static bool pair_mode_enabled() {
 static bool prefill_pairs(int H, int I) {
   const int KB1 = (H + 255) / 256, KB2 = (I + 255) / 256;
   if (!pair_mode_enabled() || KB1 > 12 || KB2 > 12) return false;
-  const int a1 = KB1 * kRec, n1 = (227 * 1024 - 3072 - a1) / 10240;
+  const int a1 = KB1 * kRec, n1 = (227 * 1024 - 3072 - 256 - a1) / kRec;   // as launch_gemm sizes the FC1 ring
   return n1 >= 3 && (512 - 256 - 16 * KB1) / 16 >= 3;
 }
 
 static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, bool pair, cudaStream_t st) {
   const int tail = 1024 + ((phase == 2) ? 8 * 32 * 144 : 0);   // barriers (+ the W4A4 FC2 epilogue's store patches)
   const int abytes = (KB * (phase >= 3 ? kMidRec : kRec) + 1023) & ~1023;   // the resident operand tile
-  const int slot_bytes = pair ? 10240 : kRec;
+  const int slot_bytes = kRec;
   int nsb = (227 * 1024 - 2048 - tail - 256 - abytes) / slot_bytes;
   const int tmem_cap = (512 - 256 - 16 * KB) / 16;
   if (nsb > tmem_cap) nsb = tmem_cap;

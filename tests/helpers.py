@@ -118,7 +118,7 @@ def check_prefill_call(w, ow, x, ids, wts, out, max_tokens, sample_tokens=None, 
     counts = np.diff(woff[: (wex >= 0).sum() + 1])
     import os
     setting = os.environ.get("B200MOE_PREFILL_PAIR", "")
-    if setting == "1" and kb1 <= 10:   # CTA pairs (opt-in): an even number of tiles per expert
+    if setting == "1" and kb1 <= 9:   # CTA pairs (opt-in): an even number of tiles per expert
         assert nt == int((2 * ((counts + 255) // 256)).sum()), f"{what}: tile count (pairs)"
     else:
         assert nt == int(((counts + 127) // 128).sum()), f"{what}: tile count"
