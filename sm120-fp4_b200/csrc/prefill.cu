@@ -306,7 +306,7 @@ struct PrefillParams {
   const float* rowscale;      // PHASE 3: 1 / g_t of every term row of the x operand [ntiles*128] (0 on padding rows)
   float act_g1;               // PHASE 3/4: global scale of the first term of the SiLU*mul activations
   int NBLK, KB, KT, KB2, H;
-  int dbg;                    // ablation build only (-DB200_PF_ABLATE): 1 epilogue without math, 2 no MMAs, 4 no scale moves
+  int dbg;                    // ablation build only (-DB200_PF_ABLATE): 1 epilogue without math, 2 no MMAs, 4 no scale moves, 8 one weight producer, bits 8-11 ring depth cap
 };
 
 struct PfShared {
@@ -582,6 +582,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
     if (lane == 0) {
       int slot = 0, use = 0;
       bool mine = warp == 14;
+      const bool solo = PF_ABLATE(8);   // diagnostic build: warp 14 issues every record, warp 15 none
       for_each_segment([&](int t, int n0, int n1, int) {
         const uint8_t* src = P.wrec + ((long long)P.tile_expert[t] * NBLK + n0) * KB * kRec;
         for (int i = 0; i < (n1 - n0) * KB; ++i) {   // the records of consecutive column blocks of an expert are contiguous
@@ -595,7 +596,7 @@ __global__ void __launch_bounds__(kPrThreads, 1) k_prefill_gemm_r(const __grid_c
             mbar_expect_tx(&S.b_full[slot], kRec - skip);
             bulk_load(ring + slot * kBSlot, src + (long long)i * kRec + skip, kRec - skip, &S.b_full[slot]);
           }
-          mine = !mine;
+          if (!solo) mine = !mine;
           if (++slot == NSB) { slot = 0; ++use; }
         }
       });
@@ -991,6 +992,9 @@ static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, bool 
   const int tmem_cap = (512 - 256 - 16 * KB) / 16;
   if (nsb > tmem_cap) nsb = tmem_cap;
   if (nsb > 12) nsb = 12;
+#ifdef B200_PF_ABLATE
+  if (((p.dbg >> 8) & 15) >= 2 && ((p.dbg >> 8) & 15) < nsb) nsb = (p.dbg >> 8) & 15;   // ring depth cap
+#endif
   if (KB <= 12 && nsb >= 3) {
     const int sm_r = 1024 + abytes + ((nsb * slot_bytes + 1023) & ~1023) + tail;
     const void* fn = pair ? (phase == 1 ? (const void*)k_prefill_gemm_r<1, true> : (const void*)k_prefill_gemm_r<2, true>)
