@@ -480,29 +480,21 @@ def ep_stack(cfg, layers, dist, world, rank, dev, stack=48, decode_tokens=16, pr
     return res
 
 
-def host_layer(cfg, seed=0):
-    """One layer's weights on the host for the CPU arm: drawn and quantised by the oracle itself (a few experts only:
-    the ones the sampled batch touches are generated lazily)."""
+_HOST_EXPERTS = {}   # (shape, seed, expert) -> packed weights of that expert: drawn and quantised once per process
+
+
+def host_expert(cfg, ex, seed=0):
+    """One expert's weights on the host for the CPU arm: drawn like the GPU arm's (bf16 N(0, 0.02)) and quantised by the
+    oracle's own quantiser. Generated lazily and kept: the sweep touches most experts, each costs a fraction of a second."""
     from oracle import nvfp4_oracle as O
-    e, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
-
-    class Lazy(O.ExpertWeights):
-        def __init__(self):
-            self.E, self.I, self.H = e, i, h
-            self._cache = {}
-
-        def dequant(self, ex):
-            if ex not in self._cache:
-                g = torch.Generator().manual_seed(seed * 1000 + ex)
-                w13 = (torch.randn(2 * i, h, generator=g) * 0.02).to(torch.bfloat16).float().numpy()
-                w2 = (torch.randn(h, i, generator=g) * 0.02).to(torch.bfloat16).float().numpy()
-                q1, s1, g1 = O.quantize_nvfp4(w13)
-                q2, s2, g2 = O.quantize_nvfp4(w2)
-                self._packed = getattr(self, "_packed", {})
-                self._packed[ex] = (q1, s1, g1, q2, s2, g2)
-                self._cache[ex] = None
-            return self._packed[ex]
-    return Lazy()
+    h, i = cfg["hidden"], cfg["inter"]
+    key = (h, i, seed, ex)
+    if key not in _HOST_EXPERTS:
+        g = torch.Generator().manual_seed(seed * 1000 + ex)
+        w13 = (torch.randn(2 * i, h, generator=g) * 0.02).to(torch.bfloat16).float().numpy()
+        w2 = (torch.randn(h, i, generator=g) * 0.02).to(torch.bfloat16).float().numpy()
+        _HOST_EXPERTS[key] = O.quantize_nvfp4(w13) + O.quantize_nvfp4(w2)
+    return _HOST_EXPERTS[key]
 
 
 def cpu_forward_timed(cfg, m, routing, repeats):
@@ -511,13 +503,12 @@ def cpu_forward_timed(cfg, m, routing, repeats):
     from oracle import nvfp4_oracle as O
     from sm120fp4_b200 import synth
     x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 1000 + m if routing == "random" else 7, routing)
-    lazy = host_layer(cfg)
     touched = sorted(set(ids.reshape(-1).tolist()))
-    packed = {ex: lazy.dequant(ex) for ex in touched}
     e, h, i = cfg["experts"], cfg["hidden"], cfg["inter"]
     q1 = np.zeros((e, 2 * i, h // 2), np.uint8); s1 = np.zeros((e, 2 * i, h // 16), np.uint8); a1 = np.ones(e, np.float32)
     q2 = np.zeros((e, h, i // 2), np.uint8); s2 = np.zeros((e, h, i // 16), np.uint8); a2 = np.ones(e, np.float32)
-    for ex, (p1, f1, g1, p2, f2, g2) in packed.items():
+    for ex in touched:
+        p1, f1, g1, p2, f2, g2 = host_expert(cfg, ex)
         q1[ex], s1[ex], a1[ex], q2[ex], s2[ex], a2[ex] = p1, f1, 1.0 / g1[0], p2, f2, 1.0 / g2[0]
     xs, idn, wn = x.float().numpy(), ids.numpy(), wts.numpy()
     times = []
@@ -540,27 +531,46 @@ def workload_name(shape, cfg):
             f"I={cfg['inter']} top-{cfg['top_k']}")
 
 
+REFERENCE_BUDGET_S = float(os.environ.get("B200MOE_REFERENCE_BUDGET_S", "120"))   # timed CPU work of the whole reference run
+
+
 def run_reference(a):
     """The reference arm: the reference's CPU algorithm for this path (the oracle port; the reference itself is a PyTorch
     package that cannot travel to the GPU box) on the host cores, with all the threads numpy's BLAS takes. One step = one
-    layer call for each of the ten cases of the sweep (same seeds as the GPU arm); dequantisation of the touched experts is
-    inside the timed region, as in the reference's CPU path (sm120fp4/kernels/bench_moe_baseline.py:53-74)."""
+    layer call for each of the ten cases of the sweep (same seeds as the GPU arm) when `steps` such steps fit the time budget
+    of the run; otherwise every step takes the next few cases of the ten in turn (a bounded sample, evenly spread over the
+    sweep). Dequantisation of the touched experts is inside the timed region, as in the reference's CPU path
+    (sm120fp4/kernels/bench_moe_baseline.py:53-74); drawing and quantising the synthetic weights is not."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
     from sm120fp4_b200 import synth
     cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
     sweep = [(m, routing) for routing in ROUTINGS for m in MS]
-    for _ in range(min(a.warmup, 1)):
-        cpu_forward_timed(cfg, 1, "random", 1)
-    tot_s, tot_b = 0.0, 0
+    # warm-up: the smallest case once (BLAS threads, page faults); it also gives the time of one touched expert
+    per_expert = None
+    for _ in range(max(1, min(a.warmup, 2))):
+        s, b = cpu_forward_timed(cfg, 1, "fixed8", 1)
+        per_expert = s / 8
+    touched_per_step = sum(8 if r == "fixed8" else min(cfg["experts"], round(cfg["experts"] * (1 - (1 - 1 / cfg["experts"]) ** (m * cfg["top_k"]))))
+                           for m, r in sweep)
+    full_step_s = per_expert * touched_per_step
+    per_step = len(sweep)
+    if full_step_s * a.steps > REFERENCE_BUDGET_S:
+        per_step = max(1, min(len(sweep), int(len(sweep) * REFERENCE_BUDGET_S / (full_step_s * a.steps))))
+    tot_s, tot_b, pos, ran = 0.0, 0, 0, 0
     for _ in range(a.steps):
-        for m, routing in sweep:
+        for _ in range(per_step):
+            m, routing = sweep[pos % len(sweep)]
+            pos += 1
             s, b = cpu_forward_timed(cfg, m, routing, 1)
             tot_s += s
             tot_b += b
+            ran += 1
     val = tot_b / tot_s / 1e9
-    sample = "per step: one layer call for each of the ten cases of the sweep; numpy/BLAS threads; dequantisation inside the timed region"
+    what = ("one layer call for each of the ten cases of the sweep" if per_step == len(sweep)
+            else f"{per_step} of the ten cases of the sweep, taken in turn ({ran} layer calls in all, {ran / len(sweep):.1f} passes over the sweep)")
+    sample = f"per step: {what}; numpy/BLAS threads; dequantisation inside the timed region; {tot_s:.0f} s of timed CPU work"
     line = {"impl": "reference", "metric": "moe_decode_layer_hbm_gbs_on_touched_expert_bytes", "value": round(val, 4), "unit": "GB/s",
             "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(tot_s / a.steps * 1e3, 1),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 on dequantised NVFP4", "data": "synthetic",
