@@ -205,7 +205,10 @@ __global__ void __launch_bounds__(256) k_mid_rowmap(const int* __restrict__ ids,
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gsz = gridDim.x * blockDim.x;
   for (int p = gtid; p < P; p += gsz)
     if (ids[p] < 0) dst_row[p] = -1;
-  for (int prow = gtid; prow < NT * 16; prow += gsz) {
+  // one thread per (pair row, K box): the row's entry of the tables (by the thread of box 0) and, for a row that holds no
+  // pair, the sixteen scale words of its four term rows in this box's record
+  for (long long it = gtid; it < (long long)NT * 16 * KB; it += gsz) {
+    const int prow = (int)(it / KB), kb = (int)(it - (long long)prow * KB);
     const int t = prow >> 4, p = prow & 15;
     int a = 0, b = 255;
     while (a < b) {
@@ -214,19 +217,19 @@ __global__ void __launch_bounds__(256) k_mid_rowmap(const int* __restrict__ ids,
     }
     const int j = s_lo[a] + (t - tbase[a]) * 16 + p;
     const int pr = j < s_hi[a] ? pairs[j] : -1;
+    if (kb == 0) {
 #pragma unroll
-    for (int q = 0; q < kTerms; ++q) row_pair[t * 64 + 4 * p + q] = pr;
-    if (pr >= 0) {
-      dst_row[pr] = prow;
-    } else {
-      for (int kb = 0; kb < KB; ++kb)
+      for (int q = 0; q < kTerms; ++q) row_pair[t * 64 + 4 * p + q] = pr;
+      if (pr >= 0) dst_row[pr] = prow;
+    }
+    if (pr < 0) {
 #pragma unroll
-        for (int q = 0; q < kTerms; ++q) {
-          const int r = 4 * p + q;
-          uint8_t* sfp = rec + ((long long)t * KB + kb) * kMidRec + 8192 + (r & 31) * 16 + (r >> 5) * 4;
+      for (int q = 0; q < kTerms; ++q) {
+        const int r = 4 * p + q;
+        uint8_t* sfp = rec + ((long long)t * KB + kb) * kMidRec + 8192 + (r & 31) * 16 + (r >> 5) * 4;
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<uint32_t*>(sfp + jj * 512) = 0u;
-        }
+        for (int jj = 0; jj < 4; ++jj) *reinterpret_cast<uint32_t*>(sfp + jj * 512) = 0u;
+      }
     }
   }
 }
@@ -1159,7 +1162,7 @@ int b200_mid_forward(int E, int H, int I, int top_k, const uint8_t* w1t, const u
   const int max_tiles = P / 16 + Umax;
   int* tile_end = tile_first + max_tiles;
   {
-    int grid = (max_tiles * 16 + 255) / 256;
+    int grid = (max_tiles * 16 * KB1 + 255) / 256;
     if (grid > sms * 4) grid = sms * 4;
     k_mid_rowmap<<<grid, 256, 0, st>>>(ids, P, experts, offsets, pairs, Umax, max_tiles, KB1, ntiles, tile_expert, tile_first, tile_end, w + L.xrec,
                                        row_pair, dst_row);
