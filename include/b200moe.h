@@ -125,9 +125,9 @@ int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const
 int b200moe_decode_forward_ex(const b200moe_layer* layer, const void* x_bf16, const int* topk_ids, const float* topk_weights,
                               int M, void* out_bf16, void* workspace, long long workspace_bytes, int flags, void* stream);
 /* b200moe_decode_forward for a caller whose tensors live in host memory: x bf16 [M, H], ids int32 [M, top_k], weights f32
- * [M, top_k] in, out bf16 [M, H] back. Page-locked buffers are read and written by the kernels directly across the host
- * link (no copy is enqueued); pageable buffers go through staging buffers inside the workspace. Everything is enqueued on
- * `stream`, nothing synchronises. M <= 16. Replaces the same call
+ * [M, top_k] in, out bf16 [M, H] back. The inputs go through staging buffers inside the workspace (three small copies on
+ * `stream`); a page-locked output buffer is written by the kernel directly across the host link, a pageable one is copied
+ * back. Everything is enqueued on `stream`, nothing synchronises. M <= 16. Replaces the same call
  * site as b200moe_decode_forward (sm120fp4/vllm_backend.py:174-190) for hosts that do not hold device tensors. */
 int b200moe_decode_forward_host(const b200moe_layer* layer, const void* x_host, const int* ids_host, const float* wts_host, int M,
                                 void* out_host, void* workspace, long long workspace_bytes, void* stream);

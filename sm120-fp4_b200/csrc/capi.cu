@@ -341,13 +341,20 @@ extern "C" int b200moe_decode_forward_host(const b200moe_layer* L, const void* x
     explicit DeviceGuard(int want) { if (cudaGetDevice(&prev) == cudaSuccess && prev != want) cudaSetDevice(want); else prev = -1; }
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
   } guard(L->device);
-  static const bool in_place = [] { const char* c = getenv("B200MOE_HOST_IN_PLACE"); return !(c && c[0] == '0'); }();
-  void* vx = in_place ? device_view(x_host) : nullptr;
-  void* vi = in_place ? device_view(ids_host) : nullptr;
-  void* vw = in_place ? device_view(wts_host) : nullptr;
-  void* vo = in_place ? device_view(out_host) : nullptr;
-  if (vx && vi && vw && vo && !((uintptr_t)vx & 15))
-    return b200moe_decode_forward(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, stream);
+  // Page-locked host buffers can be used by the kernels directly across the host link. For the OUTPUT that is a stream of
+  // posted writes and saves a copy after the kernel; for the INPUTS it means that all 148 workers fetch the ids and weights
+  // from host memory in their prologue, one round trip over the link each, which measures slower than three small copies
+  // ahead of the kernel (1.2 TB/s against 0.8 TB/s on the decode sweep). So by default the inputs are staged and the output
+  // is written in place; B200MOE_HOST_IN_PLACE=1 uses all four buffers in place, =0 stages all four.
+  static const int mode = [] { const char* c = getenv("B200MOE_HOST_IN_PLACE"); return !c ? 2 : c[0] == '0' ? 0 : c[0] == '1' ? 1 : 2; }();
+  void* vo = mode != 0 ? device_view(out_host) : nullptr;
+  if (mode == 1 && vo) {
+    void* vx = device_view(x_host);
+    void* vi = device_view(ids_host);
+    void* vw = device_view(wts_host);
+    if (vx && vi && vw && !((uintptr_t)vx & 15))
+      return b200moe_decode_forward(L, vx, (const int*)vi, (const float*)vw, M, vo, workspace, workspace_bytes, stream);
+  }
   uint8_t* w = (uint8_t*)workspace;
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* dx = w + L->off_hstage;
@@ -357,6 +364,7 @@ extern "C" int b200moe_decode_forward_host(const b200moe_layer* L, const void* x
   B200_CUDA_TRY(cudaMemcpyAsync(dx, x_host, (size_t)M * L->H * 2, cudaMemcpyHostToDevice, st));
   B200_CUDA_TRY(cudaMemcpyAsync(dids, ids_host, (size_t)M * L->top_k * 4, cudaMemcpyHostToDevice, st));
   B200_CUDA_TRY(cudaMemcpyAsync(dwts, wts_host, (size_t)M * L->top_k * 4, cudaMemcpyHostToDevice, st));
+  if (vo && !((uintptr_t)vo & 15)) return b200moe_decode_forward(L, dx, dids, dwts, M, vo, workspace, workspace_bytes, stream);
   const int rc = b200moe_decode_forward(L, dx, dids, dwts, M, dout, workspace, workspace_bytes, stream);
   if (rc != B200MOE_OK) return rc;
   B200_CUDA_TRY(cudaMemcpyAsync(out_host, dout, (size_t)M * L->H * 2, cudaMemcpyDeviceToHost, st));

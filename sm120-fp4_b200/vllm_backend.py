@@ -263,7 +263,7 @@ class Weights:
     def forward_host(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """The forward for tensors in host memory: x bf16 [tokens, H], ids int32 and weights f32 [tokens, top_k], out bf16
         [tokens, H], all on the CPU. One library call per 16 tokens enqueues everything on the current stream of the layer's
-        device (page-locked tensors are read and written by the kernels directly, pageable ones are copied); nothing
+        device (the inputs are staged by three small copies, a page-locked `out` is written by the kernel directly); nothing
         synchronises - read `out` after synchronising the stream. A set of tensors is validated once and then recognised by
         its addresses, so that a serving loop that reuses its buffers pays for one foreign-function call only."""
         m = x.shape[0]
