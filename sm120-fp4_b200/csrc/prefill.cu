@@ -996,8 +996,8 @@ static int launch_gemm(const PrefillParams& p, int phase, int KB, int sms, bool 
   if (nsb > tmem_cap) nsb = tmem_cap;
   if (nsb > 12) nsb = 12;
   // W4A4 FC2 (three K boxes per tile): five stages measure faster than the seven that fit (57.7 us against 62.5 at 4096
-  // tokens, 102 against 109 at 8192; six: 63.1, four: 59.1) - a deeper ring lets the CTAs that share an expert's weight
-  // records through L2 drift apart. The W4A16 FC2 likewise (27.6 us against 29.3 at 128 tokens over 128 experts).
+  // tokens, 102 against 109 at 8192; six: 63.1, four: 59.1); DRAM traffic is at its minimum either way, so the cause is not
+  // re-reads and is not known. The W4A16 FC2 likewise (27.6 us against 29.3 at 128 tokens over 128 experts).
   if ((phase == 2 || phase == 4) && !pair && nsb > 5) nsb = 5;
 #ifdef B200_PF_ABLATE
   if (((p.dbg >> 8) & 15) >= 2 && ((p.dbg >> 8) & 15) < nsb) nsb = (p.dbg >> 8) & 15;   // ring depth cap
