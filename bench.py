@@ -26,7 +26,8 @@ sys.path.insert(0, str(ROOT))
 
 MS = (1, 2, 4, 8, 16)
 ROUTINGS = ("random", "fixed8")
-# "peer" (default): rows stored straight into the peers' receive arrays over NVLink; "nccl": one packed all-to-all each way
+# "peer" (default): rows stored straight into the peers' memory over NVLink as flagged words; "peer_fence": plain rows, a
+# system-scope fence and arrival counters; "nccl": one packed all-to-all each way
 EP_TRANSPORT = os.environ.get("B200MOE_EP_TRANSPORT", "peer")
 
 
@@ -364,7 +365,7 @@ def finish(dist):
     gc.collect()
     torch.cuda.synchronize()
     dist.barrier()
-    if EP_TRANSPORT == "peer":
+    if EP_TRANSPORT != "nccl":
         sys.stdout.flush()
         os._exit(0)        # the mappings are released with the process; a collective teardown after that has been seen to wait forever
     dist.destroy_process_group()

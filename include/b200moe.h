@@ -208,6 +208,24 @@ int b200moe_ep_dispatch_wait(const void* x, const int* ids, const float* wts, in
 int b200moe_ep_return_combine(const void* yl, int world, int cap, int h, int rank, void* const* back_y, unsigned* const* back_flag,
                               const unsigned* flags_back, const unsigned* calls, int* status, const void* back, int m, void* out,
                               void* stream);
+
+/* The peer-store exchange in its flagged-word form: every 8-byte store carries 4 bytes of payload and the call number, so
+ * the sender never waits for its stores to be acknowledged across NVLink before it may signal (no system-scope fence, no
+ * separate counters). Twice the bytes per row, one round trip less per exchange. peers_in / peers_back: host arrays of
+ * `world` device pointers into the peers' flagged areas (entry d = where THIS rank's block starts at rank d); in / back:
+ * this rank's own areas, in: uint2 [world][cap][h/2 + 2k], back: uint2 [world][cap][h/2] followed by `world` marker words;
+ * both zeroed once. rx / rid / rw: the plain arrays the local layer call takes (bf16 [world*cap, h], int32 and f32
+ * [world*cap, k]). calls: device uint32 [2], zeroed once; status: device int32, 0 or 1 + the rank whose words never arrived
+ * within the bounded wait. A layer call is b200moe_ep_dispatch_ll, the local layer on (rx, rid, rw) -> yl,
+ * b200moe_ep_return_combine_ll, in that order on one stream; cap and world are the same on every rank. A token row is sent
+ * back only by the ranks that own one of its experts, and only those are waited for; a marker word per rank keeps a rank
+ * from starting its next call before every peer has finished reading this one. No counterpart in the reference (it declines
+ * expert parallelism, sm120fp4/vllm_classes.py:46-47). */
+int b200moe_ep_dispatch_ll(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
+                           void* const* peers_in, const void* in, void* rx, int* rid, float* rw, unsigned* calls, int* status, void* stream);
+int b200moe_ep_return_combine_ll(const void* yl, const int* rid, int world, int cap, int h, int k, int rank, int experts_per_rank,
+                                 void* const* peers_back, const void* back, const int* ids, int m, void* out, unsigned* calls, int* status,
+                                 void* stream);
 /* variable-size exchange (prefill batches; no counterpart in the reference either). plan: counts int32 [world], offsets int32
  * [world + 1], pos int32 [m, world] (row of token t in the send buffer for destination d, or -1), send_tok int32 [rows]
  * (destination-major, token order within a destination). gather: the rows of the send buffer (sx bf16 [rows, h], meta int32

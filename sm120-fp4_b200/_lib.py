@@ -58,6 +58,8 @@ SIGNATURES = {
     "b200moe_ep_dispatch": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "b200moe_ep_dispatch_wait": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b200moe_ep_return_combine": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P]),
+    "b200moe_ep_dispatch_ll": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "b200moe_ep_return_combine_ll": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P]),
     "b200moe_ep_unpack": (_I, [_P, _LL, _I, _I, _I, _I, _P, _P, _P, _P]),
     "b200moe_ep_wait": (_I, [_P, _I, _I, _P, _P, _P]),
     "b200moe_ep_return": (_I, [_P, _I, _I, _I, _I, _P, _P, _P]),

@@ -184,6 +184,202 @@ __global__ void __launch_bounds__(256) k_ep_combine(const __nv_bfloat16* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The peer-store exchange without a fence: every 8-byte store carries 4 bytes of payload and the call number ("flagged
+// words", the low-latency protocol of collective libraries). An aligned 8-byte store arrives whole, so a receiver that sees
+// the current call number in a word has that word's payload; nothing has to order the payload before a separate flag, i.e.
+// the sender never waits for its stores to be acknowledged across NVLink (a system-scope fence there costs a round trip,
+// 2-3 us, in each of the two exchanges of a layer call). The price is twice the bytes (8 KB per 4 KB row), which is
+// nothing at decode sizes. Buffers are zeroed once; call numbers start at 1 and only grow, so a stale word never matches.
+//
+// Flagged row of the dispatch: h/2 words of x (two bf16 each), then k words of local expert ids, then k words of routing
+// weights. A row whose token has no expert on the destination travels as its 2k meta words only.
+struct EpLLPeers {
+  uint2* p[kEpMaxWorld];   // per peer: where THIS rank's block starts in the peer's flagged receive area
+};
+
+__device__ __forceinline__ void ll_store(uint2* dst, uint32_t payload, uint32_t flag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(payload), "r"(flag) : "memory");
+}
+
+// Flagged words in batches: up to kLLBatch words per thread are read (or written) back to back, so their latencies overlap
+// instead of adding up (a thread that polls its words one after the other pays an L2 round trip for each).
+constexpr int kLLBatch = 8;
+
+// src[i] -> flagged words dst[i] for i = first, first + stride, ... < count
+__device__ __forceinline__ void ll_send(uint2* dst, const uint32_t* __restrict__ src, int first, int stride, int count, uint32_t flag) {
+  for (int b0 = first; b0 < count; b0 += stride * kLLBatch) {
+    uint32_t v[kLLBatch];
+#pragma unroll
+    for (int j = 0; j < kLLBatch; ++j) v[j] = b0 + j * stride < count ? src[b0 + j * stride] : 0u;
+#pragma unroll
+    for (int j = 0; j < kLLBatch; ++j)
+      if (b0 + j * stride < count) ll_store(dst + b0 + j * stride, v[j], flag);
+  }
+}
+
+// Bounded poll of the flagged words src[i], i = b0 + j * stride (j < kLLBatch, i < count): payloads into v[]; false (and
+// *status = 1 + peer) when the call number never shows up in one of them.
+__device__ __forceinline__ bool ll_recv_batch(const uint2* src, int b0, int stride, int count, uint32_t flag, uint32_t* v, int peer, int* status) {
+  unsigned pending = 0;
+#pragma unroll
+  for (int j = 0; j < kLLBatch; ++j)
+    if (b0 + j * stride < count) pending |= 1u << j;
+  for (unsigned it = 0; it < (1u << 22); ++it) {
+    uint32_t a[kLLBatch], f[kLLBatch];
+#pragma unroll
+    for (int j = 0; j < kLLBatch; ++j)
+      if ((pending >> j) & 1u)
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a[j]), "=r"(f[j]) : "l"(src + b0 + j * stride) : "memory");
+#pragma unroll
+    for (int j = 0; j < kLLBatch; ++j)
+      if (((pending >> j) & 1u) && f[j] == flag) { v[j] = a[j]; pending &= ~(1u << j); }
+    if (!pending) return true;
+    if (it > 2048u) __nanosleep(200);
+    if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) return false;   // another wait already gave up
+  }
+  *status = 1 + peer;
+  return false;
+}
+
+// Bounded poll of one flagged word; false (and *status = 1 + peer) when the call number never shows up.
+__device__ __forceinline__ bool ll_load(const uint2* src, uint32_t flag, uint32_t* payload, int peer, int* status) {
+  for (unsigned it = 0; it < (1u << 22); ++it) {
+    uint32_t a, b;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "l"(src) : "memory");
+    if (b == flag) { *payload = a; return true; }
+    if (it > 2048u) __nanosleep(200);
+    if ((it & 1023u) == 1023u && *reinterpret_cast<volatile int*>(status) != 0) return false;   // another wait already gave up
+  }
+  *status = 1 + peer;
+  return false;
+}
+
+// Dispatch and receive in one launch. Block (row, peer): first it sends token `row` to `peer` (flagged words into the peer's
+// receive area), then it receives row `row` of `peer`'s block from this rank's own receive area `in` ([world][cap][words])
+// into the plain arrays the layer call takes (rx bf16 [world * cap, h], rid int32 / rw f32 [world * cap, k]). calls[0] is
+// the number of completed layer calls (read here, advanced by the return kernel); calls[1] is advanced here for the return
+// kernel to read - neither kernel reads the word it writes, so the blocks of a launch agree on the call number.
+__global__ void __launch_bounds__(128) k_ep_dispatch_ll(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
+                                                        const float* __restrict__ wts, int m, int h, int k, int per, int cap,
+                                                        const __grid_constant__ EpLLPeers D, const uint2* __restrict__ in,
+                                                        __nv_bfloat16* __restrict__ rx, int* __restrict__ rid, float* __restrict__ rw,
+                                                        unsigned* __restrict__ calls, int* __restrict__ status) {
+  const int row = blockIdx.x, peer = blockIdx.y, tid = threadIdx.x;
+  const uint32_t n = calls[0] + 1u;
+  const int hw = h / 2, words = hw + 2 * k;
+  // ---- send
+  {
+    uint2* dst = D.p[peer] + (long long)row * words;
+    bool any = false;
+    if (row < m)
+      for (int j = 0; j < k; ++j) { const int e = ids[row * k + j]; any |= e >= 0 && e / per == peer; }
+    if (tid < 2 * k) {
+      const int j = tid < k ? tid : tid - k;
+      int id = -1;
+      float w = 0.f;
+      if (row < m) {
+        const int e = ids[row * k + j];
+        if (e >= 0 && e / per == peer) { id = e - peer * per; w = wts[row * k + j]; }
+      }
+      ll_store(dst + hw + tid, tid < k ? (uint32_t)id : __float_as_uint(w), n);
+    }
+    if (any) ll_send(dst, reinterpret_cast<const uint32_t*>(x + (long long)row * h), tid, (int)blockDim.x, hw, n);
+  }
+  // ---- receive
+  {
+    const uint2* src = in + ((long long)peer * cap + row) * words;
+    const long long o = (long long)peer * cap + row;
+    int id = -1;
+    bool ok = true;
+    if (tid < 2 * k) {
+      uint32_t v = 0;
+      ok = ll_load(src + hw + tid, n, &v, peer, status);
+      if (tid < k) { id = ok ? (int)v : -1; rid[o * k + tid] = id; }
+      else rw[o * k + tid - k] = ok ? __uint_as_float(v) : 0.f;
+    }
+    const int any = __syncthreads_or(tid < k && id >= 0);
+    if (any) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(rx + o * h);
+      const int stride = (int)blockDim.x;
+      for (int b0 = tid; b0 < hw; b0 += stride * kLLBatch) {
+        uint32_t v[kLLBatch];
+        if (!ll_recv_batch(src, b0, stride, hw, n, v, peer, status)) break;
+#pragma unroll
+        for (int j = 0; j < kLLBatch; ++j)
+          if (b0 + j * stride < hw) dst[b0 + j * stride] = v[j];
+      }
+    }
+  }
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) calls[1] = n;
+}
+
+// Return, receive and combine in one launch. Block (row, peer): if this rank computed anything for token `row` of `peer`
+// (one of the row's received ids is live), its partial row goes back as flagged words into `peer`'s return area at block
+// `rank`. Blocks (row, 0) with row < m then finish the layer call for token `row`: for every rank r in rank order that owns
+// one of the token's experts they take r's flagged partial row from this rank's own return area `back` ([world][cap][h/2])
+// and add it in fp32; one bf16 rounding. Ranks that own none of the token's experts sent nothing and are not waited for.
+// Return area of a rank: uint2 [world][cap][h/2] rows, then `world` marker words.
+__global__ void __launch_bounds__(128) k_ep_return_ll(const __nv_bfloat16* __restrict__ yl, const int* __restrict__ rid, int cap, int h, int k,
+                                                      int rank, int world, int per, const __grid_constant__ EpLLPeers B,
+                                                      const uint2* __restrict__ back, const int* __restrict__ ids, int m,
+                                                      __nv_bfloat16* __restrict__ out, unsigned* __restrict__ calls, int* __restrict__ status) {
+  const int row = blockIdx.x, peer = blockIdx.y, tid = threadIdx.x;
+  const uint32_t n = calls[1];
+  const int hw = h / 2;
+  const long long marks = (long long)world * cap * hw;   // after the rows of a return area: one word per rank, "rank r has reached its return of call n"
+  if (row == 0 && tid == 0) ll_store(B.p[peer] - (long long)rank * cap * hw + marks + rank, 0u, n);
+  {
+    const long long o = (long long)peer * cap + row;
+    bool any = false;
+    for (int j = 0; j < k; ++j) any |= rid[o * k + j] >= 0;
+    if (any) {
+      ll_send(B.p[peer] + (long long)row * hw, reinterpret_cast<const uint32_t*>(yl + o * h), tid, (int)blockDim.x, hw, n);
+    }
+  }
+  if (peer == 0 && row < m) {
+    unsigned owners = 0;   // bit r: rank r owns one of this token's experts and returns a partial row
+    for (int j = 0; j < k; ++j) {
+      const int e = ids[row * k + j];
+      if (e >= 0 && e / per < world) owners |= 1u << (e / per);
+    }
+    const int stride = (int)blockDim.x;
+    for (int b0 = tid; b0 < hw; b0 += stride * kLLBatch) {
+      float a0[kLLBatch], a1[kLLBatch];
+#pragma unroll
+      for (int j = 0; j < kLLBatch; ++j) a0[j] = a1[j] = 0.f;
+      bool ok = true;
+      for (int r = 0; r < world && ok; ++r) {
+        if (!((owners >> r) & 1u)) continue;
+        uint32_t v[kLLBatch];
+        ok = ll_recv_batch(back + ((long long)r * cap + row) * hw, b0, stride, hw, n, v, r, status);
+#pragma unroll
+        for (int j = 0; j < kLLBatch; ++j)
+          if (ok && b0 + j * stride < hw) {
+            a0[j] += __uint_as_float(v[j] << 16);
+            a1[j] += __uint_as_float(v[j] & 0xffff0000u);
+          }
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int j = 0; j < kLLBatch; ++j)
+        if (b0 + j * stride < hw) {
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(a0[j], a1[j]);
+          reinterpret_cast<uint32_t*>(out + (long long)row * h)[b0 + j * stride] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+    }
+  }
+  // The call is complete on this rank once every rank has reached its own return kernel: from then on no peer reads this
+  // call's words of this rank any more, so the next call's words may overwrite them. (The row waits above skip the ranks
+  // that own none of a token's experts, so they alone would not order this rank behind all the others.)
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid < 32) {
+    uint32_t v;
+    if (tid < world) ll_load(back + marks + tid, n, &v, tid, status);
+    __syncwarp();
+    if (tid == 0) calls[0] = n;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -433,6 +629,52 @@ extern "C" int b200moe_ep_combine_rows(const void* back, const int* pos, int m, 
   int grid = (total + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;
   k_ep_combine_rows<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)back, pos, m, h, world, (__nv_bfloat16*)out);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Flagged-word form of the peer-store exchange (see k_ep_dispatch_ll). peers_in: host array of `world` device pointers, entry
+// d = where this rank's block starts inside rank d's flagged receive area (uint2 [cap][h/2 + 2k] per source rank); in: this
+// rank's own receive area (uint2 [world][cap][h/2 + 2k]); rx / rid / rw: the plain arrays the layer call takes;
+// calls: device uint32 [2], zeroed once together with the areas; status: device int32, 0 or 1 + the rank whose words never
+// arrived. One layer call = b200moe_ep_dispatch_ll, the local layer, b200moe_ep_return_combine_ll, in that order.
+extern "C" int b200moe_ep_dispatch_ll(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank,
+                                      int cap, void* const* peers_in, const void* in, void* rx, int* rid, float* rw, unsigned* calls, int* status,
+                                      void* stream) {
+  if ((m > 0 && (!x || !ids || !wts)) || !peers_in || !in || !rx || !rid || !rw || !calls || !status) return B200MOE_ERR_ARG;
+  if (m < 0 || m > cap || h <= 0 || h % 8 || k < 1 || 2 * k > 128 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1 || cap < 1)
+    return B200MOE_ERR_SHAPE;
+  EpLLPeers D;
+  for (int d = 0; d < kEpMaxWorld; ++d) {
+    D.p[d] = d < world ? (uint2*)peers_in[d] : nullptr;
+    if (d < world && (!D.p[d] || ((uintptr_t)D.p[d] & 7))) return B200MOE_ERR_ARG;
+  }
+  k_ep_dispatch_ll<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ids, wts, m, h, k, experts_per_rank, cap, D,
+                                                                        (const uint2*)in, (__nv_bfloat16*)rx, rid, rw, calls, status);
+  B200_LAUNCH_CHECK();
+  return B200MOE_OK;
+}
+
+// yl bf16 [world * cap, h]: this rank's partial rows (block s for source s); rid: the ids b200moe_ep_dispatch_ll received
+// (which rows carry anything); peers_back: host array, entry s = where block `rank` starts inside rank s's flagged return
+// area (uint2 [cap][h/2] per computing rank); back: this rank's own return area (uint2 [world][cap][h/2], then `world` marker
+// words: (world * cap * h/2 + world) * 8 bytes); ids: the caller's
+// global top-k ids of this call (int32 [m, k]); out bf16 [m, h].
+extern "C" int b200moe_ep_return_combine_ll(const void* yl, const int* rid, int world, int cap, int h, int k, int rank, int experts_per_rank,
+                                            void* const* peers_back, const void* back, const int* ids, int m, void* out, unsigned* calls,
+                                            int* status, void* stream) {
+  if (!yl || !rid || !peers_back || !back || !calls || !status || (m > 0 && (!ids || !out))) return B200MOE_ERR_ARG;
+  if (world < 1 || world > kEpMaxWorld || cap < 1 || h <= 0 || h % 8 || k < 1 || rank < 0 || rank >= world || m < 0 || m > cap ||
+      experts_per_rank < 1)
+    return B200MOE_ERR_SHAPE;
+  EpLLPeers B;
+  for (int d = 0; d < kEpMaxWorld; ++d) {
+    B.p[d] = d < world ? (uint2*)peers_back[d] : nullptr;
+    if (d < world && (!B.p[d] || ((uintptr_t)B.p[d] & 7))) return B200MOE_ERR_ARG;
+  }
+  k_ep_return_ll<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)yl, rid, cap, h, k, rank, world, experts_per_rank, B,
+                                                                      (const uint2*)back, ids, m, (__nv_bfloat16*)out, calls, status);
   B200_LAUNCH_CHECK();
   return B200MOE_OK;
 }

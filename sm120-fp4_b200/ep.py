@@ -16,8 +16,10 @@ synchronisation per layer call), or - for decode batches - `capacity` fixes ever
 constant number of rows so that nothing has to come back to the host and the call is CUDA-graph capturable. The
 fixed-capacity exchange has two transports: one packed NCCL all-to-all each way (rows, ids and weights in one buffer), or -
 `transport="peer"`, when the ranks can map one another's memory - kernels that store the rows straight into the destination
-GPU's receive arrays over NVLink and bump a counter there, with a bounded wait on the receiving side (no NCCL call, no
-multicast; a peer that never arrives shows up as an error status, not as a hang).
+GPU's memory over NVLink as flagged words (4 bytes of payload + the call number in every 8-byte store, so nothing waits for
+an acknowledgement across the link), with a bounded wait on the receiving side (no NCCL call, no multicast; a peer that
+never arrives shows up as an error status, not as a hang). `transport="peer_fence"` is the same exchange with plain rows,
+a system-scope fence and arrival counters.
 """
 from __future__ import annotations
 
@@ -65,8 +67,8 @@ class ExpertParallelMoE:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.lo, self.hi = shard_range(num_experts, self.rank, self.world)
         self.capacity = capacity
-        if transport not in ("nccl", "peer"):
-            raise ValueError("transport is 'nccl' or 'peer'")
+        if transport not in ("nccl", "peer", "peer_fence"):
+            raise ValueError("transport is 'nccl', 'peer' or 'peer_fence'")
         self.transport = transport if (capacity is not None and self.world > 1) else "nccl"
         self.last_sent_rows = 0   # rows this rank dispatched in the last call (for traffic accounting)
         try:
@@ -193,7 +195,11 @@ class ExpertParallelMoE:
             x = x.contiguous()
         st = torch.cuda.current_stream(x.device).cuda_stream
         w, k = self.world, self.k
-        if b.peer:   # rows stored straight into the peers' receive arrays; the kernel completes when the peers' rows are here
+        if b.peer == "ll":   # flagged words stored straight into the peers' receive areas; the kernel completes when the peers' rows are here
+            _lib.check(lib.b200moe_ep_dispatch_ll(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.peers_in, b.ll_in,
+                                                  b.rx.data_ptr(), b.rid.data_ptr(), b.rw.data_ptr(), b.calls.data_ptr(), b.status.data_ptr(), st),
+                       "ep dispatch")
+        elif b.peer:   # rows stored straight into the peers' receive arrays, counters after a system-scope fence
             _lib.check(lib.b200moe_ep_dispatch_wait(x.data_ptr(), ids.data_ptr(), wts.data_ptr(), m, h, k, w, per, c, b.dst_x, b.dst_ids, b.dst_wts,
                                                     b.dst_flag, b.flags_in.data_ptr(), b.calls.data_ptr(), b.status.data_ptr(), st), "ep dispatch")
         else:
@@ -211,6 +217,10 @@ class ExpertParallelMoE:
             yl = self.local_forward(b.rx, b.rid, b.rw)
         if out is None:
             out = torch.empty(m, h, dtype=x.dtype, device=x.device)
+        if b.peer == "ll":   # partial rows back as flagged words, wait for this rank's own, sum in rank order: one launch
+            _lib.check(lib.b200moe_ep_return_combine_ll(yl.data_ptr(), b.rid.data_ptr(), w, c, h, k, self.rank, per, b.peers_back, b.ll_back,
+                                                        ids.data_ptr(), m, out.data_ptr(), b.calls.data_ptr(), b.status.data_ptr(), st), "ep return")
+            return out
         if b.peer:   # partial rows back to their sources, wait for this rank's own, sum in rank order: one launch
             _lib.check(lib.b200moe_ep_return_combine(yl.data_ptr(), w, c, h, self.rank, b.back_y, b.back_flag, b.flags_back.data_ptr(),
                                                      b.calls.data_ptr(), b.status.data_ptr(), b.y.data_ptr(), m, out.data_ptr(), st), "ep return")
@@ -246,17 +256,21 @@ class ExpertParallelMoE:
         b = SimpleNamespace(block_bytes=block, peer=False, rx=None, rid=None, rw=None, y=None,
                             yl=z(w * c, h, dt=dtype), dst_flag=None)
         parr = lambda vals: (C.c_void_p * len(vals))(*vals)  # noqa: E731
-        if self.transport == "peer":
+        if self.transport in ("peer", "peer_fence"):
             try:
-                self._peer_buffers(b, c, h, device, dtype, parr)
+                if self.transport == "peer":
+                    self._peer_ll_buffers(b, c, h, device, dtype, parr)
+                else:
+                    self._peer_buffers(b, c, h, device, dtype, parr)
             except Exception as ex:  # noqa: BLE001 - no peer mapping on this system: fall back to the NCCL transport, loudly
                 import sys
                 print(f"expert-parallel peer transport unavailable ({type(ex).__name__}: {ex}); using the NCCL exchange", file=sys.stderr)
                 b.peer = False
-        if self.transport == "peer" and self.world > 1:
+        if self.transport in ("peer", "peer_fence") and self.world > 1:
             ok = torch.tensor([1 if b.peer else 0], dtype=torch.int32, device=device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
-            b.peer = bool(int(ok.item()))
+            if not int(ok.item()):
+                b.peer = False
         if not b.peer:
             b.sbuf, b.rbuf = z(w, block, dt=torch.uint8), z(w, block, dt=torch.uint8)
             b.rx, b.rid, b.rw = z(w * c, h, dt=dtype), z(w * c, k, dt=torch.int32), z(w * c, k, dt=torch.float32)
@@ -303,6 +317,30 @@ class ExpertParallelMoE:
         b.back_y = parr([ptrs[s] + off_back for s in range(w)])
         b.back_flag = parr([ptrs[s] + off_fback + 4 * r for s in range(w)])
         b.peer = True
+
+    def _peer_ll_buffers(self, b, c, h, device, dtype, parr) -> None:
+        """The flagged-word exchange: one symmetric allocation per rank, [receive area | return area + markers], mapped into
+        every peer; the arrays the layer call reads (rx, rid, rw) are ordinary local tensors the dispatch kernel fills."""
+        import torch.distributed._symmetric_memory as symm
+        w, k = self.world, self.k
+        words, hw = h // 2 + 2 * k, h // 2
+        n_in, n_back = w * c * words * 8, (w * c * hw + w) * 8
+        buf = symm.empty(n_in + n_back, dtype=torch.uint8, device=device)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+        torch.cuda.synchronize(device)
+        hdl.barrier()
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        r = self.rank
+        b.symm, b.handle = buf, hdl
+        b.ll_in, b.ll_back = ptrs[r], ptrs[r] + n_in
+        b.peers_in = parr([ptrs[d] + r * c * words * 8 for d in range(w)])            # my block inside rank d's receive area
+        b.peers_back = parr([ptrs[s] + n_in + r * c * hw * 8 for s in range(w)])      # my block inside rank s's return area
+        z = lambda *shape, dt: torch.zeros(*shape, dtype=dt, device=device)  # noqa: E731
+        b.rx, b.rid, b.rw = z(w * c, h, dt=dtype), z(w * c, k, dt=torch.int32), z(w * c, k, dt=torch.float32)
+        b.calls = torch.zeros(2, dtype=torch.int32, device=device)
+        b.status = torch.zeros(1, dtype=torch.int32, device=device)
+        b.peer = "ll"
 
     def _forward_fixed_torch(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, c: int) -> torch.Tensor:
         m, h = x.shape

@@ -96,7 +96,8 @@ def _worker(rank, world, port, q):
                 extra += np.abs(O.moe_reference(x.float().numpy(), full, ids.numpy(), wr)) * 2.0 ** -9
             return extra
 
-        for cap, m, transport in ((None, 7 + rank, "nccl"), (16, 16, "nccl"), (None, 40, "nccl"), (16, 9 + rank, "peer"), (None, 5 * rank, "nccl")):
+        for cap, m, transport in ((None, 7 + rank, "nccl"), (16, 16, "nccl"), (None, 40, "nccl"), (16, 9 + rank, "peer"), (16, 3 + 9 * rank, "peer_fence"),
+                                   (16, 4 * rank, "peer"), (None, 5 * rank, "nccl")):
             print(f"rank {rank}: capacity={cap} m={m} {transport}", file=sys.stderr, flush=True)
             x, ids, wts = synth.decode_inputs(m, cfg["experts"], cfg["hidden"], cfg["top_k"], 300 + rank + m)
             ep = ExpertParallelMoE(local.forward, cfg["experts"], cfg["top_k"], capacity=cap, transport=transport)
@@ -286,3 +287,104 @@ def test_fused_peer_exchange_kernels_single_rank():
         assert int(status.item()) == 0 and int(calls.item()) == call + 1 and flags.tolist() == [cap * (call + 1)] * 2
         assert torch.equal(rid[:m], ids) and torch.equal(rw[:m], wts) and torch.equal(rx[:m], x)
         assert torch.equal(out, (x.float() * 2).to(torch.bfloat16))
+
+
+def _ll_rank(cap, h, k, world):
+    """Buffers of one rank of the flagged-word exchange, as b200moe_ep_dispatch_ll / _return_combine_ll take them."""
+    words, hw = h // 2 + 2 * k, h // 2
+    z = lambda *shape, dt=torch.int32: torch.zeros(*shape, dtype=dt, device="cuda")  # noqa: E731
+    return dict(ll_in=z(world, cap, words, 2), ll_back=z(world * cap * hw + world, 2), rx=z(world * cap, h, dt=torch.bfloat16),
+                rid=z(world * cap, k), rw=z(world * cap, k, dt=torch.float32), calls=z(2), status=z(1), words=words, hw=hw)
+
+
+def _ll_call(lib, L, ranks, r, x, ids, wts, cap, h, k, per, phase, yl=None, out=None):
+    import ctypes as C
+    arr = lambda v: (C.c_void_p * len(v))(*v)  # noqa: E731
+    me, world, m = ranks[r], len(ranks), x.shape[0]
+    if phase == "dispatch":
+        peers = arr([p["ll_in"].data_ptr() + r * cap * me["words"] * 8 for p in ranks])
+        L.check(lib.b200moe_ep_dispatch_ll(L.ptr(x), L.ptr(ids), L.ptr(wts), m, h, k, world, per, cap, peers, L.ptr(me["ll_in"]), L.ptr(me["rx"]),
+                                           L.ptr(me["rid"]), L.ptr(me["rw"]), L.ptr(me["calls"]), L.ptr(me["status"]), L.stream_ptr()), "dispatch_ll")
+    else:
+        peers = arr([p["ll_back"].data_ptr() + r * cap * me["hw"] * 8 for p in ranks])
+        L.check(lib.b200moe_ep_return_combine_ll(L.ptr(yl), L.ptr(me["rid"]), world, cap, h, k, r, per, peers, L.ptr(me["ll_back"]), L.ptr(ids), m,
+                                                 L.ptr(out), L.ptr(me["calls"]), L.ptr(me["status"]), L.stream_ptr()), "return_combine_ll")
+    torch.cuda.synchronize()
+    return int(me["status"].item())
+
+
+def test_flagged_word_exchange_single_rank():
+    """The flagged-word form of the peer-store exchange with this GPU as its own only peer: what a call sends to itself
+    arrives in the plain arrays and comes back summed, call after call, masked slots and an empty batch included."""
+    import sm120fp4_b200._lib as L
+    lib = L.lib()
+    cap, h, k, experts = 8, 256, 4, 8
+    g = torch.Generator().manual_seed(19)
+    ranks = [_ll_rank(cap, h, k, 1)]
+    for call, m in enumerate((5, 8, 0, 3)):
+        x = torch.randn(m, h, generator=g).to(torch.bfloat16).cuda()
+        ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(max(m, 1))]).to(torch.int32)[:m]
+        if m:
+            ids[0, 1:] = -1          # a token with one live slot
+            ids[m - 1, :] = -1       # a token with none: its row does not travel and its output is zero
+        ids = ids.cuda()
+        wts = torch.rand(m, k, generator=g).cuda()
+        out = torch.full((m, h), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert _ll_call(lib, L, ranks, 0, x, ids, wts, cap, h, k, experts, "dispatch") == 0
+        me = ranks[0]
+        live = (ids >= 0).any(1)
+        assert torch.equal(me["rid"][:m], ids) and torch.equal(me["rw"][:m][ids >= 0], wts[ids >= 0]) and not me["rw"][:m][ids < 0].any()
+        assert (me["rid"][m:] == -1).all() and torch.equal(me["rx"][:m][live], x[live])
+        yl = (me["rx"].float() * 2).to(torch.bfloat16)                       # stands for the local layer
+        assert _ll_call(lib, L, ranks, 0, x, ids, wts, cap, h, k, experts, "return", yl=yl, out=out) == 0
+        assert me["calls"].tolist() == [call + 1, call + 1]
+        want = torch.where(live[:, None], (x.float() * 2).to(torch.bfloat16), torch.zeros_like(x))
+        assert torch.equal(out, want)
+
+
+def test_flagged_word_exchange_two_ranks_one_after_the_other():
+    """Two ranks' buffers on one GPU, their kernels run one after the other (never at the same time): rank 1 goes first, finds
+    nothing from rank 0 and gives up after its bounded wait with the status word naming rank 0 - the context stays usable;
+    rank 0 then finds rank 1's words in place and completes, and rank 1 repeats its call to pick up rank 0's rows. Checks the
+    cross-rank addressing, the rank-order sum and that a peer that never arrives is an error status, not a hang."""
+    import sm120fp4_b200._lib as L
+    lib = L.lib()
+    cap, h, k, experts, world = 4, 256, 4, 8, 2
+    per = experts // world
+    g = torch.Generator().manual_seed(23)
+    ranks = [_ll_rank(cap, h, k, world) for _ in range(world)]
+    batch = []
+    for r in range(world):
+        m = 3 + r
+        x = torch.randn(m, h, generator=g).to(torch.bfloat16).cuda()
+        ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(m)]).to(torch.int32)
+        ids[0] = torch.tensor([0, 1, 2, 3] if r == 0 else [4, 5, 6, 7], dtype=torch.int32)   # a token all of whose experts sit on one rank
+        batch.append((x, ids.cuda(), torch.rand(m, k, generator=g).cuda()))
+    assert _ll_call(lib, L, ranks, 1, *batch[1], cap, h, k, per, "dispatch") == 1     # 1 + rank 0: its words never came
+    ranks[1]["status"].zero_()
+    assert _ll_call(lib, L, ranks, 0, *batch[0], cap, h, k, per, "dispatch") == 0
+    assert _ll_call(lib, L, ranks, 1, *batch[1], cap, h, k, per, "dispatch") == 0     # the same call again: now rank 0's words are there
+    me = ranks[0]
+    for src in range(world):
+        x, ids, wts = batch[src]
+        m = x.shape[0]
+        mine = (ids >= 0) & (ids // per == 0)
+        blk = slice(src * cap, src * cap + m)
+        assert torch.equal(me["rid"][blk], torch.where(mine, ids, torch.full_like(ids, -1)))
+        assert torch.equal(me["rw"][blk], torch.where(mine, wts, torch.zeros_like(wts)))
+        assert torch.equal(me["rx"][blk][mine.any(1)], x[mine.any(1)])
+        assert (me["rid"][src * cap + m:(src + 1) * cap] == -1).all()
+    outs = []
+    for r in (1, 0):   # rank 1 first again: it returns its partial rows, then waits in vain for rank 0's
+        x, ids, wts = batch[r]
+        yl = (ranks[r]["rx"].float() * (2 + r)).to(torch.bfloat16)    # rank r's "layer": (2 + r) * x
+        out = torch.full_like(x, float("nan"))
+        st = _ll_call(lib, L, ranks, r, x, ids, wts, cap, h, k, per, "return", yl=yl, out=out)
+        assert st == (1 if r == 1 else 0)
+        outs.append(out)
+    x, ids, _ = batch[0]
+    on0, on1 = ((ids // per) == 0).any(1), ((ids // per) == 1).any(1)
+    want = (torch.where(on0[:, None], (x.float() * 2).to(torch.bfloat16).float(), torch.zeros_like(x, dtype=torch.float32))
+            + torch.where(on1[:, None], (x.float() * 3).to(torch.bfloat16).float(), torch.zeros_like(x, dtype=torch.float32))).to(torch.bfloat16)
+    assert torch.equal(outs[1], want)
+    assert ranks[0]["calls"].tolist() == [1, 1]
