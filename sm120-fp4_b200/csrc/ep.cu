@@ -2,8 +2,10 @@
 // NCCL all-to-all, replacing a dozen framework element-wise launches. The reference has no expert parallelism (its
 // `fits()` declines `use_ep`, sm120fp4/vllm_classes.py:46-47), so these entry points have no counterpart there.
 #include "common.cuh"
+#include "ptx.cuh"
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <string.h>
 
 namespace b200 {
 
@@ -297,8 +299,14 @@ __global__ void __launch_bounds__(128) k_ep_dispatch_ll(const __nv_bfloat16* __r
       ok = ll_load(src + hw + tid, n, &v, peer, status);
       if (tid < k) { id = ok ? (int)v : -1; rid[o * k + tid] = id; }
       else rw[o * k + tid - k] = ok ? __uint_as_float(v) : 0.f;
+      __threadfence();
     }
     const int any = __syncthreads_or(tid < k && id >= 0);
+    // The ids and weights of this block's row are in place: a layer kernel launched programmatically behind this one may
+    // start once every block is this far - it reads them in its prologue (and checks them again after the stream dependency
+    // has resolved), builds its routing tables and starts streaming weights while the rows themselves are still arriving;
+    // it waits for this kernel to complete before it touches a row.
+    grid_launch_dependents();
     if (any) {
       uint32_t* dst = reinterpret_cast<uint32_t*>(rx + o * h);
       const int stride = (int)blockDim.x;
@@ -325,6 +333,7 @@ __global__ void __launch_bounds__(128) k_ep_return_ll(const __nv_bfloat16* __res
                                                       const uint2* __restrict__ back, const int* __restrict__ ids, int m,
                                                       __nv_bfloat16* __restrict__ out, unsigned* __restrict__ calls, int* __restrict__ status) {
   const int row = blockIdx.x, peer = blockIdx.y, tid = threadIdx.x;
+  grid_dependency_wait();   // launched programmatically behind the layer kernel (its launch latency hidden): yl is complete from here on
   const uint32_t n = calls[1];
   const int hw = h / 2;
   const long long marks = (long long)world * cap * hw;   // after the rows of a return area: one word per rank, "rank r has reached its return of call n"
@@ -673,8 +682,14 @@ extern "C" int b200moe_ep_return_combine_ll(const void* yl, const int* rid, int 
     B.p[d] = d < world ? (uint2*)peers_back[d] : nullptr;
     if (d < world && (!B.p[d] || ((uintptr_t)B.p[d] & 7))) return B200MOE_ERR_ARG;
   }
-  k_ep_return_ll<<<dim3(cap, world), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)yl, rid, cap, h, k, rank, world, experts_per_rank, B,
-                                                                      (const uint2*)back, ids, m, (__nv_bfloat16*)out, calls, status);
-  B200_LAUNCH_CHECK();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(cap, world), cfg.blockDim = dim3(128), cfg.dynamicSmemBytes = 0, cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_ep_return_ll, (const __nv_bfloat16*)yl, rid, cap, h, k, rank, world, experts_per_rank, B,
+                                   (const uint2*)back, ids, m, (__nv_bfloat16*)out, calls, status));
   return B200MOE_OK;
 }
