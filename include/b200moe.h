@@ -220,7 +220,9 @@ int b200moe_ep_return_combine(const void* yl, int world, int cap, int h, int ran
  * b200moe_ep_return_combine_ll, in that order on one stream; cap and world are the same on every rank. A token row is sent
  * back only by the ranks that own one of its experts, and only those are waited for; a marker word per rank keeps a rank
  * from starting its next call before every peer has finished reading this one. No counterpart in the reference (it declines
- * expert parallelism, sm120fp4/vllm_classes.py:46-47). */
+ * expert parallelism, sm120fp4/vllm_classes.py:46-47). cap * world <= 1024 (B200MOE_ERR_LIMIT otherwise; the same holds
+ * for b200moe_ep_return_combine): blocks of these kernels wait for blocks of the peers' kernels, so a grid must be resident
+ * as a whole; larger blocks go through the stream-ordered exchange. */
 int b200moe_ep_dispatch_ll(const void* x, const int* ids, const float* wts, int m, int h, int k, int world, int experts_per_rank, int cap,
                            void* const* peers_in, const void* in, void* rx, int* rid, float* rw, unsigned* calls, int* status, void* stream);
 int b200moe_ep_return_combine_ll(const void* yl, const int* rid, int world, int cap, int h, int k, int rank, int experts_per_rank,

@@ -17,6 +17,11 @@ namespace b200 {
 // destination GPU's receive arrays across NVLink (plain stores; no multicast), and D.flag[dest] is a counter in the
 // destination's memory that every block bumps (system-scope, after a system-scope fence) once its row has been stored.
 constexpr int kEpMaxWorld = 16;
+// Kernels whose blocks wait for a peer's words or counters need every block of their grid (cap x world blocks of 128 threads)
+// resident at once, on every rank: a waiting block that keeps the block it waits for (on the peer) from being scheduled
+// would only end by its bounded wait. 1024 blocks fit beside a layer kernel on any B200; the peer-store exchange is for
+// decode-sized blocks, larger ones go through the stream-ordered exchange.
+constexpr int kEpMaxWaitingBlocks = 1024;
 
 struct EpDest {
   __nv_bfloat16* x[kEpMaxWorld];
@@ -487,6 +492,7 @@ extern "C" int b200moe_ep_return_combine(const void* yl, int world, int cap, int
                                          const unsigned* flags_back, const unsigned* calls, int* status, const void* back, int m, void* out,
                                          void* stream) {
   if (!flags_back || !calls || !status || !back || !out) return B200MOE_ERR_ARG;
+  if ((long long)cap * world > kEpMaxWaitingBlocks) return B200MOE_ERR_LIMIT;   // its combining blocks wait for the peers' blocks
   const EpWait W = {flags_back, const_cast<unsigned*>(calls), status, world, (unsigned)cap};
   return ep_return(yl, world, cap, h, rank, back_y, back_flag, W, back, m, out, stream);
 }
@@ -654,6 +660,7 @@ extern "C" int b200moe_ep_dispatch_ll(const void* x, const int* ids, const float
   if ((m > 0 && (!x || !ids || !wts)) || !peers_in || !in || !rx || !rid || !rw || !calls || !status) return B200MOE_ERR_ARG;
   if (m < 0 || m > cap || h <= 0 || h % 8 || k < 1 || 2 * k > 128 || world < 1 || world > kEpMaxWorld || experts_per_rank < 1 || cap < 1)
     return B200MOE_ERR_SHAPE;
+  if ((long long)cap * world > kEpMaxWaitingBlocks) return B200MOE_ERR_LIMIT;
   EpLLPeers D;
   for (int d = 0; d < kEpMaxWorld; ++d) {
     D.p[d] = d < world ? (uint2*)peers_in[d] : nullptr;
@@ -677,6 +684,7 @@ extern "C" int b200moe_ep_return_combine_ll(const void* yl, const int* rid, int 
   if (world < 1 || world > kEpMaxWorld || cap < 1 || h <= 0 || h % 8 || k < 1 || rank < 0 || rank >= world || m < 0 || m > cap ||
       experts_per_rank < 1)
     return B200MOE_ERR_SHAPE;
+  if ((long long)cap * world > kEpMaxWaitingBlocks) return B200MOE_ERR_LIMIT;
   EpLLPeers B;
   for (int d = 0; d < kEpMaxWorld; ++d) {
     B.p[d] = d < world ? (uint2*)peers_back[d] : nullptr;

@@ -29,6 +29,9 @@ import torch
 import torch.distributed as dist
 
 
+PEER_MAX_BLOCKS = 1024   # rows x ranks the peer-store kernels take (their grids must be resident as a whole on every rank)
+
+
 def shard_range(num_experts: int, rank: int, world: int) -> tuple[int, int]:
     """Experts [lo, hi) owned by `rank`: an even split (the number of experts must divide by the world size)."""
     if num_experts % world:
@@ -181,6 +184,9 @@ class ExpertParallelMoE:
         c = self.capacity if rows is None else int(rows)
         if m > c or c > self.capacity:
             raise ValueError(f"batch of {m} tokens / block of {c} rows exceeds the dispatch capacity {self.capacity}")
+        if self.transport != "nccl" and c * self.world > PEER_MAX_BLOCKS:
+            raise ValueError(f"the peer-store exchange takes decode-sized blocks (rows x ranks <= {PEER_MAX_BLOCKS}, got {c} x {self.world}): "
+                             "its kernels wait for the peers' kernels block by block; use transport='nccl' or the variable-size exchange")
         per = self.E // self.world
         self.last_sent_rows = self.world * c
         if not x.is_cuda:

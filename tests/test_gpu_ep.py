@@ -340,6 +340,11 @@ def test_flagged_word_exchange_single_rank():
         assert me["calls"].tolist() == [call + 1, call + 1]
         want = torch.where(live[:, None], (x.float() * 2).to(torch.bfloat16), torch.zeros_like(x))
         assert torch.equal(out, want)
+    # blocks of more rows than a grid can hold resident are refused before anything is launched
+    big = _ll_rank(2048, h, k, 1)
+    x, ids, wts = torch.zeros(1, h, dtype=torch.bfloat16, device="cuda"), torch.zeros(1, k, dtype=torch.int32, device="cuda"), torch.zeros(1, k, device="cuda")
+    with pytest.raises(L.B200MoEError, match="maximum"):
+        _ll_call(lib, L, [big], 0, x, ids, wts, 2048, h, k, experts, "dispatch")
 
 
 def test_flagged_word_exchange_two_ranks_one_after_the_other():
