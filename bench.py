@@ -335,7 +335,7 @@ def run_ours(a):
     line = {
         "metric": "moe_decode_layer_hbm_gbs_on_touched_expert_bytes", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(r["step_ms"], 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "nvfp4 weights x f16 activations, fp32 accumulate (W4A16)", "data": "synthetic",
+        "vs_baseline": None, "dtype": "nvfp4 weights x bf16 activations written as four nvfp4 terms (tcgen05 mxf4nvf4), fp32 accumulate (W4A16)", "data": "synthetic",
         "config": {"workload": workload_name(a.shape, cfg),
                    "layers_in_chain": a.layers, "l2": f"inputs larger than L2: each call reads one of {a.layers} distinct {r['ebytes'] * cfg['experts'] / 1e6:.0f} MB weight sets",
                    "graph_replay": r["graph"], "parallelism": par,
