@@ -273,7 +273,7 @@ def run_ours(a):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=240))   # a lost rank ends the run, it does not hang it
     from sm120fp4_b200 import synth
     from sm120fp4_b200.ep import ExpertParallelMoE, shard_range
     cfg = dict(synth.QWEN if a.shape == "qwen" else synth.GEMMA)
