@@ -118,7 +118,8 @@ int b200moe_decode_forward(const b200moe_layer* layer, const void* x_bf16, const
 /* The same with flags. B200MOE_ORDERED: the two kernels of the call are ordinary stream-ordered launches. By default they are
  * launched programmatically, so that the call's prologue and weight stream overlap the tail of whatever precedes it in
  * the stream, and topk_ids / topk_weights are read at kernel entry: they must be complete when the kernel BEFORE this call
- * starts (true for any producer that does not itself release its successors early). A violation is detected (the inputs are
+ * starts (true for any producer that does not itself release its successors early, or that releases them only after these
+ * tensors are written and fenced, as b200moe_ep_dispatch_ll does). A violation is detected (the inputs are
  * re-read after the stream dependency has resolved) and reported by b200moe_layer_status as B200MOE_ERR_ORDER. This is the
  * per-call form of the reference's module-wide switches fc1_set_pdl / fc2_set_pdl (sm120fp4/vllm_backend.py:174-190). */
 #define B200MOE_ORDERED 1
